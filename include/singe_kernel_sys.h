@@ -1,0 +1,305 @@
+/*
+ * singe_kernel_sys.h -- the C ABI of libsinge_kernel_sys.so.
+ *
+ * These are the symbols the (today empty) `singe-kernel-sys` crate of tinrab/singe would bind
+ * (singe-kernel-sys/src/lib.rs:1-6) so that the public operators of `singe_kernel::cuda` and the CUDA
+ * kernels behind `singe::Tensor` run on hand-written sm_100a kernels.  Each declaration cites the
+ * reference interface it replaces (path:line inside tinrab/singe).
+ *
+ * Conventions, which are the reference's raw-kernel execution contract
+ * (singe-kernel/src/cuda/mod.rs:3-13, singe-kernel/docs/kernels.md:55-80):
+ *   - every call only ENQUEUES work on `stream` (a CUstream / cudaStream_t passed as void*); nothing
+ *     synchronises, and the caller keeps every buffer alive until the queued work completes;
+ *   - all pointers are device pointers unless a parameter says "host";
+ *   - the caller owns every buffer, scratch included; outputs may be uninitialised and only logical
+ *     elements are written;
+ *   - sizes are element counts (not bytes) and must fit a signed 32-bit integer, as the reference
+ *     checks with `checked_i32_value` (singe-kernel/src/cuda/attention/mod.rs:2963-3011);
+ *   - the return value is SINGE_OK or one SINGE_ERR_* code mirroring a variant of
+ *     `singe_kernel::error::Error` (singe-kernel/src/error.rs:13-189); CUDA runtime failures come back
+ *     as SINGE_ERR_CUDA_BASE + cudaError_t;
+ *   - data-dependent index errors (a page or slot outside the cache) never fault: the access is
+ *     dropped and code 1 is written to the optional `status` word, the reference's status-word
+ *     protocol (singe/src/backend/cuda/kernel_plan/source/paged_attention.rs:52-54,
+ *     kernel_plan/mod.rs:192-204).  Code 2 in that word means a bounded device-side wait ran out.
+ *
+ * There is no CPU fallback: on a machine without a CUDA device the compute entry points return
+ * SINGE_ERR_CUDA_BASE + cudaErrorNoDevice (or the driver's own error).
+ */
+#ifndef SINGE_KERNEL_SYS_H
+#define SINGE_KERNEL_SYS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes: singe-kernel/src/error.rs:13-189 ---- */
+#define SINGE_OK 0
+#define SINGE_ERR_INVALID_LENGTH 1            /* Error::InvalidLength */
+#define SINGE_ERR_LENGTH_TOO_SHORT 2          /* Error::LengthTooShort { .. } */
+#define SINGE_ERR_LENGTH_EXCEEDS_I32 3        /* Error::LengthExceedsI32 */
+#define SINGE_ERR_NULL_POINTER 4              /* Error::NullPointer */
+#define SINGE_ERR_SIZE_OVERFLOW 5             /* Error::SizeOverflow */
+#define SINGE_ERR_UNSUPPORTED_WIDTH 6         /* Error::UnsupportedWidth { op, width } */
+#define SINGE_ERR_UNSUPPORTED_CONFIGURATION 7 /* Error::UnsupportedConfiguration { op, reason } */
+#define SINGE_ERR_LENGTH_MISMATCH 8           /* Error::LengthMismatch */
+#define SINGE_ERR_INDEX_OUT_OF_BOUNDS 9       /* singe::Error::IndexOutOfBounds (host-side checks) */
+#define SINGE_ERR_INVALID_ARGUMENT 10         /* singe::Error::invalid_argument */
+#define SINGE_ERR_OUT_OF_RANGE 11             /* singe::Error::out_of_range */
+#define SINGE_ERR_AUTOTUNE_DURING_CAPTURE 12  /* Error::AutotuneDuringCapture (workspace growth under capture) */
+#define SINGE_ERR_CUDA_BASE 1000              /* + cudaError_t */
+
+/* Device-side status word values. */
+#define SINGE_STATUS_INDEX_OUT_OF_BOUNDS 1u
+#define SINGE_STATUS_WAIT_TIMEOUT 2u
+
+typedef void *singe_stream_t; /* CUstream / cudaStream_t */
+
+/* Library version (major * 1000 + minor). */
+int singe_kernel_sys_version(void);
+
+/* Static description of a status code. */
+const char *singe_status_string(int status);
+
+/* =================================================================================================
+ * Slot-mapped KV-cache write
+ * Replaces: KvCache::write = two index_put_ scatters at DecodeStep::slots()
+ *   (singe/src/nn/decode/cache.rs:97-101, singe/src/nn/decode/step.rs:104-111), whose CPU meaning is
+ *   index_write/plan (singe/src/backend/cpu/shape/multi_index.rs:95-125,204-236), and the slot-mapped
+ *   store of singe_rotary_cache_write (singe/src/backend/cuda/kernel_plan/source/rotary_cache.rs:238-427).
+ * cache[pages[t], slots[t], :, :] = rows[t, :, :] as a byte copy, for keys and values in one launch.
+ * A negative page or slot wraps by its extent; a value still outside is dropped and reported through
+ * `status` (code 1).  Duplicate positions: unspecified winner, as the reference's CUDA path
+ * (singe/src/index/advanced.rs:79).
+ *   key_cache, value_cache : [pages, page_size, kv_heads, head_dim]
+ *   keys, values           : [tokens, kv_heads, head_dim]; `values`/`value_cache` may both be NULL
+ *   write_pages, write_slots : [tokens], int64 when index_width == 8, int32 when index_width == 4
+ * ================================================================================================= */
+int singe_kv_cache_write_bf16(singe_stream_t stream, void *key_cache, void *value_cache, const void *keys,
+                              const void *values, const void *write_pages, const void *write_slots,
+                              int index_width, size_t tokens, size_t kv_heads, size_t head_dim, size_t pages,
+                              size_t page_size, uint32_t *status);
+int singe_kv_cache_write_f16(singe_stream_t stream, void *key_cache, void *value_cache, const void *keys,
+                             const void *values, const void *write_pages, const void *write_slots, int index_width,
+                             size_t tokens, size_t kv_heads, size_t head_dim, size_t pages, size_t page_size,
+                             uint32_t *status);
+int singe_kv_cache_write_f32(singe_stream_t stream, void *key_cache, void *value_cache, const void *keys,
+                             const void *values, const void *write_pages, const void *write_slots, int index_width,
+                             size_t tokens, size_t kv_heads, size_t head_dim, size_t pages, size_t page_size,
+                             uint32_t *status);
+
+/* =================================================================================================
+ * Paged-KV decode attention (one query token per sequence)
+ * Replaces: singe_kernel::cuda::attention::paged_kv_decode_attention_{f32,f16,bf16}
+ *   (singe-kernel/src/cuda/attention/paged.rs:118-249; argument order of the launcher call :230-248),
+ *   config PagedKvDecodeAttentionConfig (singe-kernel/src/cuda/attention/mod.rs:81-90,686-744,2963-2985),
+ *   CPU meaning paged_kv_decode_attention_f32 (singe-kernel/src/cpu/attention.rs:1172-1246).
+ *   out, query            : [batch, heads, head_dim]
+ *   key_cache, value_cache: [physical_blocks, block_size, kv_heads, head_dim]
+ *   actual_seq_lens       : int32 [batch]; a sequence of length 0 writes zeros
+ *   block_table           : uint32 [batch, block_table_batch_stride]
+ * The bf16/f16 entry points run the split-K flash-decode kernel (TMA-staged pages, tensor-core
+ * tiles, log-sum-exp combine) when head_dim is 64 or 128, block_size is 16 and heads/kv_heads <= 8,
+ * and a general one-warp-per-row kernel otherwise.  Their split-K partials live in a per-device
+ * workspace the library grows on demand (never while the stream is capturing: that returns
+ * SINGE_ERR_AUTOTUNE_DURING_CAPTURE; call once outside capture first, or use the *_splitk_reduce_*
+ * entry points below with caller-owned scratch).
+ * ================================================================================================= */
+int singe_paged_kv_decode_attention_bf16(singe_stream_t stream, void *out, const void *query,
+                                         const void *key_cache, const void *value_cache,
+                                         const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch,
+                                         size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
+                                         size_t physical_blocks, size_t block_table_batch_stride, float scale);
+int singe_paged_kv_decode_attention_f16(singe_stream_t stream, void *out, const void *query, const void *key_cache,
+                                        const void *value_cache, const int32_t *actual_seq_lens,
+                                        const uint32_t *block_table, size_t batch, size_t heads, size_t kv_heads,
+                                        size_t head_dim, size_t block_size, size_t physical_blocks,
+                                        size_t block_table_batch_stride, float scale);
+int singe_paged_kv_decode_attention_f32(singe_stream_t stream, float *out, const float *query,
+                                        const float *key_cache, const float *value_cache,
+                                        const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch,
+                                        size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
+                                        size_t physical_blocks, size_t block_table_batch_stride, float scale);
+
+/* =================================================================================================
+ * Split-K decode with caller-owned scratch, and the log-sum-exp combine
+ * Replaces: fmha_decode_splitk_{f32,f16,bf16}, splitk_reduce_f32, fmha_decode_splitk_reduce_f32 and their
+ *   configs FmhaDecodeSplitKConfig / SplitKReduceConfig / FmhaDecodeSplitKReduceConfig
+ *   (singe-kernel/src/cuda/attention/fmha.rs:1038-1313, splitk.rs:187-284, mod.rs:366-499,2232-2560),
+ *   CPU meaning splitk_reduce_f32 (singe-kernel/src/cpu/attention.rs:2157-2193).  The reference applies
+ *   split-K to contiguous K/V only; here the same partial layout is applied to the paged decode above.
+ *
+ * Partial layout (singe-kernel/src/cuda/attention/mod.rs:2456-2509):
+ *   attn_scratch f32 [batch, heads, max_splits, head_dim]  -- softmax-within-split . V, normalised
+ *   lse_scratch  f32 [batch, heads, max_splits]            -- max + ln(sum exp), natural log
+ * Split s of a sequence covers keys [s * split_tokens, (s+1) * split_tokens) where
+ *   split_tokens = singe_paged_kv_decode_split_tokens(block_table_batch_stride * block_size, max_splits),
+ * a multiple of block_size; splits past a sequence's length hold lse = -inf and zeros.
+ * ================================================================================================= */
+
+/* Tokens per split for a key-length bound and a split budget (host arithmetic, no device work). */
+size_t singe_paged_kv_decode_split_tokens(size_t key_len_bound, size_t max_splits, size_t block_size);
+
+/* Writes the partials only (all `max_splits` slots of every row are defined afterwards). */
+int singe_paged_kv_decode_splitk_bf16(singe_stream_t stream, float *attn_scratch, float *lse_scratch,
+                                      const void *query, const void *key_cache, const void *value_cache,
+                                      const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch,
+                                      size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
+                                      size_t physical_blocks, size_t block_table_batch_stride, size_t max_splits,
+                                      float scale);
+
+/* splitk_reduce_f32 with the strides of SplitKReduceConfig (singe-kernel/src/cuda/attention/mod.rs:2320-2370). */
+int singe_splitk_reduce_f32(singe_stream_t stream, float *out, const float *attn_splitk, const float *lse_splitk,
+                            size_t batch, size_t heads, size_t splits, size_t head_dim, size_t attn_batch_stride,
+                            size_t attn_head_stride, size_t attn_split_stride, size_t lse_batch_stride,
+                            size_t lse_head_stride, size_t output_batch_stride, size_t output_head_stride);
+
+/* Decode + combine in one call with caller scratch sized for `max_splits` (>= 1). */
+int singe_paged_kv_decode_splitk_reduce_bf16(singe_stream_t stream, void *out, float *attn_scratch,
+                                             float *lse_scratch, const void *query, const void *key_cache,
+                                             const void *value_cache, const int32_t *actual_seq_lens,
+                                             const uint32_t *block_table, size_t batch, size_t heads,
+                                             size_t kv_heads, size_t head_dim, size_t block_size,
+                                             size_t physical_blocks, size_t block_table_batch_stride,
+                                             size_t max_splits, float scale);
+int singe_paged_kv_decode_splitk_reduce_f16(singe_stream_t stream, void *out, float *attn_scratch,
+                                            float *lse_scratch, const void *query, const void *key_cache,
+                                            const void *value_cache, const int32_t *actual_seq_lens,
+                                            const uint32_t *block_table, size_t batch, size_t heads,
+                                            size_t kv_heads, size_t head_dim, size_t block_size,
+                                            size_t physical_blocks, size_t block_table_batch_stride,
+                                            size_t max_splits, float scale);
+
+/* =================================================================================================
+ * Tensor-surface paged attention (FlashInfer-style paging, decode and prefill rows mixed)
+ * Replaces: the CUDA kernels registered for Operation::PagedAttention behind Tensor::paged_attention
+ *   (singe/src/tensor/neural.rs:405-457; singe_paged_attention / singe_tcgen05_paged_attention /
+ *   singe_paged_attention_general in singe/src/backend/cuda/kernel_plan/source/paged_attention.rs:68-208,
+ *   544-868 and paged_general.rs:73-247), CPU meaning attend_paged
+ *   (singe/src/backend/cpu/normalization/attention.rs:424-540), refusals check_paged_values
+ *   (singe/src/backend/spec/neural/attention.rs:363-416).
+ *   query, out : [tokens, heads, head_dim];  lse : f32 [tokens, heads], BASE 2, -inf for a row with no key
+ *   key_cache, value_cache : [cache_pages, page_size, kv_heads, head_dim]
+ *   query_offsets, page_offsets : [sequences + 1]; pages : [table_len]; last_page_lengths : [sequences]
+ *   (int64 when index_width == 8, int32 when 4).  Queries are the LAST tokens of their sequence.
+ *   window == 0 means no sliding window.  Paging values that would address outside the queries, the
+ *   table or the cache set *status = 1 and the affected rows are skipped.
+ * ================================================================================================= */
+int singe_paged_attention_bf16(singe_stream_t stream, void *out, float *lse, const void *query,
+                               const void *key_cache, const void *value_cache, const void *query_offsets,
+                               const void *page_offsets, const void *pages, const void *last_page_lengths,
+                               int index_width, size_t tokens, size_t heads, size_t kv_heads, size_t head_dim,
+                               size_t page_size, size_t cache_pages, size_t sequences, size_t table_len, float scale,
+                               int causal, size_t window, uint32_t *status);
+int singe_paged_attention_f32(singe_stream_t stream, float *out, float *lse, const float *query,
+                              const float *key_cache, const float *value_cache, const void *query_offsets,
+                              const void *page_offsets, const void *pages, const void *last_page_lengths,
+                              int index_width, size_t tokens, size_t heads, size_t kv_heads, size_t head_dim,
+                              size_t page_size, size_t cache_pages, size_t sequences, size_t table_len, float scale,
+                              int causal, size_t window, uint32_t *status);
+
+/* =================================================================================================
+ * Packed variable-length prefill attention
+ * Replaces: paged_kv_prefill_attention_{f32,bf16} + PagedKvPrefillAttentionConfig and
+ *   ragged_kv_prefill_attention_{f32,bf16} + RaggedKvPrefillAttentionConfig
+ *   (singe-kernel/src/cuda/attention/paged.rs:256-576, launcher argument order :396-418;
+ *   mod.rs:97-123,746-882), CPU meaning singe-kernel/src/cpu/attention.rs:1248-1420.
+ *   query, out : [total_query_tokens, heads, head_dim]; lse : f32 [total_query_tokens, heads], natural
+ *   log, -1.0e20 for a row that sees no key.  Sequence b owns query tokens
+ *   [offsets[b], offsets[b] + lens_q[b]) and keys 0..lens_kv[b]; causal hides key_index > query_index
+ *   with sequence-local indices (singe-kernel/src/cpu/attention.rs:1282,1377).
+ *   ragged: key, value [total_kv_tokens, kv_heads, head_dim], key k of sequence b at row offsets[b] + k.
+ * The bf16 ragged entry point runs the tcgen05/TMEM flash-attention kernel when head_dim == 128;
+ * other shapes, the paged form and f32 run the general kernel.
+ * ================================================================================================= */
+int singe_paged_kv_prefill_attention_bf16(singe_stream_t stream, void *out, float *lse, const void *query,
+                                          const void *key_cache, const void *value_cache,
+                                          const int32_t *actual_seq_lens_q, const int32_t *actual_seq_lens_kv,
+                                          const int32_t *actual_seq_offsets, const uint32_t *block_table,
+                                          size_t batch, size_t total_query_tokens, size_t heads, size_t kv_heads,
+                                          size_t head_dim, size_t block_size, size_t physical_blocks,
+                                          size_t block_table_batch_stride, int causal, float scale);
+int singe_paged_kv_prefill_attention_f32(singe_stream_t stream, float *out, float *lse, const float *query,
+                                         const float *key_cache, const float *value_cache,
+                                         const int32_t *actual_seq_lens_q, const int32_t *actual_seq_lens_kv,
+                                         const int32_t *actual_seq_offsets, const uint32_t *block_table,
+                                         size_t batch, size_t total_query_tokens, size_t heads, size_t kv_heads,
+                                         size_t head_dim, size_t block_size, size_t physical_blocks,
+                                         size_t block_table_batch_stride, int causal, float scale);
+int singe_ragged_kv_prefill_attention_bf16(singe_stream_t stream, void *out, float *lse, const void *query,
+                                           const void *key, const void *value, const int32_t *actual_seq_lens_q,
+                                           const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
+                                           size_t batch, size_t total_query_tokens, size_t total_kv_tokens,
+                                           size_t heads, size_t kv_heads, size_t head_dim, int causal, float scale);
+int singe_ragged_kv_prefill_attention_f32(singe_stream_t stream, float *out, float *lse, const float *query,
+                                          const float *key, const float *value, const int32_t *actual_seq_lens_q,
+                                          const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
+                                          size_t batch, size_t total_query_tokens, size_t total_kv_tokens,
+                                          size_t heads, size_t kv_heads, size_t head_dim, int causal, float scale);
+
+/* Prefill with the slot-mapped KV-cache write in the same pass: ragged prefill as above, and every
+ * key/value row t is also stored at (write_pages[t], write_slots[t]) of the paged caches, with the
+ * semantics of singe_kv_cache_write_bf16.  This is the reference's prompt step: KvCache::write followed
+ * by attention inside GroupedQueryAttention::decode (singe/src/nn/layers/attention/grouped.rs:92-115). */
+int singe_ragged_kv_prefill_attention_cache_write_bf16(
+    singe_stream_t stream, void *out, float *lse, const void *query, const void *key, const void *value,
+    const int32_t *actual_seq_lens_q, const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
+    size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads, size_t kv_heads, size_t head_dim,
+    int causal, float scale, void *key_cache, void *value_cache, const void *write_pages, const void *write_slots,
+    int index_width, size_t pages, size_t page_size, uint32_t *status);
+
+/* Dense prefill with log-sum-exp.
+ * Replaces: fmha_prefill_lse_{f32,bf16} + FmhaPrefillConfig (singe-kernel/src/cuda/attention/fmha.rs:48-790,
+ *   mod.rs:253-274,1602-1756), CPU meaning fmha_prefill_lse_f32 (singe-kernel/src/cpu/attention.rs:1758-1833).
+ *   query, out [batch, query_len, heads, head_dim]; key, value [batch, key_len, kv_heads, head_dim];
+ *   lse f32 [batch, heads, query_len], natural log. */
+int singe_fmha_prefill_lse_f32(singe_stream_t stream, float *out, float *lse, const float *query, const float *key,
+                               const float *value, size_t batch, size_t query_len, size_t key_len, size_t heads,
+                               size_t kv_heads, size_t head_dim, float scale, int causal);
+int singe_fmha_prefill_lse_bf16(singe_stream_t stream, void *out, float *lse, const void *query, const void *key,
+                                const void *value, size_t batch, size_t query_len, size_t key_len, size_t heads,
+                                size_t kv_heads, size_t head_dim, float scale, int causal);
+
+/* =================================================================================================
+ * Dense scaled-dot-product attention (Tensor::attend)
+ * Replaces: the CUDA kernels of Operation::ScaledDotProductAttention (singe_fused_attention /
+ *   singe_tcgen05_attention, singe/src/backend/cuda/kernel_plan/source/attention.rs:179-545), CPU meaning
+ *   execute_scaled_dot_product_attention (singe/src/backend/cpu/normalization/attention.rs:191-276).
+ *   query, out [batch, heads, query_len, head_dim]; key, value [batch, kv_heads, key_len, head_dim];
+ *   causal: query i sees keys 0..min(key_len, i+1); window == 0 means none.
+ * ================================================================================================= */
+int singe_scaled_dot_product_attention_f32(singe_stream_t stream, float *out, const float *query, const float *key,
+                                           const float *value, size_t batch, size_t heads, size_t kv_heads,
+                                           size_t query_len, size_t key_len, size_t head_dim, float scale,
+                                           int causal, size_t window);
+
+/* =================================================================================================
+ * Linear-layer GEMM
+ * Replaces: singe_kernel::cuda::matmul::{matmul_bf16_f32, matmul_mma_bf16_f32} + MatmulConfig
+ *   (singe-kernel/src/cuda/matmul.rs:45-55,218-230,1302-1378; launcher argument order :1317-1337;
+ *   validation :2977-3020) and the eager GEMM behind Linear::forward / Tensor::matmul
+ *   (singe/src/nn/layers/linear/mod.rs:49-70, singe/src/backend/cuda/eager/linear_algebra.rs:20-67,
+ *   singe_tcgen05_matmul in kernel_plan/source/tcgen05.rs:137-266, singe_dot_product in dot_product.rs:133-243).
+ *   CPU meaning: singe-kernel/src/cpu/matmul/mod.rs:12-45, blocked.rs:27-95,
+ *   singe/src/backend/cpu/binary/matmul.rs:18-43 (bf16 widened to f32, one rounding of the result).
+ * out[rows, columns] = lhs . rhs with f32 accumulation.  The tensor-core path needs the linear-layer
+ * layout (transpose_lhs == 0, transpose_rhs == 1: rhs is a weight [columns, reduction]) with
+ * reduction a multiple of 8 (16-byte rows for TMA); other layouts return
+ * SINGE_ERR_UNSUPPORTED_CONFIGURATION.  `_bf16` rounds the result once to bf16 (Tensor surface);
+ * `_f32` keeps f32 (singe-kernel surface).
+ * ================================================================================================= */
+int singe_matmul_bf16_bf16(singe_stream_t stream, void *out, const void *lhs, const void *rhs, size_t rows,
+                           size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
+                           size_t output_row_stride, int transpose_lhs, int transpose_rhs);
+int singe_matmul_bf16_f32(singe_stream_t stream, float *out, const void *lhs, const void *rhs, size_t rows,
+                          size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
+                          size_t output_row_stride, int transpose_lhs, int transpose_rhs);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SINGE_KERNEL_SYS_H */

@@ -1,0 +1,868 @@
+// C-ABI entry points of the attention surfaces: host-side validation that mirrors the reference's
+// config validators, dispatch between the specialised kernels and the general one, and the policies
+// that describe each surface to the general kernel.
+#include <mutex>
+
+#include "attention_general.cuh"
+#include "common.cuh"
+
+namespace singe {
+
+// paged_decode.cu
+bool paged_decode_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t block_size, const void *key_cache,
+                            const void *value_cache, const void *query);
+size_t paged_decode_split_tokens(size_t key_len_bound, size_t max_splits, size_t block_size);
+int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn_scratch, float *lse_scratch,
+                        const void *query, const void *key_cache, const void *value_cache,
+                        const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch, size_t heads,
+                        size_t kv_heads, size_t head_dim, size_t physical_blocks, size_t block_table_batch_stride,
+                        size_t max_splits, float scale, bool partials_only, uint32_t *status);
+// prefill_tcgen05.cu
+bool prefill_fast_path(size_t heads, size_t kv_heads, size_t head_dim, const void *query, const void *key,
+                       const void *value, const void *out);
+int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void *query, const void *key,
+                         const void *value, const int32_t *lens_q, const int32_t *lens_kv, const int32_t *offsets,
+                         size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads,
+                         size_t kv_heads, size_t head_dim, int causal, float scale);
+// kv_cache_write.cu
+int kv_cache_write(cudaStream_t stream, void *key_cache, void *value_cache, const void *keys, const void *values,
+                   const void *write_pages, const void *write_slots, int index_width, size_t tokens, size_t kv_heads,
+                   size_t head_dim, size_t pages, size_t page_size, uint32_t *status, size_t element_bytes);
+
+namespace {
+
+bool finite(float value) { return value == value && value - value == 0.0f; }
+
+// validate_paged_kv_decode_attention_config (singe-kernel/src/cuda/attention/mod.rs:2963-2985)
+int validate_paged_decode(size_t batch, size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
+                          size_t physical_blocks, size_t stride, float scale) {
+    if (batch == 0 || heads == 0 || kv_heads == 0 || head_dim == 0 || block_size == 0 || physical_blocks == 0 ||
+        stride == 0 || heads % kv_heads != 0 || !finite(scale)) {
+        return SINGE_ERR_INVALID_LENGTH;
+    }
+    if (!fits_i32(batch) || !fits_i32(heads) || !fits_i32(kv_heads) || !fits_i32(head_dim) || !fits_i32(block_size) ||
+        !fits_i32(physical_blocks) || !fits_i32(stride)) {
+        return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    }
+    return SINGE_OK;
+}
+
+// validate_paged_kv_prefill_attention_config (singe-kernel/src/cuda/attention/mod.rs:2987-3011)
+int validate_paged_prefill(size_t batch, size_t total, size_t heads, size_t kv_heads, size_t head_dim,
+                           size_t block_size, size_t physical_blocks, size_t stride, float scale) {
+    if (total == 0) return SINGE_ERR_INVALID_LENGTH;
+    if (!fits_i32(total)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    return validate_paged_decode(batch, heads, kv_heads, head_dim, block_size, physical_blocks, stride, scale);
+}
+
+// validate_ragged_kv_prefill_attention_config (singe-kernel/src/cuda/attention/mod.rs:3013-3040)
+int validate_ragged_prefill(size_t batch, size_t total_q, size_t total_kv, size_t heads, size_t kv_heads,
+                            size_t head_dim, float scale) {
+    if (batch == 0 || total_q == 0 || total_kv == 0 || heads == 0 || kv_heads == 0 || head_dim == 0 ||
+        heads % kv_heads != 0 || !finite(scale)) {
+        return SINGE_ERR_INVALID_LENGTH;
+    }
+    if (!fits_i32(batch) || !fits_i32(total_q) || !fits_i32(total_kv) || !fits_i32(heads) || !fits_i32(kv_heads) ||
+        !fits_i32(head_dim)) {
+        return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    }
+    return SINGE_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Policies of the general kernel
+// ---------------------------------------------------------------------------------------------
+
+// paged_kv_decode_attention (singe-kernel/src/cpu/attention.rs:1172-1246): one query per sequence.
+template <typename T>
+struct DecodePagedPolicy {
+    const T *query;
+    T *out;
+    const T *key_cache;
+    const T *value_cache;
+    const int32_t *lens;
+    const uint32_t *table;
+    int heads, kv_heads, head_dim, block_size;
+    long long physical_blocks, stride;
+
+    __device__ int locate(size_t row, RowPlan<T> &plan) const {
+        const size_t b = row / heads;
+        const int head = static_cast<int>(row - b * heads);
+        long long len = lens[b];
+        if (len < 0) len = 0;
+        if (len > stride * block_size) return -1;
+        plan.query = query + row * head_dim;
+        plan.out = out + row * head_dim;
+        plan.lse = nullptr;
+        plan.start = 0;
+        plan.end = static_cast<int>(len);
+        plan.kv_head = head / (heads / kv_heads);
+        plan.handle = static_cast<long long>(b) * stride;
+        return 1;
+    }
+    __device__ long long key_offset(const RowPlan<T> &plan, int pos) const {
+        const long long block = table[plan.handle + pos / block_size];
+        if (block >= physical_blocks) return -1;
+        return ((block * block_size + pos % block_size) * kv_heads + plan.kv_head) * head_dim;
+    }
+    __device__ const T *key_base() const { return key_cache; }
+    __device__ const T *value_base() const { return value_cache; }
+};
+
+// paged / ragged packed prefill (singe-kernel/src/cpu/attention.rs:1248-1420).  table == nullptr selects ragged.
+template <typename T>
+struct PackedPrefillPolicy {
+    const T *query;
+    T *out;
+    float *lse;
+    const T *key;
+    const T *value;
+    const int32_t *lens_q;
+    const int32_t *lens_kv;
+    const int32_t *offsets;
+    const uint32_t *table;
+    int batch, heads, kv_heads, head_dim, block_size, causal;
+    long long physical_blocks, stride, total_query_tokens, total_kv_tokens;
+
+    __device__ int locate(size_t row, RowPlan<T> &plan) const {
+        const long long token = static_cast<long long>(row / heads);
+        const int head = static_cast<int>(row - static_cast<size_t>(token) * heads);
+        int owner = -1;
+        long long local = 0;
+        for (int b = 0; b < batch; ++b) {
+            const long long first = offsets[b];
+            const long long count = lens_q[b];
+            if (token >= first && token < first + count) {
+                owner = b;
+                local = token - first;
+                break;
+            }
+        }
+        if (owner < 0) return 0;
+        long long keys = lens_kv[owner];
+        if (keys < 0) keys = 0;
+        if (table != nullptr) {
+            if (keys > stride * block_size) return -1;
+        } else {
+            if (static_cast<long long>(offsets[owner]) + keys > total_kv_tokens) return -1;
+        }
+        long long end = keys;
+        if (causal && local + 1 < end) end = local + 1;
+        plan.query = query + row * head_dim;
+        plan.out = out + row * head_dim;
+        plan.lse = lse + row;
+        plan.start = 0;
+        plan.end = static_cast<int>(end);
+        plan.kv_head = head / (heads / kv_heads);
+        plan.handle = table != nullptr ? static_cast<long long>(owner) * stride : static_cast<long long>(offsets[owner]);
+        return 1;
+    }
+    __device__ long long key_offset(const RowPlan<T> &plan, int pos) const {
+        if (table != nullptr) {
+            const long long block = table[plan.handle + pos / block_size];
+            if (block >= physical_blocks) return -1;
+            return ((block * block_size + pos % block_size) * kv_heads + plan.kv_head) * head_dim;
+        }
+        return ((plan.handle + pos) * kv_heads + plan.kv_head) * head_dim;
+    }
+    __device__ const T *key_base() const { return key; }
+    __device__ const T *value_base() const { return value; }
+};
+
+// Tensor::paged_attention (singe/src/backend/cpu/normalization/attention.rs:424-540) with the refusals of
+// check_paged_values (singe/src/backend/spec/neural/attention.rs:363-416) applied to the row's own sequence.
+template <typename T, typename Index>
+struct TensorPagedPolicy {
+    const T *query;
+    T *out;
+    float *lse;
+    const T *key_cache;
+    const T *value_cache;
+    const Index *query_offsets;
+    const Index *page_offsets;
+    const Index *pages;
+    const Index *last_page_lengths;
+    int sequences, heads, kv_heads, head_dim, page_size, causal;
+    long long tokens, cache_pages, table_len, window;
+
+    __device__ int locate(size_t row, RowPlan<T> &plan) const {
+        const long long token = static_cast<long long>(row / heads);
+        const int head = static_cast<int>(row - static_cast<size_t>(token) * heads);
+        int owner = -1;
+        long long first_query = 0, end_query = 0;
+        for (int s = 0; s < sequences; ++s) {
+            const long long first = static_cast<long long>(query_offsets[s]);
+            const long long last = static_cast<long long>(query_offsets[s + 1]);
+            if (token >= first && token < last) {
+                owner = s;
+                first_query = first;
+                end_query = last;
+                break;
+            }
+        }
+        if (owner < 0) return 0;
+        if (first_query < 0 || end_query > tokens) return -1;
+        const long long first_page = static_cast<long long>(page_offsets[owner]);
+        const long long last_page = static_cast<long long>(page_offsets[owner + 1]);
+        if (first_page < 0 || first_page > last_page || last_page > table_len) return -1;
+        const long long page_count = last_page - first_page;
+        long long keys = 0;
+        if (page_count > 0) {
+            const long long last_length = static_cast<long long>(last_page_lengths[owner]);
+            if (last_length < 0 || last_length > page_size) return -1;
+            keys = (page_count - 1) * page_size + last_length;
+        }
+        const long long queries = end_query - first_query;
+        long long position = keys + (token - first_query) - queries;  // queries are the sequence's last tokens
+        if (position < 0) position = 0;
+        long long end = keys;
+        if (causal && position + 1 < end) end = position + 1;
+        long long start = 0;
+        if (window > 0 && position + 1 > window) start = position + 1 - window;
+        if (end < start) end = start;
+        plan.query = query + row * head_dim;
+        plan.out = out + row * head_dim;
+        plan.lse = lse + row;
+        plan.start = static_cast<int>(start);
+        plan.end = static_cast<int>(end);
+        plan.kv_head = head / (heads / kv_heads);
+        plan.handle = first_page;
+        return 1;
+    }
+    __device__ long long key_offset(const RowPlan<T> &plan, int pos) const {
+        const long long page = static_cast<long long>(pages[plan.handle + pos / page_size]);
+        if (page < 0 || page >= cache_pages) return -1;
+        return ((page * page_size + pos % page_size) * kv_heads + plan.kv_head) * head_dim;
+    }
+    __device__ const T *key_base() const { return key_cache; }
+    __device__ const T *value_base() const { return value_cache; }
+};
+
+// The whole-table refusal of check_paged_values: any sequence with bad offsets, pages or last length sets the status.
+template <typename Index>
+__global__ void check_paged_values_kernel(const Index *query_offsets, const Index *page_offsets, const Index *pages,
+                                          const Index *last_page_lengths, int sequences, long long tokens,
+                                          long long cache_pages, long long table_len, long long page_size,
+                                          uint32_t *status) {
+    for (int s = blockIdx.x * blockDim.x + threadIdx.x; s < sequences; s += gridDim.x * blockDim.x) {
+        const long long qf = static_cast<long long>(query_offsets[s]), ql = static_cast<long long>(query_offsets[s + 1]);
+        const long long pf = static_cast<long long>(page_offsets[s]), pl = static_cast<long long>(page_offsets[s + 1]);
+        bool bad = !(0 <= qf && qf <= ql && ql <= tokens) || !(0 <= pf && pf <= pl && pl <= table_len);
+        if (!bad && pf != pl) {
+            const long long last = static_cast<long long>(last_page_lengths[s]);
+            bad = last < 0 || last > page_size;
+            for (long long i = pf; i < pl && !bad; ++i) {
+                const long long page = static_cast<long long>(pages[i]);
+                bad = page < 0 || page >= cache_pages;
+            }
+        }
+        if (bad) report_status(status, kStatusIndexOutOfBounds);
+    }
+}
+
+// Dense layouts with explicit strides: Tensor::attend [B,H,L,D] over [B,G,S,D]
+// (singe/src/backend/cpu/normalization/attention.rs:191-276) and fmha_prefill_lse [B,L,H,D] over [B,S,G,D]
+// (singe-kernel/src/cpu/attention.rs:1758-1833).
+template <typename T>
+struct DensePolicy {
+    const T *query;
+    T *out;
+    float *lse;
+    const T *key;
+    const T *value;
+    int heads, kv_heads, query_len, key_len, head_dim, causal;
+    long long window;
+    long long q_batch, q_head, q_row;     // element strides of query/out
+    long long k_batch, k_head, k_row;     // element strides of key/value
+    long long lse_batch, lse_head, lse_row;
+
+    __device__ int locate(size_t row, RowPlan<T> &plan) const {
+        const long long i = static_cast<long long>(row % query_len);
+        const long long bh = static_cast<long long>(row / query_len);
+        const long long head = bh % heads;
+        const long long b = bh / heads;
+        long long end = key_len;
+        if (causal && i + 1 < end) end = i + 1;
+        long long start = 0;
+        if (window > 0 && i + 1 > window) start = i + 1 - window;
+        if (end < start) end = start;
+        const long long at = b * q_batch + head * q_head + i * q_row;
+        plan.query = query + at;
+        plan.out = out + at;
+        plan.lse = lse == nullptr ? nullptr : lse + b * lse_batch + head * lse_head + i * lse_row;
+        plan.start = static_cast<int>(start);
+        plan.end = static_cast<int>(end);
+        plan.kv_head = static_cast<int>(head / (heads / kv_heads));
+        plan.handle = b * k_batch + plan.kv_head * k_head;
+        return 1;
+    }
+    __device__ long long key_offset(const RowPlan<T> &plan, int pos) const { return plan.handle + pos * k_row; }
+    __device__ const T *key_base() const { return key; }
+    __device__ const T *value_base() const { return value; }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Per-device split-K workspace of the drop-in decode entry points
+// ---------------------------------------------------------------------------------------------
+struct Workspace {
+    float *data = nullptr;
+    size_t floats = 0;
+};
+constexpr int kMaxDevices = 64;
+Workspace g_workspace[kMaxDevices];
+std::mutex g_workspace_mutex;
+
+int workspace_for(cudaStream_t stream, size_t floats, float **data) {
+    int device = 0;
+    SINGE_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    std::lock_guard<std::mutex> guard(g_workspace_mutex);
+    Workspace &space = g_workspace[device];
+    if (space.floats < floats) {
+        cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+        SINGE_CUDA_TRY(cudaStreamIsCapturing(stream, &capture));
+        if (capture != cudaStreamCaptureStatusNone) {
+            return SINGE_ERR_AUTOTUNE_DURING_CAPTURE;
+        }
+        // Work queued on the old buffer must finish before it is released.
+        SINGE_CUDA_TRY(cudaDeviceSynchronize());
+        if (space.data != nullptr) {
+            SINGE_CUDA_TRY(cudaFree(space.data));
+            space.data = nullptr;
+            space.floats = 0;
+        }
+        const size_t grown = floats + floats / 2;
+        SINGE_CUDA_TRY(cudaMalloc(&space.data, grown * sizeof(float)));
+        space.floats = grown;
+    }
+    *data = space.data;
+    return SINGE_OK;
+}
+
+// Splits the drop-in decode uses when the caller gives no budget: ~512-token splits, more when few CTAs would run.
+size_t default_splits(size_t batch, size_t kv_heads, size_t bound_tokens) {
+    size_t splits = (bound_tokens + 511) / 512;
+    const size_t wanted = static_cast<size_t>(device_sm_count()) * 4;
+    const size_t rows = batch * kv_heads;
+    if (rows * splits < wanted) {
+        const size_t more = (wanted + rows - 1) / rows;
+        const size_t finest = (bound_tokens + 127) / 128;
+        splits = more < finest ? more : finest;
+    }
+    if (splits < 1) splits = 1;
+    if (splits > 256) splits = 256;
+    return splits;
+}
+
+template <typename T>
+int decode_general(cudaStream_t stream, void *out, const void *query, const void *key_cache, const void *value_cache,
+                   const int32_t *lens, const uint32_t *table, size_t batch, size_t heads, size_t kv_heads,
+                   size_t head_dim, size_t block_size, size_t physical_blocks, size_t stride, float scale) {
+    DecodePagedPolicy<T> policy;
+    policy.query = static_cast<const T *>(query);
+    policy.out = static_cast<T *>(out);
+    policy.key_cache = static_cast<const T *>(key_cache);
+    policy.value_cache = static_cast<const T *>(value_cache);
+    policy.lens = lens;
+    policy.table = table;
+    policy.heads = static_cast<int>(heads);
+    policy.kv_heads = static_cast<int>(kv_heads);
+    policy.head_dim = static_cast<int>(head_dim);
+    policy.block_size = static_cast<int>(block_size);
+    policy.physical_blocks = static_cast<long long>(physical_blocks);
+    policy.stride = static_cast<long long>(stride);
+    return launch_attention_general<T>(stream, policy, batch * heads, head_dim, scale, LseKind::None, 0.0f, nullptr);
+}
+
+// element: 0 bf16, 1 f16
+int decode_half(cudaStream_t stream, int element, void *out, const void *query, const void *key_cache,
+                const void *value_cache, const int32_t *lens, const uint32_t *table, size_t batch, size_t heads,
+                size_t kv_heads, size_t head_dim, size_t block_size, size_t physical_blocks, size_t stride,
+                float scale) {
+    SINGE_TRY(validate_paged_decode(batch, heads, kv_heads, head_dim, block_size, physical_blocks, stride, scale));
+    if (out == nullptr || query == nullptr || key_cache == nullptr || value_cache == nullptr || lens == nullptr ||
+        table == nullptr) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    if (paged_decode_fast_path(heads, kv_heads, head_dim, block_size, key_cache, value_cache, query)) {
+        const size_t splits = default_splits(batch, kv_heads, stride * block_size);
+        float *scratch = nullptr;
+        const size_t rows = batch * heads * splits;
+        SINGE_TRY(workspace_for(stream, rows * (head_dim + 1), &scratch));
+        return paged_decode_splitk(stream, element, out, scratch, scratch + rows * head_dim, query, key_cache,
+                                   value_cache, lens, table, batch, heads, kv_heads, head_dim, physical_blocks, stride,
+                                   splits, scale, false, device_error_word());
+    }
+    if (element == 0) {
+        return decode_general<__nv_bfloat16>(stream, out, query, key_cache, value_cache, lens, table, batch, heads,
+                                             kv_heads, head_dim, block_size, physical_blocks, stride, scale);
+    }
+    return decode_general<__half>(stream, out, query, key_cache, value_cache, lens, table, batch, heads, kv_heads,
+                                  head_dim, block_size, physical_blocks, stride, scale);
+}
+
+int decode_splitk_half(cudaStream_t stream, int element, void *out, float *attn_scratch, float *lse_scratch,
+                       const void *query, const void *key_cache, const void *value_cache, const int32_t *lens,
+                       const uint32_t *table, size_t batch, size_t heads, size_t kv_heads, size_t head_dim,
+                       size_t block_size, size_t physical_blocks, size_t stride, size_t max_splits, float scale,
+                       bool partials_only) {
+    SINGE_TRY(validate_paged_decode(batch, heads, kv_heads, head_dim, block_size, physical_blocks, stride, scale));
+    if (max_splits == 0) return SINGE_ERR_INVALID_LENGTH;  // validate_fmha_decode_splitk_reduce_config, mod.rs:2553-2559
+    if (!fits_i32(max_splits)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    if ((out == nullptr && !partials_only) || attn_scratch == nullptr || lse_scratch == nullptr || query == nullptr ||
+        key_cache == nullptr || value_cache == nullptr || lens == nullptr || table == nullptr) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    if (!paged_decode_fast_path(heads, kv_heads, head_dim, block_size, key_cache, value_cache, query)) {
+        return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    }
+    return paged_decode_splitk(stream, element, out, attn_scratch, lse_scratch, query, key_cache, value_cache, lens,
+                               table, batch, heads, kv_heads, head_dim, physical_blocks, stride, max_splits, scale,
+                               partials_only, device_error_word());
+}
+
+template <typename T>
+int packed_prefill_general(cudaStream_t stream, void *out, float *lse, const void *query, const void *key,
+                           const void *value, const int32_t *lens_q, const int32_t *lens_kv, const int32_t *offsets,
+                           const uint32_t *table, size_t batch, size_t total_q, size_t total_kv, size_t heads,
+                           size_t kv_heads, size_t head_dim, size_t block_size, size_t physical_blocks, size_t stride,
+                           int causal, float scale) {
+    PackedPrefillPolicy<T> policy;
+    policy.query = static_cast<const T *>(query);
+    policy.out = static_cast<T *>(out);
+    policy.lse = lse;
+    policy.key = static_cast<const T *>(key);
+    policy.value = static_cast<const T *>(value);
+    policy.lens_q = lens_q;
+    policy.lens_kv = lens_kv;
+    policy.offsets = offsets;
+    policy.table = table;
+    policy.batch = static_cast<int>(batch);
+    policy.heads = static_cast<int>(heads);
+    policy.kv_heads = static_cast<int>(kv_heads);
+    policy.head_dim = static_cast<int>(head_dim);
+    policy.block_size = static_cast<int>(block_size);
+    policy.causal = causal ? 1 : 0;
+    policy.physical_blocks = static_cast<long long>(physical_blocks);
+    policy.stride = static_cast<long long>(stride);
+    policy.total_query_tokens = static_cast<long long>(total_q);
+    policy.total_kv_tokens = static_cast<long long>(total_kv);
+    return launch_attention_general<T>(stream, policy, total_q * heads, head_dim, scale, LseKind::Natural, -1.0e20f,
+                                       nullptr);
+}
+
+template <typename T, typename Index>
+int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, const void *key_cache,
+                 const void *value_cache, const void *query_offsets, const void *page_offsets, const void *pages,
+                 const void *last_page_lengths, size_t tokens, size_t heads, size_t kv_heads, size_t head_dim,
+                 size_t page_size, size_t cache_pages, size_t sequences, size_t table_len, float scale, int causal,
+                 size_t window, uint32_t *status) {
+    TensorPagedPolicy<T, Index> policy;
+    policy.query = static_cast<const T *>(query);
+    policy.out = static_cast<T *>(out);
+    policy.lse = lse;
+    policy.key_cache = static_cast<const T *>(key_cache);
+    policy.value_cache = static_cast<const T *>(value_cache);
+    policy.query_offsets = static_cast<const Index *>(query_offsets);
+    policy.page_offsets = static_cast<const Index *>(page_offsets);
+    policy.pages = static_cast<const Index *>(pages);
+    policy.last_page_lengths = static_cast<const Index *>(last_page_lengths);
+    policy.sequences = static_cast<int>(sequences);
+    policy.heads = static_cast<int>(heads);
+    policy.kv_heads = static_cast<int>(kv_heads);
+    policy.head_dim = static_cast<int>(head_dim);
+    policy.page_size = static_cast<int>(page_size);
+    policy.causal = causal ? 1 : 0;
+    policy.tokens = static_cast<long long>(tokens);
+    policy.cache_pages = static_cast<long long>(cache_pages);
+    policy.table_len = static_cast<long long>(table_len);
+    policy.window = static_cast<long long>(window);
+    if (status != nullptr) {
+        const unsigned blocks = static_cast<unsigned>((sequences + 127) / 128);
+        check_paged_values_kernel<Index><<<blocks > 64 ? 64 : blocks, 128, 0, stream>>>(
+            policy.query_offsets, policy.page_offsets, policy.pages, policy.last_page_lengths, policy.sequences,
+            policy.tokens, policy.cache_pages, policy.table_len, static_cast<long long>(page_size), status);
+        SINGE_TRY(launch_status());
+    }
+    return launch_attention_general<T>(stream, policy, tokens * heads, head_dim, scale, LseKind::Base2, -INFINITY,
+                                       status);
+}
+
+template <typename T>
+int tensor_paged_entry(singe_stream_t stream, void *out, float *lse, const void *query, const void *key_cache,
+                       const void *value_cache, const void *query_offsets, const void *page_offsets,
+                       const void *pages, const void *last_page_lengths, int index_width, size_t tokens, size_t heads,
+                       size_t kv_heads, size_t head_dim, size_t page_size, size_t cache_pages, size_t sequences,
+                       size_t table_len, float scale, int causal, size_t window, uint32_t *status) {
+    // paged_attention_problem (singe/src/backend/spec/neural/attention.rs:337-361)
+    if (heads == 0 || kv_heads == 0 || head_dim == 0 || page_size == 0 || heads % kv_heads != 0 || !finite(scale)) {
+        return SINGE_ERR_INVALID_ARGUMENT;
+    }
+    if (index_width != 4 && index_width != 8) return SINGE_ERR_INVALID_ARGUMENT;
+    if (!fits_i32(tokens) || !fits_i32(heads) || !fits_i32(head_dim) || !fits_i32(page_size) ||
+        !fits_i32(cache_pages) || !fits_i32(sequences) || !fits_i32(table_len)) {
+        return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    }
+    if (tokens == 0 || sequences == 0) return SINGE_OK;
+    if (out == nullptr || lse == nullptr || query == nullptr || key_cache == nullptr || value_cache == nullptr ||
+        query_offsets == nullptr || page_offsets == nullptr || last_page_lengths == nullptr ||
+        (pages == nullptr && table_len != 0)) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (index_width == 8) {
+        return tensor_paged<T, long long>(s, out, lse, query, key_cache, value_cache, query_offsets, page_offsets,
+                                          pages, last_page_lengths, tokens, heads, kv_heads, head_dim, page_size,
+                                          cache_pages, sequences, table_len, scale, causal, window, status);
+    }
+    return tensor_paged<T, int>(s, out, lse, query, key_cache, value_cache, query_offsets, page_offsets, pages,
+                                last_page_lengths, tokens, heads, kv_heads, head_dim, page_size, cache_pages, sequences,
+                                table_len, scale, causal, window, status);
+}
+
+template <typename T>
+int dense_entry(cudaStream_t stream, T *out, float *lse, const T *query, const T *key, const T *value, size_t batch,
+                size_t heads, size_t kv_heads, size_t query_len, size_t key_len, size_t head_dim, float scale,
+                int causal, size_t window, bool bshd) {
+    if (batch == 0 || heads == 0 || kv_heads == 0 || query_len == 0 || key_len == 0 || head_dim == 0 ||
+        heads % kv_heads != 0 || !finite(scale)) {
+        return SINGE_ERR_INVALID_LENGTH;
+    }
+    if (!fits_i32(batch) || !fits_i32(heads) || !fits_i32(query_len) || !fits_i32(key_len) || !fits_i32(head_dim)) {
+        return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    }
+    if (out == nullptr || query == nullptr || key == nullptr || value == nullptr) return SINGE_ERR_NULL_POINTER;
+    DensePolicy<T> policy;
+    policy.query = query;
+    policy.out = out;
+    policy.lse = lse;
+    policy.key = key;
+    policy.value = value;
+    policy.heads = static_cast<int>(heads);
+    policy.kv_heads = static_cast<int>(kv_heads);
+    policy.query_len = static_cast<int>(query_len);
+    policy.key_len = static_cast<int>(key_len);
+    policy.head_dim = static_cast<int>(head_dim);
+    policy.causal = causal ? 1 : 0;
+    policy.window = static_cast<long long>(window);
+    const long long d = static_cast<long long>(head_dim);
+    if (bshd) {
+        policy.q_batch = static_cast<long long>(query_len) * heads * d;
+        policy.q_head = d;
+        policy.q_row = static_cast<long long>(heads) * d;
+        policy.k_batch = static_cast<long long>(key_len) * kv_heads * d;
+        policy.k_head = d;
+        policy.k_row = static_cast<long long>(kv_heads) * d;
+    } else {
+        policy.q_batch = static_cast<long long>(heads) * query_len * d;
+        policy.q_head = static_cast<long long>(query_len) * d;
+        policy.q_row = d;
+        policy.k_batch = static_cast<long long>(kv_heads) * key_len * d;
+        policy.k_head = static_cast<long long>(key_len) * d;
+        policy.k_row = d;
+    }
+    policy.lse_batch = static_cast<long long>(heads) * query_len;
+    policy.lse_head = static_cast<long long>(query_len);
+    policy.lse_row = 1;
+    return launch_attention_general<T>(stream, policy, batch * heads * query_len, head_dim, scale,
+                                       lse == nullptr ? LseKind::None : LseKind::Natural, -INFINITY, nullptr);
+}
+
+// splitk_reduce_f32 (singe-kernel/src/cpu/attention.rs:2157-2193) with SplitKReduceConfig strides.
+__global__ void splitk_reduce_kernel(float *out, const float *attn, const float *lse, int heads, int splits,
+                                     int head_dim, long long attn_batch, long long attn_head, long long attn_split,
+                                     long long lse_batch, long long lse_head, long long out_batch, long long out_head) {
+    const int b = blockIdx.y;
+    const int head = blockIdx.x;
+    const float *row_lse = lse + b * lse_batch + head * lse_head;
+    float top = -INFINITY;
+    for (int s = 0; s < splits; ++s) top = fmaxf(top, row_lse[s]);
+    float denom = 0.0f;
+    for (int s = 0; s < splits; ++s) denom += expf(row_lse[s] - top);
+    const float *row_attn = attn + b * attn_batch + head * attn_head;
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float sum = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            sum = fmaf(expf(row_lse[s] - top), row_attn[s * attn_split + d], sum);
+        }
+        out[b * out_batch + head * out_head + d] = sum / denom;
+    }
+}
+
+}  // namespace
+}  // namespace singe
+
+using namespace singe;
+
+extern "C" {
+
+int singe_kernel_sys_version(void) { return 1000; }
+
+const char *singe_status_string(int status) {
+    switch (status) {
+        case SINGE_OK: return "ok";
+        case SINGE_ERR_INVALID_LENGTH: return "invalid length";
+        case SINGE_ERR_LENGTH_TOO_SHORT: return "length too short";
+        case SINGE_ERR_LENGTH_EXCEEDS_I32: return "length exceeds i32";
+        case SINGE_ERR_NULL_POINTER: return "null pointer";
+        case SINGE_ERR_SIZE_OVERFLOW: return "size overflow";
+        case SINGE_ERR_UNSUPPORTED_WIDTH: return "unsupported width";
+        case SINGE_ERR_UNSUPPORTED_CONFIGURATION: return "unsupported configuration";
+        case SINGE_ERR_LENGTH_MISMATCH: return "length mismatch";
+        case SINGE_ERR_INDEX_OUT_OF_BOUNDS: return "index out of bounds";
+        case SINGE_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case SINGE_ERR_OUT_OF_RANGE: return "out of range";
+        case SINGE_ERR_AUTOTUNE_DURING_CAPTURE: return "workspace growth during cuda graph capture";
+        default: return status >= SINGE_ERR_CUDA_BASE ? "cuda runtime error" : "unknown status";
+    }
+}
+
+int singe_kv_cache_write_bf16(singe_stream_t stream, void *key_cache, void *value_cache, const void *keys,
+                              const void *values, const void *write_pages, const void *write_slots, int index_width,
+                              size_t tokens, size_t kv_heads, size_t head_dim, size_t pages, size_t page_size,
+                              uint32_t *status) {
+    return kv_cache_write(static_cast<cudaStream_t>(stream), key_cache, value_cache, keys, values, write_pages,
+                          write_slots, index_width, tokens, kv_heads, head_dim, pages, page_size, status, 2);
+}
+
+int singe_kv_cache_write_f16(singe_stream_t stream, void *key_cache, void *value_cache, const void *keys,
+                             const void *values, const void *write_pages, const void *write_slots, int index_width,
+                             size_t tokens, size_t kv_heads, size_t head_dim, size_t pages, size_t page_size,
+                             uint32_t *status) {
+    return kv_cache_write(static_cast<cudaStream_t>(stream), key_cache, value_cache, keys, values, write_pages,
+                          write_slots, index_width, tokens, kv_heads, head_dim, pages, page_size, status, 2);
+}
+
+int singe_kv_cache_write_f32(singe_stream_t stream, void *key_cache, void *value_cache, const void *keys,
+                             const void *values, const void *write_pages, const void *write_slots, int index_width,
+                             size_t tokens, size_t kv_heads, size_t head_dim, size_t pages, size_t page_size,
+                             uint32_t *status) {
+    return kv_cache_write(static_cast<cudaStream_t>(stream), key_cache, value_cache, keys, values, write_pages,
+                          write_slots, index_width, tokens, kv_heads, head_dim, pages, page_size, status, 4);
+}
+
+int singe_paged_kv_decode_attention_bf16(singe_stream_t stream, void *out, const void *query, const void *key_cache,
+                                         const void *value_cache, const int32_t *actual_seq_lens,
+                                         const uint32_t *block_table, size_t batch, size_t heads, size_t kv_heads,
+                                         size_t head_dim, size_t block_size, size_t physical_blocks,
+                                         size_t block_table_batch_stride, float scale) {
+    return decode_half(static_cast<cudaStream_t>(stream), 0, out, query, key_cache, value_cache, actual_seq_lens,
+                       block_table, batch, heads, kv_heads, head_dim, block_size, physical_blocks,
+                       block_table_batch_stride, scale);
+}
+
+int singe_paged_kv_decode_attention_f16(singe_stream_t stream, void *out, const void *query, const void *key_cache,
+                                        const void *value_cache, const int32_t *actual_seq_lens,
+                                        const uint32_t *block_table, size_t batch, size_t heads, size_t kv_heads,
+                                        size_t head_dim, size_t block_size, size_t physical_blocks,
+                                        size_t block_table_batch_stride, float scale) {
+    return decode_half(static_cast<cudaStream_t>(stream), 1, out, query, key_cache, value_cache, actual_seq_lens,
+                       block_table, batch, heads, kv_heads, head_dim, block_size, physical_blocks,
+                       block_table_batch_stride, scale);
+}
+
+int singe_paged_kv_decode_attention_f32(singe_stream_t stream, float *out, const float *query, const float *key_cache,
+                                        const float *value_cache, const int32_t *actual_seq_lens,
+                                        const uint32_t *block_table, size_t batch, size_t heads, size_t kv_heads,
+                                        size_t head_dim, size_t block_size, size_t physical_blocks,
+                                        size_t block_table_batch_stride, float scale) {
+    SINGE_TRY(validate_paged_decode(batch, heads, kv_heads, head_dim, block_size, physical_blocks,
+                                    block_table_batch_stride, scale));
+    if (out == nullptr || query == nullptr || key_cache == nullptr || value_cache == nullptr ||
+        actual_seq_lens == nullptr || block_table == nullptr) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    return decode_general<float>(static_cast<cudaStream_t>(stream), out, query, key_cache, value_cache,
+                                 actual_seq_lens, block_table, batch, heads, kv_heads, head_dim, block_size,
+                                 physical_blocks, block_table_batch_stride, scale);
+}
+
+size_t singe_paged_kv_decode_split_tokens(size_t key_len_bound, size_t max_splits, size_t block_size) {
+    return paged_decode_split_tokens(key_len_bound, max_splits, block_size);
+}
+
+int singe_paged_kv_decode_splitk_bf16(singe_stream_t stream, float *attn_scratch, float *lse_scratch,
+                                      const void *query, const void *key_cache, const void *value_cache,
+                                      const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch,
+                                      size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
+                                      size_t physical_blocks, size_t block_table_batch_stride, size_t max_splits,
+                                      float scale) {
+    return decode_splitk_half(static_cast<cudaStream_t>(stream), 0, nullptr, attn_scratch, lse_scratch, query,
+                              key_cache, value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim,
+                              block_size, physical_blocks, block_table_batch_stride, max_splits, scale, true);
+}
+
+int singe_paged_kv_decode_splitk_reduce_bf16(singe_stream_t stream, void *out, float *attn_scratch,
+                                             float *lse_scratch, const void *query, const void *key_cache,
+                                             const void *value_cache, const int32_t *actual_seq_lens,
+                                             const uint32_t *block_table, size_t batch, size_t heads, size_t kv_heads,
+                                             size_t head_dim, size_t block_size, size_t physical_blocks,
+                                             size_t block_table_batch_stride, size_t max_splits, float scale) {
+    return decode_splitk_half(static_cast<cudaStream_t>(stream), 0, out, attn_scratch, lse_scratch, query, key_cache,
+                              value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim, block_size,
+                              physical_blocks, block_table_batch_stride, max_splits, scale, false);
+}
+
+int singe_paged_kv_decode_splitk_reduce_f16(singe_stream_t stream, void *out, float *attn_scratch, float *lse_scratch,
+                                            const void *query, const void *key_cache, const void *value_cache,
+                                            const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch,
+                                            size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
+                                            size_t physical_blocks, size_t block_table_batch_stride,
+                                            size_t max_splits, float scale) {
+    return decode_splitk_half(static_cast<cudaStream_t>(stream), 1, out, attn_scratch, lse_scratch, query, key_cache,
+                              value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim, block_size,
+                              physical_blocks, block_table_batch_stride, max_splits, scale, false);
+}
+
+int singe_splitk_reduce_f32(singe_stream_t stream, float *out, const float *attn_splitk, const float *lse_splitk,
+                            size_t batch, size_t heads, size_t splits, size_t head_dim, size_t attn_batch_stride,
+                            size_t attn_head_stride, size_t attn_split_stride, size_t lse_batch_stride,
+                            size_t lse_head_stride, size_t output_batch_stride, size_t output_head_stride) {
+    // validate_splitk_reduce_config (singe-kernel/src/cuda/attention/mod.rs): every extent non-zero and within i32.
+    if (batch == 0 || heads == 0 || splits == 0 || head_dim == 0) return SINGE_ERR_INVALID_LENGTH;
+    if (attn_split_stride < head_dim || attn_head_stride < splits * attn_split_stride - (attn_split_stride - head_dim) ||
+        lse_head_stride < splits || output_head_stride < head_dim) {
+        return SINGE_ERR_INVALID_LENGTH;
+    }
+    if (!fits_i32(batch) || !fits_i32(heads) || !fits_i32(splits) || !fits_i32(head_dim)) {
+        return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    }
+    if (out == nullptr || attn_splitk == nullptr || lse_splitk == nullptr) return SINGE_ERR_NULL_POINTER;
+    if (batch > 65535) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    dim3 grid(static_cast<unsigned>(heads), static_cast<unsigned>(batch));
+    splitk_reduce_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        out, attn_splitk, lse_splitk, static_cast<int>(heads), static_cast<int>(splits), static_cast<int>(head_dim),
+        static_cast<long long>(attn_batch_stride), static_cast<long long>(attn_head_stride),
+        static_cast<long long>(attn_split_stride), static_cast<long long>(lse_batch_stride),
+        static_cast<long long>(lse_head_stride), static_cast<long long>(output_batch_stride),
+        static_cast<long long>(output_head_stride));
+    return launch_status();
+}
+
+int singe_paged_attention_bf16(singe_stream_t stream, void *out, float *lse, const void *query, const void *key_cache,
+                               const void *value_cache, const void *query_offsets, const void *page_offsets,
+                               const void *pages, const void *last_page_lengths, int index_width, size_t tokens,
+                               size_t heads, size_t kv_heads, size_t head_dim, size_t page_size, size_t cache_pages,
+                               size_t sequences, size_t table_len, float scale, int causal, size_t window,
+                               uint32_t *status) {
+    return tensor_paged_entry<__nv_bfloat16>(stream, out, lse, query, key_cache, value_cache, query_offsets,
+                                             page_offsets, pages, last_page_lengths, index_width, tokens, heads,
+                                             kv_heads, head_dim, page_size, cache_pages, sequences, table_len, scale,
+                                             causal, window, status);
+}
+
+int singe_paged_attention_f32(singe_stream_t stream, float *out, float *lse, const float *query,
+                              const float *key_cache, const float *value_cache, const void *query_offsets,
+                              const void *page_offsets, const void *pages, const void *last_page_lengths,
+                              int index_width, size_t tokens, size_t heads, size_t kv_heads, size_t head_dim,
+                              size_t page_size, size_t cache_pages, size_t sequences, size_t table_len, float scale,
+                              int causal, size_t window, uint32_t *status) {
+    return tensor_paged_entry<float>(stream, out, lse, query, key_cache, value_cache, query_offsets, page_offsets,
+                                     pages, last_page_lengths, index_width, tokens, heads, kv_heads, head_dim,
+                                     page_size, cache_pages, sequences, table_len, scale, causal, window, status);
+}
+
+#define SINGE_PAGED_PREFILL(NAME, T, POINTER)                                                                         \
+    int NAME(singe_stream_t stream, POINTER *out, float *lse, const POINTER *query, const POINTER *key_cache,         \
+             const POINTER *value_cache, const int32_t *actual_seq_lens_q, const int32_t *actual_seq_lens_kv,         \
+             const int32_t *actual_seq_offsets, const uint32_t *block_table, size_t batch,                            \
+             size_t total_query_tokens, size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,            \
+             size_t physical_blocks, size_t block_table_batch_stride, int causal, float scale) {                      \
+        SINGE_TRY(validate_paged_prefill(batch, total_query_tokens, heads, kv_heads, head_dim, block_size,            \
+                                         physical_blocks, block_table_batch_stride, scale));                          \
+        if (out == nullptr || lse == nullptr || query == nullptr || key_cache == nullptr || value_cache == nullptr || \
+            actual_seq_lens_q == nullptr || actual_seq_lens_kv == nullptr || actual_seq_offsets == nullptr ||         \
+            block_table == nullptr) {                                                                                 \
+            return SINGE_ERR_NULL_POINTER;                                                                            \
+        }                                                                                                             \
+        return packed_prefill_general<T>(static_cast<cudaStream_t>(stream), out, lse, query, key_cache, value_cache,  \
+                                         actual_seq_lens_q, actual_seq_lens_kv, actual_seq_offsets, block_table,      \
+                                         batch, total_query_tokens, 0, heads, kv_heads, head_dim, block_size,         \
+                                         physical_blocks, block_table_batch_stride, causal, scale);                   \
+    }
+
+SINGE_PAGED_PREFILL(singe_paged_kv_prefill_attention_bf16, __nv_bfloat16, void)
+SINGE_PAGED_PREFILL(singe_paged_kv_prefill_attention_f32, float, float)
+#undef SINGE_PAGED_PREFILL
+
+int singe_ragged_kv_prefill_attention_f32(singe_stream_t stream, float *out, float *lse, const float *query,
+                                          const float *key, const float *value, const int32_t *actual_seq_lens_q,
+                                          const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
+                                          size_t batch, size_t total_query_tokens, size_t total_kv_tokens,
+                                          size_t heads, size_t kv_heads, size_t head_dim, int causal, float scale) {
+    SINGE_TRY(validate_ragged_prefill(batch, total_query_tokens, total_kv_tokens, heads, kv_heads, head_dim, scale));
+    if (out == nullptr || lse == nullptr || query == nullptr || key == nullptr || value == nullptr ||
+        actual_seq_lens_q == nullptr || actual_seq_lens_kv == nullptr || actual_seq_offsets == nullptr) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    return packed_prefill_general<float>(static_cast<cudaStream_t>(stream), out, lse, query, key, value,
+                                         actual_seq_lens_q, actual_seq_lens_kv, actual_seq_offsets, nullptr, batch,
+                                         total_query_tokens, total_kv_tokens, heads, kv_heads, head_dim, 1, 1, 1,
+                                         causal, scale);
+}
+
+int singe_ragged_kv_prefill_attention_bf16(singe_stream_t stream, void *out, float *lse, const void *query,
+                                           const void *key, const void *value, const int32_t *actual_seq_lens_q,
+                                           const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
+                                           size_t batch, size_t total_query_tokens, size_t total_kv_tokens,
+                                           size_t heads, size_t kv_heads, size_t head_dim, int causal, float scale) {
+    SINGE_TRY(validate_ragged_prefill(batch, total_query_tokens, total_kv_tokens, heads, kv_heads, head_dim, scale));
+    if (out == nullptr || lse == nullptr || query == nullptr || key == nullptr || value == nullptr ||
+        actual_seq_lens_q == nullptr || actual_seq_lens_kv == nullptr || actual_seq_offsets == nullptr) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    if (prefill_fast_path(heads, kv_heads, head_dim, query, key, value, out)) {
+        return prefill_tcgen05_bf16(static_cast<cudaStream_t>(stream), out, lse, query, key, value, actual_seq_lens_q,
+                                    actual_seq_lens_kv, actual_seq_offsets, batch, total_query_tokens,
+                                    total_kv_tokens, heads, kv_heads, head_dim, causal, scale);
+    }
+    return packed_prefill_general<__nv_bfloat16>(static_cast<cudaStream_t>(stream), out, lse, query, key, value,
+                                                 actual_seq_lens_q, actual_seq_lens_kv, actual_seq_offsets, nullptr,
+                                                 batch, total_query_tokens, total_kv_tokens, heads, kv_heads,
+                                                 head_dim, 1, 1, 1, causal, scale);
+}
+
+int singe_ragged_kv_prefill_attention_cache_write_bf16(
+    singe_stream_t stream, void *out, float *lse, const void *query, const void *key, const void *value,
+    const int32_t *actual_seq_lens_q, const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
+    size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads, size_t kv_heads, size_t head_dim,
+    int causal, float scale, void *key_cache, void *value_cache, const void *write_pages, const void *write_slots,
+    int index_width, size_t pages, size_t page_size, uint32_t *status) {
+    // The cache write is pure HBM copy and the attention is tensor-bound: they are enqueued back to back on the
+    // caller's stream so one call performs the prompt step's KvCache::write + attention.
+    SINGE_TRY(kv_cache_write(static_cast<cudaStream_t>(stream), key_cache, value_cache, key, value, write_pages,
+                             write_slots, index_width, total_kv_tokens, kv_heads, head_dim, pages, page_size, status,
+                             2));
+    return singe_ragged_kv_prefill_attention_bf16(stream, out, lse, query, key, value, actual_seq_lens_q,
+                                                  actual_seq_lens_kv, actual_seq_offsets, batch, total_query_tokens,
+                                                  total_kv_tokens, heads, kv_heads, head_dim, causal, scale);
+}
+
+int singe_fmha_prefill_lse_f32(singe_stream_t stream, float *out, float *lse, const float *query, const float *key,
+                               const float *value, size_t batch, size_t query_len, size_t key_len, size_t heads,
+                               size_t kv_heads, size_t head_dim, float scale, int causal) {
+    if (lse == nullptr) return SINGE_ERR_NULL_POINTER;
+    return dense_entry<float>(static_cast<cudaStream_t>(stream), out, lse, query, key, value, batch, heads, kv_heads,
+                              query_len, key_len, head_dim, scale, causal, 0, true);
+}
+
+int singe_fmha_prefill_lse_bf16(singe_stream_t stream, void *out, float *lse, const void *query, const void *key,
+                                const void *value, size_t batch, size_t query_len, size_t key_len, size_t heads,
+                                size_t kv_heads, size_t head_dim, float scale, int causal) {
+    if (lse == nullptr) return SINGE_ERR_NULL_POINTER;
+    return dense_entry<__nv_bfloat16>(static_cast<cudaStream_t>(stream), static_cast<__nv_bfloat16 *>(out), lse,
+                                      static_cast<const __nv_bfloat16 *>(query),
+                                      static_cast<const __nv_bfloat16 *>(key),
+                                      static_cast<const __nv_bfloat16 *>(value), batch, heads, kv_heads, query_len,
+                                      key_len, head_dim, scale, causal, 0, true);
+}
+
+int singe_scaled_dot_product_attention_f32(singe_stream_t stream, float *out, const float *query, const float *key,
+                                           const float *value, size_t batch, size_t heads, size_t kv_heads,
+                                           size_t query_len, size_t key_len, size_t head_dim, float scale, int causal,
+                                           size_t window) {
+    return dense_entry<float>(static_cast<cudaStream_t>(stream), out, nullptr, query, key, value, batch, heads,
+                              kv_heads, query_len, key_len, head_dim, scale, causal, window, false);
+}
+
+}  // extern "C"

@@ -1,0 +1,357 @@
+// bf16 linear-layer GEMM on the tcgen05 tensor core:  out[M, N] = lhs[M, K] . rhs[N, K]^T, f32 accumulate.
+//
+// Meaning: Linear::forward = x.matmul(W^T) (singe/src/nn/layers/linear/mod.rs:49-70); CPU form bf16 -> f32,
+// ascending-k sum, one rounding of the result (singe/src/backend/cpu/binary/matmul.rs:18-43,
+// singe-kernel/src/cpu/matmul/blocked.rs:27-95).  Replaces singe_tcgen05_matmul
+// (singe/src/backend/cuda/kernel_plan/source/tcgen05.rs:137-266), which is single-stage and cp.async-fed.
+//
+// Structure: persistent CTAs (one per SM), warp-specialised.
+//   warp 0   TMA producer: A tile [a_rows x 64] and B tile [BN x 64] of bf16 per stage, SWIZZLE_128B, ring of
+//            `stages` mbarrier pairs.
+//   warp 1   MMA issuer: owns tensor memory (2 accumulators of BN columns), issues four
+//            tcgen05.mma 128 x BN x 16 per stage, commits the stage back to the producer and, after the last
+//            k-block, the accumulator to the epilogue.
+//   warps 2-5 epilogue: tcgen05.ld 32 columns at a time, convert, store; then hand the accumulator back, so
+//            the MMA of the next tile overlaps this tile's epilogue.
+// Both operands are K-major, so M/N/K tails come for free from TMA's zero fill; stores are masked.
+// Small M (decode batches) uses narrow BN so that enough CTAs stream the weight matrix to fill HBM, and a
+// short A box: rows past the box are stale shared memory, which only reaches output rows that are not stored.
+// Tiles are ordered in groups of eight M-tiles so that one wave of CTAs shares A and B tiles through L2.
+// Every mbarrier wait is bounded; a wait that runs out sets the device error word and the CTA leaves.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace singe {
+
+namespace {
+
+constexpr int kGemmThreads = 192;
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;
+constexpr int kMaxStages = 16;
+constexpr int kGroupM = 8;
+
+struct GemmParams {
+    void *out;
+    int out_f32;
+    int m, n, k;
+    long long ldo;
+    int a_rows;       // rows of the A box (multiple of 8, <= 128)
+    int stages;
+    int stage_bytes;  // a_rows * 128 + BN * 128
+    int tiles_m, tiles_n, k_blocks;
+    int vector_store;  // 16-byte stores are legal (alignment and stride)
+    uint32_t *error;   // sticky device error word (2 = a bounded wait ran out)
+};
+
+__device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tiles_n, int &tm, int &tn) {
+    const int per_group = kGroupM * tiles_n;
+    const int group = tile / per_group;
+    const int first_m = group * kGroupM;
+    const int rows = min(kGroupM, tiles_m - first_m);
+    const int within = tile - group * per_group;
+    tm = first_m + within % rows;
+    tn = within / rows;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_bf16_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
+                     const GemmParams p) {
+    constexpr uint32_t kTmemColumns = 2 * BN < 32 ? 32 : 2 * BN;
+    constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, 0, 0);
+    constexpr int kBBytes = BN * 128;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    // [stages x stage_bytes][16 KB over-read pad][barriers]
+    const uint32_t bars = base + p.stages * p.stage_bytes + kBlockM * 128;
+    const uint32_t bar_full = bars;
+    const uint32_t bar_empty = bars + kMaxStages * 8;
+    const uint32_t bar_acc_full = bars + 2 * kMaxStages * 8;
+    const uint32_t bar_acc_empty = bar_acc_full + 16;
+    const uint32_t tmem_holder = bar_acc_empty + 16;
+    volatile uint32_t *tmem_holder_ptr =
+        reinterpret_cast<volatile uint32_t *>(smem_raw + (tmem_holder - raw));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int a_bytes = p.a_rows * 128;
+    const int total_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_acc_full + a * 8, 1);
+            mbar_init(bar_acc_empty + a * 8, 4);
+        }
+        mbar_init_fence();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_holder, kTmemColumns);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_holder_ptr;
+
+    bool failed = false;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            prefetch_tensor_map(&a_map);
+            prefetch_tensor_map(&b_map);
+        }
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+            int tm, tn;
+            tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
+            for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                const int s = it % p.stages;
+                const uint32_t phase = (it / p.stages) & 1;
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(bar_empty + s * 8, phase ^ 1) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    failed = true;
+                    break;
+                }
+                if (lane == 0) {
+                    const uint32_t stage = base + s * p.stage_bytes;
+                    const uint32_t full = bar_full + s * 8;
+                    mbar_expect_tx(full, a_bytes + kBBytes);
+                    tma_load_2d(stage, &a_map, full, kb * kBlockK, tm * kBlockM);
+                    tma_load_2d(stage + a_bytes, &b_map, full, kb * kBlockK, tn * BN);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        int it = 0;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++local) {
+            const int acc = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_empty + acc * 8, acc_phase ^ 1) ? 1 : 0)) {
+                failed = true;
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t tmem_d = tmem_base + acc * BN;
+            for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                const int s = it % p.stages;
+                const uint32_t phase = (it / p.stages) & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait(bar_full + s * 8, phase) ? 1 : 0)) {
+                    failed = true;
+                    break;
+                }
+                tcgen05_fence_after();
+                if (lane == 0) {
+                    const uint32_t stage = base + s * p.stage_bytes;
+                    const uint64_t a_desc = make_smem_desc(stage, 16, 1024);
+                    const uint64_t b_desc = make_smem_desc(stage + a_bytes, 16, 1024);
+#pragma unroll
+                    for (int ks = 0; ks < kBlockK / 16; ++ks) {
+                        // 16 bf16 of K = 32 bytes = 2 descriptor address units
+                        umma_ss(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kIdesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(bar_empty + s * 8);
+                }
+                __syncwarp();
+            }
+            if (failed) break;
+            if (lane == 0) {
+                tcgen05_commit(bar_acc_full + acc * 8);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;  // tensor-memory lanes 32*quarter .. +31
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++local) {
+            int tm, tn;
+            tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
+            const int acc = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_full + acc * 8, acc_phase) ? 1 : 0)) {
+                failed = true;
+                break;
+            }
+            tcgen05_fence_after();
+            const int row = tm * kBlockM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld_x32(taddr + c, r);
+                tmem_wait_ld();
+                const int col = tn * BN + c;
+                if (row < p.m && col < p.n) {
+                    if (p.out_f32) {
+                        float *dst = static_cast<float *>(p.out) + static_cast<long long>(row) * p.ldo + col;
+                        if (p.vector_store && col + 32 <= p.n) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                *reinterpret_cast<uint4 *>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (col + j < p.n) dst[j] = __uint_as_float(r[j]);
+                            }
+                        }
+                    } else {
+                        __nv_bfloat16 *dst =
+                            static_cast<__nv_bfloat16 *>(p.out) + static_cast<long long>(row) * p.ldo + col;
+                        if (p.vector_store && col + 32 <= p.n) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 packed;
+                                packed.x = pack2<__nv_bfloat16>(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                                packed.y = pack2<__nv_bfloat16>(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                                packed.z = pack2<__nv_bfloat16>(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                                packed.w = pack2<__nv_bfloat16>(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                                *reinterpret_cast<uint4 *>(dst + j) = packed;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (col + j < p.n) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                            }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_acc_empty + acc * 8);
+            }
+        }
+    }
+    if (failed && lane == 0) {
+        report_status(p.error, kStatusWaitTimeout);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+template <int BN>
+int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const void *rhs, size_t lhs_row_stride,
+                size_t rhs_row_stride) {
+    constexpr int kSmemLimit = 227 * 1024;
+    const int b_bytes = BN * 128;
+    params.stage_bytes = params.a_rows * 128 + b_bytes;
+    const int fixed = kBlockM * 128 + 2 * kMaxStages * 8 + 64 + 1024;
+    int stages = (kSmemLimit - fixed) / params.stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages > params.k_blocks + 1 && params.k_blocks + 1 >= 2) stages = params.k_blocks + 1;
+    if (stages < 2) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    params.stages = stages;
+    params.tiles_n = (params.n + BN - 1) / BN;
+    const int smem = stages * params.stage_bytes + fixed;
+    SINGE_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+
+    CUtensorMap a_map, b_map;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(params.k), static_cast<uint64_t>(params.m)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(lhs_row_stride) * 2};
+        const uint32_t box[2] = {kBlockK, static_cast<uint32_t>(params.a_rows)};
+        SINGE_TRY(encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, lhs, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(params.k), static_cast<uint64_t>(params.n)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(rhs_row_stride) * 2};
+        const uint32_t box[2] = {kBlockK, static_cast<uint32_t>(BN)};
+        SINGE_TRY(encode_tensor_map(&b_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rhs, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+    }
+    const int total = params.tiles_m * params.tiles_n;
+    const int grid = total < device_sm_count() ? total : device_sm_count();
+    gemm_bf16_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(a_map, b_map, params);
+    return launch_status();
+}
+
+}  // namespace
+
+// validate_matmul (singe-kernel/src/cuda/matmul.rs:2977-3020), then the layout gate of the tensor-core path.
+int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, const void *rhs, size_t rows,
+              size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
+              size_t output_row_stride, int transpose_lhs, int transpose_rhs) {
+    const size_t lhs_min = transpose_lhs ? rows : reduction;
+    const size_t rhs_min = transpose_rhs ? reduction : columns;
+    if (rows == 0 || columns == 0 || reduction == 0 || lhs_row_stride < lhs_min || rhs_row_stride < rhs_min ||
+        output_row_stride < columns) {
+        return SINGE_ERR_INVALID_LENGTH;
+    }
+    if (!fits_i32(rows) || !fits_i32(columns) || !fits_i32(reduction) || !fits_i32(lhs_row_stride) ||
+        !fits_i32(rhs_row_stride) || !fits_i32(output_row_stride)) {
+        return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    }
+    if (out == nullptr || lhs == nullptr || rhs == nullptr) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    // Tensor-core path: linear-layer layout, 16-byte aligned rows for TMA.
+    const bool aligned = ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15u) == 0 &&
+                         lhs_row_stride % 8 == 0 && rhs_row_stride % 8 == 0;
+    if (transpose_lhs || !transpose_rhs || !aligned) {
+        return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    }
+    GemmParams params;
+    params.error = device_error_word();
+    params.out = out;
+    params.out_f32 = out_f32 ? 1 : 0;
+    params.m = static_cast<int>(rows);
+    params.n = static_cast<int>(columns);
+    params.k = static_cast<int>(reduction);
+    params.ldo = static_cast<long long>(output_row_stride);
+    params.tiles_m = (params.m + kBlockM - 1) / kBlockM;
+    params.k_blocks = (params.k + kBlockK - 1) / kBlockK;
+    int a_rows = kBlockM;
+    if (params.m < kBlockM) {
+        a_rows = (params.m + 7) / 8 * 8;
+    }
+    params.a_rows = a_rows;
+    const size_t element = out_f32 ? 4 : 2;
+    params.vector_store =
+        ((reinterpret_cast<uintptr_t>(out) & 15u) == 0 && (output_row_stride * element) % 16 == 0) ? 1 : 0;
+    // Widest tile that still gives every SM a tile; narrow tiles for skinny (HBM-bound) problems.
+    const int sms = device_sm_count();
+    auto tiles = [&](int bn) { return params.tiles_m * ((params.n + bn - 1) / bn); };
+    if (tiles(256) >= sms) return launch_gemm<256>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
+    if (tiles(128) >= sms) return launch_gemm<128>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
+    if (tiles(64) >= sms) return launch_gemm<64>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
+    return launch_gemm<32>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
+}
+
+}  // namespace singe
+
+extern "C" {
+
+int singe_matmul_bf16_bf16(singe_stream_t stream, void *out, const void *lhs, const void *rhs, size_t rows,
+                           size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
+                           size_t output_row_stride, int transpose_lhs, int transpose_rhs) {
+    return singe::gemm_bf16(static_cast<cudaStream_t>(stream), out, false, lhs, rhs, rows, columns, reduction,
+                            lhs_row_stride, rhs_row_stride, output_row_stride, transpose_lhs, transpose_rhs);
+}
+
+int singe_matmul_bf16_f32(singe_stream_t stream, float *out, const void *lhs, const void *rhs, size_t rows,
+                          size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
+                          size_t output_row_stride, int transpose_lhs, int transpose_rhs) {
+    return singe::gemm_bf16(static_cast<cudaStream_t>(stream), out, true, lhs, rhs, rows, columns, reduction,
+                            lhs_row_stride, rhs_row_stride, output_row_stride, transpose_lhs, transpose_rhs);
+}
+
+}  // extern "C"

@@ -1,0 +1,457 @@
+// Paged-KV flash-decode with split-K and a log-sum-exp combine, for bf16/f16 caches laid out
+// [pages, 16, kv_heads, head_dim] with head_dim 64 or 128 and up to 8 query heads per KV head.
+//
+// Meaning: paged_kv_decode_attention (singe-kernel/src/cpu/attention.rs:1172-1246) with the split
+// partials of the reference's split-K decode (singe-kernel/src/cuda/attention/mod.rs:2456-2509) and
+// the combine of splitk_reduce_f32 (singe-kernel/src/cpu/attention.rs:2157-2193).
+//
+// Structure (HBM-bound; 2 * kv_heads * head_dim * 2 bytes per cached token must cross HBM once):
+//   grid  = (max_splits, kv_heads, batch); one CTA owns up to `split_tokens` keys of one (sequence,
+//           KV head) and ALL query heads of that KV head, so K and V are read once for the group.
+//   warp 4 (producer): reads the block table 32 entries at a time and issues one TMA tile load per
+//           (page, 64-wide half of the head) -- 16 rows x 128 bytes, SWIZZLE_128B -- for K and V into a
+//           ring of stages, one mbarrier pair per stage.
+//   warps 0-3 (consumers): page i belongs to warp i % 4.  S = Q K^T and O += P V run as m16n8k16
+//           tensor-core tiles fed by ldmatrix from the swizzled stage (conflict-free), softmax runs in
+//           f32 with warp-shuffle row reductions in the exp2 domain.
+//   The four warps' (max, sum, O) states are merged through shared memory; the CTA writes either the
+//   final row (the sequence fits one split) or a normalised partial + natural-log LSE.
+//   decode_combine_kernel folds the partials of sequences that needed more than one split.
+// Every mbarrier wait is bounded; a wait that runs out sets status code 2 and the CTA leaves.
+#include "common.cuh"
+
+namespace singe {
+
+namespace {
+
+constexpr int kDecodeWarps = 4;
+constexpr int kDecodeThreads = (kDecodeWarps + 1) * 32;
+constexpr int kDecodeStages = 10;
+constexpr int kPageTokens = 16;
+constexpr int kHalfBytes = kPageTokens * 128;  // one TMA box: 16 rows x 128 bytes
+
+struct DecodeParams {
+    void *out;            // [batch, heads, head_dim] in the cache dtype, or nullptr (partials only)
+    float *attn_partial;  // [batch, heads, max_splits, head_dim]
+    float *lse_partial;   // [batch, heads, max_splits]
+    const void *query;    // [batch, heads, head_dim]
+    const int32_t *lens;
+    const uint32_t *table;
+    int heads;
+    int kv_heads;
+    int group;
+    int physical_blocks;
+    int table_stride;
+    int split_tokens;  // multiple of 16
+    int max_splits;
+    int partials_only;  // 1: every split slot is written, nothing goes to `out`
+    float scale_log2;   // scale * log2(e)
+    uint32_t *status;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int HD>
+constexpr int decode_stage_bytes() {
+    return 2 * (HD / 64) * kHalfBytes;
+}
+
+template <int HD>
+constexpr int decode_smem_bytes() {
+    // stages + merge buffers (O: 4 warps x 8 rows x HD f32; max/sum: 4 x 8 each) + barriers + alignment slack
+    return kDecodeStages * decode_stage_bytes<HD>() + kDecodeWarps * 8 * HD * 4 + 2 * kDecodeWarps * 8 * 4 +
+           2 * kDecodeStages * 8 + 1024;
+}
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(kDecodeThreads, 2)
+    paged_decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                        const DecodeParams p) {
+    constexpr int NHALF = HD / 64;
+    constexpr int KSTEPS = HD / 16;
+    constexpr int NTILES = HD / 8;
+    constexpr int STAGE = decode_stage_bytes<HD>();
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *aligned = smem_raw + (base - raw);
+    float *merge_o = reinterpret_cast<float *>(aligned + kDecodeStages * STAGE);  // [4][8][HD]
+    float *merge_m = merge_o + kDecodeWarps * 8 * HD;                              // [4][8]
+    float *merge_l = merge_m + kDecodeWarps * 8;                                   // [4][8]
+    const uint32_t bar_full = base + kDecodeStages * STAGE + kDecodeWarps * 8 * HD * 4 + 2 * kDecodeWarps * 8 * 4;
+    const uint32_t bar_empty = bar_full + kDecodeStages * 8;
+
+    const int split = blockIdx.x;
+    const int g = blockIdx.y;
+    const int b = blockIdx.z;
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const T *query = static_cast<const T *>(p.query);
+
+    int len = p.lens[b];
+    const int bound = p.table_stride * kPageTokens;
+    len = len < 0 ? 0 : (len > bound ? bound : len);
+    const int n_splits = (len + p.split_tokens - 1) / p.split_tokens;
+
+    if (split >= n_splits) {
+        // Nothing to attend.  Split 0 of an empty sequence still owns the row: zeros, as the reference writes.
+        const bool owns_row = split == 0 && !p.partials_only;
+        if (owns_row || p.partials_only) {
+            for (int r = 0; r < p.group; ++r) {
+                const size_t row = static_cast<size_t>(b) * p.heads + g * p.group + r;
+                for (int d = tid; d < HD; d += kDecodeThreads) {
+                    if (owns_row) {
+                        static_cast<T *>(p.out)[row * HD + d] = from_float<T>(0.0f);
+                    } else {
+                        p.attn_partial[(row * p.max_splits + split) * HD + d] = 0.0f;
+                    }
+                }
+                if (p.partials_only && tid == 0) {
+                    p.lse_partial[row * p.max_splits + split] = -INFINITY;
+                }
+            }
+        }
+        return;
+    }
+
+    const int tok_begin = split * p.split_tokens;
+    const int tok_end = min(len, tok_begin + p.split_tokens);
+    const int npages = (tok_end - tok_begin + kPageTokens - 1) / kPageTokens;
+    const int first_page = tok_begin / kPageTokens;
+
+    if (tid == 0) {
+        for (int s = 0; s < kDecodeStages; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    bool failed = false;
+
+    if (warp == kDecodeWarps) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            prefetch_tensor_map(&k_map);
+            prefetch_tensor_map(&v_map);
+        }
+        const uint32_t *table = p.table + static_cast<size_t>(b) * p.table_stride + first_page;
+        for (int chunk = 0; chunk < npages && !failed; chunk += 32) {
+            const int mine = chunk + lane;
+            uint32_t page = mine < npages ? table[mine] : 0u;
+            if (page >= static_cast<uint32_t>(p.physical_blocks)) {
+                report_status(p.status, kStatusIndexOutOfBounds);
+                page = 0u;
+            }
+            const int count = min(32, npages - chunk);
+            for (int j = 0; j < count; ++j) {
+                const uint32_t pg = __shfl_sync(0xffffffffu, page, j);
+                const int i = chunk + j;
+                const int s = i % kDecodeStages;
+                const int use = i / kDecodeStages;
+                if (use > 0) {
+                    // Lane 0 alone issues the loads, so it alone waits; the verdict is made warp-uniform.
+                    int ok = 1;
+                    if (lane == 0) {
+                        ok = mbar_wait(bar_empty + s * 8, (use - 1) & 1) ? 1 : 0;
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) {
+                        failed = true;
+                        break;
+                    }
+                }
+                if (lane == 0) {
+                    const uint32_t full = bar_full + s * 8;
+                    const uint32_t stage = base + s * STAGE;
+                    mbar_expect_tx(full, STAGE);
+#pragma unroll
+                    for (int hf = 0; hf < NHALF; ++hf) {
+                        tma_load_4d(stage + hf * kHalfBytes, &k_map, full, hf * 64, g, 0, static_cast<int32_t>(pg));
+                    }
+#pragma unroll
+                    for (int hf = 0; hf < NHALF; ++hf) {
+                        tma_load_4d(stage + (NHALF + hf) * kHalfBytes, &v_map, full, hf * 64, g, 0,
+                                    static_cast<int32_t>(pg));
+                    }
+                }
+            }
+        }
+        if (failed && lane == 0) {
+            report_status(p.status, kStatusWaitTimeout);
+        }
+    } else {
+        // ---------------- consumers ----------------
+        const int row = lane >> 2;   // query head within the group (rows >= group are zero padding)
+        const int quad = lane & 3;
+        uint32_t qa[KSTEPS][2];
+        {
+            const size_t head = static_cast<size_t>(b) * p.heads + g * p.group + row;
+            const uint32_t *q32 = reinterpret_cast<const uint32_t *>(query + head * HD);
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                qa[ks][0] = row < p.group ? q32[ks * 8 + quad] : 0u;
+                qa[ks][1] = row < p.group ? q32[ks * 8 + 4 + quad] : 0u;
+            }
+        }
+        float o[NTILES][4];
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt) {
+            o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+        }
+        float run_max = -INFINITY;
+        float run_sum = 0.0f;
+
+        // Per-lane constants of the ldmatrix addresses (see the layout note at the top of the file).
+        const int mat = lane >> 3;
+        const int k_tok = ((mat >> 1) << 3) + (lane & 7);
+        const int k_sel = mat & 1;
+        const int v_tok = ((mat & 1) << 3) + (lane & 7);
+        const int v_sel = mat >> 1;
+
+        for (int i = warp; i < npages; i += kDecodeWarps) {
+            const int s = i % kDecodeStages;
+            const int use = i / kDecodeStages;
+            // Every lane observes the phase itself (it reads the TMA-written tile); the verdict is warp-uniform.
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_full + s * 8, use & 1) ? 1 : 0)) {
+                failed = true;
+                break;
+            }
+            const uint32_t stage_k = base + s * STAGE;
+            const uint32_t stage_v = stage_k + NHALF * kHalfBytes;
+
+            float s0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float s1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                const int hf = ks >> 2;
+                const int c = ((ks & 3) << 1) + k_sel;
+                uint32_t r0, r1, r2, r3;
+                ldmatrix_x4(stage_k + hf * kHalfBytes + k_tok * 128 + ((c ^ (k_tok & 7)) << 4), r0, r1, r2, r3);
+                mma_m16n8k16<T>(s0, qa[ks][0], 0u, qa[ks][1], 0u, r0, r1);
+                mma_m16n8k16<T>(s1, qa[ks][0], 0u, qa[ks][1], 0u, r2, r3);
+            }
+            // Row `row` of this lane: keys t0, t0+1 (tile 0) and t0+8, t0+9 (tile 1).
+            const int t0 = tok_begin + i * kPageTokens + quad * 2;
+            float x00 = t0 < tok_end ? s0[0] * p.scale_log2 : -INFINITY;
+            float x01 = t0 + 1 < tok_end ? s0[1] * p.scale_log2 : -INFINITY;
+            float x10 = t0 + 8 < tok_end ? s1[0] * p.scale_log2 : -INFINITY;
+            float x11 = t0 + 9 < tok_end ? s1[1] * p.scale_log2 : -INFINITY;
+            float tile_max = fmaxf(fmaxf(x00, x01), fmaxf(x10, x11));
+            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+            const float next_max = fmaxf(run_max, tile_max);
+            const float correction = fast_exp2(run_max - next_max);
+            run_max = next_max;
+            x00 = fast_exp2(x00 - next_max);
+            x01 = fast_exp2(x01 - next_max);
+            x10 = fast_exp2(x10 - next_max);
+            x11 = fast_exp2(x11 - next_max);
+            run_sum = run_sum * correction + (x00 + x01) + (x10 + x11);
+#pragma unroll
+            for (int nt = 0; nt < NTILES; ++nt) {
+                o[nt][0] *= correction;
+                o[nt][1] *= correction;
+            }
+            const uint32_t pa0 = pack2<T>(x00, x01);
+            const uint32_t pa2 = pack2<T>(x10, x11);
+#pragma unroll
+            for (int j = 0; j < NTILES / 2; ++j) {
+                const int cg = 2 * j + v_sel;
+                const int hf = cg >> 3;
+                const int c = cg & 7;
+                uint32_t r0, r1, r2, r3;
+                ldmatrix_x4_trans(stage_v + hf * kHalfBytes + v_tok * 128 + ((c ^ (v_tok & 7)) << 4), r0, r1, r2, r3);
+                mma_m16n8k16<T>(o[2 * j], pa0, 0u, pa2, 0u, r0, r1);
+                mma_m16n8k16<T>(o[2 * j + 1], pa0, 0u, pa2, 0u, r2, r3);
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_empty + s * 8);
+            }
+        }
+        if (failed && lane == 0) {
+            report_status(p.status, kStatusWaitTimeout);
+        }
+        run_sum += __shfl_xor_sync(0xffffffffu, run_sum, 1);
+        run_sum += __shfl_xor_sync(0xffffffffu, run_sum, 2);
+        if (quad == 0) {
+            merge_m[warp * 8 + row] = run_max;
+            merge_l[warp * 8 + row] = run_sum;
+        }
+        float *mine = merge_o + (warp * 8 + row) * HD;
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt) {
+            *reinterpret_cast<float2 *>(mine + nt * 8 + quad * 2) = make_float2(o[nt][0], o[nt][1]);
+        }
+    }
+    __syncthreads();
+
+    // ---------------- merge the four warps and write ----------------
+    const bool direct = n_splits == 1 && !p.partials_only;
+    for (int item = tid; item < p.group * HD; item += kDecodeThreads) {
+        const int r = item / HD;
+        const int d = item - r * HD;
+        float top = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w) {
+            top = fmaxf(top, merge_m[w * 8 + r]);
+        }
+        float total = 0.0f;
+        float value = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w) {
+            const float m = merge_m[w * 8 + r];
+            const float weight = m == -INFINITY ? 0.0f : fast_exp2(m - top);
+            total += merge_l[w * 8 + r] * weight;
+            value += merge_o[(w * 8 + r) * HD + d] * weight;
+        }
+        const size_t head_row = static_cast<size_t>(b) * p.heads + g * p.group + r;
+        const float result = value / total;
+        if (direct) {
+            static_cast<T *>(p.out)[head_row * HD + d] = from_float<T>(result);
+        } else {
+            p.attn_partial[(head_row * p.max_splits + split) * HD + d] = result;
+            if (d == 0) {
+                // natural-log LSE of the scaled scores: (max2 + log2(sum)) * ln 2
+                p.lse_partial[head_row * p.max_splits + split] = (top + log2f(total)) * 0.6931471805599453f;
+            }
+        }
+    }
+}
+
+// Folds the split partials of every (sequence, head) row that needed more than one split.
+// Follows splitk_reduce_f32 (singe-kernel/src/cpu/attention.rs:2157-2193): out = sum_s exp(lse_s - M) attn_s / sum_s exp(lse_s - M).
+template <typename T>
+__global__ void decode_combine_kernel(T *out, const float *attn_partial, const float *lse_partial, const int32_t *lens,
+                                      int heads, int head_dim, int split_tokens, int max_splits, int bound) {
+    const int b = blockIdx.y;
+    const int head = blockIdx.x;
+    int len = lens[b];
+    len = len < 0 ? 0 : (len > bound ? bound : len);
+    const int n = (len + split_tokens - 1) / split_tokens;
+    if (n <= 1) {
+        return;  // the decode kernel already wrote the row
+    }
+    const size_t row = static_cast<size_t>(b) * heads + head;
+    const float *lse = lse_partial + row * max_splits;
+    float top = -INFINITY;
+    for (int s = 0; s < n; ++s) top = fmaxf(top, lse[s]);
+    float denom = 0.0f;
+    for (int s = 0; s < n; ++s) denom += expf(lse[s] - top);
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float sum = 0.0f;
+        for (int s = 0; s < n; ++s) {
+            sum = fmaf(expf(lse[s] - top), attn_partial[(row * max_splits + s) * head_dim + d], sum);
+        }
+        out[row * head_dim + d] = from_float<T>(sum / denom);
+    }
+}
+
+template <typename T, int HD>
+int launch_decode(cudaStream_t stream, const DecodeParams &params, const void *key_cache, const void *value_cache,
+                  size_t batch) {
+    static bool configured = false;
+    constexpr int smem = decode_smem_bytes<HD>();
+    if (!configured) {
+        SINGE_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured = true;
+    }
+    CUtensorMap k_map, v_map;
+    const uint64_t dims[4] = {static_cast<uint64_t>(HD), static_cast<uint64_t>(params.kv_heads), kPageTokens,
+                              static_cast<uint64_t>(params.physical_blocks)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(HD) * sizeof(T),
+                                 static_cast<uint64_t>(HD) * sizeof(T) * params.kv_heads,
+                                 static_cast<uint64_t>(HD) * sizeof(T) * params.kv_heads * kPageTokens};
+    const uint32_t box[4] = {64, 1, kPageTokens, 1};
+    SINGE_TRY(encode_tensor_map(&k_map, TensorMapType<T>::value, 4, key_cache, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B));
+    SINGE_TRY(encode_tensor_map(&v_map, TensorMapType<T>::value, 4, value_cache, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B));
+    dim3 grid(static_cast<unsigned>(params.max_splits), static_cast<unsigned>(params.kv_heads),
+              static_cast<unsigned>(batch));
+    paged_decode_kernel<T, HD><<<grid, kDecodeThreads, smem, stream>>>(k_map, v_map, params);
+    return launch_status();
+}
+
+}  // namespace
+
+// True when the tensor-core flash-decode kernel takes this shape.
+bool paged_decode_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t block_size, const void *key_cache,
+                            const void *value_cache, const void *query) {
+    const size_t group = heads / kv_heads;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(key_cache) | reinterpret_cast<uintptr_t>(value_cache)) & 15u) == 0 &&
+                         (reinterpret_cast<uintptr_t>(query) & 3u) == 0;
+    return (head_dim == 64 || head_dim == 128) && block_size == kPageTokens && group >= 1 && group <= 8 && aligned;
+}
+
+size_t paged_decode_split_tokens(size_t key_len_bound, size_t max_splits, size_t block_size) {
+    if (max_splits == 0) max_splits = 1;
+    if (block_size == 0) block_size = 1;
+    size_t per = (key_len_bound + max_splits - 1) / max_splits;
+    per = (per + block_size - 1) / block_size * block_size;
+    return per == 0 ? block_size : per;
+}
+
+// Launches the flash-decode kernel and, unless `partials_only`, the combine.  The caller has validated the
+// configuration and chosen the fast path.  T is selected by `element` (0 = bf16, 1 = f16).
+int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn_scratch, float *lse_scratch,
+                        const void *query, const void *key_cache, const void *value_cache,
+                        const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch, size_t heads,
+                        size_t kv_heads, size_t head_dim, size_t physical_blocks, size_t block_table_batch_stride,
+                        size_t max_splits, float scale, bool partials_only, uint32_t *status) {
+    DecodeParams params;
+    params.out = out;
+    params.attn_partial = attn_scratch;
+    params.lse_partial = lse_scratch;
+    params.query = query;
+    params.lens = actual_seq_lens;
+    params.table = block_table;
+    params.heads = static_cast<int>(heads);
+    params.kv_heads = static_cast<int>(kv_heads);
+    params.group = static_cast<int>(heads / kv_heads);
+    params.physical_blocks = static_cast<int>(physical_blocks);
+    params.table_stride = static_cast<int>(block_table_batch_stride);
+    const size_t bound = block_table_batch_stride * kPageTokens;
+    params.split_tokens = static_cast<int>(paged_decode_split_tokens(bound, max_splits, kPageTokens));
+    params.max_splits = static_cast<int>(max_splits);
+    params.partials_only = partials_only ? 1 : 0;
+    params.scale_log2 = scale * 1.4426950408889634f;
+    params.status = status;
+    if (batch > 65535 || max_splits > 0x7fffffffull || kv_heads > 65535) {
+        return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    }
+    int result;
+    if (element == 0) {
+        result = head_dim == 128 ? launch_decode<__nv_bfloat16, 128>(stream, params, key_cache, value_cache, batch)
+                                 : launch_decode<__nv_bfloat16, 64>(stream, params, key_cache, value_cache, batch);
+    } else {
+        result = head_dim == 128 ? launch_decode<__half, 128>(stream, params, key_cache, value_cache, batch)
+                                 : launch_decode<__half, 64>(stream, params, key_cache, value_cache, batch);
+    }
+    SINGE_TRY(result);
+    if (!partials_only && max_splits > 1) {
+        dim3 grid(static_cast<unsigned>(heads), static_cast<unsigned>(batch));
+        const int threads = head_dim >= 128 ? 128 : 64;
+        if (element == 0) {
+            decode_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+                static_cast<__nv_bfloat16 *>(out), attn_scratch, lse_scratch, actual_seq_lens, params.heads,
+                static_cast<int>(head_dim), params.split_tokens, params.max_splits, static_cast<int>(bound));
+        } else {
+            decode_combine_kernel<__half><<<grid, threads, 0, stream>>>(
+                static_cast<__half *>(out), attn_scratch, lse_scratch, actual_seq_lens, params.heads,
+                static_cast<int>(head_dim), params.split_tokens, params.max_splits, static_cast<int>(bound));
+        }
+        return launch_status();
+    }
+    return SINGE_OK;
+}
+
+}  // namespace singe

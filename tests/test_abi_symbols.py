@@ -1,0 +1,63 @@
+"""The C-ABI library loads on a machine without a GPU and exports every symbol the header declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from singe_b200 import kernel_sys as ks
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "singe_kernel_sys.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(singe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_is_built_and_exports_every_declared_symbol():
+    if not os.path.exists(ks.LIB_PATH):
+        from singe_b200 import build
+
+        build.build()
+    handle = ctypes.CDLL(ks.LIB_PATH)
+    declared = _declared()
+    assert len(declared) >= 20
+    missing = [name for name in declared if not hasattr(handle, name)]
+    assert not missing, f"declared in include/singe_kernel_sys.h but not exported: {missing}"
+
+
+def test_python_binding_covers_the_header():
+    declared = set(_declared())
+    bound = set(ks.SIGNATURES)
+    assert declared - bound == set(), f"unbound symbols: {sorted(declared - bound)}"
+    assert bound - declared <= {"singe_debug_take_device_error"}
+
+
+def test_status_strings_and_host_only_helpers_need_no_gpu():
+    lib = ks.lib()
+    assert lib.singe_kernel_sys_version() >= 1000
+    assert ks.status_string(ks.OK) == "ok"
+    assert ks.status_string(ks.ERR_INVALID_LENGTH) == "invalid length"
+    # split sizing is host arithmetic: ceil(bound / splits) rounded up to whole pages
+    assert lib.singe_paged_kv_decode_split_tokens(4096, 8, 16) == 512
+    assert lib.singe_paged_kv_decode_split_tokens(4096, 6, 16) == 688
+    assert lib.singe_paged_kv_decode_split_tokens(100, 64, 16) == 16
+
+
+def test_validation_runs_before_any_device_work():
+    lib = ks.lib()
+    # heads not a multiple of kv_heads -> InvalidLength; checked before the (absent) device is touched
+    assert lib.singe_paged_kv_decode_attention_f32(None, None, None, None, None, None, None, 1, 3, 2, 8, 4, 2, 2,
+                                                   1.0) == ks.ERR_INVALID_LENGTH
+    assert lib.singe_kv_cache_write_bf16(None, None, None, None, None, None, None, 8, 0, 1, 1, 1, 1,
+                                         None) == ks.ERR_INVALID_LENGTH
+    assert lib.singe_matmul_bf16_f32(None, None, None, None, 0, 1, 1, 1, 1, 1, 0, 1) == ks.ERR_INVALID_LENGTH
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(ks, "_lib", None)
+    monkeypatch.setattr(ks, "LIB_PATH", os.path.join(ROOT, "no_such_dir", "libsinge_kernel_sys.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        ks.lib()

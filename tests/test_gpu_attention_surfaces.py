@@ -1,0 +1,180 @@
+"""Dense, packed-prefill and Tensor-surface paged attention on the GPU against the CPU restatements."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from singe_b200 import ops, workloads
+from tests.gpu_util import assert_close_bf16, assert_close_f32, dev, dev_u32, host
+
+pytestmark = pytest.mark.gpu
+
+
+def test_config1_causal_sdpa_f32_matches_the_reference_cpu_kernel():
+    # Config 1: batch 1, 8 heads, seq 512, head_dim 64, N(0,1) seed 0, scale 1/8, causal -> [1,8,512,64] f32.
+    rng = np.random.default_rng(0)
+    q, k, v = (rng.standard_normal((1, 8, 512, 64), dtype=np.float32) for _ in range(3))
+    got = ops.scaled_dot_product_attention(dev(q), dev(k), dev(v), scale=1.0 / 8.0, causal=True)
+    torch.cuda.synchronize()
+    ref = oracle.scaled_dot_product_attention_f32(q, k, v, scale=1.0 / 8.0, causal=True)
+    assert got.shape == (1, 8, 512, 64)
+    assert_close_f32(host(got), ref, "config 1 SDPA")
+
+
+def test_sdpa_gqa_window_and_non_causal():
+    rng = np.random.default_rng(5)
+    q = rng.standard_normal((2, 4, 33, 16), dtype=np.float32)
+    k = rng.standard_normal((2, 2, 40, 16), dtype=np.float32)
+    v = rng.standard_normal((2, 2, 40, 16), dtype=np.float32)
+    rep = lambda x: np.repeat(x, 2, axis=1)  # repeat_kv (singe/src/backend/cpu/normalization/attention.rs:20-130)
+    for causal, window in [(False, 0), (True, 0), (True, 5)]:
+        got = ops.scaled_dot_product_attention(dev(q), dev(k), dev(v), scale=0.25, causal=causal, window=window)
+        ref = oracle.scaled_dot_product_attention_f32(q, rep(k), rep(v), scale=0.25, causal=causal, window=window)
+        assert_close_f32(host(got), ref, f"sdpa causal={causal} window={window}")
+
+
+def test_fmha_prefill_lse_f32():
+    rng = np.random.default_rng(6)
+    b, l, s, h, g, d = 2, 19, 19, 4, 2, 32
+    q = rng.standard_normal((b, l, h, d), dtype=np.float32)
+    k = rng.standard_normal((b, s, g, d), dtype=np.float32)
+    v = rng.standard_normal((b, s, g, d), dtype=np.float32)
+    out = torch.empty((b, l, h, d), device="cuda")
+    lse = torch.empty((b, h, l), device="cuda")
+    ops.fmha_prefill_lse(out, lse, dev(q), dev(k), dev(v), batch=b, query_len=l, key_len=s, heads=h, kv_heads=g,
+                         head_dim=d, scale=0.2, causal=True)
+    ref_out, ref_lse = oracle.fmha_prefill_lse_f32(q, k, v, batch=b, query_len=l, key_len=s, heads=h, kv_heads=g,
+                                                   head_dim=d, scale=0.2, causal=True)
+    assert_close_f32(host(out), ref_out, "fmha_prefill out")
+    assert_close_f32(host(lse), ref_lse, "fmha_prefill lse")
+
+
+def _ragged_case(rng, lens, heads, kv_heads, head_dim, bf16):
+    total = int(sum(lens))
+    make = (lambda shape: workloads.normal_bf16(rng, shape)) if bf16 else (
+        lambda shape: rng.standard_normal(shape, dtype=np.float32))
+    q = make((total, heads, head_dim))
+    k = make((total, kv_heads, head_dim))
+    v = make((total, kv_heads, head_dim))
+    offsets = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
+    return q, k, v, np.asarray(lens, dtype=np.int32), offsets
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_ragged_prefill_f32_general_kernel(causal):
+    rng = np.random.default_rng(7)
+    lens = [5, 1, 40]
+    heads, kv_heads, head_dim = 4, 2, 24
+    q, k, v, lens_np, offsets = _ragged_case(rng, lens, heads, kv_heads, head_dim, bf16=False)
+    total = int(lens_np.sum())
+    cfg = ops.RaggedKvPrefillAttentionConfig(3, total, total, heads, kv_heads, head_dim, causal, 0.3)
+    out = torch.zeros((total, heads, head_dim), device="cuda")
+    lse = torch.zeros((total, heads), device="cuda")
+    ops.ragged_kv_prefill_attention(out, lse, dev(q), dev(k), dev(v), dev(lens_np), dev(lens_np), dev(offsets), cfg)
+    ref_out, ref_lse = oracle.ragged_kv_prefill_attention_f32(q, k, v, lens_np, lens_np, offsets, batch=3,
+                                                              total_query_tokens=total, heads=heads,
+                                                              kv_heads=kv_heads, head_dim=head_dim, causal=causal,
+                                                              scale=0.3)
+    assert_close_f32(host(out), ref_out, "ragged prefill out")
+    assert_close_f32(host(lse), ref_lse, "ragged prefill lse")
+
+
+def test_paged_prefill_f32_and_empty_rows():
+    # len_kv == 0 for one sequence: rows that see no key get out = 0 and lse = -1e20 (cpu/attention.rs:1304)
+    rng = np.random.default_rng(8)
+    heads, kv_heads, head_dim, block = 4, 2, 16, 4
+    lens_q = np.array([6, 2, 3], dtype=np.int32)
+    lens_kv = np.array([6, 0, 9], dtype=np.int32)
+    offsets = np.array([0, 6, 8], dtype=np.int32)
+    total = 11
+    pool, stride = 8, 3
+    perm = rng.permutation(pool).astype(np.uint32)
+    table = np.zeros((3, stride), dtype=np.uint32)
+    table[0, :2] = perm[:2]
+    table[2, :3] = perm[2:5]
+    q = rng.standard_normal((total, heads, head_dim), dtype=np.float32)
+    kc = rng.standard_normal((pool, block, kv_heads, head_dim), dtype=np.float32)
+    vc = rng.standard_normal((pool, block, kv_heads, head_dim), dtype=np.float32)
+    for causal in (True, False):
+        cfg = ops.PagedKvPrefillAttentionConfig(3, total, heads, kv_heads, head_dim, block, pool, stride, causal, 0.25)
+        out = torch.full((total, heads, head_dim), 7.0, device="cuda")
+        lse = torch.full((total, heads), 7.0, device="cuda")
+        ops.paged_kv_prefill_attention(out, lse, dev(q), dev(kc), dev(vc), dev(lens_q), dev(lens_kv), dev(offsets),
+                                       dev_u32(table), cfg)
+        ref_out, ref_lse = oracle.paged_kv_prefill_attention_f32(
+            q, kc, vc, lens_q, lens_kv, offsets, table, batch=3, total_query_tokens=total, heads=heads,
+            kv_heads=kv_heads, head_dim=head_dim, block_size=block, block_table_batch_stride=stride, causal=causal,
+            scale=0.25)
+        assert_close_f32(host(out), ref_out, f"paged prefill out causal={causal}")
+        assert_close_f32(host(lse), ref_lse, f"paged prefill lse causal={causal}")
+
+
+# ---- Tensor-surface paged attention: singe/tests/nn/paged_attention.rs ----
+TOKENS, HEADS, DIM, SLOTS, PAGES = 2, 2, 16, 4, 2
+VALID = dict(query_offsets=[0, 2], page_offsets=[0, 1], pages=[0], last_page_lengths=[2])
+INVALID = [
+    dict(VALID, query_offsets=[0, 3]), dict(VALID, query_offsets=[-1, 2]), dict(VALID, query_offsets=[2, 0]),
+    dict(VALID, page_offsets=[0, 2]), dict(VALID, page_offsets=[-1, 1]), dict(VALID, pages=[PAGES]),
+    dict(VALID, pages=[-1]), dict(VALID, last_page_lengths=[SLOTS + 1]), dict(VALID, last_page_lengths=[-1]),
+]
+
+
+def _attend(paging, dtype, index_dtype=np.int64):
+    q = torch.zeros((TOKENS, HEADS, DIM), dtype=dtype, device="cuda")
+    cache = torch.zeros((PAGES, SLOTS, HEADS, DIM), dtype=dtype, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    idx = {name: dev(np.asarray(values, dtype=index_dtype)) for name, values in paging.items()}
+    out, lse = ops.paged_attention(q, cache, cache, idx["query_offsets"], idx["page_offsets"], idx["pages"],
+                                   idx["last_page_lengths"], causal=True, status=status)
+    torch.cuda.synchronize()
+    return int(status.item()), out, lse
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("index_dtype", [np.int64, np.int32])
+def test_paging_values_outside_their_buffers_set_the_status_word_and_never_fault(dtype, index_dtype):
+    # singe/tests/nn/paged_attention.rs:145-184: nine invalid tuples -> IndexOutOfBounds, two valid edge cases.
+    status, out, lse = _attend(VALID, dtype, index_dtype)
+    assert status == 0
+    assert np.allclose(host(lse)[:, 0], [0.0, 1.0])  # zero scores: log2 of 1 and 2 visible keys
+    for paging in INVALID:
+        assert _attend(paging, dtype, index_dtype)[0] == 1, paging
+    assert _attend(dict(VALID, last_page_lengths=[SLOTS]), dtype, index_dtype)[0] == 0
+    assert _attend(dict(query_offsets=[0, 0], page_offsets=[0, 0], pages=[PAGES + 7], last_page_lengths=[-1]),
+                   dtype, index_dtype)[0] == 0
+
+
+@pytest.mark.parametrize("dtype,bf16", [(torch.float32, False), (torch.bfloat16, True)])
+def test_tensor_paged_attention_mixes_prefill_and_decode_rows(dtype, bf16):
+    # Three sequences: a prompt of 7 tokens, a single decode token over 21 keys, and 3 new tokens over 12 keys.
+    rng = np.random.default_rng(9)
+    heads, kv_heads, head_dim, page = 4, 2, 32, 4
+    keys = [7, 21, 12]
+    queries = [7, 1, 3]
+    pages_per = [(n + page - 1) // page for n in keys]
+    pool = sum(pages_per) + 2
+    perm = rng.permutation(pool)
+    pages = perm[: sum(pages_per)]
+    page_offsets = np.concatenate([[0], np.cumsum(pages_per)])
+    query_offsets = np.concatenate([[0], np.cumsum(queries)])
+    last = [(n - 1) % page + 1 for n in keys]
+    total = sum(queries)
+    make = (lambda shape: workloads.normal_bf16(rng, shape)) if bf16 else (
+        lambda shape: rng.standard_normal(shape, dtype=np.float32))
+    q = make((total, heads, head_dim))
+    kc = make((pool, page, kv_heads, head_dim))
+    vc = make((pool, page, kv_heads, head_dim))
+    for causal, window in [(True, 0), (True, 6), (False, 0)]:
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out, lse = ops.paged_attention(dev(q, dtype), dev(kc, dtype), dev(vc, dtype), dev(query_offsets),
+                                       dev(page_offsets), dev(pages.astype(np.int64)),
+                                       dev(np.asarray(last, dtype=np.int64)), scale=0.2, causal=causal,
+                                       window=window, status=status)
+        code, ref_out, ref_lse = oracle.attend_paged_f32(q, kc, vc, query_offsets, page_offsets, pages, last,
+                                                         scale=0.2, causal=causal, window=window)
+        assert code == oracle.OK and int(status.item()) == 0
+        if bf16:
+            assert_close_bf16(host(out), ref_out, f"tensor paged bf16 causal={causal} window={window}")
+        else:
+            assert_close_f32(host(out), ref_out, f"tensor paged out causal={causal} window={window}")
+        assert_close_f32(host(lse), ref_lse, "tensor paged lse (base 2)", 2e-4)

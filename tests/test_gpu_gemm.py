@@ -1,0 +1,83 @@
+"""bf16 linear-layer GEMM on the tcgen05 tensor core against the CPU restatement of the reference GEMM."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from singe_b200 import ops
+from singe_b200 import kernel_sys as ks
+from tests.gpu_util import assert_close_bf16, dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _case(m, n, k, seed=2):
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn((m, k), generator=gen, device="cuda").to(torch.bfloat16)            # X ~ N(0, 1)
+    w = (torch.randn((n, k), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)   # W ~ N(0, 0.02)
+    return x, w
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (16, 512, 1024), (128, 384, 64), (200, 136, 72), (256, 256, 4096),
+                                   (129, 1000, 520), (64, 4096, 4096), (1, 14336, 4096)])
+def test_linear_matches_the_oracle_bf16_and_f32(m, n, k):
+    x, w = _case(m, n, k)
+    y = ops.linear(x, w)
+    y32 = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    ops.matmul_bf16(y32, x, w, ops.MatmulConfig.row_major_transposed_rhs(m, n, k))
+    torch.cuda.synchronize()
+    assert ops.take_device_error() == 0
+    ref = oracle.linear_bf16_f32(_bits(x), _bits(w), m=m, n=n, k=k)
+    assert_close_bf16(host(y32), ref, f"matmul_bf16_f32 {m}x{n}x{k}")
+    assert_close_bf16(host(y), oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(ref)), f"linear bf16 {m}x{n}x{k}")
+    # the f32 result is far tighter than the bf16 tolerance: accumulation order is the only difference
+    scale = np.abs(ref).max() + 1e-6
+    assert np.abs(host(y32) - ref).max() / scale < 2e-3
+
+
+def test_config3_full_size_gemm_through_linearity():
+    # M = 4096 against (N, K) = (4096, 4096): too large for the scalar oracle, so check sampled rows against
+    # it, and the whole product through linearity: (X1 + X2) W^T == X1 W^T + X2 W^T for exactly representable sums.
+    m, n, k = 4096, 4096, 4096
+    x, w = _case(m, n, k)
+    y32 = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    ops.matmul_bf16(y32, x, w, ops.MatmulConfig.row_major_transposed_rhs(m, n, k))
+    rows = [0, 1, 127, 128, 2049, 4095]
+    ref = oracle.linear_bf16_f32(_bits(x[rows]), _bits(w), m=len(rows), n=n, k=k)
+    assert_close_bf16(host(y32[rows]), ref, "config 3 sampled rows")
+    half = (x.float() * 0.5).to(torch.bfloat16)  # exact: halving a bf16 keeps it representable
+    y_half = torch.empty_like(y32)
+    ops.matmul_bf16(y_half, half, w, ops.MatmulConfig.row_major_transposed_rhs(m, n, k))
+    torch.cuda.synchronize()
+    assert ops.take_device_error() == 0
+    assert torch.equal(y_half * 2.0, y32)  # scaling by a power of two commutes with every rounding
+
+
+def test_strided_operands_and_output():
+    m, n, k = 96, 160, 192
+    x_full, w_full = _case(m, n + 8, k + 64)
+    x = x_full[:, :k]                       # row stride k + 64
+    w = w_full[:n, 64:]                     # row stride k + 64, offset start (128-byte aligned)
+    out = torch.full((m, n + 24), -7.0, dtype=torch.bfloat16, device="cuda")
+    view = out[:, :n]
+    ops.matmul_bf16(view, x, w, ops.MatmulConfig(m, n, k, x.stride(0), w.stride(0), out.stride(0), False, True))
+    torch.cuda.synchronize()
+    ref = oracle.linear_bf16_f32(_bits(x.contiguous()), _bits(w.contiguous()), m=m, n=n, k=k)
+    assert_close_bf16(host(view), ref, "strided gemm")
+    assert (out[:, n:] == -7.0).all()      # only logical output elements are written
+
+
+def test_matmul_validation_mirrors_the_reference():
+    # validate_matmul (singe-kernel/src/cuda/matmul.rs:2977-3020)
+    lib = ks.lib()
+    one = 16
+    assert lib.singe_matmul_bf16_bf16(None, one, one, one, 0, 4, 4, 4, 4, 4, 0, 1) == ks.ERR_INVALID_LENGTH
+    assert lib.singe_matmul_bf16_bf16(None, one, one, one, 4, 4, 8, 4, 8, 4, 0, 1) == ks.ERR_INVALID_LENGTH  # lhs stride < k
+    assert lib.singe_matmul_bf16_bf16(None, one, one, one, 4, 4, 8, 8, 8, 2, 0, 1) == ks.ERR_INVALID_LENGTH  # out stride < n
+    assert lib.singe_matmul_bf16_bf16(None, None, one, one, 4, 4, 8, 8, 8, 4, 0, 1) == ks.ERR_NULL_POINTER
+    # layouts outside the linear-layer form are refused, not silently mis-computed
+    assert lib.singe_matmul_bf16_bf16(None, one, one, one, 8, 8, 8, 8, 8, 8, 0, 0) == ks.ERR_UNSUPPORTED_CONFIGURATION

@@ -1,0 +1,375 @@
+#!/usr/bin/env python
+"""Benchmark of the attention-and-linear hot path.
+
+``python bench.py --gpus N --steps K --warmup W`` prints ONE JSON line for the headline metric: achieved HBM
+GB/s of the paged-KV decode attention (config 2: 32 sequences with context lengths uniform in [128, 4096],
+32 query / 8 KV heads, head_dim 128, 16-token pages, bf16).  A "step" is one decode call over the whole batch.
+
+  * ``value``     device-resident: inputs already in HBM, K calls timed with CUDA events on the launching stream.
+  * ``e2e``       the same call through the host-facing API with HOST buffers: the step's query, lengths and
+                  block table are copied from pinned host memory and the output is copied back inside the
+                  timed region (the KV cache itself is device state of the operator, as in the reference,
+                  whose operators take device buffers).
+  * ``roofline``  algorithmic bytes per launch / average launch duration against the measured HBM peak.
+  * ``cpu_baseline`` the CPU restatement of the reference kernel timed on this host (rank 0, N=1 only).
+  * ``also``      secondary figures of the same metric family (prefill TFLOP/s, GEMM TFLOP/s, cache-write GB/s).
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank decodes its own batch of the same shape
+(different seed): sequences are independent, so there is no data-path collective and scaling is weak.
+``--impl reference`` times the reference's own CPU algorithm (the restatement under oracle/) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "paged_decode_hbm_gbs"
+UNIT = "GB/s"
+WORKLOAD = ("config2 paged-decode bf16: 32 seqs, ctx U[128,4096] seed 1, 32Q/8KV heads, head_dim 128, "
+            "block 16, pool +10%, permuted block table")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as handle:
+            data = json.load(handle)
+        return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]),
+                "bf16_tflops_sustained": float(data.get("bf16_tflops_sustained", data["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nvml = None
+
+    def _run(self):
+        nv = self._nvml
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": int(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def dist_setup(gpus: int):
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        group = dist
+    return rank, local, world, group
+
+
+def barrier_sync(group):
+    import torch
+
+    if group is not None:
+        group.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(value: float, group) -> float:
+    import torch
+
+    if group is None:
+        return value
+    tensor = torch.tensor([value], dtype=torch.float64, device="cuda")
+    group.all_reduce(tensor, op=group.ReduceOp.MAX)
+    return float(tensor.item())
+
+
+def sum_over_ranks(value: float, group) -> float:
+    import torch
+
+    if group is None:
+        return value
+    tensor = torch.tensor([value], dtype=torch.float64, device="cuda")
+    group.all_reduce(tensor, op=group.ReduceOp.SUM)
+    return float(tensor.item())
+
+
+# ----------------------------------------------------------------------------------------------------------
+# headline: config 2 paged decode
+# ----------------------------------------------------------------------------------------------------------
+
+def decode_device_inputs(case, seed: int):
+    import torch
+
+    generator = torch.Generator(device="cuda").manual_seed(seed)
+    shape = (case.physical_blocks, case.block_size, case.kv_heads, case.head_dim)
+    key_cache = torch.randn(shape, generator=generator, device="cuda").to(torch.bfloat16)
+    value_cache = torch.randn(shape, generator=generator, device="cuda").to(torch.bfloat16)
+    query = torch.randn((case.batch, case.heads, case.head_dim), generator=generator, device="cuda").to(torch.bfloat16)
+    return query, key_cache, value_cache
+
+
+def run_decode(args, rank, world, group):
+    import torch
+
+    from singe_b200 import ops, workloads
+
+    case = workloads.paged_decode_case(seed=1 + rank)
+    query, key_cache, value_cache = decode_device_inputs(case, seed=1 + rank)
+    lens = torch.from_numpy(case.lens).cuda()
+    table = torch.from_numpy(case.block_table.view(np.int32)).cuda()
+    out = torch.empty_like(query)
+    config = ops.PagedKvDecodeAttentionConfig.contiguous(case.batch, case.heads, case.kv_heads, case.head_dim,
+                                                         case.block_size, case.physical_blocks,
+                                                         case.block_table_batch_stride, case.scale)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        ops.paged_kv_decode_attention(out, query, key_cache, value_cache, lens, table, config, stream=stream)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier_sync(group)
+
+    # ---- device-resident region: K steps, CUDA events on the launching stream ----
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(torch.cuda.current_device())
+    with sampler:
+        barrier_sync(group)
+        start.record(stream)
+        for _ in range(args.steps):
+            step()
+        stop.record(stream)
+        barrier_sync(group)
+    seconds = max_over_ranks(start.elapsed_time(stop) * 1e-3, group)
+    my_bytes = float(case.algorithmic_bytes())
+    total_bytes = sum_over_ranks(my_bytes, group)
+    value = total_bytes * args.steps / seconds / 1e9
+
+    # ---- kernel duration for the roofline: per-launch events over the same K steps (rank 0's own kernels) ----
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+             for _ in range(min(args.steps, 200))]
+    torch.cuda.synchronize()
+    for begin, end in pairs:
+        begin.record(stream)
+        step()
+        end.record(stream)
+    torch.cuda.synchronize()
+    launch_seconds = float(np.mean([b.elapsed_time(e) for b, e in pairs])) * 1e-3
+    peaks = measured_peaks()
+    achieved = my_bytes / launch_seconds / 1e9
+
+    # ---- end to end through the host-facing call: pinned host inputs in, result out, every step ----
+    host_query = query.cpu().pin_memory()
+    host_lens = torch.from_numpy(case.lens).pin_memory()
+    host_table = torch.from_numpy(case.block_table.view(np.int32)).pin_memory()
+    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = host_query.numel() * 2 + host_lens.numel() * 4 + host_table.numel() * 4
+    d2h = host_out.numel() * 2
+
+    def e2e_step():
+        query.copy_(host_query, non_blocking=True)
+        lens.copy_(host_lens, non_blocking=True)
+        table.copy_(host_table, non_blocking=True)
+        step()
+        host_out.copy_(out, non_blocking=True)
+        stream.synchronize()  # the caller reads the result before the next step
+
+    for _ in range(3):
+        e2e_step()
+    barrier_sync(group)
+    begin = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier_sync(group)
+    e2e_seconds = max_over_ranks(time.perf_counter() - begin, group)
+    e2e_value = total_bytes * args.steps / e2e_seconds / 1e9
+
+    if ops.take_device_error() != 0:
+        raise RuntimeError("a device-side bounded wait ran out during the benchmark")
+
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(seconds / args.steps * 1e3, 5),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sequences_per_gpu": case.batch, "tokens_per_gpu": case.total_tokens,
+                   "algorithmic_bytes_per_step_per_gpu": int(my_bytes), "l2": "inputs (277 MB) larger than L2",
+                   "sharding": "by sequence, no collective"},
+        "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": 2 * args.steps,
+        "clocks": sampler.summary(),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                     "peak_source": peaks["source"], "launch_us": round(launch_seconds * 1e6, 2),
+                     "kernels": "paged_decode_kernel + decode_combine_kernel"},
+    }
+    return line, case
+
+
+def cpu_baseline_decode(case, threads: int):
+    """Times the CPU restatement of paged_kv_decode_attention_f32 on the full config-2 batch."""
+    from oracle import oracle
+    from singe_b200 import workloads
+
+    rng = np.random.default_rng(1)
+    q = workloads.normal_bf16(rng, (case.batch, case.heads, case.head_dim))
+    shape = (case.physical_blocks, case.block_size, case.kv_heads, case.head_dim)
+    k = workloads.normal_bf16(rng, shape)
+    v = workloads.normal_bf16(rng, shape)
+    oracle.set_threads(threads)
+    best = float("inf")
+    for _ in range(2):
+        begin = time.perf_counter()
+        oracle.paged_kv_decode_attention_f32(q, k, v, case.lens, case.block_table, batch=case.batch,
+                                             heads=case.heads, kv_heads=case.kv_heads, head_dim=case.head_dim,
+                                             block_size=case.block_size,
+                                             block_table_batch_stride=case.block_table_batch_stride, scale=case.scale)
+        best = min(best, time.perf_counter() - begin)
+    return case.algorithmic_bytes() / best / 1e9, best
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path (restated under oracle/) on all host cores."""
+    from oracle import oracle
+    from singe_b200 import workloads
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    case = workloads.paged_decode_case(seed=1)
+    threads = oracle.max_threads()
+    rng = np.random.default_rng(1)
+    q = workloads.normal_bf16(rng, (case.batch, case.heads, case.head_dim))
+    shape = (case.physical_blocks, case.block_size, case.kv_heads, case.head_dim)
+    k = workloads.normal_bf16(rng, shape)
+    v = workloads.normal_bf16(rng, shape)
+    oracle.set_threads(threads)
+
+    def step():
+        oracle.paged_kv_decode_attention_f32(q, k, v, case.lens, case.block_table, batch=case.batch,
+                                             heads=case.heads, kv_heads=case.kv_heads, head_dim=case.head_dim,
+                                             block_size=case.block_size,
+                                             block_table_batch_stride=case.block_table_batch_stride, scale=case.scale)
+
+    warmup = min(max(args.warmup, 1), 3)
+    steps = min(args.steps, 20)
+    for _ in range(warmup):
+        step()
+    begin = time.perf_counter()
+    for _ in range(steps):
+        step()
+    seconds = time.perf_counter() - begin
+    value = case.algorithmic_bytes() * steps / seconds / 1e9
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    sample = f"full config-2 batch ({case.total_tokens} cached tokens), {steps} calls"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT, "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(seconds / steps * 1e3, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD},
+        "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=500)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--no-also", action="store_true", help="skip the secondary figures")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path")
+    rank, local, world, group = dist_setup(args.gpus)
+    line, case = run_decode(args, rank, world, group)
+    if rank == 0:
+        if world == 1:
+            threads = 1  # the reference's singe-kernel CPU decode is serial
+            cpu_value, cpu_seconds = cpu_baseline_decode(case, threads)
+            line["cpu_baseline"] = {"value": round(cpu_value, 3), "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": f"full config-2 batch, best of 2 calls ({cpu_seconds:.2f} s each)"}
+        if not args.no_also:
+            try:
+                from singe_b200 import bench_extra
+
+                line["also"] = bench_extra.run_all(measured_peaks())
+            except Exception as error:  # secondary figures never take the headline down
+                line["also"] = {"error": repr(error)}
+        print(json.dumps(line), flush=True)
+    if group is not None:
+        group.barrier()
+        group.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,114 @@
+"""Secondary figures reported beside the headline decode number: the other kernels of the hot path on their
+own benchmark configurations (config 3 GEMM shapes, config 4 prefill and cache write), each as achieved
+throughput and as a fraction of the measured roofline.  Inputs are seeded synthetic tensors created on the
+device; every kernel is timed with CUDA events around a CUDA graph of repeated launches.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops, workloads
+
+
+def graph_seconds(fn, reps: int = 10, rounds: int = 3) -> float:
+    """Average duration of one call of ``fn`` inside a CUDA graph of ``reps`` launches (best of ``rounds``)."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(reps):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(rounds):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record(stream)
+            graph.replay()
+            end.record(stream)
+            torch.cuda.synchronize()
+            best = min(best, begin.elapsed_time(end) * 1e-3 / reps)
+    return best
+
+
+def gemm_figures(peaks) -> dict:
+    out = {}
+    generator = torch.Generator(device="cuda").manual_seed(2)
+    for n, k in workloads.GEMM_SHAPES:
+        w = (torch.randn((n, k), generator=generator, device="cuda") * 0.02).to(torch.bfloat16)
+        for m in workloads.GEMM_ROWS:
+            x = torch.randn((m, k), generator=generator, device="cuda").to(torch.bfloat16)
+            y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+            seconds = graph_seconds(lambda: ops.linear(x, w, y), reps=4 if m == 4096 else 10)
+            flops = 2.0 * m * n * k
+            moved = 2.0 * (m * k + n * k + m * n)
+            entry = {"us": round(seconds * 1e6, 2)}
+            if m == 4096:
+                entry["tflops"] = round(flops / seconds / 1e12, 1)
+                entry["frac_of_bf16_peak"] = round(flops / seconds / 1e12 / peaks["bf16_tflops"], 4)
+            else:
+                entry["gbs"] = round(moved / seconds / 1e9, 1)
+                entry["frac_of_hbm_peak"] = round(moved / seconds / 1e9 / peaks["hbm_gbs"], 4)
+            out[f"M{m}_N{n}_K{k}"] = entry
+    return out
+
+
+def cache_write_figures(peaks) -> dict:
+    case = workloads.prefill_case()
+    total = case.total_tokens
+    shape = (case.pages, case.page_size, case.kv_heads, case.head_dim)
+    key_cache = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+    value_cache = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+    keys = torch.randn((total, case.kv_heads, case.head_dim), device="cuda").to(torch.bfloat16)
+    values = torch.randn((total, case.kv_heads, case.head_dim), device="cuda").to(torch.bfloat16)
+    pages = torch.from_numpy(case.write_pages).cuda()
+    slots = torch.from_numpy(case.write_slots).cuda()
+    seconds = graph_seconds(lambda: ops.kv_cache_write(key_cache, value_cache, keys, values, pages, slots))
+    moved = 4.0 * total * case.kv_heads * case.head_dim * 2  # K and V rows read once and written once
+    return {"us": round(seconds * 1e6, 2), "gbs": round(moved / seconds / 1e9, 1),
+            "frac_of_hbm_peak": round(moved / seconds / 1e9 / peaks["hbm_gbs"], 4), "bytes": int(moved)}
+
+
+def prefill_figures(peaks) -> dict:
+    case = workloads.prefill_case()
+    total = case.total_tokens
+    generator = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn((total, case.heads, case.head_dim), generator=generator, device="cuda").to(torch.bfloat16)
+    k = torch.randn((total, case.kv_heads, case.head_dim), generator=generator, device="cuda").to(torch.bfloat16)
+    v = torch.randn((total, case.kv_heads, case.head_dim), generator=generator, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    lse = torch.empty((total, case.heads), dtype=torch.float32, device="cuda")
+    lens = torch.from_numpy(case.lens).cuda()
+    offsets = torch.from_numpy(case.offsets).cuda()
+    shape = (case.pages, case.page_size, case.kv_heads, case.head_dim)
+    key_cache = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+    value_cache = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+    pages = torch.from_numpy(case.write_pages).cuda()
+    slots = torch.from_numpy(case.write_slots).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    config = ops.RaggedKvPrefillAttentionConfig(len(case.lens), total, total, case.heads, case.kv_heads,
+                                                case.head_dim, True, case.scale)
+    seconds = graph_seconds(
+        lambda: ops.ragged_kv_prefill_attention(out, lse, q, k, v, lens, lens, offsets, config,
+                                                cache_write=(key_cache, value_cache, pages, slots, status)),
+        reps=3)
+    flops = case.causal_flops()
+    return {"us": round(seconds * 1e6, 1), "tflops": round(flops / seconds / 1e12, 1),
+            "frac_of_bf16_peak": round(flops / seconds / 1e12 / peaks["bf16_tflops"], 4),
+            "causal_gflop": round(flops / 1e9, 1), "includes": "slot-mapped KV-cache write of all 15360 tokens"}
+
+
+def run_all(peaks) -> dict:
+    result = {}
+    for name, fn in (("kv_cache_write_config4", cache_write_figures), ("gemm_config3", gemm_figures),
+                     ("prefill_config4", prefill_figures)):
+        try:
+            result[name] = fn(peaks)
+        except Exception as error:
+            result[name] = {"error": repr(error)}
+    if ops.take_device_error() != 0:
+        result["device_error"] = "a bounded wait ran out"
+    return result

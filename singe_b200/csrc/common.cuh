@@ -171,17 +171,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
-// Waits for the phase with `parity` to complete, for at most `kWaitLimitNs`.  Returns false when the
-// limit ran out, so callers can flag the failure and leave instead of spinning for ever.
-constexpr uint64_t kWaitLimitNs = 400ull * 1000ull * 1000ull;
+// Waits for the phase with `parity` to complete, for at most `kWaitLimitCycles` SM clock cycles
+// (about half a second at full clock).  Returns false when the limit ran out, so callers can flag the
+// failure and leave instead of spinning for ever.  The SM cycle counter is used because it is
+// monotonic for a resident thread; the global nanosecond timer can jump when the GPU leaves idle.
+constexpr long long kWaitLimitCycles = 1ll << 30;
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) {
         return true;
     }
-    const uint64_t start = global_timer_ns();
+    const long long start = clock64();
     while (!mbar_try_wait(bar, parity)) {
-        if (global_timer_ns() - start > kWaitLimitNs) {
+        if (clock64() - start > kWaitLimitCycles) {
             return false;
         }
     }

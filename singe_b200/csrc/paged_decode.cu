@@ -26,7 +26,11 @@ namespace {
 
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeThreads = (kDecodeWarps + 1) * 32;
-constexpr int kDecodeStages = 10;
+// A multiple of the consumer-warp count, so every use of a stage belongs to the same warp: a warp then
+// waits for phase n+1 of a stage's barrier only after it consumed phase n, and a parity wait can never
+// alias a phase that is two behind (TMA tiles may complete out of order).
+constexpr int kDecodeStages = 12;
+static_assert(kDecodeStages % kDecodeWarps == 0, "stage ownership must be fixed per consumer warp");
 constexpr int kPageTokens = 16;
 constexpr int kHalfBytes = kPageTokens * 128;  // one TMA box: 16 rows x 128 bytes
 
@@ -62,9 +66,9 @@ constexpr int decode_stage_bytes() {
 
 template <int HD>
 constexpr int decode_smem_bytes() {
-    // stages + merge buffers (O: 4 warps x 8 rows x HD f32; max/sum: 4 x 8 each) + barriers + alignment slack
-    return kDecodeStages * decode_stage_bytes<HD>() + kDecodeWarps * 8 * HD * 4 + 2 * kDecodeWarps * 8 * 4 +
-           2 * kDecodeStages * 8 + 1024;
+    // stages (a warp's first stage doubles as its merge buffer: 8 rows x HD f32 fit one stage) + max/sum of
+    // 4 warps x 8 rows + barriers + alignment slack
+    return kDecodeStages * decode_stage_bytes<HD>() + 2 * kDecodeWarps * 8 * 4 + 2 * kDecodeStages * 8 + 1024;
 }
 
 template <typename T, int HD>
@@ -80,10 +84,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *aligned = smem_raw + (base - raw);
-    float *merge_o = reinterpret_cast<float *>(aligned + kDecodeStages * STAGE);  // [4][8][HD]
-    float *merge_m = merge_o + kDecodeWarps * 8 * HD;                              // [4][8]
+    static_assert(8 * HD * 4 <= STAGE, "a warp's merge rows must fit its first stage");
+    float *merge_m = reinterpret_cast<float *>(aligned + kDecodeStages * STAGE);  // [4][8]
     float *merge_l = merge_m + kDecodeWarps * 8;                                   // [4][8]
-    const uint32_t bar_full = base + kDecodeStages * STAGE + kDecodeWarps * 8 * HD * 4 + 2 * kDecodeWarps * 8 * 4;
+    const uint32_t bar_full = base + kDecodeStages * STAGE + 2 * kDecodeWarps * 8 * 4;
     const uint32_t bar_empty = bar_full + kDecodeStages * 8;
 
     const int split = blockIdx.x;
@@ -286,7 +290,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
             merge_m[warp * 8 + row] = run_max;
             merge_l[warp * 8 + row] = run_sum;
         }
-        float *mine = merge_o + (warp * 8 + row) * HD;
+        // Stage `warp` is only ever filled for and read by this warp, and all of its tiles have been consumed.
+        float *mine = reinterpret_cast<float *>(aligned + warp * STAGE) + row * HD;
 #pragma unroll
         for (int nt = 0; nt < NTILES; ++nt) {
             *reinterpret_cast<float2 *>(mine + nt * 8 + quad * 2) = make_float2(o[nt][0], o[nt][1]);
@@ -311,7 +316,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
             const float m = merge_m[w * 8 + r];
             const float weight = m == -INFINITY ? 0.0f : fast_exp2(m - top);
             total += merge_l[w * 8 + r] * weight;
-            value += merge_o[(w * 8 + r) * HD + d] * weight;
+            value += reinterpret_cast<const float *>(aligned + w * STAGE)[r * HD + d] * weight;
         }
         const size_t head_row = static_cast<size_t>(b) * p.heads + g * p.group + r;
         const float result = value / total;

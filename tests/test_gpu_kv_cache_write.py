@@ -82,6 +82,7 @@ def test_odd_row_width_takes_the_narrow_path():
     cache = np.zeros((3, 2, 1, 3), dtype=np.float32)   # 12-byte rows: not 16-byte vectorisable
     rows = (np.arange(6, dtype=np.float32) + 1).reshape(2, 1, 3)
     gk, gv, status = _run(cache, cache.copy(), rows, -rows, [2, 0], [1, 0])
-    expect = cache.copy()
-    oracle.kv_cache_write(expect, rows, [2, 0], [1, 0])
-    assert status == 0 and gk.tobytes() == expect.tobytes() and gv.tobytes() == (-expect).tobytes()
+    expect_k, expect_v = cache.copy(), cache.copy()
+    oracle.kv_cache_write(expect_k, rows, [2, 0], [1, 0])
+    oracle.kv_cache_write(expect_v, -rows, [2, 0], [1, 0])
+    assert status == 0 and gk.tobytes() == expect_k.tobytes() and gv.tobytes() == expect_v.tobytes()

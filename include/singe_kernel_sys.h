@@ -50,6 +50,7 @@ extern "C" {
 #define SINGE_ERR_INVALID_ARGUMENT 10         /* singe::Error::invalid_argument */
 #define SINGE_ERR_OUT_OF_RANGE 11             /* singe::Error::out_of_range */
 #define SINGE_ERR_AUTOTUNE_DURING_CAPTURE 12  /* Error::AutotuneDuringCapture (workspace growth under capture) */
+#define SINGE_ERR_STATIC_SCRATCH_EXCEEDED 13  /* the problem needs more than the library's fixed scratch array */
 #define SINGE_ERR_CUDA_BASE 1000              /* + cudaError_t */
 
 /* Device-side status word values. */
@@ -123,6 +124,29 @@ int singe_paged_kv_decode_attention_f32(singe_stream_t stream, float *out, const
                                         const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch,
                                         size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
                                         size_t physical_blocks, size_t block_table_batch_stride, float scale);
+
+/* -------------------------------------------------------------------------------------------------
+ * Paged-KV decode that never allocates (no counterpart in the reference: this entry point exists only here).
+ * Same arguments and result as singe_paged_kv_decode_attention_bf16, for hosts that cannot let the library
+ * call cudaMalloc: a runtime that gives all device memory to its own pool (the reference's operators never
+ * allocate, singe-kernel/src/cuda/attention/mod.rs:3-7), or a decode loop that cannot take the device-wide
+ * synchronisation an allocation implies.  The split-K partials live in a fixed array inside the library,
+ * singe_paged_kv_decode_attention_static_scratch_floats() floats (8 MiB) per GPU that loads it, held until
+ * the process exits.  The call needs batch * heads * (head_dim + 1) floats per split; it lowers the split count
+ * to fit and returns SINGE_ERR_STATIC_SCRATCH_EXCEEDED when even one split does not fit.  It takes only the
+ * shapes of the tiled kernel (head_dim 64/128, block_size 16, heads/kv_heads <= 8) and calls no cudaMalloc,
+ * cudaFree or other allocating routine.  The first call on each device looks up the array's device address
+ * (a runtime query, not stream work): make that first call before starting any stream capture.  All calls on
+ * a device share the one array, so two calls whose kernels can overlap on the GPU (different streams) race;
+ * calls on one stream are ordered and safe.  Nothing in the array has to be cleared between calls.
+ * ------------------------------------------------------------------------------------------------- */
+size_t singe_paged_kv_decode_attention_static_scratch_floats(void);
+int singe_paged_kv_decode_attention_static_bf16(singe_stream_t stream, void *out, const void *query,
+                                                const void *key_cache, const void *value_cache,
+                                                const int32_t *actual_seq_lens, const uint32_t *block_table,
+                                                size_t batch, size_t heads, size_t kv_heads, size_t head_dim,
+                                                size_t block_size, size_t physical_blocks,
+                                                size_t block_table_batch_stride, float scale);
 
 /* =================================================================================================
  * Split-K decode with caller-owned scratch, and the log-sum-exp combine

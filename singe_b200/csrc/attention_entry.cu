@@ -613,6 +613,7 @@ const char *singe_status_string(int status) {
         case SINGE_ERR_INVALID_ARGUMENT: return "invalid argument";
         case SINGE_ERR_OUT_OF_RANGE: return "out of range";
         case SINGE_ERR_AUTOTUNE_DURING_CAPTURE: return "workspace growth during cuda graph capture";
+        case SINGE_ERR_STATIC_SCRATCH_EXCEEDED: return "problem exceeds the library's fixed scratch array";
         default: return status >= SINGE_ERR_CUDA_BASE ? "cuda runtime error" : "unknown status";
     }
 }

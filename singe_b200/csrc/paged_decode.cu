@@ -460,3 +460,94 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
 }
 
 }  // namespace singe
+
+// -------------------------------------------------------------------------------------------------
+// Decode with library-resident scratch: an entry point that never allocates.
+//
+// Some hosts cannot let this library call cudaMalloc.  A runtime that follows the reference's rule that
+// operators never allocate hands every byte of device memory to its own pool at start-up, so a library-side
+// cudaMalloc has nothing left to take (or fragments the pool); a latency-critical decode loop cannot afford
+// the device-wide synchronisation cudaMalloc and cudaFree imply.  The reference's paged-decode signature has
+// no scratch parameter either, so such a caller has nowhere to pass split-K scratch.  For them the split
+// partials live in the fixed array below, which every GPU that loads the library carries until the process
+// exits.
+// -------------------------------------------------------------------------------------------------
+namespace singe {
+namespace {
+
+// 2 Mi floats = 8 MiB: partials [batch, heads, splits, head_dim] followed by their LSEs [batch, heads, splits].
+constexpr size_t kStaticScratchFloats = size_t(2) << 20;
+static __device__ __align__(256) float g_decode_static_scratch[kStaticScratchFloats];
+
+// In host code the array's name is only a handle for the runtime, not a device address; the address the
+// kernels need is looked up once per device, with that device current.
+int static_scratch_address(float **address) {
+    constexpr int kMaxDevices = 64;
+    static float *resolved[kMaxDevices] = {nullptr};
+    int device = 0;
+    SINGE_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) {
+        return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    }
+    if (resolved[device] == nullptr) {
+        void *pointer = nullptr;
+        SINGE_CUDA_TRY(cudaGetSymbolAddress(&pointer, g_decode_static_scratch));
+        if (pointer == nullptr) {
+            return SINGE_ERR_NULL_POINTER;
+        }
+        resolved[device] = static_cast<float *>(pointer);
+    }
+    *address = resolved[device];
+    return SINGE_OK;
+}
+
+}  // namespace
+}  // namespace singe
+
+extern "C" {
+
+size_t singe_paged_kv_decode_attention_static_scratch_floats(void) { return singe::kStaticScratchFloats; }
+
+int singe_paged_kv_decode_attention_static_bf16(singe_stream_t stream, void *out, const void *query,
+                                                const void *key_cache, const void *value_cache,
+                                                const int32_t *actual_seq_lens, const uint32_t *block_table,
+                                                size_t batch, size_t heads, size_t kv_heads, size_t head_dim,
+                                                size_t block_size, size_t physical_blocks,
+                                                size_t block_table_batch_stride, float scale) {
+    using namespace singe;
+    if (batch == 0 || heads == 0 || kv_heads == 0 || head_dim == 0 || block_size == 0 || physical_blocks == 0 ||
+        block_table_batch_stride == 0 || heads % kv_heads != 0 || !(scale - scale == 0.0f)) {
+        return SINGE_ERR_INVALID_LENGTH;
+    }
+    if (!fits_i32(batch) || !fits_i32(heads) || !fits_i32(kv_heads) || !fits_i32(head_dim) || !fits_i32(block_size) ||
+        !fits_i32(physical_blocks) || !fits_i32(block_table_batch_stride)) {
+        return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    }
+    if (out == nullptr || query == nullptr || key_cache == nullptr || value_cache == nullptr ||
+        actual_seq_lens == nullptr || block_table == nullptr) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    if (!paged_decode_fast_path(heads, kv_heads, head_dim, block_size, key_cache, value_cache, query)) {
+        return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    }
+    // One split needs batch * heads * (head_dim + 1) floats; a problem that does not fit even unsplit is refused.
+    const size_t per_split = batch * heads * (head_dim + 1);
+    if (per_split > kStaticScratchFloats) {
+        return SINGE_ERR_STATIC_SCRATCH_EXCEEDED;
+    }
+    // ~512 keys per split, capped by what the fixed array holds.
+    size_t splits = (block_table_batch_stride * block_size + 511) / 512;
+    const size_t room = kStaticScratchFloats / per_split;
+    if (splits > room) splits = room;
+    if (splits < 1) splits = 1;
+    float *scratch = nullptr;
+    SINGE_TRY(static_scratch_address(&scratch));
+    const size_t rows = batch * heads * splits;
+    // Every partial the combine reads is written by the decode kernel of the same call, so nothing in the
+    // array has to start at zero; what an earlier call left behind is never read.
+    return paged_decode_splitk(static_cast<cudaStream_t>(stream), 0, out, scratch, scratch + rows * head_dim, query,
+                               key_cache, value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim,
+                               physical_blocks, block_table_batch_stride, splits, scale, false, device_error_word());
+}
+
+}  // extern "C"

@@ -25,6 +25,7 @@ ERR_INDEX_OUT_OF_BOUNDS = 9
 ERR_INVALID_ARGUMENT = 10
 ERR_OUT_OF_RANGE = 11
 ERR_AUTOTUNE_DURING_CAPTURE = 12
+ERR_STATIC_SCRATCH_EXCEEDED = 13
 ERR_CUDA_BASE = 1000
 
 STATUS_INDEX_OUT_OF_BOUNDS = 1
@@ -46,6 +47,8 @@ SIGNATURES = {
     "singe_paged_kv_decode_attention_bf16": [_p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _f],
     "singe_paged_kv_decode_attention_f16": [_p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _f],
     "singe_paged_kv_decode_attention_f32": [_p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _f],
+    "singe_paged_kv_decode_attention_static_bf16": [_p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _f],
+    "singe_paged_kv_decode_attention_static_scratch_floats": [],
     "singe_paged_kv_decode_split_tokens": [_z, _z, _z],
     "singe_paged_kv_decode_splitk_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z, _f],
     "singe_splitk_reduce_f32": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z, _z, _z, _z],
@@ -75,6 +78,7 @@ SIGNATURES = {
 _RESTYPES = {
     "singe_status_string": ctypes.c_char_p,
     "singe_paged_kv_decode_split_tokens": ctypes.c_size_t,
+    "singe_paged_kv_decode_attention_static_scratch_floats": ctypes.c_size_t,
 }
 
 _lib = None

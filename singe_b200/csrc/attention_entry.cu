@@ -18,8 +18,8 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
                         size_t kv_heads, size_t head_dim, size_t physical_blocks, size_t block_table_batch_stride,
                         size_t max_splits, float scale, bool partials_only, uint32_t *status);
 // prefill_tcgen05.cu
-bool prefill_fast_path(size_t heads, size_t kv_heads, size_t head_dim, const void *query, const void *key,
-                       const void *value, const void *out);
+bool prefill_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t total_query_tokens, const void *query,
+                       const void *key, const void *value, const void *out);
 int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void *query, const void *key,
                          const void *value, const int32_t *lens_q, const int32_t *lens_kv, const int32_t *offsets,
                          size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads,
@@ -812,7 +812,7 @@ int singe_ragged_kv_prefill_attention_bf16(singe_stream_t stream, void *out, flo
         actual_seq_lens_q == nullptr || actual_seq_lens_kv == nullptr || actual_seq_offsets == nullptr) {
         return SINGE_ERR_NULL_POINTER;
     }
-    if (prefill_fast_path(heads, kv_heads, head_dim, query, key, value, out)) {
+    if (prefill_fast_path(heads, kv_heads, head_dim, total_query_tokens, query, key, value, out)) {
         return prefill_tcgen05_bf16(static_cast<cudaStream_t>(stream), out, lse, query, key, value, actual_seq_lens_q,
                                     actual_seq_lens_kv, actual_seq_offsets, batch, total_query_tokens,
                                     total_kv_tokens, heads, kv_heads, head_dim, causal, scale);

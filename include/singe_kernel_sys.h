@@ -322,6 +322,16 @@ int singe_matmul_bf16_f32(singe_stream_t stream, float *out, const void *lhs, co
                           size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
                           size_t output_row_stride, int transpose_lhs, int transpose_rhs);
 
+/* Explicit tile choice for the two GEMM entry points, process-wide: block_n in {32,64,128,256},
+ * k_slices_per_stage in {1,2,4,8}; 0 = choose from the problem shape.
+ * Replaces: TuningChoice::Explicit(MatmulTuning { tile, .. }) (singe-kernel/src/cuda/matmul.rs:58-77). */
+int singe_matmul_set_tuning(int block_n, int k_slices_per_stage);
+
+/* Reads and clears the library's sticky device error word for the current device (synchronises the device).
+ * 0 = no kernel-side failure; 2 = a bounded device-side wait ran out.  Plays the role of the planner's status
+ * word read-back (singe/src/backend/cuda/kernel_plan/mod.rs:192-204) for entry points without a status argument. */
+int singe_debug_take_device_error(uint32_t *value);
+
 #ifdef __cplusplus
 }
 #endif

@@ -38,8 +38,8 @@ struct GemmParams {
     long long ldo;
     int a_rows;       // rows of the A box (multiple of 8, <= 128)
     int stages;
-    int stage_bytes;  // a_rows * 128 + BN * 128
-    int tiles_m, tiles_n, k_blocks;
+    int stage_bytes;  // KPS * (a_rows * 128 + BN * 128)
+    int tiles_m, tiles_n, k_blocks;  // k_blocks counts stages: KPS 64-wide slices each
     int vector_store;  // 16-byte stores are legal (alignment and stride)
     uint32_t *error;   // sticky device error word (2 = a bounded wait ran out)
 };
@@ -54,7 +54,10 @@ __device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tile
     tn = within / rows;
 }
 
-template <int BN>
+// KPS = 64-wide K slices per pipeline stage.  Skinny problems stream the weight matrix from HBM; with one
+// slice per stage every request touches 128 contiguous bytes of a weight row, which opens a DRAM page for two
+// bursts.  Several adjacent slices issued together give the memory controller 512-1024 contiguous bytes per row.
+template <int BN, int KPS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                      const GemmParams p) {
@@ -125,9 +128,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 if (lane == 0) {
                     const uint32_t stage = base + s * p.stage_bytes;
                     const uint32_t full = bar_full + s * 8;
-                    mbar_expect_tx(full, a_bytes + kBBytes);
-                    tma_load_2d(stage, &a_map, full, kb * kBlockK, tm * kBlockM);
-                    tma_load_2d(stage + a_bytes, &b_map, full, kb * kBlockK, tn * BN);
+                    mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
+#pragma unroll
+                    for (int sub = 0; sub < KPS; ++sub) {
+                        // slices past K are zero-filled by TMA and add nothing
+                        tma_load_2d(stage + sub * a_bytes, &a_map, full, (kb * KPS + sub) * kBlockK, tm * kBlockM);
+                    }
+#pragma unroll
+                    for (int sub = 0; sub < KPS; ++sub) {
+                        tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
+                                    tn * BN);
+                    }
                 }
             }
         }
@@ -154,12 +165,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 tcgen05_fence_after();
                 if (lane == 0) {
                     const uint32_t stage = base + s * p.stage_bytes;
-                    const uint64_t a_desc = make_smem_desc(stage, 16, 1024);
-                    const uint64_t b_desc = make_smem_desc(stage + a_bytes, 16, 1024);
 #pragma unroll
-                    for (int ks = 0; ks < kBlockK / 16; ++ks) {
-                        // 16 bf16 of K = 32 bytes = 2 descriptor address units
-                        umma_ss(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kIdesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                    for (int sub = 0; sub < KPS; ++sub) {
+                        const uint64_t a_desc = make_smem_desc(stage + sub * a_bytes, 16, 1024);
+                        const uint64_t b_desc = make_smem_desc(stage + KPS * a_bytes + sub * kBBytes, 16, 1024);
+#pragma unroll
+                        for (int ks = 0; ks < kBlockK / 16; ++ks) {
+                            // 16 bf16 of K = 32 bytes = 2 descriptor address units
+                            umma_ss(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kIdesc,
+                                    (kb > 0 || sub > 0 || ks > 0) ? 1u : 0u);
+                        }
                     }
                     tcgen05_commit(bar_empty + s * 8);
                 }
@@ -247,12 +262,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
 }
 
-template <int BN>
+template <int BN, int KPS>
 int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const void *rhs, size_t lhs_row_stride,
                 size_t rhs_row_stride) {
     constexpr int kSmemLimit = 227 * 1024;
     const int b_bytes = BN * 128;
-    params.stage_bytes = params.a_rows * 128 + b_bytes;
+    params.stage_bytes = KPS * (params.a_rows * 128 + b_bytes);
+    params.k_blocks = (params.k + kBlockK * KPS - 1) / (kBlockK * KPS);
     const int fixed = kBlockM * 128 + 2 * kMaxStages * 8 + 64 + 1024;
     int stages = (kSmemLimit - fixed) / params.stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
@@ -261,7 +277,7 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
     params.stages = stages;
     params.tiles_n = (params.n + BN - 1) / BN;
     const int smem = stages * params.stage_bytes + fixed;
-    SINGE_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    SINGE_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_kernel<BN, KPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
 
     CUtensorMap a_map, b_map;
     {
@@ -280,9 +296,14 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
     }
     const int total = params.tiles_m * params.tiles_n;
     const int grid = total < device_sm_count() ? total : device_sm_count();
-    gemm_bf16_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(a_map, b_map, params);
+    gemm_bf16_kernel<BN, KPS><<<grid, kGemmThreads, smem, stream>>>(a_map, b_map, params);
     return launch_status();
 }
+
+// Explicit tuning (the reference's TuningChoice::Explicit(MatmulTuning), singe-kernel/src/cuda/matmul.rs:58-77):
+// 0 = choose from the problem shape.
+int g_tuning_block_n = 0;
+int g_tuning_slices = 0;
 
 }  // namespace
 
@@ -327,13 +348,49 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
     const size_t element = out_f32 ? 4 : 2;
     params.vector_store =
         ((reinterpret_cast<uintptr_t>(out) & 15u) == 0 && (output_row_stride * element) % 16 == 0) ? 1 : 0;
-    // Widest tile that still gives every SM a tile; narrow tiles for skinny (HBM-bound) problems.
+    // Widest tile that still gives every SM a tile; narrow tiles for skinny (HBM-bound) problems, which also take
+    // several K slices per stage so that each weight row is requested in long contiguous runs.
     const int sms = device_sm_count();
     auto tiles = [&](int bn) { return params.tiles_m * ((params.n + bn - 1) / bn); };
-    if (tiles(256) >= sms) return launch_gemm<256>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
-    if (tiles(128) >= sms) return launch_gemm<128>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
-    if (tiles(64) >= sms) return launch_gemm<64>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
-    return launch_gemm<32>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
+    int bn = 32;
+    int slices = 1;
+    if (params.m > kBlockM) {
+        if (tiles(256) >= sms) bn = 256;
+        else if (tiles(128) >= sms) bn = 128;
+        else if (tiles(64) >= sms) bn = 64;
+    } else {
+        // One M tile: the weight matrix is streamed once.  Measured on B200 (M = 1..128, N = 4096..28672,
+        // K = 4096/14336): 128-wide tiles with 2 slices win once they give two thirds of the SMs a tile,
+        // otherwise the narrowest tile that does, with as many slices per stage as two stages allow.
+        const int enough = (sms * 2) / 3;
+        if (tiles(128) >= enough) {
+            bn = 128;
+            slices = 2;
+        } else {
+            bn = tiles(64) >= enough ? 64 : 32;
+            const int slice_bytes = (params.a_rows + bn) * 128;
+            slices = 8;
+            while (slices > 1 && slices * slice_bytes * 2 > 200 * 1024) slices >>= 1;
+        }
+    }
+    if (g_tuning_block_n != 0) bn = g_tuning_block_n;
+    if (g_tuning_slices != 0) slices = g_tuning_slices;
+#define SINGE_GEMM_CASE(BN_, KPS_)                                                                    \
+    if (bn == BN_ && slices == KPS_)                                                                  \
+        return launch_gemm<BN_, KPS_>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
+    SINGE_GEMM_CASE(256, 1)
+    SINGE_GEMM_CASE(128, 1)
+    SINGE_GEMM_CASE(128, 2)
+    SINGE_GEMM_CASE(64, 1)
+    SINGE_GEMM_CASE(64, 2)
+    SINGE_GEMM_CASE(64, 4)
+    SINGE_GEMM_CASE(64, 8)
+    SINGE_GEMM_CASE(32, 1)
+    SINGE_GEMM_CASE(32, 2)
+    SINGE_GEMM_CASE(32, 4)
+    SINGE_GEMM_CASE(32, 8)
+#undef SINGE_GEMM_CASE
+    return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
 }
 
 }  // namespace singe
@@ -352,6 +409,16 @@ int singe_matmul_bf16_f32(singe_stream_t stream, float *out, const void *lhs, co
                           size_t output_row_stride, int transpose_lhs, int transpose_rhs) {
     return singe::gemm_bf16(static_cast<cudaStream_t>(stream), out, true, lhs, rhs, rows, columns, reduction,
                             lhs_row_stride, rhs_row_stride, output_row_stride, transpose_lhs, transpose_rhs);
+}
+
+// Overrides the tile choice of the GEMM entry points for this process: block_n in {32, 64, 128, 256} and
+// k_slices_per_stage in {1, 2, 4, 8}; 0 restores the shape-based choice.  Mirrors TuningChoice::Explicit
+// (singe-kernel/src/cuda/matmul.rs:58-77).  Unsupported pairs make the next call return
+// SINGE_ERR_UNSUPPORTED_CONFIGURATION.
+int singe_matmul_set_tuning(int block_n, int k_slices_per_stage) {
+    singe::g_tuning_block_n = block_n;
+    singe::g_tuning_slices = k_slices_per_stage;
+    return SINGE_OK;
 }
 
 }  // extern "C"

@@ -322,6 +322,48 @@ int singe_matmul_bf16_f32(singe_stream_t stream, float *out, const void *lhs, co
                           size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
                           size_t output_row_stride, int transpose_lhs, int transpose_rhs);
 
+/* =================================================================================================
+ * Decode-step glue (bf16 tensors, f32 arithmetic inside)
+ * Replaces the eager tensor ops the reference's Llama block runs between its GEMMs and attention
+ * (singe/src/nn/layers/blocks/mod.rs:56-83, singe/src/nn/layers/networks/causal_lm.rs:121-148); the fused forms
+ * correspond to the modules its compiled plans recognise (RotaryCacheWrite, singe/src/backend/cuda/compiled/plan/
+ * fusion/module.rs:28-74, kernel singe_rotary_cache_write in kernel_plan/source/rotary_cache.rs:238-427).
+ * ================================================================================================= */
+
+/* Embedding lookup (singe::nn Embedding = index_select): out[t, :] = table[ids[t], :]; negative ids wrap, ids
+ * outside the table write zeros and set *status = 1. */
+int singe_embedding_bf16(singe_stream_t stream, void *out, const void *table, const void *ids, int index_width,
+                         size_t tokens, size_t width, size_t vocab, uint32_t *status);
+
+/* Residual add fused with RMSNorm (RmsNorm: singe/src/backend/cpu/normalization/standard.rs:43-60):
+ *   hidden[r, :] = bf16(hidden[r, :] + delta[r, :])      when delta != NULL
+ *   normed[r, :] = hidden[r, :] * 1/sqrt(mean(hidden[r, :]^2) + eps) * weight[:]   when normed != NULL */
+int singe_add_rms_norm_bf16(singe_stream_t stream, void *hidden, const void *delta, void *normed, const void *weight,
+                            size_t rows, size_t width, float eps);
+
+/* Half-split rotary embedding of Q and K (RotaryAngles::rotate_pairs, singe/src/nn/layers/positional/rotary.rs:
+ * 274-304; cos/sin tables [capacity, head_dim/2] in the model dtype, :166-219) fused with KvCache::write
+ * (singe/src/nn/decode/cache.rs:97-101).  qkv rows are [heads*D | kv_heads*D | kv_heads*D] (the fused q/k/v
+ * projection); q_out [tokens, heads, D] receives the rotated queries, the rotated keys and the values go to
+ * (write_pages[t], write_slots[t]) of caches [pages, page_size, kv_heads, D].  Bad positions or slots are dropped
+ * and reported through *status = 1. */
+int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void *qkv, size_t qkv_row_stride,
+                                  const void *cos_table, const void *sin_table, const void *positions,
+                                  void *key_cache, void *value_cache, const void *write_pages,
+                                  const void *write_slots, int index_width, size_t tokens, size_t heads,
+                                  size_t kv_heads, size_t head_dim, size_t pages, size_t page_size, size_t capacity,
+                                  uint32_t *status);
+
+/* GatedMlp activation (singe/src/nn/layers/feed_forward/mod.rs:58-66): out = bf16(bf16(silu(gate)) * up);
+ * gate and up are [rows, width] views with row stride input_row_stride (halves of a fused gate/up projection). */
+int singe_silu_mul_bf16(singe_stream_t stream, void *out, const void *gate, const void *up, size_t input_row_stride,
+                        size_t rows, size_t width);
+
+/* Greedy next token (argmax over logits rows, singe/src/generation/mod.rs:352-365): lowest index wins ties;
+ * best_index gets index + index_offset (a vocabulary shard reports global ids), best_value the winning logit. */
+int singe_argmax_bf16(singe_stream_t stream, float *best_value, int64_t *best_index, const void *logits,
+                      size_t row_stride, size_t rows, size_t width, int64_t index_offset);
+
 /* Explicit tile choice for the two GEMM entry points, process-wide: block_n in {32,64,128,256},
  * k_slices_per_stage in {1,2,4,8}; 0 = choose from the problem shape.
  * Replaces: TuningChoice::Explicit(MatmulTuning { tile, .. }) (singe-kernel/src/cuda/matmul.rs:58-77). */

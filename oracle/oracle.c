@@ -630,38 +630,3 @@ void oracle_rms_norm_f32(float *out, const float *input, const float *weight, si
         for (size_t i = 0; i < width; ++i) out[r * width + i] = x[i] * inv * weight[i];
     }
 }
-
-/* Half-split rotary embedding: singe/src/nn/layers/positional/rotary.rs:166-304.
- * inv_freq[i] = 1 / theta^(2i / D) in f32, angle = position * inv_freq[i]; for i < D/2:
- *   out[i]       = x[i] * cos - x[i + D/2] * sin
- *   out[i + D/2] = x[i + D/2] * cos + x[i] * sin
- * `table_bf16` != 0 rounds cos/sin to bf16 first, as a bf16 model's table is cast to the model dtype. */
-void oracle_rotary_half_split_f32(float *x, const int64_t *positions, size_t tokens, size_t heads, size_t head_dim,
-                                  float theta, int table_bf16) {
-    size_t half = head_dim / 2;
-    for (size_t t = 0; t < tokens; ++t) {
-        for (size_t i = 0; i < half; ++i) {
-            float inv_freq = 1.0f / powf(theta, (float)(2 * i) / (float)head_dim);
-            float angle = (float)positions[t] * inv_freq;
-            float c = cosf(angle), s = sinf(angle);
-            if (table_bf16) {
-                c = oracle_bf16_bits_to_f32(oracle_f32_to_bf16_bits(c));
-                s = oracle_bf16_bits_to_f32(oracle_f32_to_bf16_bits(s));
-            }
-            for (size_t h = 0; h < heads; ++h) {
-                float *row = x + (t * heads + h) * head_dim;
-                float a = row[i], b = row[i + half];
-                row[i] = a * c - b * s;
-                row[i + half] = b * c + a * s;
-            }
-        }
-    }
-}
-
-/* GatedMlp activation: singe/src/nn/layers/feed_forward/mod.rs:58-66  silu(gate) * up, silu(x) = x / (1 + exp(-x)). */
-void oracle_silu_mul_f32(float *out, const float *gate, const float *up, size_t count) {
-    for (size_t i = 0; i < count; ++i) {
-        float g = gate[i];
-        out[i] = (g / (1.0f + expf(-g))) * up[i];
-    }
-}

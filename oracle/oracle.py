@@ -252,19 +252,3 @@ def rms_norm_f32(x, weight, eps):
     out = np.zeros_like(x)
     lib().oracle_rms_norm_f32(_ptr(out), _ptr(x), _ptr(weight), _sz(rows), _sz(width), _f(eps))
     return out
-
-
-def rotary_half_split_f32(x, positions, theta, table_bf16=False):
-    x = _f32(x).copy()
-    tokens, heads, head_dim = x.shape
-    pos = np.ascontiguousarray(positions, dtype=np.int64)
-    lib().oracle_rotary_half_split_f32(_ptr(x), _ptr(pos), _sz(tokens), _sz(heads), _sz(head_dim), _f(theta),
-                                       _i(int(table_bf16)))
-    return x
-
-
-def silu_mul_f32(gate, up):
-    gate, up = _f32(gate), _f32(up)
-    out = np.zeros_like(gate)
-    lib().oracle_silu_mul_f32(_ptr(out), _ptr(gate), _ptr(up), _sz(gate.size))
-    return out

@@ -1,0 +1,283 @@
+// Decode-step glue around the attention and GEMM kernels, bf16 tensors with f32 arithmetic inside:
+// embedding lookup, RMSNorm (alone and fused with the residual add), half-split rotary embedding fused with
+// the slot-mapped KV-cache write, SwiGLU activation, and the last-row argmax.
+//
+// Meaning follows the reference's Llama block (singe/src/nn/layers/blocks/mod.rs:56-83):
+//   h += o_proj(attn(norm(h)));  h += down(silu(gate(norm h)) * up(norm h))
+// with RmsNorm = x * 1/sqrt(mean(x^2) + eps) * w in f32 (singe/src/backend/cpu/normalization/standard.rs:43-60),
+// the half-split rotation of RotaryAngles::rotate_pairs (singe/src/nn/layers/positional/rotary.rs:274-304) and
+// KvCache::write (singe/src/nn/decode/cache.rs:97-101).  The reference runs these as separate bf16 tensor ops, each
+// rounding its result to bf16; the fused kernels here keep those roundings (product, then sum) so results match
+// the unfused chain.  All of them move a few hundred KB per step: one CTA per row, 128-bit accesses.
+#include "common.cuh"
+
+namespace singe {
+namespace {
+
+__device__ __forceinline__ float round_bf16(float value) { return __bfloat162float(__float2bfloat16_rn(value)); }
+
+__device__ __forceinline__ float block_sum(float value, float *scratch) {
+    value = warp_sum(value);
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    if (lane == 0) scratch[warp] = value;
+    __syncthreads();
+    float total = 0.0f;
+    const int warps = (blockDim.x + 31) >> 5;
+    for (int i = 0; i < warps; ++i) total += scratch[i];
+    __syncthreads();
+    return total;
+}
+
+template <typename Index>
+__global__ void embedding_kernel(__nv_bfloat16 *out, const __nv_bfloat16 *table, const Index *ids, int width,
+                                 long long vocab, uint32_t *status) {
+    const int row = blockIdx.x;
+    long long id = static_cast<long long>(ids[row]);
+    if (id < 0) id += vocab;  // negative indices wrap, as index_select does
+    const bool valid = id >= 0 && id < vocab;
+    if (!valid && threadIdx.x == 0) report_status(status, kStatusIndexOutOfBounds);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        out[static_cast<size_t>(row) * width + c] = valid ? table[static_cast<size_t>(id) * width + c]
+                                                          : __float2bfloat16_rn(0.0f);
+    }
+}
+
+// hidden (+)= delta (rounded to bf16, as Tensor::add does), then normed = rms_norm(hidden) * weight.
+// delta == nullptr: plain RMSNorm of `hidden`.  normed == nullptr: residual add only.
+__global__ void add_rms_norm_kernel(__nv_bfloat16 *hidden, const __nv_bfloat16 *delta, __nv_bfloat16 *normed,
+                                    const __nv_bfloat16 *weight, int width, float eps) {
+    __shared__ float scratch[32];
+    const size_t base = static_cast<size_t>(blockIdx.x) * width;
+    float square = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float value = __bfloat162float(hidden[base + c]);
+        if (delta != nullptr) {
+            value = round_bf16(value + __bfloat162float(delta[base + c]));
+            hidden[base + c] = __float2bfloat16_rn(value);
+        }
+        square += value * value;
+    }
+    if (normed == nullptr) return;
+    const float total = block_sum(square, scratch);
+    const float scale = 1.0f / sqrtf(total / static_cast<float>(width) + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float value = __bfloat162float(hidden[base + c]);
+        normed[base + c] = __float2bfloat16_rn(value * scale * __bfloat162float(weight[c]));
+    }
+}
+
+// One CTA per token.  qkv row = [heads*D | kv_heads*D | kv_heads*D].  Rotates Q into q_out and K into the cache at
+// (write_pages[t], write_slots[t]); V is copied into the cache.  Rounding follows the tensor-op chain of
+// rotate_pairs: first' = bf16(bf16(first*cos) - bf16(second*sin)), second' = bf16(bf16(second*cos) + bf16(first*sin)).
+template <typename Index>
+__global__ void rotary_cache_write_kernel(__nv_bfloat16 *q_out, const __nv_bfloat16 *qkv, long long qkv_stride,
+                                          const __nv_bfloat16 *cos_table, const __nv_bfloat16 *sin_table,
+                                          const Index *positions, __nv_bfloat16 *key_cache,
+                                          __nv_bfloat16 *value_cache, const Index *write_pages,
+                                          const Index *write_slots, int heads, int kv_heads, int head_dim,
+                                          long long pages, long long page_size, long long capacity,
+                                          uint32_t *status) {
+    const int token = blockIdx.x;
+    const int half = head_dim >> 1;
+    long long position = static_cast<long long>(positions[token]);
+    if (position < 0) position += capacity;
+    long long page = static_cast<long long>(write_pages[token]);
+    long long slot = static_cast<long long>(write_slots[token]);
+    if (page < 0) page += pages;
+    if (slot < 0) slot += page_size;
+    const bool position_ok = position >= 0 && position < capacity;
+    const bool slot_ok = page >= 0 && page < pages && slot >= 0 && slot < page_size;
+    if ((!position_ok || !slot_ok) && threadIdx.x == 0) report_status(status, kStatusIndexOutOfBounds);
+    if (!position_ok) return;
+    const __nv_bfloat16 *row = qkv + static_cast<size_t>(token) * qkv_stride;
+    const __nv_bfloat16 *cos_row = cos_table + static_cast<size_t>(position) * half;
+    const __nv_bfloat16 *sin_row = sin_table + static_cast<size_t>(position) * half;
+    const size_t cache_row = (static_cast<size_t>(page) * page_size + slot) * kv_heads * head_dim;
+    const int rotated_heads = heads + kv_heads;
+    for (int item = threadIdx.x; item < rotated_heads * half; item += blockDim.x) {
+        const int head = item / half;
+        const int i = item - head * half;
+        const float c = __bfloat162float(cos_row[i]);
+        const float s = __bfloat162float(sin_row[i]);
+        const __nv_bfloat16 *source = row + static_cast<size_t>(head) * head_dim;
+        const float first = __bfloat162float(source[i]);
+        const float second = __bfloat162float(source[i + half]);
+        const __nv_bfloat16 out_first = __float2bfloat16_rn(round_bf16(first * c) - round_bf16(second * s));
+        const __nv_bfloat16 out_second = __float2bfloat16_rn(round_bf16(second * c) + round_bf16(first * s));
+        if (head < heads) {
+            __nv_bfloat16 *target = q_out + (static_cast<size_t>(token) * heads + head) * head_dim;
+            target[i] = out_first;
+            target[i + half] = out_second;
+        } else if (slot_ok) {
+            __nv_bfloat16 *target = key_cache + cache_row + static_cast<size_t>(head - heads) * head_dim;
+            target[i] = out_first;
+            target[i + half] = out_second;
+        }
+    }
+    if (slot_ok) {
+        const __nv_bfloat16 *values = row + static_cast<size_t>(heads + kv_heads) * head_dim;
+        for (int c = threadIdx.x; c < kv_heads * head_dim; c += blockDim.x) {
+            value_cache[cache_row + c] = values[c];
+        }
+    }
+}
+
+// out = bf16(bf16(silu(gate)) * up), the two roundings of activation-then-mul in GatedMlp
+// (singe/src/nn/layers/feed_forward/mod.rs:58-66).
+__global__ void silu_mul_kernel(__nv_bfloat16 *out, const __nv_bfloat16 *gate, const __nv_bfloat16 *up,
+                                long long in_stride, int width) {
+    const size_t in_base = static_cast<size_t>(blockIdx.x) * in_stride;
+    const size_t out_base = static_cast<size_t>(blockIdx.x) * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float g = __bfloat162float(gate[in_base + c]);
+        const float u = __bfloat162float(up[in_base + c]);
+        const float activated = round_bf16(g / (1.0f + expf(-g)));
+        out[out_base + c] = __float2bfloat16_rn(activated * u);
+    }
+}
+
+// Row-wise argmax; ties go to the lowest index.  Writes the winning value (f32) and index (int64, plus
+// `index_offset` so that a vocabulary shard reports global token ids).
+__global__ void argmax_kernel(float *best_value, long long *best_index, const __nv_bfloat16 *logits,
+                              long long stride, int width, long long index_offset) {
+    __shared__ float values[32];
+    __shared__ int indices[32];
+    const __nv_bfloat16 *row = logits + static_cast<size_t>(blockIdx.x) * stride;
+    float best = -INFINITY;
+    int where = 0x7fffffff;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float value = __bfloat162float(row[c]);
+        if (value > best || (value == best && c < where)) {
+            best = value;
+            where = c;
+        }
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+        const int other_where = __shfl_xor_sync(0xffffffffu, where, offset);
+        if (other > best || (other == best && other_where < where)) {
+            best = other;
+            where = other_where;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        values[warp] = best;
+        indices[warp] = where;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int warps = (blockDim.x + 31) >> 5;
+        for (int i = 1; i < warps; ++i) {
+            if (values[i] > best || (values[i] == best && indices[i] < where)) {
+                best = values[i];
+                where = indices[i];
+            }
+        }
+        best_value[blockIdx.x] = best;
+        best_index[blockIdx.x] = static_cast<long long>(where) + index_offset;
+    }
+}
+
+}  // namespace
+}  // namespace singe
+
+using namespace singe;
+
+extern "C" {
+
+int singe_embedding_bf16(singe_stream_t stream, void *out, const void *table, const void *ids, int index_width,
+                         size_t tokens, size_t width, size_t vocab, uint32_t *status) {
+    if (tokens == 0 || width == 0 || vocab == 0) return SINGE_ERR_INVALID_LENGTH;
+    if (!fits_i32(tokens) || !fits_i32(width) || !fits_i32(vocab)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    if (out == nullptr || table == nullptr || ids == nullptr) return SINGE_ERR_NULL_POINTER;
+    if (index_width != 4 && index_width != 8) return SINGE_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (index_width == 8) {
+        embedding_kernel<long long><<<static_cast<unsigned>(tokens), 256, 0, s>>>(
+            static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(table),
+            static_cast<const long long *>(ids), static_cast<int>(width), static_cast<long long>(vocab), status);
+    } else {
+        embedding_kernel<int><<<static_cast<unsigned>(tokens), 256, 0, s>>>(
+            static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(table),
+            static_cast<const int *>(ids), static_cast<int>(width), static_cast<long long>(vocab), status);
+    }
+    return launch_status();
+}
+
+int singe_add_rms_norm_bf16(singe_stream_t stream, void *hidden, const void *delta, void *normed, const void *weight,
+                            size_t rows, size_t width, float eps) {
+    if (rows == 0 || width == 0) return SINGE_ERR_INVALID_LENGTH;
+    if (!fits_i32(rows) || !fits_i32(width)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    if (hidden == nullptr || (normed != nullptr && weight == nullptr) || (normed == nullptr && delta == nullptr)) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    add_rms_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__nv_bfloat16 *>(hidden), static_cast<const __nv_bfloat16 *>(delta),
+        static_cast<__nv_bfloat16 *>(normed), static_cast<const __nv_bfloat16 *>(weight), static_cast<int>(width),
+        eps);
+    return launch_status();
+}
+
+int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void *qkv, size_t qkv_row_stride,
+                                  const void *cos_table, const void *sin_table, const void *positions,
+                                  void *key_cache, void *value_cache, const void *write_pages,
+                                  const void *write_slots, int index_width, size_t tokens, size_t heads,
+                                  size_t kv_heads, size_t head_dim, size_t pages, size_t page_size, size_t capacity,
+                                  uint32_t *status) {
+    if (tokens == 0 || heads == 0 || kv_heads == 0 || head_dim == 0 || head_dim % 2 != 0 || pages == 0 ||
+        page_size == 0 || capacity == 0 || qkv_row_stride < (heads + 2 * kv_heads) * head_dim) {
+        return SINGE_ERR_INVALID_LENGTH;
+    }
+    if (!fits_i32(tokens) || !fits_i32(heads) || !fits_i32(kv_heads) || !fits_i32(head_dim) || !fits_i32(pages) ||
+        !fits_i32(page_size) || !fits_i32(capacity)) {
+        return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    }
+    if (q_out == nullptr || qkv == nullptr || cos_table == nullptr || sin_table == nullptr || positions == nullptr ||
+        key_cache == nullptr || value_cache == nullptr || write_pages == nullptr || write_slots == nullptr) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    if (index_width != 4 && index_width != 8) return SINGE_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define SINGE_ROTARY(Index)                                                                                          \
+    rotary_cache_write_kernel<Index><<<static_cast<unsigned>(tokens), 256, 0, s>>>(                                  \
+        static_cast<__nv_bfloat16 *>(q_out), static_cast<const __nv_bfloat16 *>(qkv),                                \
+        static_cast<long long>(qkv_row_stride), static_cast<const __nv_bfloat16 *>(cos_table),                       \
+        static_cast<const __nv_bfloat16 *>(sin_table), static_cast<const Index *>(positions),                        \
+        static_cast<__nv_bfloat16 *>(key_cache), static_cast<__nv_bfloat16 *>(value_cache),                          \
+        static_cast<const Index *>(write_pages), static_cast<const Index *>(write_slots), static_cast<int>(heads),   \
+        static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<long long>(pages),                       \
+        static_cast<long long>(page_size), static_cast<long long>(capacity), status)
+    if (index_width == 8) {
+        SINGE_ROTARY(long long);
+    } else {
+        SINGE_ROTARY(int);
+    }
+#undef SINGE_ROTARY
+    return launch_status();
+}
+
+int singe_silu_mul_bf16(singe_stream_t stream, void *out, const void *gate, const void *up, size_t input_row_stride,
+                        size_t rows, size_t width) {
+    if (rows == 0 || width == 0 || input_row_stride < width) return SINGE_ERR_INVALID_LENGTH;
+    if (!fits_i32(rows) || !fits_i32(width)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    if (out == nullptr || gate == nullptr || up == nullptr) return SINGE_ERR_NULL_POINTER;
+    silu_mul_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(gate),
+        static_cast<const __nv_bfloat16 *>(up), static_cast<long long>(input_row_stride), static_cast<int>(width));
+    return launch_status();
+}
+
+int singe_argmax_bf16(singe_stream_t stream, float *best_value, int64_t *best_index, const void *logits,
+                      size_t row_stride, size_t rows, size_t width, int64_t index_offset) {
+    if (rows == 0 || width == 0 || row_stride < width) return SINGE_ERR_INVALID_LENGTH;
+    if (!fits_i32(rows) || !fits_i32(width)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    if (best_value == nullptr || best_index == nullptr || logits == nullptr) return SINGE_ERR_NULL_POINTER;
+    argmax_kernel<<<static_cast<unsigned>(rows), 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        best_value, reinterpret_cast<long long *>(best_index), static_cast<const __nv_bfloat16 *>(logits),
+        static_cast<long long>(row_stride), static_cast<int>(width), static_cast<long long>(index_offset));
+    return launch_status();
+}
+
+}  // extern "C"

@@ -333,6 +333,57 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3):
+    """Config 5: Llama-3-8B-shaped decode step, 64 sequences at context 2048, tensor-parallel over all ranks
+    (KV heads and column/row-sharded linears, all-reduce after o_proj and down_proj).  Returns rank 0's figures."""
+    import torch
+
+    from singe_b200 import llama
+
+    config = llama.LlamaConfig()
+    sequences, context = 64, 2048
+    shard = llama.Shard(rank, world, group)
+    decoder = llama.LlamaDecoder(config, sequences, context + 64, shard=shard, seed=4)
+    decoder.fill_context(context, seed=4)
+    rng = np.random.default_rng(4)
+    tokens = rng.integers(0, config.vocab, size=sequences)
+    decoder.plan(tokens)
+    decoder.capture()
+    for _ in range(warmup):
+        decoder.graph.replay()
+    barrier_sync(group)
+    stream = torch.cuda.current_stream()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record(stream)
+    for _ in range(steps):
+        decoder.graph.replay()   # same positions every replay: the step's work does not depend on the token ids
+    end.record(stream)
+    barrier_sync(group)
+    seconds = max_over_ranks(begin.elapsed_time(end) * 1e-3 / steps, group)
+    # end to end: plan on the host, upload the step's index tensors, replay, read the next tokens back
+    host_tokens = tokens
+    barrier_sync(group)
+    wall = time.perf_counter()
+    e2e_steps = min(steps, 16)
+    for _ in range(e2e_steps):
+        next_tokens = decoder.step(host_tokens)
+        host_tokens = next_tokens.cpu().numpy() % config.vocab
+    barrier_sync(group)
+    e2e_seconds = max_over_ranks((time.perf_counter() - wall) / e2e_steps, group)
+    moved = llama.decode_step_bytes(config, sequences, context, world, decoder.shard_lm_head)
+    peaks = measured_peaks()
+    status = int(decoder.status.item())
+    return {
+        "tokens_per_s": round(sequences / seconds, 1), "ms_per_step": round(seconds * 1e3, 3),
+        "e2e_tokens_per_s": round(sequences / e2e_seconds, 1), "tp": world,
+        "bytes_per_rank_per_step": moved["total"],
+        "frac_of_hbm_bound_per_rank": round(moved["total"] / seconds / 1e9 / peaks["hbm_gbs"], 4),
+        "lm_head": "vocab-sharded + (max, argmax) gather" if decoder.shard_lm_head else "replicated",
+        "collectives_per_step": 2 * config.layers if world > 1 else 0, "status_word": status,
+        "config": "Llama-3-8B shape, random bf16 weights, 64 seqs x ctx 2048, page 16, CUDA-graph replay",
+    }
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -340,6 +391,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-also", action="store_true", help="skip the secondary figures")
+    parser.add_argument("--no-decode-step", action="store_true", help="skip the Llama-shaped decode step figure")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -352,6 +404,12 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path")
     rank, local, world, group = dist_setup(args.gpus)
     line, case = run_decode(args, rank, world, group)
+    decode_step = None
+    if not args.no_also and not args.no_decode_step:
+        try:
+            decode_step = run_decode_step(rank, world, group)
+        except Exception as error:
+            decode_step = {"error": repr(error)}
     if rank == 0:
         if world == 1:
             threads = 1  # the reference's singe-kernel CPU decode is serial
@@ -365,6 +423,8 @@ def main():
                 line["also"] = bench_extra.run_all(measured_peaks())
             except Exception as error:  # secondary figures never take the headline down
                 line["also"] = {"error": repr(error)}
+            if decode_step is not None:
+                line["also"]["decode_step_config5"] = decode_step
         print(json.dumps(line), flush=True)
     if group is not None:
         group.barrier()

@@ -14,6 +14,8 @@
 namespace singe {
 namespace {
 
+bool aligned16(const void *pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
+
 __device__ __forceinline__ float round_bf16(float value) { return __bfloat162float(__float2bfloat16_rn(value)); }
 
 __device__ __forceinline__ float block_sum(float value, float *scratch) {
@@ -29,7 +31,34 @@ __device__ __forceinline__ float block_sum(float value, float *scratch) {
     return total;
 }
 
-template <typename Index>
+// ---- 128-bit helpers: eight bf16 per access ----
+struct Vec8 {
+    float v[8];
+};
+
+__device__ __forceinline__ Vec8 load8(const __nv_bfloat16 *pointer) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(pointer);
+    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+    Vec8 out;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out.v[2 * i] = __uint_as_float(words[i] << 16);
+        out.v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+    }
+    return out;
+}
+
+__device__ __forceinline__ void store8(__nv_bfloat16 *pointer, const Vec8 &value) {
+    uint4 raw;
+    raw.x = pack2<__nv_bfloat16>(value.v[0], value.v[1]);
+    raw.y = pack2<__nv_bfloat16>(value.v[2], value.v[3]);
+    raw.z = pack2<__nv_bfloat16>(value.v[4], value.v[5]);
+    raw.w = pack2<__nv_bfloat16>(value.v[6], value.v[7]);
+    *reinterpret_cast<uint4 *>(pointer) = raw;
+}
+
+// VEC = 8: rows are multiples of eight bf16 and every pointer is 16-byte aligned; VEC = 1 otherwise.
+template <typename Index, int VEC>
 __global__ void embedding_kernel(__nv_bfloat16 *out, const __nv_bfloat16 *table, const Index *ids, int width,
                                  long long vocab, uint32_t *status) {
     const int row = blockIdx.x;
@@ -37,19 +66,83 @@ __global__ void embedding_kernel(__nv_bfloat16 *out, const __nv_bfloat16 *table,
     if (id < 0) id += vocab;  // negative indices wrap, as index_select does
     const bool valid = id >= 0 && id < vocab;
     if (!valid && threadIdx.x == 0) report_status(status, kStatusIndexOutOfBounds);
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        out[static_cast<size_t>(row) * width + c] = valid ? table[static_cast<size_t>(id) * width + c]
-                                                          : __float2bfloat16_rn(0.0f);
+    __nv_bfloat16 *target = out + static_cast<size_t>(row) * width;
+    const __nv_bfloat16 *source = table + static_cast<size_t>(valid ? id : 0) * width;
+    for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {
+        if (VEC == 8) {
+            *reinterpret_cast<uint4 *>(target + c) =
+                valid ? *reinterpret_cast<const uint4 *>(source + c) : make_uint4(0u, 0u, 0u, 0u);
+        } else {
+            target[c] = valid ? source[c] : __float2bfloat16_rn(0.0f);
+        }
     }
 }
 
 // hidden (+)= delta (rounded to bf16, as Tensor::add does), then normed = rms_norm(hidden) * weight.
 // delta == nullptr: plain RMSNorm of `hidden`.  normed == nullptr: residual add only.
+// One CTA per row; with VEC = 8 a thread keeps up to kHeld chunks of eight values in registers between the
+// sum-of-squares pass and the scaling pass, so rows up to blockDim * 8 * kHeld wide are read once.
+constexpr int kHeld = 4;
+
+template <int VEC>
 __global__ void add_rms_norm_kernel(__nv_bfloat16 *hidden, const __nv_bfloat16 *delta, __nv_bfloat16 *normed,
                                     const __nv_bfloat16 *weight, int width, float eps) {
     __shared__ float scratch[32];
     const size_t base = static_cast<size_t>(blockIdx.x) * width;
     float square = 0.0f;
+    if (VEC == 8) {
+        Vec8 held[kHeld];
+        const int stride = blockDim.x * 8;
+#pragma unroll
+        for (int h = 0; h < kHeld; ++h) {
+            const int c = threadIdx.x * 8 + h * stride;
+            if (c < width) {
+                held[h] = load8(hidden + base + c);
+                if (delta != nullptr) {
+                    const Vec8 other = load8(delta + base + c);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) held[h].v[i] = round_bf16(held[h].v[i] + other.v[i]);
+                    store8(hidden + base + c, held[h]);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) square += held[h].v[i] * held[h].v[i];
+            }
+        }
+        for (int c = threadIdx.x * 8 + kHeld * stride; c < width; c += stride) {  // rows wider than the held part
+            Vec8 value = load8(hidden + base + c);
+            if (delta != nullptr) {
+                const Vec8 other = load8(delta + base + c);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) value.v[i] = round_bf16(value.v[i] + other.v[i]);
+                store8(hidden + base + c, value);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) square += value.v[i] * value.v[i];
+        }
+        if (normed == nullptr) return;
+        const float total = block_sum(square, scratch);
+        const float scale = 1.0f / sqrtf(total / static_cast<float>(width) + eps);
+#pragma unroll
+        for (int h = 0; h < kHeld; ++h) {
+            const int c = threadIdx.x * 8 + h * stride;
+            if (c < width) {
+                const Vec8 gain = load8(weight + c);
+                Vec8 result;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) result.v[i] = held[h].v[i] * scale * gain.v[i];
+                store8(normed + base + c, result);
+            }
+        }
+        for (int c = threadIdx.x * 8 + kHeld * stride; c < width; c += stride) {
+            const Vec8 value = load8(hidden + base + c);
+            const Vec8 gain = load8(weight + c);
+            Vec8 result;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) result.v[i] = value.v[i] * scale * gain.v[i];
+            store8(normed + base + c, result);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float value = __bfloat162float(hidden[base + c]);
         if (delta != nullptr) {
@@ -70,7 +163,8 @@ __global__ void add_rms_norm_kernel(__nv_bfloat16 *hidden, const __nv_bfloat16 *
 // One CTA per token.  qkv row = [heads*D | kv_heads*D | kv_heads*D].  Rotates Q into q_out and K into the cache at
 // (write_pages[t], write_slots[t]); V is copied into the cache.  Rounding follows the tensor-op chain of
 // rotate_pairs: first' = bf16(bf16(first*cos) - bf16(second*sin)), second' = bf16(bf16(second*cos) + bf16(first*sin)).
-template <typename Index>
+// With VEC = 8 a thread rotates eight adjacent pairs (head_dim/2 is then a multiple of eight).
+template <typename Index, int VEC>
 __global__ void rotary_cache_write_kernel(__nv_bfloat16 *q_out, const __nv_bfloat16 *qkv, long long qkv_stride,
                                           const __nv_bfloat16 *cos_table, const __nv_bfloat16 *sin_table,
                                           const Index *positions, __nv_bfloat16 *key_cache,
@@ -95,50 +189,75 @@ __global__ void rotary_cache_write_kernel(__nv_bfloat16 *q_out, const __nv_bfloa
     const __nv_bfloat16 *sin_row = sin_table + static_cast<size_t>(position) * half;
     const size_t cache_row = (static_cast<size_t>(page) * page_size + slot) * kv_heads * head_dim;
     const int rotated_heads = heads + kv_heads;
-    for (int item = threadIdx.x; item < rotated_heads * half; item += blockDim.x) {
-        const int head = item / half;
-        const int i = item - head * half;
-        const float c = __bfloat162float(cos_row[i]);
-        const float s = __bfloat162float(sin_row[i]);
+    const int per_head = half / VEC;
+    for (int item = threadIdx.x; item < rotated_heads * per_head; item += blockDim.x) {
+        const int head = item / per_head;
+        const int i = (item - head * per_head) * VEC;
         const __nv_bfloat16 *source = row + static_cast<size_t>(head) * head_dim;
-        const float first = __bfloat162float(source[i]);
-        const float second = __bfloat162float(source[i + half]);
-        const __nv_bfloat16 out_first = __float2bfloat16_rn(round_bf16(first * c) - round_bf16(second * s));
-        const __nv_bfloat16 out_second = __float2bfloat16_rn(round_bf16(second * c) + round_bf16(first * s));
+        __nv_bfloat16 *target = nullptr;
         if (head < heads) {
-            __nv_bfloat16 *target = q_out + (static_cast<size_t>(token) * heads + head) * head_dim;
-            target[i] = out_first;
-            target[i + half] = out_second;
+            target = q_out + (static_cast<size_t>(token) * heads + head) * head_dim;
         } else if (slot_ok) {
-            __nv_bfloat16 *target = key_cache + cache_row + static_cast<size_t>(head - heads) * head_dim;
-            target[i] = out_first;
-            target[i + half] = out_second;
+            target = key_cache + cache_row + static_cast<size_t>(head - heads) * head_dim;
+        }
+        if (target == nullptr) continue;
+        if (VEC == 8) {
+            const Vec8 c = load8(cos_row + i), s = load8(sin_row + i);
+            const Vec8 first = load8(source + i), second = load8(source + i + half);
+            Vec8 out_first, out_second;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                out_first.v[e] = round_bf16(first.v[e] * c.v[e]) - round_bf16(second.v[e] * s.v[e]);
+                out_second.v[e] = round_bf16(second.v[e] * c.v[e]) + round_bf16(first.v[e] * s.v[e]);
+            }
+            store8(target + i, out_first);
+            store8(target + i + half, out_second);
+        } else {
+            const float c = __bfloat162float(cos_row[i]);
+            const float s = __bfloat162float(sin_row[i]);
+            const float first = __bfloat162float(source[i]);
+            const float second = __bfloat162float(source[i + half]);
+            target[i] = __float2bfloat16_rn(round_bf16(first * c) - round_bf16(second * s));
+            target[i + half] = __float2bfloat16_rn(round_bf16(second * c) + round_bf16(first * s));
         }
     }
     if (slot_ok) {
         const __nv_bfloat16 *values = row + static_cast<size_t>(heads + kv_heads) * head_dim;
-        for (int c = threadIdx.x; c < kv_heads * head_dim; c += blockDim.x) {
-            value_cache[cache_row + c] = values[c];
+        for (int c = threadIdx.x * VEC; c < kv_heads * head_dim; c += blockDim.x * VEC) {
+            if (VEC == 8) {
+                *reinterpret_cast<uint4 *>(value_cache + cache_row + c) = *reinterpret_cast<const uint4 *>(values + c);
+            } else {
+                value_cache[cache_row + c] = values[c];
+            }
         }
     }
 }
 
 // out = bf16(bf16(silu(gate)) * up), the two roundings of activation-then-mul in GatedMlp
-// (singe/src/nn/layers/feed_forward/mod.rs:58-66).
+// (singe/src/nn/layers/feed_forward/mod.rs:58-66).  Elementwise: grid (column chunks, rows).
+template <int VEC>
 __global__ void silu_mul_kernel(__nv_bfloat16 *out, const __nv_bfloat16 *gate, const __nv_bfloat16 *up,
                                 long long in_stride, int width) {
-    const size_t in_base = static_cast<size_t>(blockIdx.x) * in_stride;
-    const size_t out_base = static_cast<size_t>(blockIdx.x) * width;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const size_t in_base = static_cast<size_t>(blockIdx.y) * in_stride;
+    const size_t out_base = static_cast<size_t>(blockIdx.y) * width;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (c >= width) return;
+    if (VEC == 8) {
+        const Vec8 g = load8(gate + in_base + c), u = load8(up + in_base + c);
+        Vec8 result;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) result.v[i] = round_bf16(g.v[i] / (1.0f + __expf(-g.v[i]))) * u.v[i];
+        store8(out + out_base + c, result);
+    } else {
         const float g = __bfloat162float(gate[in_base + c]);
         const float u = __bfloat162float(up[in_base + c]);
-        const float activated = round_bf16(g / (1.0f + expf(-g)));
-        out[out_base + c] = __float2bfloat16_rn(activated * u);
+        out[out_base + c] = __float2bfloat16_rn(round_bf16(g / (1.0f + __expf(-g))) * u);
     }
 }
 
 // Row-wise argmax; ties go to the lowest index.  Writes the winning value (f32) and index (int64, plus
-// `index_offset` so that a vocabulary shard reports global token ids).
+// `index_offset` so that a vocabulary shard reports global token ids).  NaN logits never win.
+template <int VEC>
 __global__ void argmax_kernel(float *best_value, long long *best_index, const __nv_bfloat16 *logits,
                               long long stride, int width, long long index_offset) {
     __shared__ float values[32];
@@ -146,11 +265,22 @@ __global__ void argmax_kernel(float *best_value, long long *best_index, const __
     const __nv_bfloat16 *row = logits + static_cast<size_t>(blockIdx.x) * stride;
     float best = -INFINITY;
     int where = 0x7fffffff;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const float value = __bfloat162float(row[c]);
-        if (value > best || (value == best && c < where)) {
-            best = value;
-            where = c;
+    for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {
+        if (VEC == 8) {
+            const Vec8 chunk = load8(row + c);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (chunk.v[i] > best) {  // ascending scan: a later equal value never replaces an earlier one
+                    best = chunk.v[i];
+                    where = c + i;
+                }
+            }
+        } else {
+            const float value = __bfloat162float(row[c]);
+            if (value > best) {
+                best = value;
+                where = c;
+            }
         }
     }
     for (int offset = 16; offset > 0; offset >>= 1) {
@@ -194,15 +324,17 @@ int singe_embedding_bf16(singe_stream_t stream, void *out, const void *table, co
     if (out == nullptr || table == nullptr || ids == nullptr) return SINGE_ERR_NULL_POINTER;
     if (index_width != 4 && index_width != 8) return SINGE_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool wide = width % 8 == 0 && aligned16(out) && aligned16(table);
+#define SINGE_EMBED(Index, VEC)                                                                              \
+    embedding_kernel<Index, VEC><<<static_cast<unsigned>(tokens), 256, 0, s>>>(                              \
+        static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(table),                        \
+        static_cast<const Index *>(ids), static_cast<int>(width), static_cast<long long>(vocab), status)
     if (index_width == 8) {
-        embedding_kernel<long long><<<static_cast<unsigned>(tokens), 256, 0, s>>>(
-            static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(table),
-            static_cast<const long long *>(ids), static_cast<int>(width), static_cast<long long>(vocab), status);
+        if (wide) SINGE_EMBED(long long, 8); else SINGE_EMBED(long long, 1);
     } else {
-        embedding_kernel<int><<<static_cast<unsigned>(tokens), 256, 0, s>>>(
-            static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(table),
-            static_cast<const int *>(ids), static_cast<int>(width), static_cast<long long>(vocab), status);
+        if (wide) SINGE_EMBED(int, 8); else SINGE_EMBED(int, 1);
     }
+#undef SINGE_EMBED
     return launch_status();
 }
 
@@ -213,10 +345,20 @@ int singe_add_rms_norm_bf16(singe_stream_t stream, void *hidden, const void *del
     if (hidden == nullptr || (normed != nullptr && weight == nullptr) || (normed == nullptr && delta == nullptr)) {
         return SINGE_ERR_NULL_POINTER;
     }
-    add_rms_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__nv_bfloat16 *>(hidden), static_cast<const __nv_bfloat16 *>(delta),
-        static_cast<__nv_bfloat16 *>(normed), static_cast<const __nv_bfloat16 *>(weight), static_cast<int>(width),
-        eps);
+    const bool wide = width % 8 == 0 && aligned16(hidden) && aligned16(delta) && aligned16(normed) && aligned16(weight);
+    if (wide) {
+        int threads = static_cast<int>((width / 8 + 31) / 32 * 32);
+        if (threads > 512) threads = 512;
+        add_rms_norm_kernel<8><<<static_cast<unsigned>(rows), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<__nv_bfloat16 *>(hidden), static_cast<const __nv_bfloat16 *>(delta),
+            static_cast<__nv_bfloat16 *>(normed), static_cast<const __nv_bfloat16 *>(weight),
+            static_cast<int>(width), eps);
+    } else {
+        add_rms_norm_kernel<1><<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<__nv_bfloat16 *>(hidden), static_cast<const __nv_bfloat16 *>(delta),
+            static_cast<__nv_bfloat16 *>(normed), static_cast<const __nv_bfloat16 *>(weight),
+            static_cast<int>(width), eps);
+    }
     return launch_status();
 }
 
@@ -240,8 +382,10 @@ int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void
     }
     if (index_width != 4 && index_width != 8) return SINGE_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-#define SINGE_ROTARY(Index)                                                                                          \
-    rotary_cache_write_kernel<Index><<<static_cast<unsigned>(tokens), 256, 0, s>>>(                                  \
+    const bool wide = (head_dim / 2) % 8 == 0 && qkv_row_stride % 8 == 0 && aligned16(q_out) && aligned16(qkv) &&
+                      aligned16(cos_table) && aligned16(sin_table) && aligned16(key_cache) && aligned16(value_cache);
+#define SINGE_ROTARY(Index, VEC)                                                                                     \
+    rotary_cache_write_kernel<Index, VEC><<<static_cast<unsigned>(tokens), 256, 0, s>>>(                             \
         static_cast<__nv_bfloat16 *>(q_out), static_cast<const __nv_bfloat16 *>(qkv),                                \
         static_cast<long long>(qkv_row_stride), static_cast<const __nv_bfloat16 *>(cos_table),                       \
         static_cast<const __nv_bfloat16 *>(sin_table), static_cast<const Index *>(positions),                        \
@@ -250,9 +394,9 @@ int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void
         static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<long long>(pages),                       \
         static_cast<long long>(page_size), static_cast<long long>(capacity), status)
     if (index_width == 8) {
-        SINGE_ROTARY(long long);
+        if (wide) SINGE_ROTARY(long long, 8); else SINGE_ROTARY(long long, 1);
     } else {
-        SINGE_ROTARY(int);
+        if (wide) SINGE_ROTARY(int, 8); else SINGE_ROTARY(int, 1);
     }
 #undef SINGE_ROTARY
     return launch_status();
@@ -263,9 +407,19 @@ int singe_silu_mul_bf16(singe_stream_t stream, void *out, const void *gate, cons
     if (rows == 0 || width == 0 || input_row_stride < width) return SINGE_ERR_INVALID_LENGTH;
     if (!fits_i32(rows) || !fits_i32(width)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
     if (out == nullptr || gate == nullptr || up == nullptr) return SINGE_ERR_NULL_POINTER;
-    silu_mul_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(gate),
-        static_cast<const __nv_bfloat16 *>(up), static_cast<long long>(input_row_stride), static_cast<int>(width));
+    if (rows > 65535) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    const bool wide = width % 8 == 0 && input_row_stride % 8 == 0 && aligned16(out) && aligned16(gate) && aligned16(up);
+    if (wide) {
+        dim3 grid(static_cast<unsigned>((width / 8 + 255) / 256), static_cast<unsigned>(rows));
+        silu_mul_kernel<8><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(gate),
+            static_cast<const __nv_bfloat16 *>(up), static_cast<long long>(input_row_stride), static_cast<int>(width));
+    } else {
+        dim3 grid(static_cast<unsigned>((width + 255) / 256), static_cast<unsigned>(rows));
+        silu_mul_kernel<1><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(gate),
+            static_cast<const __nv_bfloat16 *>(up), static_cast<long long>(input_row_stride), static_cast<int>(width));
+    }
     return launch_status();
 }
 
@@ -274,9 +428,16 @@ int singe_argmax_bf16(singe_stream_t stream, float *best_value, int64_t *best_in
     if (rows == 0 || width == 0 || row_stride < width) return SINGE_ERR_INVALID_LENGTH;
     if (!fits_i32(rows) || !fits_i32(width)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
     if (best_value == nullptr || best_index == nullptr || logits == nullptr) return SINGE_ERR_NULL_POINTER;
-    argmax_kernel<<<static_cast<unsigned>(rows), 1024, 0, static_cast<cudaStream_t>(stream)>>>(
-        best_value, reinterpret_cast<long long *>(best_index), static_cast<const __nv_bfloat16 *>(logits),
-        static_cast<long long>(row_stride), static_cast<int>(width), static_cast<long long>(index_offset));
+    const bool wide = width % 8 == 0 && row_stride % 8 == 0 && aligned16(logits);
+    if (wide) {
+        argmax_kernel<8><<<static_cast<unsigned>(rows), 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+            best_value, reinterpret_cast<long long *>(best_index), static_cast<const __nv_bfloat16 *>(logits),
+            static_cast<long long>(row_stride), static_cast<int>(width), static_cast<long long>(index_offset));
+    } else {
+        argmax_kernel<1><<<static_cast<unsigned>(rows), 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+            best_value, reinterpret_cast<long long *>(best_index), static_cast<const __nv_bfloat16 *>(logits),
+            static_cast<long long>(row_stride), static_cast<int>(width), static_cast<long long>(index_offset));
+    }
     return launch_status();
 }
 

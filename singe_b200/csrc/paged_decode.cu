@@ -10,7 +10,8 @@
 //           KV head) and ALL query heads of that KV head, so K and V are read once for the group.
 //   warp 4 (producer): reads the block table 32 entries at a time and issues one TMA tile load per
 //           (page, 64-wide half of the head) -- 16 rows x 128 bytes, SWIZZLE_128B -- for K and V into a
-//           ring of stages, one mbarrier pair per stage.
+//           ring of eight stages, one mbarrier pair per stage; three CTAs share an SM so that one CTA's start-up
+//           (length, block table, first TMA round trip) and final merge overlap the others' streaming.
 //   warps 0-3 (consumers): page i belongs to warp i % 4.  S = Q K^T and O += P V run as m16n8k16
 //           tensor-core tiles fed by ldmatrix from the swizzled stage (conflict-free), softmax runs in
 //           f32 with warp-shuffle row reductions in the exp2 domain.
@@ -29,7 +30,7 @@ constexpr int kDecodeThreads = (kDecodeWarps + 1) * 32;
 // A multiple of the consumer-warp count, so every use of a stage belongs to the same warp: a warp then
 // waits for phase n+1 of a stage's barrier only after it consumed phase n, and a parity wait can never
 // alias a phase that is two behind (TMA tiles may complete out of order).
-constexpr int kDecodeStages = 12;
+constexpr int kDecodeStages = 8;
 static_assert(kDecodeStages % kDecodeWarps == 0, "stage ownership must be fixed per consumer warp");
 constexpr int kPageTokens = 16;
 constexpr int kHalfBytes = kPageTokens * 128;  // one TMA box: 16 rows x 128 bytes
@@ -41,6 +42,7 @@ struct DecodeParams {
     const void *query;    // [batch, heads, head_dim]
     const int32_t *lens;
     const uint32_t *table;
+    int batch;
     int heads;
     int kv_heads;
     int group;
@@ -72,7 +74,7 @@ constexpr int decode_smem_bytes() {
 }
 
 template <typename T, int HD>
-__global__ void __launch_bounds__(kDecodeThreads, 2)
+__global__ void __launch_bounds__(kDecodeThreads, 3)
     paged_decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                         const DecodeParams p) {
     constexpr int NHALF = HD / 64;
@@ -92,12 +94,27 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
 
     const int split = blockIdx.x;
     const int g = blockIdx.y;
-    const int b = blockIdx.z;
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const T *query = static_cast<const T *>(p.query);
 
+    const int b = blockIdx.z;
+
+    // Start the query-fragment loads before the length is known: their addresses depend only on the block
+    // indices, so this global round trip overlaps the length read and the block-table read.
+    uint32_t qa[KSTEPS][2];
+    if (warp < kDecodeWarps) {
+        const int row = lane >> 2;
+        const int quad = lane & 3;
+        const size_t head = static_cast<size_t>(b) * p.heads + g * p.group + row;
+        const uint32_t *q32 = reinterpret_cast<const uint32_t *>(query + head * HD);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            qa[ks][0] = row < p.group ? q32[ks * 8 + quad] : 0u;
+            qa[ks][1] = row < p.group ? q32[ks * 8 + 4 + quad] : 0u;
+        }
+    }
     int len = p.lens[b];
     const int bound = p.table_stride * kPageTokens;
     len = len < 0 ? 0 : (len > bound ? bound : len);
@@ -124,9 +141,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
         return;
     }
 
-    const int tok_begin = split * p.split_tokens;
-    const int tok_end = min(len, tok_begin + p.split_tokens);
-    const int npages = (tok_end - tok_begin + kPageTokens - 1) / kPageTokens;
+    const int piece = p.split_tokens;
+    const int tok_begin = split * piece;
+    const int tok_end = min(len, tok_begin + piece);
+    const int npages = tok_end > tok_begin ? (tok_end - tok_begin + kPageTokens - 1) / kPageTokens : 0;
     const int first_page = tok_begin / kPageTokens;
 
     if (tid == 0) {
@@ -172,18 +190,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
                         break;
                     }
                 }
-                if (lane == 0) {
+                // One box per lane: lanes 0 .. 2*NHALF-1 issue the K halves and the V halves of the page in a single
+                // warp-wide instruction instead of one thread issuing them back to back.
+                {
                     const uint32_t full = bar_full + s * 8;
                     const uint32_t stage = base + s * STAGE;
-                    mbar_expect_tx(full, STAGE);
-#pragma unroll
-                    for (int hf = 0; hf < NHALF; ++hf) {
-                        tma_load_4d(stage + hf * kHalfBytes, &k_map, full, hf * 64, g, 0, static_cast<int32_t>(pg));
-                    }
-#pragma unroll
-                    for (int hf = 0; hf < NHALF; ++hf) {
-                        tma_load_4d(stage + (NHALF + hf) * kHalfBytes, &v_map, full, hf * 64, g, 0,
-                                    static_cast<int32_t>(pg));
+                    if (lane == 0) mbar_expect_tx(full, STAGE);
+                    __syncwarp();
+                    if (lane < 2 * NHALF) {
+                        const int hf = lane % NHALF;
+                        const CUtensorMap *map = lane < NHALF ? &k_map : &v_map;
+                        tma_load_4d(stage + lane * kHalfBytes, map, full, hf * 64, g, 0, static_cast<int32_t>(pg));
                     }
                 }
             }
@@ -195,16 +212,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 2)
         // ---------------- consumers ----------------
         const int row = lane >> 2;   // query head within the group (rows >= group are zero padding)
         const int quad = lane & 3;
-        uint32_t qa[KSTEPS][2];
-        {
-            const size_t head = static_cast<size_t>(b) * p.heads + g * p.group + row;
-            const uint32_t *q32 = reinterpret_cast<const uint32_t *>(query + head * HD);
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks) {
-                qa[ks][0] = row < p.group ? q32[ks * 8 + quad] : 0u;
-                qa[ks][1] = row < p.group ? q32[ks * 8 + 4 + quad] : 0u;
-            }
-        }
         float o[NTILES][4];
 #pragma unroll
         for (int nt = 0; nt < NTILES; ++nt) {
@@ -419,6 +426,7 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
     params.query = query;
     params.lens = actual_seq_lens;
     params.table = block_table;
+    params.batch = static_cast<int>(batch);
     params.heads = static_cast<int>(heads);
     params.kv_heads = static_cast<int>(kv_heads);
     params.group = static_cast<int>(heads / kv_heads);

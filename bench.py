@@ -384,6 +384,66 @@ def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3):
     }
 
 
+def run_only(args):
+    """Launches one kernel of the path `--steps` times after `--warmup` launches and exits: the small, bounded
+    command the ncu captures under profiles/ are taken from."""
+    import torch
+
+    from singe_b200 import llama, ops, workloads
+
+    kind, _, detail = args.only.partition(":")
+    if kind == "decode":
+        case = workloads.paged_decode_case(seed=1)
+        query, key_cache, value_cache = decode_device_inputs(case, seed=1)
+        lens = torch.from_numpy(case.lens).cuda()
+        table = torch.from_numpy(case.block_table.view(np.int32)).cuda()
+        out = torch.empty_like(query)
+        config = ops.PagedKvDecodeAttentionConfig.contiguous(case.batch, case.heads, case.kv_heads, case.head_dim,
+                                                             case.block_size, case.physical_blocks,
+                                                             case.block_table_batch_stride, case.scale)
+        call = lambda: ops.paged_kv_decode_attention(out, query, key_cache, value_cache, lens, table, config)
+    elif kind == "gemm":
+        m, n, k = (int(v) for v in detail.split(","))
+        x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+        w = (torch.randn((n, k), device="cuda") * 0.02).to(torch.bfloat16)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        call = lambda: ops.linear(x, w, y)
+    elif kind in ("prefill", "kvwrite"):
+        lens = tuple(int(v) for v in detail.split(",")) if detail else (8192, 4096, 2048, 1024)
+        case = workloads.prefill_case(lens=lens)
+        total = case.total_tokens
+        q = torch.randn((total, case.heads, case.head_dim), device="cuda").to(torch.bfloat16)
+        k = torch.randn((total, case.kv_heads, case.head_dim), device="cuda").to(torch.bfloat16)
+        v = torch.randn((total, case.kv_heads, case.head_dim), device="cuda").to(torch.bfloat16)
+        out = torch.empty_like(q)
+        lse = torch.empty((total, case.heads), dtype=torch.float32, device="cuda")
+        d_lens = torch.from_numpy(case.lens).cuda()
+        d_offsets = torch.from_numpy(case.offsets).cuda()
+        shape = (case.pages, case.page_size, case.kv_heads, case.head_dim)
+        key_cache = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+        value_cache = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+        pages = torch.from_numpy(case.write_pages).cuda()
+        slots = torch.from_numpy(case.write_slots).cuda()
+        config = ops.RaggedKvPrefillAttentionConfig(len(lens), total, total, case.heads, case.kv_heads, case.head_dim,
+                                                    True, case.scale)
+        if kind == "prefill":
+            call = lambda: ops.ragged_kv_prefill_attention(out, lse, q, k, v, d_lens, d_lens, d_offsets, config)
+        else:
+            call = lambda: ops.kv_cache_write(key_cache, value_cache, k, v, pages, slots)
+    elif kind == "step":
+        config = llama.LlamaConfig(layers=int(detail or 4))
+        decoder = llama.LlamaDecoder(config, 64, 2048 + 64)
+        decoder.fill_context(2048)
+        decoder.plan(np.random.default_rng(4).integers(0, config.vocab, size=64))
+        call = decoder.forward
+    else:
+        raise SystemExit(f"unknown --only target {args.only!r}")
+    for _ in range(args.warmup + args.steps):
+        call()
+    torch.cuda.synchronize()
+    print(json.dumps({"only": args.only, "launches": args.warmup + args.steps, "device_error": ops.take_device_error()}))
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -392,10 +452,15 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-also", action="store_true", help="skip the secondary figures")
     parser.add_argument("--no-decode-step", action="store_true", help="skip the Llama-shaped decode step figure")
+    parser.add_argument("--only", default="", help="profiling aid: launch one kernel a few times and exit "
+                        "(decode | gemm:M,N,K | prefill[:len,len,...] | kvwrite | step:LAYERS)")
     args = parser.parse_args()
 
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.only:
+        run_only(args)
         return
 
     import torch

@@ -9,14 +9,22 @@
 //
 // One CTA = 256 consecutive query rows of one (sequence, head), handled as two 128-row tiles A and B that take
 // turns on the tensor core, so the softmax of one tile runs while the other tile's MMAs execute.  Roles:
-//   warps 0-7  softmax of whichever tile has scores ready (A, B, A, B ...).  A row (= tensor-memory lane) is shared
-//              by two threads, 64 score columns each, so one tile's softmax is short enough to hide behind the
-//              other tile's MMAs.  Scores are pulled into registers once (row max, then exp2 / row sum / bf16
-//              pack), P is written back over S with tcgen05.st, O is rescaled in tensor memory only when the
-//              running max grew by more than 2^8 (the stale max stays baked into P, O and the row sum, so the
-//              result is exact), epilogue O / sum -> bf16 + LSE.
-//              A quarter of the exponentials are evaluated as a polynomial on the FMA pipe: the special-function
-//              unit delivers 16 exp2 per clock per SM, which at head_dim 128 is exactly as much time as the MMAs.
+//   warps 0-3  softmax of tile A, one thread per query row (= tensor-memory lane); warps 4-7 the same for tile B.
+//              The softmax is the bottleneck next to the MMAs (instruction issue and the 16 exp2 per clock of the
+//              special-function unit), so its steady state is a single pass with as few instructions per score as
+//              possible: scores come out of tensor memory 32 columns at a time (the next load in flight while the
+//              current chunk is processed), p = exp2(s * scale - base) as packed f32x2 arithmetic, the row sum,
+//              the bf16 pack, and P goes back over S with tcgen05.st.  No row maximum is taken: `base` only has to
+//              keep the numbers in range, the result does not depend on it (out = O / sum, LSE = base +
+//              log2(sum)).  The first key tile takes the exact row maximum as base (a two-pass tile); afterwards
+//              the row is re-based by an exact power of two whenever its running sum passes 2^16 (O in tensor
+//              memory and the sum are scaled, at the start of the next tile, when the previous P V has retired).
+//              One exponential in eight is evaluated as a polynomial on the FMA pipe to unload the
+//              special-function unit.
+//              A row whose scores jump by more than ~2^64 from one key tile to the next would overflow this
+//              scheme.  The CTA then marks itself (a NaN in the LSE of its first row) and the second launch of
+//              the same kernel in SAFE mode, where every tile takes its exact row maximum first, recomputes
+//              exactly the marked CTAs; all others leave at once.
 //   warp 8     MMA issuer and tensor-memory owner.  Issue order per key tile j:
 //                 PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1)
 //              (S = Q K^T: 8 x tcgen05.mma 128x128x16, both operands K-major in shared memory; O += P V: 8 x
@@ -38,12 +46,14 @@ namespace {
 constexpr int kPrefillThreads = 320;
 constexpr int kTile = 128;           // rows of one query tile, and keys per key tile
 constexpr int kPair = 2 * kTile;     // query rows per CTA
-constexpr int kHalfRow = kTile / 2;  // score columns one softmax thread handles
+constexpr int kChunk = 32;           // score columns taken out of tensor memory at a time
 constexpr int kHeadDim = 128;
 constexpr int kHalfTileBytes = kTile * 128;       // one TMA box: 128 rows x 128 bytes
 constexpr int kTileBytes = 2 * kHalfTileBytes;    // 32 KB
 constexpr int kMaxRankTiles = 1024;               // heaviest-first dispatch: sequences up to 256 Ki tokens
-constexpr float kRescaleThreshold = 8.0f;         // log2 units
+constexpr float kRescaleThreshold = 8.0f;         // two-pass tiles: re-base when the max grew by 2^8 (log2 units)
+constexpr float kRebaseLimit = 65536.0f;          // single-pass tiles: re-base a row when its sum passes 2^16
+constexpr float kOverflowLimit = 1.8446744e19f;   // 2^64: beyond this the CTA is redone in SAFE mode
 
 struct PrefillParams {
     __nv_bfloat16 *out;
@@ -74,8 +84,8 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 }
 
 // 2^x for two values on the FMA pipe with packed f32x2 arithmetic: x = r + f with r the nearest integer and f in
-// [-0.5, 0.5]; 2^f by a degree-4 polynomial (relative error ~4e-5, far below bf16 resolution), 2^r by adding r
-// to the exponent field.
+// [-0.5, 0.5]; 2^f by a cubic (relative error 7.6e-5, a fiftieth of a bf16 ulp), 2^r by adding r to the exponent
+// field.
 __device__ __forceinline__ float2 exp2_poly2(float2 x) {
     x.x = fmaxf(x.x, -120.0f);
     x.y = fmaxf(x.y, -120.0f);
@@ -83,75 +93,111 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
     const float2 shifted = __fadd2_rn(x, magic);
     const float2 r = __fadd2_rn(shifted, make_float2(-12582912.0f, -12582912.0f));
     const float2 f = __ffma2_rn(r, make_float2(-1.0f, -1.0f), x);
-    float2 p = __ffma2_rn(f, make_float2(0.009618129f, 0.009618129f), make_float2(0.055504109f, 0.055504109f));
-    p = __ffma2_rn(p, f, make_float2(0.240226507f, 0.240226507f));
-    p = __ffma2_rn(p, f, make_float2(0.693147181f, 0.693147181f));
-    p = __ffma2_rn(p, f, make_float2(1.0f, 1.0f));
+    float2 p = __ffma2_rn(f, make_float2(0.05520551f, 0.05520551f), make_float2(0.24261396f, 0.24261396f));
+    p = __ffma2_rn(p, f, make_float2(0.69325476f, 0.69325476f));
+    p = __ffma2_rn(p, f, make_float2(0.99992773f, 0.99992773f));
     p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(shifted.x) << 23));
     p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(shifted.y) << 23));
     return p;
 }
 
-// Maximum of the 64 raw scores one thread holds (half a row).  MASKED handles tiles where some keys are hidden (the
-// diagonal tile and a sequence's last tile); the unmasked form is the steady state: three-input maxima, no compares.
+// Folds the 32 raw scores of one chunk into four running maxima (independent chains).  MASKED handles tiles where
+// some keys are hidden (the diagonal tile and a sequence's last tile) and a negative scale; `limit` counts the
+// visible columns from the chunk's first.
 template <bool MASKED>
-__device__ __forceinline__ float row_max(const uint32_t (&sc)[kHalfRow], int limit, float sign) {
-    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;  // independent chains for ILP
+__device__ __forceinline__ void chunk_max(const uint32_t (&sc)[kChunk], int limit, float sign, float (&m)[4]) {
     if (MASKED) {
 #pragma unroll
-        for (int i = 0; i < kHalfRow; i += 4) {
-            if (i < limit) m0 = fmaxf(m0, __uint_as_float(sc[i]) * sign);
-            if (i + 1 < limit) m1 = fmaxf(m1, __uint_as_float(sc[i + 1]) * sign);
-            if (i + 2 < limit) m2 = fmaxf(m2, __uint_as_float(sc[i + 2]) * sign);
-            if (i + 3 < limit) m3 = fmaxf(m3, __uint_as_float(sc[i + 3]) * sign);
+        for (int i = 0; i < kChunk; i += 4) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (i + u < limit) m[u] = fmaxf(m[u], __uint_as_float(sc[i + u]) * sign);
+            }
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < kHalfRow; i += 8) {
-            m0 = max3(m0, __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
-            m1 = max3(m1, __uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3]));
-            m2 = max3(m2, __uint_as_float(sc[i + 4]), __uint_as_float(sc[i + 5]));
-            m3 = max3(m3, __uint_as_float(sc[i + 6]), __uint_as_float(sc[i + 7]));
+        for (int i = 0; i < kChunk; i += 8) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                m[u] = max3(m[u], __uint_as_float(sc[i + 2 * u]), __uint_as_float(sc[i + 2 * u + 1]));
+            }
         }
     }
-    return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
-// P = exp2(s * scale + bias) for the 64 scores one thread holds: bf16 pairs go back to tensor memory over S, the
-// (unrounded) values are summed.  Scores are handled as f32x2 pairs; every fourth pair takes its two exponentials
-// from the polynomial on the FMA pipe instead of the special-function unit.
+// P = exp2(s * scale + bias) for one chunk of 32 scores: the bf16 pairs go back to tensor memory (16 packed
+// columns at `tmem_p`), the unrounded values are added to two running f32x2 sums.  Scores are handled as f32x2
+// pairs; pair 3 of every eight takes its exponentials from the polynomial.
 template <bool MASKED>
-__device__ __forceinline__ float row_exp_store(const uint32_t (&sc)[kHalfRow], uint32_t tmem_s, float scale_log2,
-                                               float bias, int limit) {
-    float2 sum = make_float2(0.0f, 0.0f);
-    const float2 scale2 = make_float2(scale_log2, scale_log2);
-    const float2 bias2 = make_float2(bias, bias);
+__device__ __forceinline__ void chunk_exp_store(const uint32_t (&sc)[kChunk], uint32_t tmem_p, float2 scale2,
+                                                float2 bias2, int limit, float2 (&sum)[2]) {
+    uint32_t packed[kChunk / 2];
 #pragma unroll
-    for (int c = 0; c < kHalfRow; c += 32) {
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-            const float2 x = __ffma2_rn(make_float2(__uint_as_float(sc[c + i]), __uint_as_float(sc[c + i + 1])),
-                                        scale2, bias2);
-            float2 e;
-            if ((i & 7) == 6) {
-                e = exp2_poly2(x);
-            } else {
-                e.x = exp2_approx(x.x);
-                e.y = exp2_approx(x.y);
-            }
-            if (MASKED) {
-                e.x = (c + i < limit) ? e.x : 0.0f;
-                e.y = (c + i + 1 < limit) ? e.y : 0.0f;
-            }
-            sum = __fadd2_rn(sum, e);
-            packed[i >> 1] = pack2<__nv_bfloat16>(e.x, e.y);
+    for (int i = 0; i < kChunk; i += 2) {
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])), scale2, bias2);
+        float2 e;
+        if ((i & 15) == 6) {
+            e = exp2_poly2(x);
+        } else {
+            e.x = exp2_approx(x.x);
+            e.y = exp2_approx(x.y);
         }
-        tmem_st_x16(tmem_s + (c >> 1), packed);
+        if (MASKED) {
+            e.x = (i < limit) ? e.x : 0.0f;
+            e.y = (i + 1 < limit) ? e.y : 0.0f;
+        }
+        sum[(i >> 1) & 1] = __fadd2_rn(sum[(i >> 1) & 1], e);
+        packed[i >> 1] = pack2<__nv_bfloat16>(e.x, e.y);
     }
-    return sum.x + sum.y;
+    tmem_st_x16(tmem_p, packed);
 }
 
+// One row of one key tile: S (128 f32 columns at `tmem_s`) -> P (64 packed columns over the same place), chunk by
+// chunk with the next chunk's load in flight.
+template <bool MASKED>
+__device__ __forceinline__ void tile_exp(uint32_t tmem_s, float2 scale2, float2 bias2, int limit, float2 (&sum)[2]) {
+    uint32_t buf[2][kChunk];
+    tmem_ld_x32(tmem_s, buf[0]);
+#pragma unroll
+    for (int c = 0; c < kTile / kChunk; ++c) {
+        tmem_wait_ld_into(buf[c & 1]);
+        if (c + 1 < kTile / kChunk) tmem_ld_x32(tmem_s + (c + 1) * kChunk, buf[(c + 1) & 1]);
+        chunk_exp_store<MASKED>(buf[c & 1], tmem_s + c * (kChunk / 2), scale2, bias2, limit - c * kChunk, sum);
+    }
+}
+
+// Exact maximum of the visible raw scores (times `sign`) of one row of one key tile.
+template <bool MASKED>
+__device__ __forceinline__ float tile_max(uint32_t tmem_s, int limit, float sign) {
+    float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    uint32_t buf[2][kChunk];
+    tmem_ld_x32(tmem_s, buf[0]);
+#pragma unroll
+    for (int c = 0; c < kTile / kChunk; ++c) {
+        tmem_wait_ld_into(buf[c & 1]);
+        if (c + 1 < kTile / kChunk) tmem_ld_x32(tmem_s + (c + 1) * kChunk, buf[(c + 1) & 1]);
+        chunk_max<MASKED>(buf[c & 1], limit - c * kChunk, sign, m);
+    }
+    return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+}
+
+// Multiplies this thread's row of O (128 f32 columns of tensor memory) by `factor`.
+__device__ __forceinline__ void scale_o_row(uint32_t tmem_o, float factor) {
+#pragma unroll 1
+    for (int c = 0; c < kHeadDim; c += 32) {
+        uint32_t r[32];
+        tmem_ld_x32(tmem_o + c, r);
+        tmem_wait_ld_into(r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+        tmem_st_x32(tmem_o + c, r);
+    }
+    tmem_wait_st();
+}
+
+// SAFE = false: first launch, single-pass softmax after the first key tile.  SAFE = true: second launch, redoes the
+// CTAs the first launch marked, with the exact row maximum on every tile.
+template <bool SAFE>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
     prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                            const __grid_constant__ CUtensorMap v_map, const PrefillParams p) {
@@ -170,12 +216,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     const uint32_t bar_s_full = bars + 72;    // [2 tiles]
     const uint32_t bar_p_full = bars + 88;    // [2 tiles]
     const uint32_t bar_o_full = bars + 104;   // [2 tiles]
-    const uint32_t bar_exchange = bars + 120;
     const uint32_t tmem_holder = bars + 128;
     volatile uint32_t *holder_ptr = reinterpret_cast<volatile uint32_t *>(smem_raw + (tmem_holder - raw));
     volatile int *picked = reinterpret_cast<volatile int *>(smem_raw + (tmem_holder + 8 - raw));  // [2]
-    float *exchange = reinterpret_cast<float *>(smem_raw + (bars + 160 - raw));  // [2 buffers][2 halves][128 rows]
-    int *counts = reinterpret_cast<int *>(smem_raw + (bars + 160 + 4 * kTile * 4 - raw));  // [kMaxRankTiles] dispatch scratch
+    volatile int *out_of_range = reinterpret_cast<volatile int *>(smem_raw + (tmem_holder + 16 - raw));
+    int *counts = reinterpret_cast<int *>(smem_raw + (bars + 160 - raw));  // [kMaxRankTiles] dispatch scratch
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -220,6 +265,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             }
             picked[0] = chosen_seq;
             picked[1] = chosen_pair;
+            *out_of_range = 0;
         }
         __syncthreads();
     }
@@ -234,7 +280,12 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     const int q0 = pair * kPair;  // sequence-local index of the CTA's first query
     const int kv_head = head / (p.heads / p.kv_heads);
     if (offset < 0 || offset + len_q > p.total_q || offset + len_kv > p.total_kv) {
-        if (tid == 0) report_status(p.error, kStatusIndexOutOfBounds);
+        if (tid == 0 && !SAFE) report_status(p.error, kStatusIndexOutOfBounds);
+        return;
+    }
+    // The first launch marks a CTA it could not finish in range by a NaN in the LSE of the CTA's first row.
+    float *mark = p.lse + (static_cast<size_t>(offset) + q0) * p.heads + head;
+    if (SAFE && !isnan(*mark)) {
         return;
     }
     // key tiles each query tile needs (0 when the tile has no real row or sees no key)
@@ -265,10 +316,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     }
 
     if (tid == 0) {
-        for (int i = 0; i < 16; ++i) {
-            // p_full[2] and the exchange barrier take one arrival per softmax warp (eight warps share every tile)
-            const bool by_warps = i == 11 || i == 12 || i == 15;
-            mbar_init(bars + 8 * i, by_warps ? 8 : 1);
+        for (int i = 0; i < 15; ++i) {
+            // p_full[2] take one arrival per softmax warp of the tile
+            const bool by_warps = i == 11 || i == 12;
+            mbar_init(bars + 8 * i, by_warps ? 4 : 1);
         }
         mbar_init_fence();
     }
@@ -412,139 +463,105 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             }
         }
     } else {
-        // ---------------- softmax / correction / epilogue ----------------
-        // All eight warps work on the tile whose scores are ready, A then B in turn: a row is shared by two
-        // threads, warp w (columns 0-63) and warp w+4 (columns 64-127) of the same tensor-memory lane quarter, so a
-        // tile's softmax takes half as long and is done before the other tile's MMAs finish.  The two halves
-        // exchange their row maxima through shared memory (an mbarrier with a bounded wait, double-buffered).
+        // ---------------- softmax / correction / epilogue: warps 0-3 tile A, warps 4-7 tile B ----------------
+        const int x = warp >> 2;
+        const int my_tiles = x == 0 ? tiles_needed[0] : tiles_needed[1];
         const int quarter = warp & 3;                  // tensor-memory lanes 32*quarter .. +31
-        const int half = warp >> 2;                    // which 64 columns of the row
         const int local_row = quarter * 32 + lane;
+        const int row = q0 + x * kTile + local_row;    // sequence-local query index
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        float used_max[2] = {-INFINITY, -INFINITY};   // per tile: the max baked into P, O and row_sum
-        float row_sum[2] = {0.0f, 0.0f};               // per tile: this half's share of the row sum
-        int turn = 0;                                  // exchanges done so far (selects buffer and barrier phase)
-        for (int j = 0; j < key_tiles && !failed; ++j) {
-#pragma unroll
-            for (int x = 0; x < 2; ++x) {
-                if (j >= tiles_needed[x] || failed) continue;
-                const int row = q0 + x * kTile + local_row;  // sequence-local query index
-                const uint32_t tmem_s = tmem_base + x * kTile + lane_base;
-                const uint32_t tmem_o = tmem_base + 2 * kTile + x * kHeadDim + lane_base;
-                if (!__all_sync(0xffffffffu, mbar_wait(bar_s_full + x * 8, j & 1) ? 1 : 0)) {
-                    failed = true;
-                    continue;
-                }
-                tcgen05_fence_after();
-                const int key0 = j * kTile + half * kHalfRow;
-                // number of keys of this half-tile the row may see
-                int limit = len_kv - key0;
-                if (p.causal) limit = min(limit, row + 1 - key0);
-                limit = row < len_q ? limit : 0;
-                const bool partial = __any_sync(0xffffffffu, limit < kHalfRow);
-
-                uint32_t sc[kHalfRow];
-                tmem_ld_x32(tmem_s + half * kHalfRow, *reinterpret_cast<uint32_t(*)[32]>(&sc[0]));
-                tmem_ld_x32(tmem_s + half * kHalfRow + 32, *reinterpret_cast<uint32_t(*)[32]>(&sc[32]));
-                tmem_wait_ld();
-
-                // pass 1: maximum of this half, then the row maximum through the partner's half
-                const float sign = p.scale_log2 < 0.0f ? -1.0f : 1.0f;
-                float tile_max = (partial || sign < 0.0f) ? row_max<true>(sc, limit, sign) : row_max<false>(sc, limit, sign);
-                tile_max *= fabsf(p.scale_log2);
-                float *mine = exchange + ((turn & 1) * 2 + half) * kTile;
-                const float *theirs = exchange + ((turn & 1) * 2 + (half ^ 1)) * kTile;
-                mine[local_row] = tile_max;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_exchange);
-                if (!__all_sync(0xffffffffu, mbar_wait(bar_exchange, turn & 1) ? 1 : 0)) {
-                    failed = true;
-                    continue;
-                }
-                ++turn;
-                tile_max = fmaxf(tile_max, theirs[local_row]);
-                const float wanted = fmaxf(used_max[x], tile_max);
-                // Rescale O only when some row's max grew past the threshold; then every row of the warp re-bases.
-                // Both halves see the same row maxima, so they take the same decision.
-                const bool grow = wanted > used_max[x] + kRescaleThreshold ||
-                                  (used_max[x] == -INFINITY && wanted > -INFINITY);
-                if (__any_sync(0xffffffffu, grow)) {
-                    const float factor = used_max[x] == -INFINITY ? 0.0f : exp2_approx(used_max[x] - wanted);
-                    if (j > 0) {
-                        row_sum[x] *= factor;
-#pragma unroll 1
-                        for (int c = 0; c < kHalfRow; c += 32) {  // this half's 64 columns of O
-                            uint32_t r[32];
-                            tmem_ld_x32(tmem_o + half * kHalfRow + c, r);
-                            tmem_wait_ld();
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
-                            tmem_st_x32(tmem_o + half * kHalfRow + c, r);
-                        }
-                        tmem_wait_st();
-                    }
-                    used_max[x] = wanted;
-                }
-                // pass 2: P = exp2(s * scale - used_max), row sum, bf16 pairs back into tensor memory
-                const float bias = used_max[x] == -INFINITY ? 0.0f : -used_max[x];
-                row_sum[x] += partial ? row_exp_store<true>(sc, tmem_s + half * (kHalfRow / 2), p.scale_log2, bias, limit)
-                                      : row_exp_store<false>(sc, tmem_s + half * (kHalfRow / 2), p.scale_log2, bias, limit);
-                tmem_wait_st();
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(bar_p_full + x * 8);
-                }
-            }
-        }
-        // ---- epilogue: the halves add their row sums, then each writes its 64 output columns ----
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-            if (tiles_needed[x] == 0 || failed) continue;
-            const int row = q0 + x * kTile + local_row;
-            const uint32_t tmem_o = tmem_base + 2 * kTile + x * kHeadDim + lane_base;
-            float *mine = exchange + ((turn & 1) * 2 + half) * kTile;
-            const float *theirs = exchange + ((turn & 1) * 2 + (half ^ 1)) * kTile;
-            mine[local_row] = row_sum[x];
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_exchange);
-            if (!__all_sync(0xffffffffu, mbar_wait(bar_exchange, turn & 1) ? 1 : 0)) {
+        const uint32_t tmem_s = tmem_base + x * kTile + lane_base;
+        const uint32_t tmem_o = tmem_base + 2 * kTile + x * kHeadDim + lane_base;
+        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+        const float sign = p.scale_log2 < 0.0f ? -1.0f : 1.0f;
+        float base_log2 = -INFINITY;  // what P, O and the row sum are relative to (log2 units); finite after tile 0
+        float row_sum = 0.0f;
+        bool in_range = true;
+        for (int j = 0; j < my_tiles && !failed; ++j) {
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_s_full + x * 8, j & 1) ? 1 : 0)) {
                 failed = true;
-                continue;
+                break;
             }
-            ++turn;
-            const float total = row_sum[x] + theirs[local_row];
+            tcgen05_fence_after();  // S(j) is ready, and with it every earlier MMA of this tile: O holds P V up to j-1
+            // number of keys of this key tile the row may see
+            int limit = len_kv - j * kTile;
+            if (p.causal) limit = min(limit, row + 1 - j * kTile);
+            limit = row < len_q ? limit : 0;
+            const bool partial = __any_sync(0xffffffffu, limit < kTile);
+
+            if (SAFE || j == 0) {
+                float wanted = (partial || sign < 0.0f) ? tile_max<true>(tmem_s, limit, sign)
+                                                        : tile_max<false>(tmem_s, limit, sign);
+                wanted = fmaxf(base_log2, wanted * fabsf(p.scale_log2));
+                wanted = wanted == -INFINITY ? 0.0f : wanted;  // nothing visible yet: any base will do
+                // Re-base O only when some row's max grew past the threshold; then every row of the warp does.
+                const bool grow = wanted > base_log2 + kRescaleThreshold;
+                if (__any_sync(0xffffffffu, grow)) {
+                    if (j > 0) {
+                        const float factor = exp2_approx(base_log2 - wanted);
+                        row_sum *= factor;
+                        scale_o_row(tmem_o, factor);
+                    }
+                    base_log2 = wanted;
+                }
+            } else if (__any_sync(0xffffffffu, row_sum > kRebaseLimit)) {
+                // Single-pass tiles: pull the row back by the exponent of its sum, an exact power of two.
+                const int exponent = row_sum > kRebaseLimit ? ((__float_as_int(row_sum) >> 23) & 0xff) - 127 : 0;
+                const float factor = __int_as_float((127 - exponent) << 23);
+                row_sum *= factor;
+                base_log2 += static_cast<float>(exponent);
+                scale_o_row(tmem_o, factor);
+            }
+            const float2 bias2 = make_float2(-base_log2, -base_log2);
+            float2 sum[2] = {make_float2(row_sum, 0.0f), make_float2(0.0f, 0.0f)};
+            if (partial) {
+                tile_exp<true>(tmem_s, scale2, bias2, limit, sum);
+            } else {
+                tile_exp<false>(tmem_s, scale2, bias2, limit, sum);
+            }
+            row_sum = (sum[0].x + sum[0].y) + (sum[1].x + sum[1].y);
+            tmem_wait_st();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_p_full + x * 8);
+            }
+            in_range = in_range && row_sum < kOverflowLimit;  // false for inf and NaN too
+        }
+        if (!SAFE && !in_range) *out_of_range = 1;
+        // ---- epilogue: O / sum -> bf16, LSE ----
+        if (my_tiles > 0 && !failed) {
             if (!__all_sync(0xffffffffu, mbar_wait(bar_o_full + x * 8, 0) ? 1 : 0)) {
                 failed = true;
-                continue;
-            }
-            tcgen05_fence_after();
-            const bool real = row < len_q;
-            const bool empty = total == 0.0f;
-            const float inverse = empty ? 0.0f : 1.0f / total;
-            const size_t token = static_cast<size_t>(offset) + (real ? row : 0);
-            __nv_bfloat16 *dst = p.out + (token * p.heads + head) * kHeadDim + half * kHalfRow;
+            } else {
+                tcgen05_fence_after();
+                const bool real = row < len_q;
+                const bool empty = row_sum == 0.0f;
+                const float inverse = empty ? 0.0f : 1.0f / row_sum;
+                const size_t token = static_cast<size_t>(offset) + (real ? row : 0);
+                __nv_bfloat16 *dst = p.out + (token * p.heads + head) * kHeadDim;
 #pragma unroll 1
-            for (int c = 0; c < kHalfRow; c += 32) {
-                uint32_t r[32];
-                tmem_ld_x32(tmem_o + half * kHalfRow + c, r);
-                tmem_wait_ld();
-                if (real) {
+                for (int c = 0; c < kHeadDim; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld_x32(tmem_o + c, r);
+                    tmem_wait_ld_into(r);
+                    if (real) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 word;
-                        word.x = pack2<__nv_bfloat16>(__uint_as_float(r[i]) * inverse, __uint_as_float(r[i + 1]) * inverse);
-                        word.y = pack2<__nv_bfloat16>(__uint_as_float(r[i + 2]) * inverse, __uint_as_float(r[i + 3]) * inverse);
-                        word.z = pack2<__nv_bfloat16>(__uint_as_float(r[i + 4]) * inverse, __uint_as_float(r[i + 5]) * inverse);
-                        word.w = pack2<__nv_bfloat16>(__uint_as_float(r[i + 6]) * inverse, __uint_as_float(r[i + 7]) * inverse);
-                        if (empty) word = make_uint4(0u, 0u, 0u, 0u);
-                        *reinterpret_cast<uint4 *>(dst + c + i) = word;
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 word;
+                            word.x = pack2<__nv_bfloat16>(__uint_as_float(r[i]) * inverse, __uint_as_float(r[i + 1]) * inverse);
+                            word.y = pack2<__nv_bfloat16>(__uint_as_float(r[i + 2]) * inverse, __uint_as_float(r[i + 3]) * inverse);
+                            word.z = pack2<__nv_bfloat16>(__uint_as_float(r[i + 4]) * inverse, __uint_as_float(r[i + 5]) * inverse);
+                            word.w = pack2<__nv_bfloat16>(__uint_as_float(r[i + 6]) * inverse, __uint_as_float(r[i + 7]) * inverse);
+                            if (empty) word = make_uint4(0u, 0u, 0u, 0u);
+                            *reinterpret_cast<uint4 *>(dst + c + i) = word;
+                        }
                     }
                 }
-            }
-            if (real && half == 0) {
-                p.lse[token * p.heads + head] =
-                    empty ? -1.0e20f : (used_max[x] + log2f(total)) * 0.6931471805599453f;
+                if (real) {
+                    p.lse[token * p.heads + head] =
+                        empty ? -1.0e20f : (base_log2 + log2f(row_sum)) * 0.6931471805599453f;
+                }
             }
         }
     }
@@ -557,9 +574,12 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
+    if (!SAFE && tid == 0 && *out_of_range != 0) {
+        *mark = __int_as_float(0x7fc00000);  // after this thread's own LSE store for the same row
+    }
 }
 
-constexpr int kPrefillSmem = 6 * kTileBytes + 160 + 4 * kTile * 4 + kMaxRankTiles * 4 + 1024;
+constexpr int kPrefillSmem = 6 * kTileBytes + 160 + kMaxRankTiles * 4 + 1024;
 
 }  // namespace
 
@@ -577,7 +597,9 @@ int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void 
                          size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads,
                          size_t kv_heads, size_t head_dim, int causal, float scale) {
     if (head_dim != kHeadDim) return SINGE_ERR_UNSUPPORTED_WIDTH;
-    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        kPrefillSmem));
+    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kPrefillSmem));
     CUtensorMap q_map, k_map, v_map;
     const uint32_t box[3] = {64, 1, kTile};
@@ -613,7 +635,10 @@ int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void 
     const size_t pairs = total_query_tokens / kPair + batch;
     if (pairs > 0x7fffffffull) return SINGE_ERR_LENGTH_EXCEEDS_I32;
     dim3 grid(static_cast<unsigned>(pairs), static_cast<unsigned>(heads));
-    prefill_tcgen05_kernel<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
+    prefill_tcgen05_kernel<false><<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
+    SINGE_TRY(launch_status());
+    // Redo pass: CTAs the first launch did not mark leave after one load.
+    prefill_tcgen05_kernel<true><<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
     return launch_status();
 }
 

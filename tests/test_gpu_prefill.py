@@ -98,6 +98,28 @@ def test_large_scores_exercise_the_lazy_rescale():
     assert_close_f32(lse, ref_lse, "lse under large scores", 5e-3)
 
 
+def test_a_score_jump_beyond_the_single_pass_range_is_redone_exactly():
+    # After the first key tile the kernel keeps no row maximum; a row whose scores jump by more than 2^64 between key
+    # tiles leaves that scheme's range and its CTA is recomputed with exact maxima.  Keys from index 300 on are 12x
+    # larger, so with scale 1 the later tiles' scores exceed the earlier ones by hundreds of log2 units.  The second
+    # sequence stays in range and shares the launch.
+    rng = np.random.default_rng(11)
+    heads, kv_heads = 4, 2
+    lens = [600, 300]
+    total = sum(lens)
+    q = workloads.normal_bf16(rng, (total, heads, 128))
+    k = rng.standard_normal((total, kv_heads, 128), dtype=np.float32)
+    k[300:600] *= 12.0
+    k = oracle.round_to_bf16(k).reshape(total, kv_heads, 128)
+    v = workloads.normal_bf16(rng, (total, kv_heads, 128))
+    for causal in (True, False):
+        out, lse = _run(q, k, v, lens, lens, [0, 600], heads, kv_heads, causal, 1.0)
+        ref_out, ref_lse = _oracle(q, k, v, lens, lens, [0, 600], heads, kv_heads, causal, 1.0)
+        assert np.isfinite(out).all() and np.isfinite(lse).all()
+        assert_close_bf16(out, ref_out, f"out across a score jump, causal={causal}")
+        assert np.allclose(lse, ref_lse, rtol=1e-5, atol=5e-3), "lse across a score jump"
+
+
 def test_config4_prefill_with_the_cache_write_in_the_same_call():
     # lengths {8192, 4096, 2048, 1024}, 32 Q / 8 KV heads, head_dim 128, seed 3, causal; K/V also stored into 16-token
     # pages of a permuted pool.  The scalar oracle covers the whole 1024-token sequence; rows of the longer

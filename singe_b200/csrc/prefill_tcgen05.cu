@@ -51,6 +51,10 @@ constexpr int kHeadDim = 128;
 constexpr int kHalfTileBytes = kTile * 128;       // one TMA box: 128 rows x 128 bytes
 constexpr int kTileBytes = 2 * kHalfTileBytes;    // 32 KB
 constexpr int kMaxRankTiles = 1024;               // heaviest-first dispatch: sequences up to 256 Ki tokens
+#ifndef SINGE_PREFILL_POLY_PAIRS
+#define SINGE_PREFILL_POLY_PAIRS 0x08
+#endif
+constexpr unsigned kPolyPairs = SINGE_PREFILL_POLY_PAIRS;  // which of every eight f32x2 pairs use the polynomial exp2
 constexpr float kRescaleThreshold = 8.0f;         // two-pass tiles: re-base when the max grew by 2^8 (log2 units)
 constexpr float kRebaseLimit = 65536.0f;          // single-pass tiles: re-base a row when its sum passes 2^16
 constexpr float kOverflowLimit = 1.8446744e19f;   // 2^64: beyond this the CTA is redone in SAFE mode
@@ -136,7 +140,7 @@ __device__ __forceinline__ void chunk_exp_store(const uint32_t (&sc)[kChunk], ui
     for (int i = 0; i < kChunk; i += 2) {
         const float2 x = __ffma2_rn(make_float2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])), scale2, bias2);
         float2 e;
-        if ((i & 15) == 6) {
+        if ((kPolyPairs >> ((i >> 1) & 7)) & 1) {
             e = exp2_poly2(x);
         } else {
             e.x = exp2_approx(x.x);
@@ -195,8 +199,93 @@ __device__ __forceinline__ void scale_o_row(uint32_t tmem_o, float factor) {
     tmem_wait_st();
 }
 
-// SAFE = false: first launch, single-pass softmax after the first key tile.  SAFE = true: second launch, redoes the
-// CTAs the first launch marked, with the exact row maximum on every tile.
+// One unit of work: 256 query rows (tiles A and B) of one (sequence, head).
+struct Item {
+    int head;
+    int kv_head;
+    int offset;     // first packed row of the sequence
+    int q0;         // sequence-local index of the first query row
+    int len_q;
+    int len_kv;
+    int tiles[2];   // key tiles tile A / tile B need (0: no real row, or no visible key)
+    int key_tiles;  // max of the two
+    bool valid;     // false: the sequence's offsets leave the packed tensors
+};
+
+__device__ __forceinline__ int pairs_of(int len_q) { return (max(len_q, 0) + kPair - 1) / kPair; }
+
+// Items are numbered heaviest first: rank = index / heads walks the query pairs of all sequences from the highest
+// pair index down (under a causal mask a pair's work grows with its index), head = index % heads.  `counts[t]` is
+// the number of sequences that have a pair t, `tmax` the largest pair count.  Every lane of the calling warp
+// takes part and receives the same answer.
+__device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *counts, int tmax, int index, int lane) {
+    constexpr unsigned kFull = 0xffffffffu;
+    Item item;
+    int rank = index / p.heads;
+    item.head = index - rank * p.heads;
+    item.kv_head = item.head / (p.heads / p.kv_heads);
+    int pair = -1;
+    for (int first = 0; first < tmax && pair < 0; first += 32) {
+        const int t = tmax - 1 - (first + lane);
+        const int count = t >= 0 ? counts[t] : 0;
+        int prefix = count;  // inclusive prefix sum over the lanes
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int other = __shfl_up_sync(kFull, prefix, d);
+            if (lane >= d) prefix += other;
+        }
+        const unsigned hit = __ballot_sync(kFull, rank < prefix);
+        if (hit != 0) {
+            const int where = __ffs(hit) - 1;
+            pair = tmax - 1 - (first + where);
+            rank -= __shfl_sync(kFull, prefix - count, where);
+        } else {
+            rank -= __shfl_sync(kFull, prefix, 31);
+        }
+    }
+    int seq = -1;
+    for (int first = 0; first < p.batch && seq < 0 && pair >= 0; first += 32) {
+        const int b = first + lane;
+        const bool has = b < p.batch && pairs_of(p.lens_q[b]) > pair;
+        const unsigned mask = __ballot_sync(kFull, has);
+        const int n = __popc(mask);
+        if (rank < n) {
+            seq = first + static_cast<int>(__fns(mask, 0, rank + 1));
+        } else {
+            rank -= n;
+        }
+    }
+    item.valid = false;
+    item.offset = 0;
+    item.q0 = max(pair, 0) * kPair;
+    item.len_q = 0;
+    item.len_kv = 0;
+    item.tiles[0] = item.tiles[1] = 0;
+    item.key_tiles = 0;
+    if (seq < 0) return item;
+    item.len_q = max(p.lens_q[seq], 0);
+    item.len_kv = max(p.lens_kv[seq], 0);
+    item.offset = p.offsets[seq];
+    item.valid = item.offset >= 0 && item.offset + item.len_q <= p.total_q && item.offset + item.len_kv <= p.total_kv;
+    if (!item.valid) return item;
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int first = item.q0 + x * kTile;
+        const int real = min(max(item.len_q - first, 0), kTile);
+        int visible = real > 0 ? item.len_kv : 0;
+        if (p.causal && real > 0) visible = min(visible, first + real);
+        item.tiles[x] = (visible + kTile - 1) / kTile;
+    }
+    item.key_tiles = max(item.tiles[0], item.tiles[1]);
+    return item;
+}
+
+// SAFE = false: the first launch.  One persistent CTA per SM walks its share of the items (item round r of CTA c is
+// index r * grid + c on even rounds and r * grid + grid - 1 - c on odd ones, which evens out the heaviest-first
+// order); all pipelines run on across items, so the next item's loads and first MMAs overlap the current item's
+// last tile and epilogue.  Softmax is single-pass after an item's first key tile.
+// SAFE = true: the second launch, one CTA per item: it leaves at once unless the first launch marked the item, and
+// otherwise recomputes it with the exact row maximum on every tile.
 template <bool SAFE>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
     prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
@@ -208,123 +297,76 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     const uint32_t k_smem = base + 2 * kTileBytes;       // [2 stages]
     const uint32_t v_smem = base + 4 * kTileBytes;       // [2 stages]
     const uint32_t bars = base + 6 * kTileBytes;
-    const uint32_t bar_q_full = bars;
-    const uint32_t bar_k_full = bars + 8;     // [2]
-    const uint32_t bar_k_empty = bars + 24;   // [2]
-    const uint32_t bar_v_full = bars + 40;    // [2]
-    const uint32_t bar_v_empty = bars + 56;   // [2]
-    const uint32_t bar_s_full = bars + 72;    // [2 tiles]
-    const uint32_t bar_p_full = bars + 88;    // [2 tiles]
-    const uint32_t bar_o_full = bars + 104;   // [2 tiles]
-    const uint32_t tmem_holder = bars + 128;
-    volatile uint32_t *holder_ptr = reinterpret_cast<volatile uint32_t *>(smem_raw + (tmem_holder - raw));
-    volatile int *picked = reinterpret_cast<volatile int *>(smem_raw + (tmem_holder + 8 - raw));  // [2]
-    volatile int *out_of_range = reinterpret_cast<volatile int *>(smem_raw + (tmem_holder + 16 - raw));
-    int *counts = reinterpret_cast<int *>(smem_raw + (bars + 160 - raw));  // [kMaxRankTiles] dispatch scratch
+    const uint32_t bar_q_full = bars;         // [2 tiles]
+    const uint32_t bar_q_empty = bars + 16;   // [2 tiles]
+    const uint32_t bar_k_full = bars + 32;    // [2 stages]
+    const uint32_t bar_k_empty = bars + 48;   // [2]
+    const uint32_t bar_v_full = bars + 64;    // [2]
+    const uint32_t bar_v_empty = bars + 80;   // [2]
+    const uint32_t bar_s_full = bars + 96;    // [2 tiles]
+    const uint32_t bar_p_full = bars + 112;   // [2 tiles], one arrival per softmax warp of the tile
+    const uint32_t bar_o_full = bars + 128;   // [2 tiles]
+    const uint32_t bar_o_empty = bars + 144;  // [2 tiles], one arrival per softmax warp of the tile
+    constexpr int kBarriers = 20;
+    const uint32_t words = bars + 8 * kBarriers;
+    volatile uint32_t *holder_ptr = reinterpret_cast<volatile uint32_t *>(smem_raw + (words - raw));
+    volatile int *shared_tmax = reinterpret_cast<volatile int *>(smem_raw + (words + 4 - raw));
+    volatile int *shared_ranks = reinterpret_cast<volatile int *>(smem_raw + (words + 8 - raw));
+    int *counts = reinterpret_cast<int *>(smem_raw + (words + 32 - raw));  // [kMaxRankTiles]
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int head = blockIdx.y;
 
-    // ---- which (sequence, 256-row pair) is this CTA?  rank 0 = highest pair index over all sequences ----
+    // ---- the table behind the heaviest-first item order ----
     {
         int tmax = 0;
-        for (int b = 0; b < p.batch; ++b) {
-            tmax = max(tmax, (max(p.lens_q[b], 0) + kPair - 1) / kPair);
-        }
+        for (int b = 0; b < p.batch; ++b) tmax = max(tmax, pairs_of(p.lens_q[b]));
         tmax = min(tmax, kMaxRankTiles);
         for (int t = tid; t < tmax; t += kPrefillThreads) {
             int count = 0;
-            for (int b = 0; b < p.batch; ++b) {
-                count += ((max(p.lens_q[b], 0) + kPair - 1) / kPair) > t ? 1 : 0;
-            }
+            for (int b = 0; b < p.batch; ++b) count += pairs_of(p.lens_q[b]) > t ? 1 : 0;
             counts[t] = count;
         }
         __syncthreads();
         if (tid == 0) {
-            int rank = blockIdx.x;
-            int chosen_pair = -1, chosen_seq = -1;
-            for (int t = tmax - 1; t >= 0; --t) {
-                if (rank < counts[t]) {
-                    chosen_pair = t;
-                    break;
-                }
-                rank -= counts[t];
-            }
-            if (chosen_pair >= 0) {
-                for (int b = 0; b < p.batch; ++b) {
-                    if (((max(p.lens_q[b], 0) + kPair - 1) / kPair) > chosen_pair) {
-                        if (rank == 0) {
-                            chosen_seq = b;
-                            break;
-                        }
-                        --rank;
-                    }
-                }
-            }
-            picked[0] = chosen_seq;
-            picked[1] = chosen_pair;
-            *out_of_range = 0;
+            int ranks = 0;
+            for (int t = 0; t < tmax; ++t) ranks += counts[t];
+            *shared_tmax = tmax;
+            *shared_ranks = ranks;
         }
         __syncthreads();
     }
-    const int seq = picked[0];
-    const int pair = picked[1];
-    if (seq < 0 || pair < 0) {
-        return;  // more CTAs were launched than there are query pairs
-    }
-    const int len_q = max(p.lens_q[seq], 0);
-    const int len_kv = max(p.lens_kv[seq], 0);
-    const int offset = p.offsets[seq];
-    const int q0 = pair * kPair;  // sequence-local index of the CTA's first query
-    const int kv_head = head / (p.heads / p.kv_heads);
-    if (offset < 0 || offset + len_q > p.total_q || offset + len_kv > p.total_kv) {
-        if (tid == 0 && !SAFE) report_status(p.error, kStatusIndexOutOfBounds);
-        return;
-    }
-    // The first launch marks a CTA it could not finish in range by a NaN in the LSE of the CTA's first row.
-    float *mark = p.lse + (static_cast<size_t>(offset) + q0) * p.heads + head;
-    if (SAFE && !isnan(*mark)) {
-        return;
-    }
-    // key tiles each query tile needs (0 when the tile has no real row or sees no key)
-    int tiles_needed[2];
-#pragma unroll
-    for (int x = 0; x < 2; ++x) {
-        const int first = q0 + x * kTile;
-        const int real = min(max(len_q - first, 0), kTile);
-        int visible = real > 0 ? len_kv : 0;
-        if (p.causal && real > 0) visible = min(visible, first + real);
-        tiles_needed[x] = (visible + kTile - 1) / kTile;
-    }
-    const int key_tiles = max(tiles_needed[0], tiles_needed[1]);
-
-    if (key_tiles == 0) {
-        // No key is visible to any row: zeros and LSE -1e20.
-        if (warp < 8) {
-            const int row = q0 + (warp >> 2) * kTile + (warp & 3) * 32 + lane;
-            if (row < len_q) {
-                const size_t token = static_cast<size_t>(offset) + row;
-                uint4 *dst = reinterpret_cast<uint4 *>(p.out + (token * p.heads + head) * kHeadDim);
-#pragma unroll
-                for (int i = 0; i < kHeadDim / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-                p.lse[token * p.heads + head] = -1.0e20f;
-            }
-        }
-        return;
+    const int tmax = *shared_tmax;
+    const long long total_items = static_cast<long long>(*shared_ranks) * p.heads;
+    // index of this CTA's item number `round`, or -1 when the CTA is done
+    auto item_index = [&](int round) -> int {
+        if (SAFE) return (round == 0 && blockIdx.x < total_items) ? static_cast<int>(blockIdx.x) : -1;
+        const long long first = static_cast<long long>(round) * gridDim.x;
+        const long long index = first + ((round & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
+        return index < total_items ? static_cast<int>(index) : -1;
+    };
+    if (SAFE) {
+        // The first launch leaves a NaN as the LSE of every row it could not finish in range.
+        const int index = item_index(0);
+        if (index < 0) return;
+        const Item item = decode_item(p, counts, tmax, index, lane);
+        if (!item.valid || item.key_tiles == 0) return;
+        const int row = item.q0 + tid;
+        const bool marked = tid < kPair && row < item.len_q &&
+                            isnan(p.lse[(static_cast<size_t>(item.offset) + row) * p.heads + item.head]);
+        if (__syncthreads_or(marked ? 1 : 0) == 0) return;
     }
 
     if (tid == 0) {
-        for (int i = 0; i < 15; ++i) {
-            // p_full[2] take one arrival per softmax warp of the tile
-            const bool by_warps = i == 11 || i == 12;
+        for (int i = 0; i < kBarriers; ++i) {
+            const bool by_warps = i == 14 || i == 15 || i == 18 || i == 19;  // p_full[2], o_empty[2]
             mbar_init(bars + 8 * i, by_warps ? 4 : 1);
         }
         mbar_init_fence();
     }
     if (warp == 8) {
-        tmem_alloc(tmem_holder, 512);
+        tmem_alloc(words, 512);
         tmem_relinquish();
     }
     tcgen05_fence_before();
@@ -340,41 +382,59 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             prefetch_tensor_map(&q_map);
             prefetch_tensor_map(&k_map);
             prefetch_tensor_map(&v_map);
-            mbar_expect_tx(bar_q_full, 2 * kTileBytes);
+        }
+        int g = 0;                // key tiles loaded so far, over all items: stage g & 1, use (g >> 1)
+        int q_loads[2] = {0, 0};  // Q tiles loaded so far
+        auto wait_lane0 = [&](uint32_t bar, uint32_t parity) -> bool {
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(bar, parity) ? 1 : 0;
+            return __shfl_sync(0xffffffffu, ok, 0) != 0;
+        };
+        for (int round = 0; !failed; ++round) {
+            const int index = item_index(round);
+            if (index < 0) break;
+            const Item item = decode_item(p, counts, tmax, index, lane);
+            if (item.key_tiles == 0) continue;
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
-                tma_load_3d(q_smem + x * kTileBytes, &q_map, bar_q_full, 0, head, offset + q0 + x * kTile);
-                tma_load_3d(q_smem + x * kTileBytes + kHalfTileBytes, &q_map, bar_q_full, 64, head,
-                            offset + q0 + x * kTile);
+                if (item.tiles[x] == 0 || failed) continue;
+                // the tile's buffer is free when the previous item's last Q K^T of this tile has retired
+                if (q_loads[x] > 0 && !wait_lane0(bar_q_empty + x * 8, (q_loads[x] - 1) & 1)) {
+                    failed = true;
+                    continue;
+                }
+                ++q_loads[x];
+                if (lane == 0) {
+                    mbar_expect_tx(bar_q_full + x * 8, kTileBytes);
+                    const int row0 = item.offset + item.q0 + x * kTile;
+                    tma_load_3d(q_smem + x * kTileBytes, &q_map, bar_q_full + x * 8, 0, item.head, row0);
+                    tma_load_3d(q_smem + x * kTileBytes + kHalfTileBytes, &q_map, bar_q_full + x * 8, 64, item.head,
+                                row0);
+                }
             }
-        }
-        for (int j = 0; j < key_tiles; ++j) {
-            const int stage = j & 1;
-            const int row0 = offset + j * kTile;
-            int ok = 1;
-            if (lane == 0 && j >= 2) ok = mbar_wait(bar_k_empty + stage * 8, ((j >> 1) - 1) & 1) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) {
-                failed = true;
-                break;
-            }
-            if (lane == 0) {
-                mbar_expect_tx(bar_k_full + stage * 8, kTileBytes);
-                tma_load_3d(k_smem + stage * kTileBytes, &k_map, bar_k_full + stage * 8, 0, kv_head, row0);
-                tma_load_3d(k_smem + stage * kTileBytes + kHalfTileBytes, &k_map, bar_k_full + stage * 8, 64, kv_head,
-                            row0);
-            }
-            if (lane == 0 && j >= 2) ok = mbar_wait(bar_v_empty + stage * 8, ((j >> 1) - 1) & 1) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) {
-                failed = true;
-                break;
-            }
-            if (lane == 0) {
-                mbar_expect_tx(bar_v_full + stage * 8, kTileBytes);
-                tma_load_3d(v_smem + stage * kTileBytes, &v_map, bar_v_full + stage * 8, 0, kv_head, row0);
-                tma_load_3d(v_smem + stage * kTileBytes + kHalfTileBytes, &v_map, bar_v_full + stage * 8, 64, kv_head,
-                            row0);
+            for (int j = 0; j < item.key_tiles && !failed; ++j, ++g) {
+                const int stage = g & 1;
+                const int row0 = item.offset + j * kTile;
+                if (g >= 2 && !wait_lane0(bar_k_empty + stage * 8, ((g >> 1) - 1) & 1)) {
+                    failed = true;
+                    break;
+                }
+                if (lane == 0) {
+                    mbar_expect_tx(bar_k_full + stage * 8, kTileBytes);
+                    tma_load_3d(k_smem + stage * kTileBytes, &k_map, bar_k_full + stage * 8, 0, item.kv_head, row0);
+                    tma_load_3d(k_smem + stage * kTileBytes + kHalfTileBytes, &k_map, bar_k_full + stage * 8, 64,
+                                item.kv_head, row0);
+                }
+                if (g >= 2 && !wait_lane0(bar_v_empty + stage * 8, ((g >> 1) - 1) & 1)) {
+                    failed = true;
+                    break;
+                }
+                if (lane == 0) {
+                    mbar_expect_tx(bar_v_full + stage * 8, kTileBytes);
+                    tma_load_3d(v_smem + stage * kTileBytes, &v_map, bar_v_full + stage * 8, 0, item.kv_head, row0);
+                    tma_load_3d(v_smem + stage * kTileBytes + kHalfTileBytes, &v_map, bar_v_full + stage * 8, 64,
+                                item.kv_head, row0);
+                }
             }
         }
     } else if (warp == 8) {
@@ -384,8 +444,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {
             return __all_sync(0xffffffffu, mbar_wait(bar, parity) ? 1 : 0) != 0;
         };
-        // S_x = Q_x K(stage)^T
-        auto issue_qk = [&](int x, int stage) {
+        // S_x = Q_x K(stage)^T; `last` releases the Q tile
+        auto issue_qk = [&](int x, int stage, bool last) {
             if (lane == 0) {
                 const uint32_t q_tile = q_smem + x * kTileBytes;
                 const uint32_t k_tile = k_smem + stage * kTileBytes;
@@ -396,6 +456,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                             make_smem_desc(k_tile + within, 16, 1024), kIdescQK, ks > 0 ? 1u : 0u);
                 }
                 tcgen05_commit(bar_s_full + x * 8);
+                if (last) tcgen05_commit(bar_q_empty + x * 8);
             }
             __syncwarp();
         };
@@ -414,154 +475,227 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             }
             __syncwarp();
         };
-        if (!wait_all(bar_q_full, 0) || !wait_all(bar_k_full, 0)) failed = true;
-        if (!failed) {
+        int g = 0;                 // key tiles consumed so far, over all items
+        int q_uses[2] = {0, 0};    // Q tiles consumed so far
+        int p_uses[2] = {0, 0};    // P tiles consumed so far
+        int o_done[2] = {0, 0};    // outputs handed to the epilogue so far
+        int round = 0;
+        // the next item with work, or key_tiles == 0 when there is none
+        auto next_item = [&]() -> Item {
+            Item item;
+            item.key_tiles = 0;
+            for (;;) {
+                const int index = item_index(round);
+                if (index < 0) {
+                    item.key_tiles = 0;
+                    return item;
+                }
+                ++round;
+                item = decode_item(p, counts, tmax, index, lane);
+                if (item.key_tiles > 0) return item;
+            }
+        };
+        // first Q K^T of both tiles of `item` on key stage `stage` (already waited for)
+        auto first_qk = [&](const Item &item, int x, int stage) -> bool {
+            if (item.tiles[x] == 0) return true;
+            if (!wait_all(bar_q_full + x * 8, q_uses[x] & 1)) return false;
+            ++q_uses[x];
             tcgen05_fence_after();
-            if (tiles_needed[0] > 0) issue_qk(0, 0);
-            if (tiles_needed[1] > 0) issue_qk(1, 0);
-            if (lane == 0) tcgen05_commit(bar_k_empty);
-            __syncwarp();
-        }
-        for (int j = 0; j < key_tiles && !failed; ++j) {
-            const int stage = j & 1;
-            const int next = (j + 1) & 1;
-            const bool more = j + 1 < key_tiles;
-            if (!wait_all(bar_v_full + stage * 8, (j >> 1) & 1)) {
-                failed = true;
-                break;
-            }
-            if (j < tiles_needed[0]) {
-                if (!wait_all(bar_p_full, j & 1)) {
-                    failed = true;
-                    break;
-                }
-                tcgen05_fence_after();
-                issue_pv(0, stage, j > 0, j == tiles_needed[0] - 1);
-            }
-            if (more) {
-                if (!wait_all(bar_k_full + next * 8, ((j + 1) >> 1) & 1)) {
-                    failed = true;
-                    break;
-                }
-                tcgen05_fence_after();
-                if (j + 1 < tiles_needed[0]) issue_qk(0, next);
-            }
-            if (j < tiles_needed[1]) {
-                if (!wait_all(bar_p_full + 8, j & 1)) {
-                    failed = true;
-                    break;
-                }
-                tcgen05_fence_after();
-                issue_pv(1, stage, j > 0, j == tiles_needed[1] - 1);
-            }
-            if (lane == 0) tcgen05_commit(bar_v_empty + stage * 8);
-            __syncwarp();
-            if (more) {
-                if (j + 1 < tiles_needed[1]) issue_qk(1, next);
-                if (lane == 0) tcgen05_commit(bar_k_empty + next * 8);
+            issue_qk(x, stage, item.tiles[x] == 1);
+            return true;
+        };
+        Item item = next_item();
+        if (item.key_tiles > 0) {
+            if (!wait_all(bar_k_full, 0)) failed = true;
+            if (!failed && (!first_qk(item, 0, 0) || !first_qk(item, 1, 0))) failed = true;
+            if (!failed) {
+                if (lane == 0) tcgen05_commit(bar_k_empty);
                 __syncwarp();
             }
+        }
+        while (item.key_tiles > 0 && !failed) {
+            const Item following = next_item();
+            for (int j = 0; j < item.key_tiles && !failed; ++j, ++g) {
+                const int stage = g & 1;
+                const int next = (g + 1) & 1;
+                const bool more = j + 1 < item.key_tiles;          // this item has another key tile
+                const bool onward = more || following.key_tiles > 0;  // some Q K^T follows on key tile g + 1
+                if (!wait_all(bar_v_full + stage * 8, (g >> 1) & 1)) {
+                    failed = true;
+                    break;
+                }
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    if (failed) continue;
+                    if (j < item.tiles[x]) {
+                        // the previous item's epilogue must have taken O out of tensor memory
+                        if (j == 0 && o_done[x] > 0 && !wait_all(bar_o_empty + x * 8, (o_done[x] - 1) & 1)) {
+                            failed = true;
+                            continue;
+                        }
+                        if (!wait_all(bar_p_full + x * 8, p_uses[x] & 1)) {
+                            failed = true;
+                            continue;
+                        }
+                        ++p_uses[x];
+                        tcgen05_fence_after();
+                        const bool last = j == item.tiles[x] - 1;
+                        issue_pv(x, stage, j > 0, last);
+                        if (last) ++o_done[x];
+                    }
+                    if (x == 1) {
+                        if (lane == 0) tcgen05_commit(bar_v_empty + stage * 8);
+                        __syncwarp();
+                    }
+                    if (onward) {
+                        if (x == 0) {
+                            if (!wait_all(bar_k_full + next * 8, ((g + 1) >> 1) & 1)) {
+                                failed = true;
+                                continue;
+                            }
+                            tcgen05_fence_after();
+                        }
+                        if (more) {
+                            if (j + 1 < item.tiles[x]) issue_qk(x, next, j + 2 == item.tiles[x]);
+                        } else if (!first_qk(following, x, next)) {
+                            failed = true;
+                            continue;
+                        }
+                        if (x == 1) {
+                            if (lane == 0) tcgen05_commit(bar_k_empty + next * 8);
+                            __syncwarp();
+                        }
+                    }
+                }
+            }
+            item = following;
         }
     } else {
         // ---------------- softmax / correction / epilogue: warps 0-3 tile A, warps 4-7 tile B ----------------
         const int x = warp >> 2;
-        const int my_tiles = x == 0 ? tiles_needed[0] : tiles_needed[1];
         const int quarter = warp & 3;                  // tensor-memory lanes 32*quarter .. +31
         const int local_row = quarter * 32 + lane;
-        const int row = q0 + x * kTile + local_row;    // sequence-local query index
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t tmem_s = tmem_base + x * kTile + lane_base;
         const uint32_t tmem_o = tmem_base + 2 * kTile + x * kHeadDim + lane_base;
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
         const float sign = p.scale_log2 < 0.0f ? -1.0f : 1.0f;
-        float base_log2 = -INFINITY;  // what P, O and the row sum are relative to (log2 units); finite after tile 0
-        float row_sum = 0.0f;
-        bool in_range = true;
-        for (int j = 0; j < my_tiles && !failed; ++j) {
-            if (!__all_sync(0xffffffffu, mbar_wait(bar_s_full + x * 8, j & 1) ? 1 : 0)) {
+        int s_uses = 0;   // score tiles consumed so far, over all items
+        int o_uses = 0;   // outputs taken so far
+        for (int round = 0; !failed; ++round) {
+            const int index = item_index(round);
+            if (index < 0) break;
+            const Item item = decode_item(p, counts, tmax, index, lane);
+            if (!item.valid) {
+                if (warp == 0 && lane == 0) report_status(p.error, kStatusIndexOutOfBounds);
+                continue;
+            }
+            const int row = item.q0 + x * kTile + local_row;    // sequence-local query index
+            const bool real = row < item.len_q;
+            const size_t token = static_cast<size_t>(item.offset) + (real ? row : 0);
+            __nv_bfloat16 *dst = p.out + (token * p.heads + item.head) * kHeadDim;
+            const int my_tiles = x == 0 ? item.tiles[0] : item.tiles[1];
+            if (my_tiles == 0) {
+                // No key is visible to this tile's rows: zeros and LSE -1e20.
+                if (real) {
+#pragma unroll
+                    for (int i = 0; i < kHeadDim / 8; ++i) reinterpret_cast<uint4 *>(dst)[i] = make_uint4(0u, 0u, 0u, 0u);
+                    p.lse[token * p.heads + item.head] = -1.0e20f;
+                }
+                continue;
+            }
+            float base_log2 = -INFINITY;  // what P, O and the row sum are relative to (log2 units); finite after tile 0
+            float row_sum = 0.0f;
+            bool in_range = true;
+            for (int j = 0; j < my_tiles && !failed; ++j, ++s_uses) {
+                if (!__all_sync(0xffffffffu, mbar_wait(bar_s_full + x * 8, s_uses & 1) ? 1 : 0)) {
+                    failed = true;
+                    break;
+                }
+                tcgen05_fence_after();  // S(j) is ready, and with it every earlier MMA of this tile: O holds P V up to j-1
+                // number of keys of this key tile the row may see
+                int limit = item.len_kv - j * kTile;
+                if (p.causal) limit = min(limit, row + 1 - j * kTile);
+                limit = real ? limit : 0;
+                const bool partial = __any_sync(0xffffffffu, limit < kTile);
+
+                if (SAFE || j == 0) {
+                    float wanted = (partial || sign < 0.0f) ? tile_max<true>(tmem_s, limit, sign)
+                                                            : tile_max<false>(tmem_s, limit, sign);
+                    wanted = fmaxf(base_log2, wanted * fabsf(p.scale_log2));
+                    wanted = wanted == -INFINITY ? 0.0f : wanted;  // nothing visible yet: any base will do
+                    // Re-base O only when some row's max grew past the threshold; then every row of the warp does.
+                    const bool grow = wanted > base_log2 + kRescaleThreshold;
+                    if (__any_sync(0xffffffffu, grow)) {
+                        if (j > 0) {
+                            const float factor = exp2_approx(base_log2 - wanted);
+                            row_sum *= factor;
+                            scale_o_row(tmem_o, factor);
+                        }
+                        base_log2 = wanted;
+                    }
+                } else if (__any_sync(0xffffffffu, row_sum > kRebaseLimit)) {
+                    // Single-pass tiles: pull the row back by the exponent of its sum, an exact power of two.
+                    const int exponent = row_sum > kRebaseLimit ? ((__float_as_int(row_sum) >> 23) & 0xff) - 127 : 0;
+                    const float factor = __int_as_float((127 - exponent) << 23);
+                    row_sum *= factor;
+                    base_log2 += static_cast<float>(exponent);
+                    scale_o_row(tmem_o, factor);
+                }
+                const float2 bias2 = make_float2(-base_log2, -base_log2);
+                float2 sum[2] = {make_float2(row_sum, 0.0f), make_float2(0.0f, 0.0f)};
+                if (partial) {
+                    tile_exp<true>(tmem_s, scale2, bias2, limit, sum);
+                } else {
+                    tile_exp<false>(tmem_s, scale2, bias2, limit, sum);
+                }
+                row_sum = (sum[0].x + sum[0].y) + (sum[1].x + sum[1].y);
+                tmem_wait_st();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar_p_full + x * 8);
+                }
+                in_range = in_range && row_sum < kOverflowLimit;  // false for inf and NaN too
+            }
+            if (failed) break;
+            // ---- epilogue: O / sum -> bf16, LSE ----
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_o_full + x * 8, o_uses & 1) ? 1 : 0)) {
                 failed = true;
                 break;
             }
-            tcgen05_fence_after();  // S(j) is ready, and with it every earlier MMA of this tile: O holds P V up to j-1
-            // number of keys of this key tile the row may see
-            int limit = len_kv - j * kTile;
-            if (p.causal) limit = min(limit, row + 1 - j * kTile);
-            limit = row < len_q ? limit : 0;
-            const bool partial = __any_sync(0xffffffffu, limit < kTile);
-
-            if (SAFE || j == 0) {
-                float wanted = (partial || sign < 0.0f) ? tile_max<true>(tmem_s, limit, sign)
-                                                        : tile_max<false>(tmem_s, limit, sign);
-                wanted = fmaxf(base_log2, wanted * fabsf(p.scale_log2));
-                wanted = wanted == -INFINITY ? 0.0f : wanted;  // nothing visible yet: any base will do
-                // Re-base O only when some row's max grew past the threshold; then every row of the warp does.
-                const bool grow = wanted > base_log2 + kRescaleThreshold;
-                if (__any_sync(0xffffffffu, grow)) {
-                    if (j > 0) {
-                        const float factor = exp2_approx(base_log2 - wanted);
-                        row_sum *= factor;
-                        scale_o_row(tmem_o, factor);
-                    }
-                    base_log2 = wanted;
-                }
-            } else if (__any_sync(0xffffffffu, row_sum > kRebaseLimit)) {
-                // Single-pass tiles: pull the row back by the exponent of its sum, an exact power of two.
-                const int exponent = row_sum > kRebaseLimit ? ((__float_as_int(row_sum) >> 23) & 0xff) - 127 : 0;
-                const float factor = __int_as_float((127 - exponent) << 23);
-                row_sum *= factor;
-                base_log2 += static_cast<float>(exponent);
-                scale_o_row(tmem_o, factor);
-            }
-            const float2 bias2 = make_float2(-base_log2, -base_log2);
-            float2 sum[2] = {make_float2(row_sum, 0.0f), make_float2(0.0f, 0.0f)};
-            if (partial) {
-                tile_exp<true>(tmem_s, scale2, bias2, limit, sum);
-            } else {
-                tile_exp<false>(tmem_s, scale2, bias2, limit, sum);
-            }
-            row_sum = (sum[0].x + sum[0].y) + (sum[1].x + sum[1].y);
-            tmem_wait_st();
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar_p_full + x * 8);
-            }
-            in_range = in_range && row_sum < kOverflowLimit;  // false for inf and NaN too
-        }
-        if (!SAFE && !in_range) *out_of_range = 1;
-        // ---- epilogue: O / sum -> bf16, LSE ----
-        if (my_tiles > 0 && !failed) {
-            if (!__all_sync(0xffffffffu, mbar_wait(bar_o_full + x * 8, 0) ? 1 : 0)) {
-                failed = true;
-            } else {
-                tcgen05_fence_after();
-                const bool real = row < len_q;
-                const bool empty = row_sum == 0.0f;
-                const float inverse = empty ? 0.0f : 1.0f / row_sum;
-                const size_t token = static_cast<size_t>(offset) + (real ? row : 0);
-                __nv_bfloat16 *dst = p.out + (token * p.heads + head) * kHeadDim;
+            ++o_uses;
+            tcgen05_fence_after();
+            const bool empty = row_sum == 0.0f;
+            const float inverse = empty ? 0.0f : 1.0f / row_sum;
 #pragma unroll 1
-                for (int c = 0; c < kHeadDim; c += 32) {
-                    uint32_t r[32];
-                    tmem_ld_x32(tmem_o + c, r);
-                    tmem_wait_ld_into(r);
-                    if (real) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 word;
-                            word.x = pack2<__nv_bfloat16>(__uint_as_float(r[i]) * inverse, __uint_as_float(r[i + 1]) * inverse);
-                            word.y = pack2<__nv_bfloat16>(__uint_as_float(r[i + 2]) * inverse, __uint_as_float(r[i + 3]) * inverse);
-                            word.z = pack2<__nv_bfloat16>(__uint_as_float(r[i + 4]) * inverse, __uint_as_float(r[i + 5]) * inverse);
-                            word.w = pack2<__nv_bfloat16>(__uint_as_float(r[i + 6]) * inverse, __uint_as_float(r[i + 7]) * inverse);
-                            if (empty) word = make_uint4(0u, 0u, 0u, 0u);
-                            *reinterpret_cast<uint4 *>(dst + c + i) = word;
-                        }
-                    }
+            for (int c = 0; c < kHeadDim; c += 32) {
+                uint32_t r[32];
+                tmem_ld_x32(tmem_o + c, r);
+                tmem_wait_ld_into(r);
+                if (c + 32 == kHeadDim) {
+                    // O is out of tensor memory: the next item's first P V may overwrite it
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_o_empty + x * 8);
                 }
                 if (real) {
-                    p.lse[token * p.heads + head] =
-                        empty ? -1.0e20f : (base_log2 + log2f(row_sum)) * 0.6931471805599453f;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 word;
+                        word.x = pack2<__nv_bfloat16>(__uint_as_float(r[i]) * inverse, __uint_as_float(r[i + 1]) * inverse);
+                        word.y = pack2<__nv_bfloat16>(__uint_as_float(r[i + 2]) * inverse, __uint_as_float(r[i + 3]) * inverse);
+                        word.z = pack2<__nv_bfloat16>(__uint_as_float(r[i + 4]) * inverse, __uint_as_float(r[i + 5]) * inverse);
+                        word.w = pack2<__nv_bfloat16>(__uint_as_float(r[i + 6]) * inverse, __uint_as_float(r[i + 7]) * inverse);
+                        if (empty) word = make_uint4(0u, 0u, 0u, 0u);
+                        *reinterpret_cast<uint4 *>(dst + c + i) = word;
+                    }
                 }
+            }
+            if (real) {
+                float value = empty ? -1.0e20f : (base_log2 + log2f(row_sum)) * 0.6931471805599453f;
+                if (!SAFE && !in_range) value = __int_as_float(0x7fc00000);  // has the second launch redo the item
+                p.lse[token * p.heads + item.head] = value;
             }
         }
     }
@@ -574,18 +708,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
-    if (!SAFE && tid == 0 && *out_of_range != 0) {
-        *mark = __int_as_float(0x7fc00000);  // after this thread's own LSE store for the same row
-    }
 }
 
-constexpr int kPrefillSmem = 6 * kTileBytes + 160 + kMaxRankTiles * 4 + 1024;
+constexpr int kPrefillSmem = 6 * kTileBytes + 8 * 20 + 32 + kMaxRankTiles * 4 + 1024;
 
 }  // namespace
 
 bool prefill_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t total_query_tokens, const void *query,
                        const void *key, const void *value, const void *out) {
-    // The heaviest-first dispatch table holds kMaxRankTiles query pairs per sequence.
+    // The heaviest-first item table holds kMaxRankTiles query pairs per sequence.
     if (total_query_tokens / kPair + 1 > kMaxRankTiles) return false;
     const uintptr_t all = reinterpret_cast<uintptr_t>(query) | reinterpret_cast<uintptr_t>(key) |
                           reinterpret_cast<uintptr_t>(value) | reinterpret_cast<uintptr_t>(out);
@@ -601,6 +732,9 @@ int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void 
                                         kPrefillSmem));
     SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kPrefillSmem));
+    int device = 0, sms = 0;
+    SINGE_CUDA_TRY(cudaGetDevice(&device));
+    SINGE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     CUtensorMap q_map, k_map, v_map;
     const uint32_t box[3] = {64, 1, kTile};
     {
@@ -631,14 +765,16 @@ int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void 
     params.causal = causal ? 1 : 0;
     params.scale_log2 = scale * 1.4426950408889634f;
     params.error = device_error_word();
-    // Upper bound on 256-row query pairs: every sequence can add one partial pair.
-    const size_t pairs = total_query_tokens / kPair + batch;
-    if (pairs > 0x7fffffffull) return SINGE_ERR_LENGTH_EXCEEDS_I32;
-    dim3 grid(static_cast<unsigned>(pairs), static_cast<unsigned>(heads));
-    prefill_tcgen05_kernel<false><<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
+    // Upper bound on the items: every sequence can add one partial 256-row pair.
+    const size_t items = (total_query_tokens / kPair + batch) * heads;
+    if (items > 0x7fffffffull) return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    if (items == 0) return SINGE_OK;
+    const unsigned persistent = static_cast<unsigned>(items < static_cast<size_t>(sms) ? items : sms);
+    prefill_tcgen05_kernel<false><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
     SINGE_TRY(launch_status());
-    // Redo pass: CTAs the first launch did not mark leave after one load.
-    prefill_tcgen05_kernel<true><<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
+    // Redo pass, one CTA per item: CTAs of items the first launch did not mark leave after one look.
+    prefill_tcgen05_kernel<true><<<static_cast<unsigned>(items), kPrefillThreads, kPrefillSmem, stream>>>(
+        q_map, k_map, v_map, params);
     return launch_status();
 }
 

@@ -19,8 +19,6 @@
 //              log2(sum)).  The first key tile takes the exact row maximum as base (a two-pass tile); afterwards
 //              the row is re-based by an exact power of two whenever its running sum passes 2^16 (O in tensor
 //              memory and the sum are scaled, at the start of the next tile, when the previous P V has retired).
-//              One exponential in eight is evaluated as a polynomial on the FMA pipe to unload the
-//              special-function unit.
 //              A row whose scores jump by more than ~2^64 from one key tile to the next would overflow this
 //              scheme.  The CTA then marks itself (a NaN in the LSE of its first row) and the second launch of
 //              the same kernel in SAFE mode, where every tile takes its exact row maximum first, recomputes
@@ -51,10 +49,6 @@ constexpr int kHeadDim = 128;
 constexpr int kHalfTileBytes = kTile * 128;       // one TMA box: 128 rows x 128 bytes
 constexpr int kTileBytes = 2 * kHalfTileBytes;    // 32 KB
 constexpr int kMaxRankTiles = 1024;               // heaviest-first dispatch: sequences up to 256 Ki tokens
-#ifndef SINGE_PREFILL_POLY_PAIRS
-#define SINGE_PREFILL_POLY_PAIRS 0x08
-#endif
-constexpr unsigned kPolyPairs = SINGE_PREFILL_POLY_PAIRS;  // which of every eight f32x2 pairs use the polynomial exp2
 constexpr float kRescaleThreshold = 8.0f;         // two-pass tiles: re-base when the max grew by 2^8 (log2 units)
 constexpr float kRebaseLimit = 65536.0f;          // single-pass tiles: re-base a row when its sum passes 2^16
 constexpr float kOverflowLimit = 1.8446744e19f;   // 2^64: beyond this the CTA is redone in SAFE mode
@@ -87,24 +81,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-// 2^x for two values on the FMA pipe with packed f32x2 arithmetic: x = r + f with r the nearest integer and f in
-// [-0.5, 0.5]; 2^f by a cubic (relative error 7.6e-5, a fiftieth of a bf16 ulp), 2^r by adding r to the exponent
-// field.
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-    x.x = fmaxf(x.x, -120.0f);
-    x.y = fmaxf(x.y, -120.0f);
-    const float2 magic = make_float2(12582912.0f, 12582912.0f);  // 1.5 * 2^23: the low mantissa bits then hold r
-    const float2 shifted = __fadd2_rn(x, magic);
-    const float2 r = __fadd2_rn(shifted, make_float2(-12582912.0f, -12582912.0f));
-    const float2 f = __ffma2_rn(r, make_float2(-1.0f, -1.0f), x);
-    float2 p = __ffma2_rn(f, make_float2(0.05520551f, 0.05520551f), make_float2(0.24261396f, 0.24261396f));
-    p = __ffma2_rn(p, f, make_float2(0.69325476f, 0.69325476f));
-    p = __ffma2_rn(p, f, make_float2(0.99992773f, 0.99992773f));
-    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(shifted.x) << 23));
-    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(shifted.y) << 23));
-    return p;
-}
-
 // Folds the 32 raw scores of one chunk into four running maxima (independent chains).  MASKED handles tiles where
 // some keys are hidden (the diagonal tile and a sequence's last tile) and a negative scale; `limit` counts the
 // visible columns from the chunk's first.
@@ -131,7 +107,8 @@ __device__ __forceinline__ void chunk_max(const uint32_t (&sc)[kChunk], int limi
 
 // P = exp2(s * scale + bias) for one chunk of 32 scores: the bf16 pairs go back to tensor memory (16 packed
 // columns at `tmem_p`), the unrounded values are added to two running f32x2 sums.  Scores are handled as f32x2
-// pairs; pair 3 of every eight takes its exponentials from the polynomial.
+// pairs.  (Evaluating part of the exponentials as a polynomial on the FMA pipe was measured slower at every ratio:
+// with one softmax warp per scheduler the extra instructions cost more than the special-function unit saves.)
 template <bool MASKED>
 __device__ __forceinline__ void chunk_exp_store(const uint32_t (&sc)[kChunk], uint32_t tmem_p, float2 scale2,
                                                 float2 bias2, int limit, float2 (&sum)[2]) {
@@ -140,12 +117,8 @@ __device__ __forceinline__ void chunk_exp_store(const uint32_t (&sc)[kChunk], ui
     for (int i = 0; i < kChunk; i += 2) {
         const float2 x = __ffma2_rn(make_float2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])), scale2, bias2);
         float2 e;
-        if ((kPolyPairs >> ((i >> 1) & 7)) & 1) {
-            e = exp2_poly2(x);
-        } else {
-            e.x = exp2_approx(x.x);
-            e.y = exp2_approx(x.y);
-        }
+        e.x = exp2_approx(x.x);
+        e.y = exp2_approx(x.y);
         if (MASKED) {
             e.x = (i < limit) ? e.x : 0.0f;
             e.y = (i + 1 < limit) ? e.y : 0.0f;

@@ -157,6 +157,11 @@ def sum_over_ranks(value: float, group) -> float:
 # headline: config 2 paged decode
 # ----------------------------------------------------------------------------------------------------------
 
+# DRAM bytes one launch of paged_decode_kernel moves on the config-2 workload (seed 1), from the ncu capture summarised
+# in profiles/paged_decode_kernel_config2.md: 277.40 MB read + 8.50 MB written (the split-K partials).
+DECODE_DRAM_TRAFFIC = 285_900_000
+
+
 def decode_device_inputs(case, seed: int):
     import torch
 
@@ -281,7 +286,10 @@ def run_decode(args, rank, world, group):
         "gpu_launches": 2 * args.steps,
         "clocks": sampler.summary(),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": DECODE_DRAM_TRAFFIC,
+                     "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum of "
+                                     "paged_decode_kernel on this workload, profiles/paged_decode_kernel_config2.md)",
+                     "algorithmic_bytes": int(my_bytes),
                      "peak_source": peaks["source"], "launch_us": round(launch_seconds * 1e6, 2),
                      "kernels": "paged_decode_kernel + decode_combine_kernel"},
     }

@@ -500,7 +500,7 @@ def main():
     rank, local, world, group = dist_setup(args.gpus)
     line, case = run_decode(args, rank, world, group)
     decode_step = None
-    if not args.no_also and not args.no_decode_step:
+    if not args.no_decode_step:
         try:
             decode_step = run_decode_step(rank, world, group)
         except Exception as error:
@@ -511,6 +511,7 @@ def main():
             cpu_value, cpu_seconds = cpu_baseline_decode(case, threads)
             line["cpu_baseline"] = {"value": round(cpu_value, 3), "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": f"full config-2 batch, best of 2 calls ({cpu_seconds:.2f} s each)"}
+        line["also"] = {}
         if not args.no_also:
             try:
                 from singe_b200 import bench_extra
@@ -518,8 +519,8 @@ def main():
                 line["also"] = bench_extra.run_all(measured_peaks())
             except Exception as error:  # secondary figures never take the headline down
                 line["also"] = {"error": repr(error)}
-            if decode_step is not None:
-                line["also"]["decode_step_config5"] = decode_step
+        if decode_step is not None:
+            line["also"]["decode_step_config5"] = decode_step
         print(json.dumps(line), flush=True)
     if group is not None:
         group.barrier()

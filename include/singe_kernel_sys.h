@@ -364,6 +364,32 @@ int singe_silu_mul_bf16(singe_stream_t stream, void *out, const void *gate, cons
 int singe_argmax_bf16(singe_stream_t stream, float *best_value, int64_t *best_index, const void *logits,
                       size_t row_stride, size_t rows, size_t width, int64_t index_offset);
 
+/* ---- tensor-parallel all-reduce over NVLink peer memory, fused with residual add + RMSNorm ----
+ * Replaces, for the decode step's two collectives per layer: Communicator::all_reduce_in_place with
+ * ReductionOperator::Sum (singe-nccl/src/communicator/operations/collectives.rs:99-134) followed by the residual
+ * add and the next RMSNorm of the pre-norm block (singe-model/src/assembly/decoder.rs:102-126).
+ *
+ * Peer buffers are plain device allocations shared between the ranks' processes through CUDA IPC handles
+ * (SINGE_PEER_HANDLE_BYTES opaque bytes, exchanged by the host's own means, e.g. the NCCL bootstrap store). */
+#define SINGE_PEER_HANDLE_BYTES 64
+int singe_peer_buffer_create(size_t bytes, void **pointer, void *handle_out); /* zero-filled */
+int singe_peer_buffer_open(const void *handle_in, void **pointer);            /* another rank's buffer */
+int singe_peer_buffer_close(void *pointer);                                   /* what _open returned */
+int singe_peer_buffer_destroy(void *pointer);                                 /* what _create returned */
+
+/* hidden[rows, width] += bf16(sum over ranks of partials[r][rows, width]) (f32 sum in rank order, so every rank
+ * gets identical bits), then normed = RMSNorm(hidden) * weight; bf16 throughout, rounding after every op as the
+ * reference's tensor ops do.  partials / flags: HOST arrays of `world` device pointers, entry r being rank r's
+ * partial buffer / flag array (uint32[world], zero at first use) as mapped into this process; entry `rank` is the
+ * local one.  state: local uint32[2], zero at first use.  The call only enqueues; ranks synchronise inside the
+ * kernel through the flag arrays (every wait is bounded: on a timeout *status gets SINGE_STATUS_WAIT_TIMEOUT and
+ * hidden/normed are left unwritten).  The local partial buffer may be rewritten only after a LATER call of this
+ * function (on another partial buffer) has been enqueued behind this one: alternate two buffers. world <= 8,
+ * width % 8 == 0, width <= 8192. */
+int singe_allreduce_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void *normed, const void *weight,
+                                      const void *const *partials, uint32_t *const *flags, uint32_t *state, int rank,
+                                      int world, size_t rows, size_t width, float eps, uint32_t *status);
+
 /* Explicit tile choice for the two GEMM entry points, process-wide: block_n in {32,64,128,256},
  * k_slices_per_stage in {1,2,4,8}; 0 = choose from the problem shape.
  * Replaces: TuningChoice::Explicit(MatmulTuning { tile, .. }) (singe-kernel/src/cuda/matmul.rs:58-77). */

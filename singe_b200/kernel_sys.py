@@ -80,6 +80,11 @@ SIGNATURES = {
                                       _p],
     "singe_silu_mul_bf16": [_p, _p, _p, _p, _z, _z, _z],
     "singe_argmax_bf16": [_p, _p, _p, _p, _z, _z, _z, ctypes.c_int64],
+    "singe_peer_buffer_create": [_z, ctypes.POINTER(ctypes.c_void_p), _p],
+    "singe_peer_buffer_open": [_p, ctypes.POINTER(ctypes.c_void_p)],
+    "singe_peer_buffer_close": [_p],
+    "singe_peer_buffer_destroy": [_p],
+    "singe_allreduce_add_rms_norm_bf16": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _z, _z, _f, _p],
 }
 
 _RESTYPES = {

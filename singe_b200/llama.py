@@ -262,7 +262,8 @@ class LlamaDecoder:
     """One rank of a tensor-parallel Llama decoder: weights, KV caches, page table and the decode step."""
 
     def __init__(self, config: LlamaConfig, sequences: int, capacity: int, shard: Shard | None = None, seed: int = 4,
-                 weights: dict | None = None, shard_lm_head: bool = True, max_splits: int = 0):
+                 weights: dict | None = None, shard_lm_head: bool = True, max_splits: int = 0,
+                 collective: str = "peer"):
         import torch
 
         self.torch = torch
@@ -319,6 +320,15 @@ class LlamaDecoder:
         self.query = torch.empty((t, self.heads, config.head_dim), dtype=bf16, device=dev)
         self.attended = torch.empty((t, self.heads * config.head_dim), dtype=bf16, device=dev)
         self.projected = torch.empty((t, w), dtype=bf16, device=dev)
+        # The two collectives of a layer: "peer" = one kernel per collective that sums the ranks' partial rows out
+        # of peer memory and applies the residual add + RMSNorm that follows; "nccl" = all-reduce, then the norm.
+        if collective not in ("peer", "nccl"):
+            raise ValueError("collective must be 'peer' or 'nccl'")
+        self.peer = None
+        if tp > 1 and collective == "peer":
+            from .peer import PeerAllReduce
+
+            self.peer = PeerAllReduce(self.shard.group, self.shard.rank, tp, t, w)
         self.gate_up = torch.empty((t, 2 * self.ffn), dtype=bf16, device=dev)
         self.activated = torch.empty((t, self.ffn), dtype=bf16, device=dev)
         self.logits = torch.empty((t, self.lm_head.shape[0]), dtype=bf16, device=dev)
@@ -390,6 +400,18 @@ class LlamaDecoder:
         self._check(ks.lib().singe_matmul_bf16_bf16(stream, out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k,
                                                     x.stride(0), weight.stride(0), out.stride(0), 0, 1), "linear")
 
+    def _linear_raw(self, out_pointer: int, out_stride: int, x, weight, stream) -> None:
+        m, k = x.shape
+        n = weight.shape[0]
+        self._check(ks.lib().singe_matmul_bf16_bf16(stream, out_pointer, x.data_ptr(), weight.data_ptr(), m, n, k,
+                                                    x.stride(0), weight.stride(0), out_stride, 0, 1), "linear")
+
+    def close(self) -> None:
+        """Releases the peer-mapped buffers (collective: every rank calls it)."""
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None
+
     def _all_reduce(self, tensor) -> None:
         if self.shard.world > 1:
             self.shard.group.all_reduce(tensor)
@@ -405,10 +427,11 @@ class LlamaDecoder:
         delta = None
         for index, layer in enumerate(self.layers):
             keys, values = self.key_caches[index], self.value_caches[index]
-            self._check(lib.singe_add_rms_norm_bf16(stream, self.hidden.data_ptr(),
-                                                    None if delta is None else delta.data_ptr(),
-                                                    self.normed.data_ptr(), layer["attn_norm"].data_ptr(), t, w,
-                                                    c.eps), "attn norm")
+            if self.peer is None or index == 0:
+                self._check(lib.singe_add_rms_norm_bf16(stream, self.hidden.data_ptr(),
+                                                        None if delta is None else delta.data_ptr(),
+                                                        self.normed.data_ptr(), layer["attn_norm"].data_ptr(), t, w,
+                                                        c.eps), "attn norm")
             self._linear(self.qkv, self.normed, layer["wqkv"], stream)
             self._check(lib.singe_rotary_cache_write_bf16(
                 stream, self.query.data_ptr(), self.qkv.data_ptr(), self.qkv.stride(0), self.cos.data_ptr(),
@@ -426,21 +449,34 @@ class LlamaDecoder:
                     stream, self.attended.data_ptr(), self.query.data_ptr(), keys.data_ptr(), values.data_ptr(),
                     self.d_lens.data_ptr(), self.d_table.data_ptr(), t, self.heads, self.kv_heads, d, c.page_size,
                     keys.shape[0], self.stride, 1.0 / math.sqrt(d)), "decode attention")
-            self._linear(self.projected, self.attended, layer["wo"], stream)
-            self._all_reduce(self.projected)
-            self._check(lib.singe_add_rms_norm_bf16(stream, self.hidden.data_ptr(), self.projected.data_ptr(),
-                                                    self.normed.data_ptr(), layer["mlp_norm"].data_ptr(), t, w,
-                                                    c.eps), "mlp norm")
+            if self.peer is not None:
+                self._linear_raw(self.peer.partial_pointer(0), w, self.attended, layer["wo"], stream)
+                self.peer.reduce_add_norm(stream, 0, self.hidden.data_ptr(), self.normed.data_ptr(),
+                                          layer["mlp_norm"].data_ptr(), c.eps, status)
+            else:
+                self._linear(self.projected, self.attended, layer["wo"], stream)
+                self._all_reduce(self.projected)
+                self._check(lib.singe_add_rms_norm_bf16(stream, self.hidden.data_ptr(), self.projected.data_ptr(),
+                                                        self.normed.data_ptr(), layer["mlp_norm"].data_ptr(), t, w,
+                                                        c.eps), "mlp norm")
             self._linear(self.gate_up, self.normed, layer["w_gate_up"], stream)
             self._check(lib.singe_silu_mul_bf16(stream, self.activated.data_ptr(), self.gate_up.data_ptr(),
                                                 self.gate_up.data_ptr() + self.ffn * 2, self.gate_up.stride(0), t,
                                                 self.ffn), "swiglu")
-            self._linear(self.projected, self.activated, layer["w_down"], stream)
-            self._all_reduce(self.projected)
-            delta = self.projected
-        self._check(lib.singe_add_rms_norm_bf16(stream, self.hidden.data_ptr(), delta.data_ptr(),
-                                                self.normed.data_ptr(), self.final_norm.data_ptr(), t, w, c.eps),
-                    "final norm")
+            if self.peer is not None:
+                # the down_proj collective also applies the norm that opens the next layer (or the final norm)
+                following = self.layers[index + 1]["attn_norm"] if index + 1 < len(self.layers) else self.final_norm
+                self._linear_raw(self.peer.partial_pointer(1), w, self.activated, layer["w_down"], stream)
+                self.peer.reduce_add_norm(stream, 1, self.hidden.data_ptr(), self.normed.data_ptr(),
+                                          following.data_ptr(), c.eps, status)
+            else:
+                self._linear(self.projected, self.activated, layer["w_down"], stream)
+                self._all_reduce(self.projected)
+                delta = self.projected
+        if self.peer is None:
+            self._check(lib.singe_add_rms_norm_bf16(stream, self.hidden.data_ptr(), delta.data_ptr(),
+                                                    self.normed.data_ptr(), self.final_norm.data_ptr(), t, w, c.eps),
+                        "final norm")
         self._linear(self.logits, self.normed, self.lm_head, stream)
         self._check(lib.singe_argmax_bf16(stream, self.best_value.data_ptr(), self.best_index.data_ptr(),
                                           self.logits.data_ptr(), self.logits.stride(0), t, self.logits.shape[1],

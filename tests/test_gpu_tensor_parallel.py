@@ -15,7 +15,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank(rank, world, port, results):
+def _rank(rank, world, port, results, collective):
     import torch.distributed as dist
 
     from singe_b200.llama import LlamaDecoder, Shard
@@ -29,7 +29,8 @@ def _rank(rank, world, port, results):
     config = MEDIUM
     context = [40, 0, 129, 700]
     weights = make_weights(config)
-    decoder = LlamaDecoder(config, len(context), 768, shard=Shard(rank, world, dist), weights=weights)
+    decoder = LlamaDecoder(config, len(context), 768, shard=Shard(rank, world, dist), weights=weights,
+                           collective=collective)
     keys, values = make_context(config, decoder.table.page_count())
     gs = slice(rank * decoder.kv_heads, (rank + 1) * decoder.kv_heads)
     for layer in range(config.layers):
@@ -52,11 +53,107 @@ def _rank(rank, world, port, results):
         results["tokens"] = tokens_out
         results["status"] = int(decoder.status.item())
     dist.barrier()
+    decoder.close()
     dist.destroy_process_group()
 
 
+def _reduce_rank(rank, world, port, results):
+    """The fused peer-memory all-reduce + residual add + RMSNorm against NCCL all-reduce + the separate norm kernel,
+    over several launches (the epoch advances on the device) and through a replayed CUDA graph."""
+    import torch.distributed as dist
+
+    from singe_b200 import kernel_sys as ks
+    from singe_b200.peer import PeerAllReduce
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    lib = ks.lib()
+    rows, width, eps = 64, 4096, 1e-5
+    peer = PeerAllReduce(dist, rank, world, rows, width)
+    generator = torch.Generator(device="cuda").manual_seed(100 + rank)
+    shared = torch.Generator(device="cuda").manual_seed(7)  # the residual stream and the gain are replicated
+    weight = (1.0 + 0.05 * torch.randn(width, generator=shared, device="cuda")).to(torch.bfloat16)
+    hidden = torch.randn((rows, width), generator=shared, device="cuda").to(torch.bfloat16)
+    expect_hidden = hidden.clone()
+    normed = torch.empty_like(hidden)
+    expect_normed = torch.empty_like(hidden)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = int(torch.cuda.current_stream().cuda_stream)
+    worst = 0.0
+    graph = None
+    staged = [torch.empty((rows, width), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    for call in range(8):
+        which = call & 1
+        partial = (0.5 * torch.randn((rows, width), generator=generator, device="cuda")).to(torch.bfloat16)
+        # expected: NCCL sum (two ranks: one exact bf16 addition, whatever the order), then the separate kernel
+        total = partial.clone()
+        dist.all_reduce(total)
+        assert lib.singe_add_rms_norm_bf16(stream, expect_hidden.data_ptr(), total.data_ptr(),
+                                           expect_normed.data_ptr(), weight.data_ptr(), rows, width, eps) == ks.OK
+        staged[which].copy_(partial)
+        if call < 4:
+            # eager: copy the partial rows into the peer buffer (stands for the GEMM), then the fused kernel
+            torch.cuda.current_stream().synchronize()
+            ctypes_copy(peer.partial_pointer(which), staged[which])
+            peer.reduce_add_norm(stream, which, hidden.data_ptr(), normed.data_ptr(), weight.data_ptr(), eps,
+                                 status.data_ptr())
+        else:
+            if graph is None:
+                # one graph = both collectives back to back, as a layer issues them
+                torch.cuda.synchronize()
+                dist.barrier()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    s = int(torch.cuda.current_stream().cuda_stream)
+                    ctypes_copy(peer.partial_pointer(0), staged[0], s)
+                    peer.reduce_add_norm(s, 0, hidden.data_ptr(), normed.data_ptr(), weight.data_ptr(), eps,
+                                         status.data_ptr())
+                    ctypes_copy(peer.partial_pointer(1), staged[1], s)
+                    peer.reduce_add_norm(s, 1, hidden.data_ptr(), normed.data_ptr(), weight.data_ptr(), eps,
+                                         status.data_ptr())
+            if which == 0:
+                continue  # the graph runs on the odd call, when both staged partials are set
+            # redo the expectation for the pair (even call's partial was folded above already)
+            graph.replay()
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert torch.equal(hidden, expect_hidden), f"hidden differs at call {call}"
+        worst = max(worst, float((normed.float() - expect_normed.float()).abs().max()))
+        assert torch.equal(normed, expect_normed), f"normed differs at call {call}"
+    if rank == 0:
+        results["reduce_ok"] = True
+    dist.barrier()
+    peer.close()
+    dist.destroy_process_group()
+
+
+def ctypes_copy(target_pointer, source, stream=None):
+    """Device-to-device copy into a raw pointer (the peer buffers are not torch tensors)."""
+    from cuda.bindings import runtime as cudart
+
+    if stream is None:
+        stream = int(torch.cuda.current_stream().cuda_stream)
+    (error,) = cudart.cudaMemcpyAsync(target_pointer, source.data_ptr(), source.numel() * source.element_size(),
+                                      cudart.cudaMemcpyKind.cudaMemcpyDeviceToDevice, stream)
+    assert int(error) == 0
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpu_decode_step_matches_the_reference_path():
+def test_fused_peer_all_reduce_matches_nccl_then_norm_bit_for_bit():
+    import torch.multiprocessing as mp
+
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_reduce_rank, args=(2, _free_port(), results), nprocs=2, join=True)
+    assert results.get("reduce_ok")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("collective", ["peer", "nccl"])
+def test_two_gpu_decode_step_matches_the_reference_path(collective):
     import torch.multiprocessing as mp
 
     from oracle import llama_ref
@@ -66,7 +163,7 @@ def test_two_gpu_decode_step_matches_the_reference_path():
 
     manager = mp.Manager()
     results = manager.dict()
-    mp.spawn(_rank, args=(2, _free_port(), results), nprocs=2, join=True)
+    mp.spawn(_rank, args=(2, _free_port(), results, collective), nprocs=2, join=True)
     config = MEDIUM
     context = [40, 0, 129, 700]
     weights = make_weights(config)

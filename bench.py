@@ -363,7 +363,7 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3):
+def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3, collective: str = "peer"):
     """Config 5: Llama-3-8B-shaped decode step, 64 sequences at context 2048, tensor-parallel over all ranks
     (KV heads and column/row-sharded linears, all-reduce after o_proj and down_proj).  Returns rank 0's figures."""
     import torch
@@ -373,7 +373,7 @@ def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3):
     config = llama.LlamaConfig()
     sequences, context = 64, 2048
     shard = llama.Shard(rank, world, group)
-    decoder = llama.LlamaDecoder(config, sequences, context + 64, shard=shard, seed=4)
+    decoder = llama.LlamaDecoder(config, sequences, context + 64, shard=shard, seed=4, collective=collective)
     decoder.fill_context(context, seed=4)
     rng = np.random.default_rng(4)
     tokens = rng.integers(0, config.vocab, size=sequences)
@@ -403,7 +403,13 @@ def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3):
     moved = llama.decode_step_bytes(config, sequences, context, world, decoder.shard_lm_head)
     peaks = measured_peaks()
     status = int(decoder.status.item())
+    decoder.close()
+    how = "none (one GPU)"
+    if world > 1:
+        how = ("one kernel per collective: sum of the ranks' partial rows read from peer memory + residual add + "
+               "RMSNorm" if collective == "peer" else "NCCL all-reduce, then the add + RMSNorm kernel")
     return {
+        "collective": how,
         "tokens_per_s": round(sequences / seconds, 1), "ms_per_step": round(seconds * 1e3, 3),
         "e2e_tokens_per_s": round(sequences / e2e_seconds, 1), "tp": world,
         "bytes_per_rank_per_step": moved["total"],
@@ -482,6 +488,8 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-also", action="store_true", help="skip the secondary figures")
     parser.add_argument("--no-decode-step", action="store_true", help="skip the Llama-shaped decode step figure")
+    parser.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                        help="how the decode step's two collectives per layer run at --gpus > 1")
     parser.add_argument("--only", default="", help="profiling aid: launch one kernel a few times and exit "
                         "(decode | gemm:M,N,K | prefill[:len,len,...] | kvwrite | step:LAYERS)")
     args = parser.parse_args()
@@ -502,7 +510,7 @@ def main():
     decode_step = None
     if not args.no_decode_step:
         try:
-            decode_step = run_decode_step(rank, world, group)
+            decode_step = run_decode_step(rank, world, group, collective=args.collective)
         except Exception as error:
             decode_step = {"error": repr(error)}
     if rank == 0:

@@ -395,6 +395,12 @@ int singe_allreduce_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void 
  * Replaces: TuningChoice::Explicit(MatmulTuning { tile, .. }) (singe-kernel/src/cuda/matmul.rs:58-77). */
 int singe_matmul_set_tuning(int block_n, int k_slices_per_stage);
 
+/* K splits for problems with at most 128 rows (a thread-block cluster of that many CTAs shares one N tile and
+ * reduces through distributed shared memory): 0 = choose from the shape, 1 = never split, 2 / 4 / 8 = as given.
+ * No reference counterpart: the reference's MatmulTuning (singe-kernel/src/cuda/matmul.rs:57-77) carries a tile and
+ * compile options only; this is a tuning knob of the same kind for this library's extra degree of freedom. */
+int singe_matmul_set_splits(int k_splits);
+
 /* Reads and clears the library's sticky device error word for the current device (synchronises the device).
  * 0 = no kernel-side failure; 2 = a bounded device-side wait ran out.  Plays the role of the planner's status
  * word read-back (singe/src/backend/cuda/kernel_plan/mod.rs:192-204) for entry points without a status argument. */

@@ -262,6 +262,289 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
 }
 
+// ---- split-K for one-M-tile problems whose N gives too few tiles to fill the machine ----
+// A thread-block cluster of `splits` CTAs owns one N tile; CTA r of the cluster streams K slice r (its own TMA ring,
+// its own accumulator in tensor memory), parks the f32 partial tile in its shared memory, and after a cluster
+// barrier every CTA sums a share of the tile's rows over all the cluster's partials through distributed shared
+// memory, in split order (so the result does not depend on timing), and stores them.  No workspace in global
+// memory, no atomics, nothing to reset between launches.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t value;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(value));
+    return value;
+}
+
+__device__ __forceinline__ uint32_t cluster_size() {
+    uint32_t value;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(value));
+    return value;
+}
+
+// Every thread of every CTA of the cluster takes part; shared-memory writes before it are visible cluster-wide after.
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float4 load_cluster_shared(uint32_t local_address, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
+    float4 value;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(value.x), "=f"(value.y), "=f"(value.z), "=f"(value.w)
+                 : "r"(remote)
+                 : "memory");
+    return value;
+}
+
+template <int BN, int KPS>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_splitk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
+                       const GemmParams p) {
+    constexpr uint32_t kTmemColumns = BN < 32 ? 32 : BN;
+    constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, 0, 0);
+    constexpr int kBBytes = BN * 128;
+    constexpr int kPartialStride = BN + 4;  // floats per parked row: 16-byte stores of a warp spread over all banks
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    // [ring: stages x stage_bytes, reused for the parked partial tile][16 KB over-read pad][barriers]
+    const uint32_t ring_bytes = max(p.stages * p.stage_bytes, kBlockM * kPartialStride * 4);
+    const uint32_t bars = base + ring_bytes + kBlockM * 128;
+    const uint32_t bar_full = bars;
+    const uint32_t bar_empty = bars + kMaxStages * 8;
+    const uint32_t bar_acc_full = bars + 2 * kMaxStages * 8;
+    const uint32_t tmem_holder = bar_acc_full + 16;
+    volatile uint32_t *tmem_holder_ptr = reinterpret_cast<volatile uint32_t *>(smem_raw + (tmem_holder - raw));
+    float *partial = reinterpret_cast<float *>(smem_raw + (base - raw));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int a_bytes = p.a_rows * 128;
+    const uint32_t rank = cluster_rank();
+    const uint32_t splits = cluster_size();
+    const int tn = blockIdx.x / splits;
+    const int per_split = (p.k_blocks + splits - 1) / splits;
+    const int kb_first = rank * per_split;
+    const int kb_last = min(kb_first + per_split, p.k_blocks);  // may leave this CTA without work: its partial is zero
+    const bool has_work = kb_first < kb_last;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        mbar_init(bar_acc_full, 1);
+        mbar_init_fence();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_holder, kTmemColumns);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_holder_ptr;
+
+    bool failed = false;
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            prefetch_tensor_map(&a_map);
+            prefetch_tensor_map(&b_map);
+        }
+        int it = 0;
+        for (int kb = kb_first; kb < kb_last; ++kb, ++it) {
+            const int s = it % p.stages;
+            const uint32_t phase = (it / p.stages) & 1;
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(bar_empty + s * 8, phase ^ 1) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                failed = true;
+                break;
+            }
+            if (lane == 0) {
+                const uint32_t stage = base + s * p.stage_bytes;
+                const uint32_t full = bar_full + s * 8;
+                mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
+#pragma unroll
+                for (int sub = 0; sub < KPS; ++sub) {
+                    tma_load_2d(stage + sub * a_bytes, &a_map, full, (kb * KPS + sub) * kBlockK, 0);
+                }
+#pragma unroll
+                for (int sub = 0; sub < KPS; ++sub) {
+                    tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK, tn * BN);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        int it = 0;
+        for (int kb = kb_first; kb < kb_last; ++kb, ++it) {
+            const int s = it % p.stages;
+            const uint32_t phase = (it / p.stages) & 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_full + s * 8, phase) ? 1 : 0)) {
+                failed = true;
+                break;
+            }
+            tcgen05_fence_after();
+            if (lane == 0) {
+                const uint32_t stage = base + s * p.stage_bytes;
+#pragma unroll
+                for (int sub = 0; sub < KPS; ++sub) {
+                    const uint64_t a_desc = make_smem_desc(stage + sub * a_bytes, 16, 1024);
+                    const uint64_t b_desc = make_smem_desc(stage + KPS * a_bytes + sub * kBBytes, 16, 1024);
+#pragma unroll
+                    for (int ks = 0; ks < kBlockK / 16; ++ks) {
+                        umma_ss(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, kIdesc,
+                                (kb > kb_first || sub > 0 || ks > 0) ? 1u : 0u);
+                    }
+                }
+                tcgen05_commit(bar_empty + s * 8);
+            }
+            __syncwarp();
+        }
+        if (!failed && has_work) {
+            if (lane == 0) tcgen05_commit(bar_acc_full);
+            __syncwarp();
+        }
+    } else {
+        // ---------------- park the partial tile in shared memory ----------------
+        // The ring is free once the accumulator is complete: every MMA that read it has retired.
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        if (has_work && !__all_sync(0xffffffffu, mbar_wait(bar_acc_full, 0) ? 1 : 0)) failed = true;
+        tcgen05_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+            uint32_t r[32];
+            if (has_work && !failed) {
+                tmem_ld_x32(taddr + c, r);
+                tmem_wait_ld();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+            if (row < p.m) {
+                float4 *dst = reinterpret_cast<float4 *>(partial + row * kPartialStride + c);
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    dst[j >> 2] = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                }
+            }
+        }
+    }
+    if (failed && lane == 0) {
+        report_status(p.error, kStatusWaitTimeout);
+    }
+    tcgen05_fence_before();
+    cluster_barrier();  // all partial tiles of the cluster are parked
+    if (warp >= 2) {
+        // ---------------- reduce: CTA r takes rows r, r + splits, ... of the tile ----------------
+        const int t = threadIdx.x - 64;                    // 0 .. 127
+        constexpr int kQuads = BN / 4;                     // float4 groups per row
+        const int my_rows = (p.m - static_cast<int>(rank) + static_cast<int>(splits) - 1) / static_cast<int>(splits);
+        const uint32_t partial_address = base;
+        for (int index = t; index < my_rows * kQuads; index += 128) {
+            const int row = static_cast<int>(rank) + (index / kQuads) * static_cast<int>(splits);
+            const int quad = index % kQuads;
+            const int col = tn * BN + quad * 4;
+            if (col >= p.n) continue;
+            const uint32_t at = partial_address + (row * kPartialStride + quad * 4) * 4;
+            float4 sum = load_cluster_shared(at, 0);
+            for (uint32_t s = 1; s < splits; ++s) {
+                const float4 other = load_cluster_shared(at, s);
+                sum.x += other.x;
+                sum.y += other.y;
+                sum.z += other.z;
+                sum.w += other.w;
+            }
+            const float values[4] = {sum.x, sum.y, sum.z, sum.w};
+            if (p.out_f32) {
+                float *dst = static_cast<float *>(p.out) + static_cast<long long>(row) * p.ldo + col;
+                if (p.vector_store && col + 4 <= p.n) {
+                    *reinterpret_cast<float4 *>(dst) = sum;
+                } else {
+                    for (int j = 0; j < 4; ++j) {
+                        if (col + j < p.n) dst[j] = values[j];
+                    }
+                }
+            } else {
+                __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.out) + static_cast<long long>(row) * p.ldo + col;
+                if (p.vector_store && col + 4 <= p.n) {
+                    *reinterpret_cast<uint2 *>(dst) =
+                        make_uint2(pack2<__nv_bfloat16>(sum.x, sum.y), pack2<__nv_bfloat16>(sum.z, sum.w));
+                } else {
+                    for (int j = 0; j < 4; ++j) {
+                        if (col + j < p.n) dst[j] = __float2bfloat16_rn(values[j]);
+                    }
+                }
+            }
+        }
+    }
+    cluster_barrier();  // nobody leaves while its shared memory is still being read
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+template <int BN, int KPS>
+int launch_gemm_splitk(cudaStream_t stream, GemmParams params, const void *lhs, const void *rhs,
+                       size_t lhs_row_stride, size_t rhs_row_stride, int splits) {
+    constexpr int kSmemLimit = 227 * 1024;
+    const int b_bytes = BN * 128;
+    params.stage_bytes = KPS * (params.a_rows * 128 + b_bytes);
+    params.k_blocks = (params.k + kBlockK * KPS - 1) / (kBlockK * KPS);
+    const int per_split = (params.k_blocks + splits - 1) / splits;
+    const int fixed = kBlockM * 128 + 2 * kMaxStages * 8 + 64 + 1024;
+    int stages = (kSmemLimit - fixed) / params.stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages > per_split + 1 && per_split + 1 >= 2) stages = per_split + 1;
+    if (stages < 2) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    params.stages = stages;
+    params.tiles_n = (params.n + BN - 1) / BN;
+    const int parked = kBlockM * (BN + 4) * 4;
+    const int ring = stages * params.stage_bytes > parked ? stages * params.stage_bytes : parked;
+    const int smem = ring + fixed;
+    if (smem > kSmemLimit) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    SINGE_CUDA_TRY(cudaFuncSetAttribute(gemm_splitk_kernel<BN, KPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+
+    CUtensorMap a_map, b_map;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(params.k), static_cast<uint64_t>(params.m)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(lhs_row_stride) * 2};
+        const uint32_t box[2] = {kBlockK, static_cast<uint32_t>(params.a_rows)};
+        SINGE_TRY(encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, lhs, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(params.k), static_cast<uint64_t>(params.n)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(rhs_row_stride) * 2};
+        const uint32_t box[2] = {kBlockK, static_cast<uint32_t>(BN)};
+        SINGE_TRY(encode_tensor_map(&b_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rhs, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(params.tiles_n * splits), 1, 1);
+    config.blockDim = dim3(kGemmThreads, 1, 1);
+    config.dynamicSmemBytes = static_cast<size_t>(smem);
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = static_cast<unsigned>(splits);
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    SINGE_CUDA_TRY(cudaLaunchKernelEx(&config, gemm_splitk_kernel<BN, KPS>, a_map, b_map, params));
+    return launch_status();
+}
+
 template <int BN, int KPS>
 int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const void *rhs, size_t lhs_row_stride,
                 size_t rhs_row_stride) {
@@ -304,6 +587,7 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
 // 0 = choose from the problem shape.
 int g_tuning_block_n = 0;
 int g_tuning_slices = 0;
+int g_tuning_splits = 0;  // 0 = choose, 1 = never split K
 
 }  // namespace
 
@@ -373,8 +657,46 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
             while (slices > 1 && slices * slice_bytes * 2 > 200 * 1024) slices >>= 1;
         }
     }
+    // One M tile and too few N tiles for the machine: split K over a cluster instead of narrowing the tile.  The
+    // tile stays 128 wide with 2 slices per stage (the best streaming shape measured).  Measured on B200 (M = 16..128,
+    // N = 768..6144, K = 512..14336): the best cluster is the largest of 2 / 4 whose CTAs still fit the machine in one
+    // wave; 8 pays only when even 4 leave two thirds of the SMs idle (then with 64-wide tiles), and a split needs at
+    // least three pipeline stages of K to amortise its fill and the reduction.
+    int splits = 1;
+    if (params.m <= kBlockM && tiles(128) < (sms * 2) / 3 && g_tuning_splits != 1) {
+        int wide = 128;
+        int wanted = 1;
+        while (wanted < 4 && tiles(wide) * wanted * 2 <= sms) wanted <<= 1;
+        if (wanted == 4 && tiles(wide) * 4 <= sms / 3) {
+            wanted = 8;
+            wide = 64;
+        }
+        const int stage_k = kBlockK * 2;
+        const int k_stages = (params.k + stage_k - 1) / stage_k;
+        while (wanted > 1 && k_stages / wanted < 3) wanted >>= 1;
+        if (wanted < 8) wide = 128;
+        if (wanted > 1) {
+            splits = wanted;
+            bn = wide;
+            slices = 2;
+        }
+    }
+    if (g_tuning_splits != 0) splits = g_tuning_splits;
     if (g_tuning_block_n != 0) bn = g_tuning_block_n;
     if (g_tuning_slices != 0) slices = g_tuning_slices;
+    if (splits > 1) {
+        if (params.m > kBlockM || (splits != 2 && splits != 4 && splits != 8)) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+#define SINGE_SPLITK_CASE(BN_, KPS_)                                                                             \
+    if (bn == BN_ && slices == KPS_)                                                                             \
+        return launch_gemm_splitk<BN_, KPS_>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride, splits);
+        SINGE_SPLITK_CASE(128, 2)
+        SINGE_SPLITK_CASE(128, 1)
+        SINGE_SPLITK_CASE(64, 2)
+        SINGE_SPLITK_CASE(64, 4)
+        SINGE_SPLITK_CASE(32, 8)
+#undef SINGE_SPLITK_CASE
+        return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    }
 #define SINGE_GEMM_CASE(BN_, KPS_)                                                                    \
     if (bn == BN_ && slices == KPS_)                                                                  \
         return launch_gemm<BN_, KPS_>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
@@ -418,6 +740,15 @@ int singe_matmul_bf16_f32(singe_stream_t stream, float *out, const void *lhs, co
 int singe_matmul_set_tuning(int block_n, int k_slices_per_stage) {
     singe::g_tuning_block_n = block_n;
     singe::g_tuning_slices = k_slices_per_stage;
+    return SINGE_OK;
+}
+
+// K splits (the cluster size) for one-M-tile problems: 0 = choose from the shape, 1 = never split, 2/4/8 = as given.
+int singe_matmul_set_splits(int k_splits) {
+    if (k_splits != 0 && k_splits != 1 && k_splits != 2 && k_splits != 4 && k_splits != 8) {
+        return SINGE_ERR_INVALID_ARGUMENT;
+    }
+    singe::g_tuning_splits = k_splits;
     return SINGE_OK;
 }
 

@@ -74,6 +74,7 @@ SIGNATURES = {
     "singe_matmul_bf16_bf16": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _i, _i],
     "singe_matmul_bf16_f32": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _i, _i],
     "singe_matmul_set_tuning": [_i, _i],
+    "singe_matmul_set_splits": [_i],
     "singe_embedding_bf16": [_p, _p, _p, _p, _i, _z, _z, _z, _p],
     "singe_add_rms_norm_bf16": [_p, _p, _p, _p, _p, _z, _z, _f],
     "singe_rotary_cache_write_bf16": [_p, _p, _p, _z, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _z, _z,

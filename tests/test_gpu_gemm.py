@@ -39,6 +39,42 @@ def test_linear_matches_the_oracle_bf16_and_f32(m, n, k):
     assert np.abs(host(y32) - ref).max() / scale < 2e-3
 
 
+@pytest.mark.parametrize("m,n,k,splits", [(64, 4096, 4096, 0), (64, 4096, 14336, 0), (64, 4096, 1792, 0),
+                                          (64, 4096, 512, 0), (128, 768, 4096, 0), (5, 1000, 520, 4),
+                                          (1, 136, 200, 8), (128, 4096, 4096, 2), (33, 264, 4096, 8)])
+def test_split_k_over_a_cluster_matches_the_oracle(m, n, k, splits):
+    # One M tile and few N tiles: K is split over a thread-block cluster that reduces through distributed shared
+    # memory (splits = 0 lets the shape decide; forced values cover N and K tails and splits that get no K at all).
+    x, w = _case(m, n, k, seed=5)
+    lib = ks.lib()
+    assert lib.singe_matmul_set_splits(splits) == ks.OK
+    try:
+        y = ops.linear(x, w)
+        y32 = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        ops.matmul_bf16(y32, x, w, ops.MatmulConfig.row_major_transposed_rhs(m, n, k))
+        again = torch.empty_like(y32)
+        ops.matmul_bf16(again, x, w, ops.MatmulConfig.row_major_transposed_rhs(m, n, k))
+        torch.cuda.synchronize()
+    finally:
+        assert lib.singe_matmul_set_splits(0) == ks.OK
+    assert ops.take_device_error() == 0
+    ref = oracle.linear_bf16_f32(_bits(x), _bits(w), m=m, n=n, k=k)
+    assert_close_bf16(host(y32), ref, f"split-K f32 {m}x{n}x{k}")
+    assert_close_bf16(host(y), oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(ref)), f"split-K bf16 {m}x{n}x{k}")
+    scale = np.abs(ref).max() + 1e-6
+    assert np.abs(host(y32) - ref).max() / scale < 2e-3
+    assert torch.equal(y32, again)  # partial sums are added in split order: the result does not depend on timing
+    # the unsplit kernel agrees to f32 accumulation-order noise
+    assert lib.singe_matmul_set_splits(1) == ks.OK
+    try:
+        whole = torch.empty_like(y32)
+        ops.matmul_bf16(whole, x, w, ops.MatmulConfig.row_major_transposed_rhs(m, n, k))
+        torch.cuda.synchronize()
+    finally:
+        assert lib.singe_matmul_set_splits(0) == ks.OK
+    assert np.abs(host(whole) - host(y32)).max() / scale < 1e-4
+
+
 def test_config3_full_size_gemm_through_linearity():
     # M = 4096 against (N, K) = (4096, 4096): too large for the scalar oracle, so check sampled rows against
     # it, and the whole product through linearity: (X1 + X2) W^T == X1 W^T + X2 W^T for exactly representable sums.

@@ -469,7 +469,12 @@ def run_only(args):
         else:
             call = lambda: ops.kv_cache_write(key_cache, value_cache, k, v, pages, slots)
     elif kind == "step":
-        config = llama.LlamaConfig(layers=int(detail or 4))
+        # step:LAYERS[:TP] - with TP > 1 one GPU runs the shapes of one rank of a TP-way split (no collective)
+        layers, _, tp = (detail or "4").partition(":")
+        tp = int(tp or 1)
+        full = llama.LlamaConfig()
+        config = llama.LlamaConfig(layers=int(layers), heads=full.heads // tp, kv_heads=full.kv_heads // tp,
+                                   ffn=full.ffn // tp, vocab=full.vocab // tp)
         decoder = llama.LlamaDecoder(config, 64, 2048 + 64)
         decoder.fill_context(2048)
         decoder.plan(np.random.default_rng(4).integers(0, config.vocab, size=64))
@@ -493,7 +498,7 @@ def main():
     parser.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                         help="how the decode step's two collectives per layer run at --gpus > 1")
     parser.add_argument("--only", default="", help="profiling aid: launch one kernel a few times and exit "
-                        "(decode | gemm:M,N,K | prefill[:len,len,...] | kvwrite | step:LAYERS)")
+                        "(decode | gemm:M,N,K | prefill[:len,len,...] | kvwrite | step:LAYERS[:TP])")
     args = parser.parse_args()
 
     if args.impl == "reference":

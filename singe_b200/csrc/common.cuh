@@ -9,6 +9,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/singe_kernel_sys.h"
 
@@ -41,6 +42,53 @@ inline int cuda_status(cudaError_t error) {
 inline bool fits_i32(size_t value) { return value <= static_cast<size_t>(INT32_MAX); }
 
 inline int launch_status() { return cuda_status(cudaGetLastError()); }
+
+// Programmatic dependent launch.  Every kernel of the decode path is launched with the attribute that lets it start
+// while the kernel before it on the stream is still draining: its CTAs do their private set-up (barriers, tensor
+// memory, tensor-map prefetch) and then block in grid_dependency_wait() until the earlier kernel has completed and
+// its writes are visible.  The wait is the first thing before any access to global memory another kernel may have
+// written or may still read, so stream order is preserved; without the attribute the wait returns at once.  A step
+// of eleven short launches per layer otherwise pays a launch ramp per kernel.  SINGE_PDL=0 turns the attribute off.
+// Measured on B200 (config-2 decode and the Llama decode step): every kind gains except the split-K combine, whose
+// thousand small CTAs, launched early, take warp slots from the decode kernel's last wave (-2 % on the headline).
+constexpr unsigned kDefaultDependentLaunchMask = 1u | 2u | 4u | 16u;  // glue, GEMM, decode, fused all-reduce
+enum LaunchKind : unsigned { kLaunchGlue = 1, kLaunchGemm = 2, kLaunchDecode = 4, kLaunchCombine = 8, kLaunchReduce = 16 };
+
+// Which kinds of kernels take the attribute (SINGE_PDL = a bit mask of LaunchKind; default: see the value below).
+inline unsigned dependent_launch_mask() {
+    static const unsigned mask = [] {
+        const char *value = getenv("SINGE_PDL");
+        return value == nullptr ? kDefaultDependentLaunchMask : static_cast<unsigned>(strtoul(value, nullptr, 0));
+    }();
+    return mask;
+}
+
+template <typename... Parameters, typename... Arguments>
+inline cudaError_t launch_dependent(void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes,
+                                    cudaStream_t stream, unsigned kind, unsigned cluster, Arguments... arguments) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    unsigned count = 0;
+    if ((dependent_launch_mask() & kind) != 0) {
+        attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
+    if (cluster > 1) {
+        attributes[count].id = cudaLaunchAttributeClusterDimension;
+        attributes[count].val.clusterDim.x = cluster;
+        attributes[count].val.clusterDim.y = 1;
+        attributes[count].val.clusterDim.z = 1;
+        ++count;
+    }
+    config.attrs = attributes;
+    config.numAttrs = count;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Parameters>(arguments)...);
+}
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
 inline PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
@@ -123,6 +171,11 @@ inline int device_sm_count() {
 constexpr uint32_t kStatusIndexOutOfBounds = 1;
 // Set when a bounded wait ran out; the kernel abandons its work instead of hanging.
 constexpr uint32_t kStatusWaitTimeout = 2;
+
+// See launch_dependent(): blocks until the kernels this launch depends on have completed and flushed.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel on the stream begin launching (it still waits for this one to complete before it reads).
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ void report_status(uint32_t *status, uint32_t code) {
     if (status != nullptr) {

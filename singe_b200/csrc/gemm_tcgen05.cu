@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, 0, 0);
     constexpr int kBBytes = BN * 128;
 
+    grid_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -102,6 +103,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_holder_ptr;
+    grid_dependency_wait();  // barriers and tensor memory are set up; the operands come from the kernel before
 
     bool failed = false;
 
@@ -306,6 +308,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     constexpr int kBBytes = BN * 128;
     constexpr int kPartialStride = BN + 4;  // floats per parked row: 16-byte stores of a warp spread over all banks
 
+    grid_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -346,6 +349,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_holder_ptr;
+    grid_dependency_wait();  // barriers and tensor memory are set up; the operands come from the kernel before
 
     bool failed = false;
     if (warp == 0) {
@@ -529,19 +533,10 @@ int launch_gemm_splitk(cudaStream_t stream, GemmParams params, const void *lhs, 
         SINGE_TRY(encode_tensor_map(&b_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rhs, dims, strides, box,
                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
     }
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(static_cast<unsigned>(params.tiles_n * splits), 1, 1);
-    config.blockDim = dim3(kGemmThreads, 1, 1);
-    config.dynamicSmemBytes = static_cast<size_t>(smem);
-    config.stream = stream;
-    cudaLaunchAttribute attribute;
-    attribute.id = cudaLaunchAttributeClusterDimension;
-    attribute.val.clusterDim.x = static_cast<unsigned>(splits);
-    attribute.val.clusterDim.y = 1;
-    attribute.val.clusterDim.z = 1;
-    config.attrs = &attribute;
-    config.numAttrs = 1;
-    SINGE_CUDA_TRY(cudaLaunchKernelEx(&config, gemm_splitk_kernel<BN, KPS>, a_map, b_map, params));
+    SINGE_CUDA_TRY(launch_dependent(gemm_splitk_kernel<BN, KPS>, dim3(static_cast<unsigned>(params.tiles_n * splits)),
+                                    dim3(kGemmThreads), smem, stream, kLaunchGemm, static_cast<unsigned>(splits), a_map,
+                                    b_map,
+                                    params));
     return launch_status();
 }
 
@@ -579,7 +574,8 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
     }
     const int total = params.tiles_m * params.tiles_n;
     const int grid = total < device_sm_count() ? total : device_sm_count();
-    gemm_bf16_kernel<BN, KPS><<<grid, kGemmThreads, smem, stream>>>(a_map, b_map, params);
+    SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS>, dim3(grid), dim3(kGemmThreads), smem, stream, kLaunchGemm, 1, a_map,
+                                    b_map, params));
     return launch_status();
 }
 

@@ -61,6 +61,8 @@ __device__ __forceinline__ void store8(__nv_bfloat16 *pointer, const Vec8 &value
 template <typename Index, int VEC>
 __global__ void embedding_kernel(__nv_bfloat16 *out, const __nv_bfloat16 *table, const Index *ids, int width,
                                  long long vocab, uint32_t *status) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int row = blockIdx.x;
     long long id = static_cast<long long>(ids[row]);
     if (id < 0) id += vocab;  // negative indices wrap, as index_select does
@@ -87,6 +89,8 @@ constexpr int kHeld = 4;
 template <int VEC>
 __global__ void add_rms_norm_kernel(__nv_bfloat16 *hidden, const __nv_bfloat16 *delta, __nv_bfloat16 *normed,
                                     const __nv_bfloat16 *weight, int width, float eps) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     __shared__ float scratch[32];
     const size_t base = static_cast<size_t>(blockIdx.x) * width;
     float square = 0.0f;
@@ -172,6 +176,8 @@ __global__ void rotary_cache_write_kernel(__nv_bfloat16 *q_out, const __nv_bfloa
                                           const Index *write_slots, int heads, int kv_heads, int head_dim,
                                           long long pages, long long page_size, long long capacity,
                                           uint32_t *status) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int token = blockIdx.x;
     const int half = head_dim >> 1;
     long long position = static_cast<long long>(positions[token]);
@@ -238,6 +244,8 @@ __global__ void rotary_cache_write_kernel(__nv_bfloat16 *q_out, const __nv_bfloa
 template <int VEC>
 __global__ void silu_mul_kernel(__nv_bfloat16 *out, const __nv_bfloat16 *gate, const __nv_bfloat16 *up,
                                 long long in_stride, int width) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const size_t in_base = static_cast<size_t>(blockIdx.y) * in_stride;
     const size_t out_base = static_cast<size_t>(blockIdx.y) * width;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
@@ -260,6 +268,8 @@ __global__ void silu_mul_kernel(__nv_bfloat16 *out, const __nv_bfloat16 *gate, c
 template <int VEC>
 __global__ void argmax_kernel(float *best_value, long long *best_index, const __nv_bfloat16 *logits,
                               long long stride, int width, long long index_offset) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     __shared__ float values[32];
     __shared__ int indices[32];
     const __nv_bfloat16 *row = logits + static_cast<size_t>(blockIdx.x) * stride;
@@ -326,7 +336,7 @@ int singe_embedding_bf16(singe_stream_t stream, void *out, const void *table, co
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool wide = width % 8 == 0 && aligned16(out) && aligned16(table);
 #define SINGE_EMBED(Index, VEC)                                                                              \
-    embedding_kernel<Index, VEC><<<static_cast<unsigned>(tokens), 256, 0, s>>>(                              \
+    launch_dependent(embedding_kernel<Index, VEC>, dim3(static_cast<unsigned>(tokens)), dim3(256), 0, s, kLaunchGlue, 1,  \
         static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(table),                        \
         static_cast<const Index *>(ids), static_cast<int>(width), static_cast<long long>(vocab), status)
     if (index_width == 8) {
@@ -349,12 +359,14 @@ int singe_add_rms_norm_bf16(singe_stream_t stream, void *hidden, const void *del
     if (wide) {
         int threads = static_cast<int>((width / 8 + 31) / 32 * 32);
         if (threads > 512) threads = 512;
-        add_rms_norm_kernel<8><<<static_cast<unsigned>(rows), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        launch_dependent(add_rms_norm_kernel<8>, dim3(static_cast<unsigned>(rows)), dim3(threads), 0,
+                         static_cast<cudaStream_t>(stream), kLaunchGlue, 1,
             static_cast<__nv_bfloat16 *>(hidden), static_cast<const __nv_bfloat16 *>(delta),
             static_cast<__nv_bfloat16 *>(normed), static_cast<const __nv_bfloat16 *>(weight),
             static_cast<int>(width), eps);
     } else {
-        add_rms_norm_kernel<1><<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        launch_dependent(add_rms_norm_kernel<1>, dim3(static_cast<unsigned>(rows)), dim3(256), 0,
+                         static_cast<cudaStream_t>(stream), kLaunchGlue, 1,
             static_cast<__nv_bfloat16 *>(hidden), static_cast<const __nv_bfloat16 *>(delta),
             static_cast<__nv_bfloat16 *>(normed), static_cast<const __nv_bfloat16 *>(weight),
             static_cast<int>(width), eps);
@@ -385,7 +397,7 @@ int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void
     const bool wide = (head_dim / 2) % 8 == 0 && qkv_row_stride % 8 == 0 && aligned16(q_out) && aligned16(qkv) &&
                       aligned16(cos_table) && aligned16(sin_table) && aligned16(key_cache) && aligned16(value_cache);
 #define SINGE_ROTARY(Index, VEC)                                                                                     \
-    rotary_cache_write_kernel<Index, VEC><<<static_cast<unsigned>(tokens), 256, 0, s>>>(                             \
+    launch_dependent(rotary_cache_write_kernel<Index, VEC>, dim3(static_cast<unsigned>(tokens)), dim3(256), 0, s, kLaunchGlue, 1, \
         static_cast<__nv_bfloat16 *>(q_out), static_cast<const __nv_bfloat16 *>(qkv),                                \
         static_cast<long long>(qkv_row_stride), static_cast<const __nv_bfloat16 *>(cos_table),                       \
         static_cast<const __nv_bfloat16 *>(sin_table), static_cast<const Index *>(positions),                        \
@@ -411,12 +423,12 @@ int singe_silu_mul_bf16(singe_stream_t stream, void *out, const void *gate, cons
     const bool wide = width % 8 == 0 && input_row_stride % 8 == 0 && aligned16(out) && aligned16(gate) && aligned16(up);
     if (wide) {
         dim3 grid(static_cast<unsigned>((width / 8 + 255) / 256), static_cast<unsigned>(rows));
-        silu_mul_kernel<8><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        launch_dependent(silu_mul_kernel<8>, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), kLaunchGlue, 1,
             static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(gate),
             static_cast<const __nv_bfloat16 *>(up), static_cast<long long>(input_row_stride), static_cast<int>(width));
     } else {
         dim3 grid(static_cast<unsigned>((width + 255) / 256), static_cast<unsigned>(rows));
-        silu_mul_kernel<1><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        launch_dependent(silu_mul_kernel<1>, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), kLaunchGlue, 1,
             static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(gate),
             static_cast<const __nv_bfloat16 *>(up), static_cast<long long>(input_row_stride), static_cast<int>(width));
     }
@@ -430,11 +442,13 @@ int singe_argmax_bf16(singe_stream_t stream, float *best_value, int64_t *best_in
     if (best_value == nullptr || best_index == nullptr || logits == nullptr) return SINGE_ERR_NULL_POINTER;
     const bool wide = width % 8 == 0 && row_stride % 8 == 0 && aligned16(logits);
     if (wide) {
-        argmax_kernel<8><<<static_cast<unsigned>(rows), 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        launch_dependent(argmax_kernel<8>, dim3(static_cast<unsigned>(rows)), dim3(1024), 0,
+                         static_cast<cudaStream_t>(stream), kLaunchGlue, 1,
             best_value, reinterpret_cast<long long *>(best_index), static_cast<const __nv_bfloat16 *>(logits),
             static_cast<long long>(row_stride), static_cast<int>(width), static_cast<long long>(index_offset));
     } else {
-        argmax_kernel<1><<<static_cast<unsigned>(rows), 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        launch_dependent(argmax_kernel<1>, dim3(static_cast<unsigned>(rows)), dim3(1024), 0,
+                         static_cast<cudaStream_t>(stream), kLaunchGlue, 1,
             best_value, reinterpret_cast<long long *>(best_index), static_cast<const __nv_bfloat16 *>(logits),
             static_cast<long long>(row_stride), static_cast<int>(width), static_cast<long long>(index_offset));
     }

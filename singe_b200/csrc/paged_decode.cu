@@ -82,6 +82,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     constexpr int NTILES = HD / 8;
     constexpr int STAGE = decode_stage_bytes<HD>();
 
+    grid_launch_dependents();
+    grid_dependency_wait();  // the queries (and, in a decode step, the newest K/V rows) come from the kernel before
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -344,6 +346,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
 template <typename T>
 __global__ void decode_combine_kernel(T *out, const float *attn_partial, const float *lse_partial, const int32_t *lens,
                                       int heads, int head_dim, int split_tokens, int max_splits, int bound) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int b = blockIdx.y;
     const int head = blockIdx.x;
     int len = lens[b];
@@ -389,7 +393,9 @@ int launch_decode(cudaStream_t stream, const DecodeParams &params, const void *k
                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B));
     dim3 grid(static_cast<unsigned>(params.max_splits), static_cast<unsigned>(params.kv_heads),
               static_cast<unsigned>(batch));
-    paged_decode_kernel<T, HD><<<grid, kDecodeThreads, smem, stream>>>(k_map, v_map, params);
+    SINGE_CUDA_TRY(launch_dependent(paged_decode_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream, kLaunchDecode, 1, k_map,
+                                    v_map,
+                                    params));
     return launch_status();
 }
 
@@ -454,13 +460,17 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
         dim3 grid(static_cast<unsigned>(heads), static_cast<unsigned>(batch));
         const int threads = head_dim >= 128 ? 128 : 64;
         if (element == 0) {
-            decode_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-                static_cast<__nv_bfloat16 *>(out), attn_scratch, lse_scratch, actual_seq_lens, params.heads,
-                static_cast<int>(head_dim), params.split_tokens, params.max_splits, static_cast<int>(bound));
+            SINGE_CUDA_TRY(launch_dependent(decode_combine_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream,
+                                            kLaunchCombine, 1,
+                                            static_cast<__nv_bfloat16 *>(out), attn_scratch, lse_scratch,
+                                            actual_seq_lens, params.heads, static_cast<int>(head_dim),
+                                            params.split_tokens, params.max_splits, static_cast<int>(bound)));
         } else {
-            decode_combine_kernel<__half><<<grid, threads, 0, stream>>>(
-                static_cast<__half *>(out), attn_scratch, lse_scratch, actual_seq_lens, params.heads,
-                static_cast<int>(head_dim), params.split_tokens, params.max_splits, static_cast<int>(bound));
+            SINGE_CUDA_TRY(launch_dependent(decode_combine_kernel<__half>, grid, dim3(threads), 0, stream,
+                                            kLaunchCombine, 1,
+                                            static_cast<__half *>(out), attn_scratch, lse_scratch, actual_seq_lens,
+                                            params.heads, static_cast<int>(head_dim), params.split_tokens,
+                                            params.max_splits, static_cast<int>(bound)));
         }
         return launch_status();
     }

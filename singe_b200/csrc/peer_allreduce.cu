@@ -72,6 +72,8 @@ __global__ void __launch_bounds__(kReduceThreads)
     __shared__ int shared_ok;
     __shared__ float scratch[kReduceThreads / 32];
     const int tid = threadIdx.x;
+    grid_launch_dependents();
+    grid_dependency_wait();  // the GEMM before this launch has written this rank's partial rows
     if (tid == 0) {
         shared_epoch = p.state[0] + 1;
         shared_ok = 1;
@@ -255,8 +257,10 @@ int singe_allreduce_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void 
     params.world = world;
     params.width = static_cast<int>(width);
     params.eps = eps;
-    singe::allreduce_add_rms_norm_kernel<<<static_cast<unsigned>(rows), singe::kReduceThreads, 0,
-                                           static_cast<cudaStream_t>(stream)>>>(params);
+    SINGE_CUDA_TRY(singe::launch_dependent(singe::allreduce_add_rms_norm_kernel, dim3(static_cast<unsigned>(rows)),
+                                           dim3(singe::kReduceThreads), 0, static_cast<cudaStream_t>(stream),
+                                           singe::kLaunchReduce, 1,
+                                           params));
     return singe::launch_status();
 }
 

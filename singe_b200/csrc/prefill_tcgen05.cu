@@ -20,9 +20,10 @@
 //              the row is re-based by an exact power of two whenever its running sum passes 2^16 (O in tensor
 //              memory and the sum are scaled, at the start of the next tile, when the previous P V has retired).
 //              A row whose scores jump by more than ~2^64 from one key tile to the next would overflow this
-//              scheme.  The CTA then marks itself (a NaN in the LSE of its first row) and the second launch of
-//              the same kernel in SAFE mode, where every tile takes its exact row maximum first, recomputes
-//              exactly the marked CTAs; all others leave at once.
+//              scheme.  Such a row gets a NaN as its LSE and raises a sticky per-device flag; the second launch of
+//              the same kernel in SAFE mode, where every tile takes its exact row maximum first, leaves at once
+//              while the flag has never been raised, and otherwise finds the marked items among its share and
+//              recomputes exactly those.
 //   warp 8     MMA issuer and tensor-memory owner.  Issue order per key tile j:
 //                 PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1)
 //              (S = Q K^T: 8 x tcgen05.mma 128x128x16, both operands K-major in shared memory; O += P V: 8 x
@@ -52,6 +53,11 @@ constexpr int kMaxRankTiles = 1024;               // heaviest-first dispatch: se
 constexpr float kRescaleThreshold = 8.0f;         // two-pass tiles: re-base when the max grew by 2^8 (log2 units)
 constexpr float kRebaseLimit = 65536.0f;          // single-pass tiles: re-base a row when its sum passes 2^16
 constexpr float kOverflowLimit = 1.8446744e19f;   // 2^64: beyond this the CTA is redone in SAFE mode
+constexpr int kRedoCapacity = 2048;               // marked items one CTA lists; past that it redoes its whole share
+
+// Raised (never lowered) by the first launch when a row leaves the single-pass range.  While it is zero the second
+// launch has nothing to look for; once it is set every later call pays the scan of the LSE marks.
+__device__ unsigned g_out_of_range_seen = 0;
 
 struct PrefillParams {
     __nv_bfloat16 *out;
@@ -257,7 +263,7 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
 // index r * grid + c on even rounds and r * grid + grid - 1 - c on odd ones, which evens out the heaviest-first
 // order); all pipelines run on across items, so the next item's loads and first MMAs overlap the current item's
 // last tile and epilogue.  Softmax is single-pass after an item's first key tile.
-// SAFE = true: the second launch, one CTA per item: it leaves at once unless the first launch marked the item, and
+// SAFE = true: the second launch, same grid and same shares: it leaves at once unless the flag above is raised, and
 // otherwise recomputes it with the exact row maximum on every tile.
 template <bool SAFE>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
@@ -286,10 +292,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     volatile int *shared_tmax = reinterpret_cast<volatile int *>(smem_raw + (words + 4 - raw));
     volatile int *shared_ranks = reinterpret_cast<volatile int *>(smem_raw + (words + 8 - raw));
     int *counts = reinterpret_cast<int *>(smem_raw + (words + 32 - raw));  // [kMaxRankTiles]
+    volatile int *redo_list = reinterpret_cast<volatile int *>(counts + kMaxRankTiles);  // [kRedoCapacity], SAFE only
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    if (SAFE && *reinterpret_cast<volatile unsigned *>(&g_out_of_range_seen) == 0u) {
+        return;  // no first launch on this device has ever marked a row
+    }
 
     // ---- the table behind the heaviest-first item order ----
     {
@@ -312,24 +322,42 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     }
     const int tmax = *shared_tmax;
     const long long total_items = static_cast<long long>(*shared_ranks) * p.heads;
-    // index of this CTA's item number `round`, or -1 when the CTA is done
-    auto item_index = [&](int round) -> int {
-        if (SAFE) return (round == 0 && blockIdx.x < total_items) ? static_cast<int>(blockIdx.x) : -1;
+    // index of this CTA's share number `round`, or -1 past the end
+    auto share_index = [&](int round) -> int {
         const long long first = static_cast<long long>(round) * gridDim.x;
         const long long index = first + ((round & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
         return index < total_items ? static_cast<int>(index) : -1;
     };
+    int listed = -1;  // SAFE: number of marked items in redo_list, or -1 = walk the whole share
     if (SAFE) {
-        // The first launch leaves a NaN as the LSE of every row it could not finish in range.
-        const int index = item_index(0);
-        if (index < 0) return;
-        const Item item = decode_item(p, counts, tmax, index, lane);
-        if (!item.valid || item.key_tiles == 0) return;
-        const int row = item.q0 + tid;
-        const bool marked = tid < kPair && row < item.len_q &&
-                            isnan(p.lse[(static_cast<size_t>(item.offset) + row) * p.heads + item.head]);
-        if (__syncthreads_or(marked ? 1 : 0) == 0) return;
+        // The first launch leaves a NaN as the LSE of every row it could not finish in range: list the marked items.
+        int found = 0;
+        bool overflow = false;
+        for (int round = 0;; ++round) {
+            const int index = share_index(round);
+            if (index < 0) break;
+            const Item item = decode_item(p, counts, tmax, index, lane);
+            const int row = item.q0 + tid;
+            const bool marked = item.valid && item.key_tiles > 0 && tid < kPair && row < item.len_q &&
+                                isnan(p.lse[(static_cast<size_t>(item.offset) + row) * p.heads + item.head]);
+            if (__syncthreads_or(marked ? 1 : 0) != 0) {
+                if (found < kRedoCapacity) {
+                    if (tid == 0) redo_list[found] = index;
+                    ++found;
+                } else {
+                    overflow = true;
+                }
+            }
+        }
+        __syncthreads();
+        if (found == 0) return;
+        listed = overflow ? -1 : found;
     }
+    // index of the item this CTA works on in `round`, or -1 when it is done
+    auto item_index = [&](int round) -> int {
+        if (SAFE && listed >= 0) return round < listed ? redo_list[round] : -1;
+        return share_index(round);
+    };
 
     if (tid == 0) {
         for (int i = 0; i < kBarriers; ++i) {
@@ -667,7 +695,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             }
             if (real) {
                 float value = empty ? -1.0e20f : (base_log2 + log2f(row_sum)) * 0.6931471805599453f;
-                if (!SAFE && !in_range) value = __int_as_float(0x7fc00000);  // has the second launch redo the item
+                if (!SAFE && !in_range) {
+                    value = __int_as_float(0x7fc00000);  // has the second launch redo the item
+                    atomicExch(&g_out_of_range_seen, 1u);
+                }
                 p.lse[token * p.heads + item.head] = value;
             }
         }
@@ -683,7 +714,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     }
 }
 
-constexpr int kPrefillSmem = 6 * kTileBytes + 8 * 20 + 32 + kMaxRankTiles * 4 + 1024;
+constexpr int kPrefillSmem = 6 * kTileBytes + 8 * 20 + 32 + kMaxRankTiles * 4 + kRedoCapacity * 4 + 1024;
 
 }  // namespace
 
@@ -745,9 +776,8 @@ int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void 
     const unsigned persistent = static_cast<unsigned>(items < static_cast<size_t>(sms) ? items : sms);
     prefill_tcgen05_kernel<false><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
     SINGE_TRY(launch_status());
-    // Redo pass, one CTA per item: CTAs of items the first launch did not mark leave after one look.
-    prefill_tcgen05_kernel<true><<<static_cast<unsigned>(items), kPrefillThreads, kPrefillSmem, stream>>>(
-        q_map, k_map, v_map, params);
+    // Redo pass over the same shares: a no-op while the device's out-of-range flag has never been raised.
+    prefill_tcgen05_kernel<true><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
     return launch_status();
 }
 

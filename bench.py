@@ -181,9 +181,20 @@ def run_decode(args, rank, world, group):
     # Weak scaling: every rank serves its own batch of config 2's shape - the same 32 context lengths and block
     # table (seed 1), its own K/V/Q values - so the work per GPU is fixed as N grows.
     case = workloads.paged_decode_case(seed=1)
-    query, key_cache, value_cache = decode_device_inputs(case, seed=1 + rank)
-    lens = torch.from_numpy(case.lens).cuda()
-    table = torch.from_numpy(case.block_table.view(np.int32)).cuda()
+    first_query, key_cache, value_cache = decode_device_inputs(case, seed=1 + rank)
+    # The step's inputs (query, block table, lengths) live in ONE device allocation, so the end-to-end step uploads
+    # them with a single copy from one pinned host buffer.
+    host_table_array = case.block_table.view(np.int32)
+    sizes = [first_query.numel() * 2, host_table_array.size * 4, case.lens.size * 4]
+    starts = [0, sizes[0], sizes[0] + sizes[1]]
+    assert all(start % 16 == 0 for start in starts)
+    step_inputs = torch.empty(sum(sizes), dtype=torch.uint8, device="cuda")
+    query = step_inputs[starts[0]:starts[1]].view(torch.bfloat16).view(first_query.shape)
+    table = step_inputs[starts[1]:starts[2]].view(torch.int32).view(host_table_array.shape)
+    lens = step_inputs[starts[2]:].view(torch.int32)
+    query.copy_(first_query)
+    table.copy_(torch.from_numpy(host_table_array))
+    lens.copy_(torch.from_numpy(case.lens))
     out = torch.empty_like(query)
     config = ops.PagedKvDecodeAttentionConfig.contiguous(case.batch, case.heads, case.kv_heads, case.head_dim,
                                                          case.block_size, case.physical_blocks,
@@ -239,20 +250,16 @@ def run_decode(args, rank, world, group):
     achieved = my_bytes / launch_seconds / 1e9
 
     # ---- end to end through the host-facing call: pinned host inputs in, result out, every step ----
-    host_query = query.cpu().pin_memory()
-    host_lens = torch.from_numpy(case.lens).pin_memory()
-    host_table = torch.from_numpy(case.block_table.view(np.int32)).pin_memory()
+    host_inputs = step_inputs.cpu().pin_memory()
     host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    h2d = host_query.numel() * 2 + host_lens.numel() * 4 + host_table.numel() * 4
+    h2d = host_inputs.numel()
     d2h = host_out.numel() * 2
 
     # One step = copies in, the decode call, copy out: captured once, replayed and waited for every step.
     e2e_graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(side):
         with torch.cuda.graph(e2e_graph, stream=side):
-            query.copy_(host_query, non_blocking=True)
-            lens.copy_(host_lens, non_blocking=True)
-            table.copy_(host_table, non_blocking=True)
+            step_inputs.copy_(host_inputs, non_blocking=True)
             step(side)
             host_out.copy_(out, non_blocking=True)
     torch.cuda.synchronize()

@@ -390,6 +390,15 @@ int singe_allreduce_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void 
                                       const void *const *partials, uint32_t *const *flags, uint32_t *state, int rank,
                                       int world, size_t rows, size_t width, float eps, uint32_t *status);
 
+/* The gate and up projections of GatedMlp (singe/src/nn/layers/feed_forward/mod.rs:58-66) and its activation in one
+ * call: rhs [columns, reduction] holds the gate and up weight rows interleaved (row 2j = gate_j, row 2j+1 = up_j),
+ * out [rows, columns / 2] = bf16(bf16(silu(g_j)) * u_j) with g, u the bf16-rounded projections: the same roundings as
+ * singe_matmul_bf16_bf16 followed by singe_silu_mul_bf16, without writing the projections out.
+ * Replaces: two Linear::forward calls + silu + mul of GatedMlp::forward. */
+int singe_matmul_bf16_swiglu_bf16(singe_stream_t stream, void *out, const void *lhs, const void *rhs, size_t rows,
+                                  size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
+                                  size_t output_row_stride);
+
 /* Explicit tile choice for the two GEMM entry points, process-wide: block_n in {32,64,128,256},
  * k_slices_per_stage in {1,2,4,8}; 0 = choose from the problem shape.
  * Replaces: TuningChoice::Explicit(MatmulTuning { tile, .. }) (singe-kernel/src/cuda/matmul.rs:58-77). */

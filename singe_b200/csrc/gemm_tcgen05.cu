@@ -41,8 +41,18 @@ struct GemmParams {
     int stage_bytes;  // KPS * (a_rows * 128 + BN * 128)
     int tiles_m, tiles_n, k_blocks;  // k_blocks counts stages: KPS 64-wide slices each
     int vector_store;  // 16-byte stores are legal (alignment and stride)
+    int gated;         // 1: columns are (gate, up) pairs; the epilogue stores bf16(bf16(silu(gate)) * up), n / 2 wide
     uint32_t *error;   // sticky device error word (2 = a bounded wait ran out)
 };
+
+// GatedMlp's activation-then-multiply (singe/src/nn/layers/feed_forward/mod.rs:58-66) on two accumulators, with the
+// roundings of the unfused chain: both projections to bf16, silu to bf16, the product to bf16 (by the caller's store).
+__device__ __forceinline__ float gated_value(float gate_acc, float up_acc) {
+    const float gate = __bfloat162float(__float2bfloat16_rn(gate_acc));
+    const float up = __bfloat162float(__float2bfloat16_rn(up_acc));
+    const float activated = __bfloat162float(__float2bfloat16_rn(gate / (1.0f + __expf(-gate))));
+    return activated * up;
+}
 
 __device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tiles_n, int &tm, int &tn) {
     const int per_group = kGroupM * tiles_n;
@@ -210,7 +220,32 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 tmem_ld_x32(taddr + c, r);
                 tmem_wait_ld();
                 const int col = tn * BN + c;
-                if (row < p.m && col < p.n) {
+                if (row < p.m && col < p.n && p.gated) {
+                    __nv_bfloat16 *dst =
+                        static_cast<__nv_bfloat16 *>(p.out) + static_cast<long long>(row) * p.ldo + col / 2;
+                    if (p.vector_store && col + 32 <= p.n) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 16) {
+                            uint4 packed;
+                            uint32_t *words = &packed.x;
+#pragma unroll
+                            for (int w = 0; w < 4; ++w) {
+                                words[w] = pack2<__nv_bfloat16>(
+                                    gated_value(__uint_as_float(r[j + 4 * w]), __uint_as_float(r[j + 4 * w + 1])),
+                                    gated_value(__uint_as_float(r[j + 4 * w + 2]), __uint_as_float(r[j + 4 * w + 3])));
+                            }
+                            *reinterpret_cast<uint4 *>(dst + j / 2) = packed;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            if (col + j + 1 < p.n) {
+                                dst[j / 2] = __float2bfloat16_rn(
+                                    gated_value(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
+                            }
+                        }
+                    }
+                } else if (row < p.m && col < p.n) {
                     if (p.out_f32) {
                         float *dst = static_cast<float *>(p.out) + static_cast<long long>(row) * p.ldo + col;
                         if (p.vector_store && col + 32 <= p.n) {
@@ -468,7 +503,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 sum.w += other.w;
             }
             const float values[4] = {sum.x, sum.y, sum.z, sum.w};
-            if (p.out_f32) {
+            if (p.gated) {
+                __nv_bfloat16 *dst =
+                    static_cast<__nv_bfloat16 *>(p.out) + static_cast<long long>(row) * p.ldo + col / 2;
+                if (col + 4 <= p.n) {
+                    *reinterpret_cast<uint32_t *>(dst) =
+                        pack2<__nv_bfloat16>(gated_value(sum.x, sum.y), gated_value(sum.z, sum.w));
+                } else if (col + 2 <= p.n) {
+                    dst[0] = __float2bfloat16_rn(gated_value(sum.x, sum.y));
+                }
+            } else if (p.out_f32) {
                 float *dst = static_cast<float *>(p.out) + static_cast<long long>(row) * p.ldo + col;
                 if (p.vector_store && col + 4 <= p.n) {
                     *reinterpret_cast<float4 *>(dst) = sum;
@@ -590,11 +634,11 @@ int g_tuning_splits = 0;  // 0 = choose, 1 = never split K
 // validate_matmul (singe-kernel/src/cuda/matmul.rs:2977-3020), then the layout gate of the tensor-core path.
 int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, const void *rhs, size_t rows,
               size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
-              size_t output_row_stride, int transpose_lhs, int transpose_rhs) {
+              size_t output_row_stride, int transpose_lhs, int transpose_rhs, bool gated) {
     const size_t lhs_min = transpose_lhs ? rows : reduction;
     const size_t rhs_min = transpose_rhs ? reduction : columns;
     if (rows == 0 || columns == 0 || reduction == 0 || lhs_row_stride < lhs_min || rhs_row_stride < rhs_min ||
-        output_row_stride < columns) {
+        output_row_stride < (gated ? columns / 2 : columns) || (gated && (columns % 2 != 0 || out_f32))) {
         return SINGE_ERR_INVALID_LENGTH;
     }
     if (!fits_i32(rows) || !fits_i32(columns) || !fits_i32(reduction) || !fits_i32(lhs_row_stride) ||
@@ -614,6 +658,7 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
     params.error = device_error_word();
     params.out = out;
     params.out_f32 = out_f32 ? 1 : 0;
+    params.gated = gated ? 1 : 0;
     params.m = static_cast<int>(rows);
     params.n = static_cast<int>(columns);
     params.k = static_cast<int>(reduction);
@@ -719,14 +764,24 @@ int singe_matmul_bf16_bf16(singe_stream_t stream, void *out, const void *lhs, co
                            size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
                            size_t output_row_stride, int transpose_lhs, int transpose_rhs) {
     return singe::gemm_bf16(static_cast<cudaStream_t>(stream), out, false, lhs, rhs, rows, columns, reduction,
-                            lhs_row_stride, rhs_row_stride, output_row_stride, transpose_lhs, transpose_rhs);
+                            lhs_row_stride, rhs_row_stride, output_row_stride, transpose_lhs, transpose_rhs, false);
+}
+
+// out[M, N/2] = bf16(bf16(silu(g)) * u) with g = bf16(lhs . rhs[2j]^T), u = bf16(lhs . rhs[2j+1]^T): the gate and up
+// projections of a gated MLP in one GEMM whose weight rows interleave gate and up, with the activation in the
+// epilogue.  Same roundings as singe_matmul_bf16_bf16 followed by singe_silu_mul_bf16.
+int singe_matmul_bf16_swiglu_bf16(singe_stream_t stream, void *out, const void *lhs, const void *rhs, size_t rows,
+                                  size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
+                                  size_t output_row_stride) {
+    return singe::gemm_bf16(static_cast<cudaStream_t>(stream), out, false, lhs, rhs, rows, columns, reduction,
+                            lhs_row_stride, rhs_row_stride, output_row_stride, 0, 1, true);
 }
 
 int singe_matmul_bf16_f32(singe_stream_t stream, float *out, const void *lhs, const void *rhs, size_t rows,
                           size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
                           size_t output_row_stride, int transpose_lhs, int transpose_rhs) {
     return singe::gemm_bf16(static_cast<cudaStream_t>(stream), out, true, lhs, rhs, rows, columns, reduction,
-                            lhs_row_stride, rhs_row_stride, output_row_stride, transpose_lhs, transpose_rhs);
+                            lhs_row_stride, rhs_row_stride, output_row_stride, transpose_lhs, transpose_rhs, false);
 }
 
 // Overrides the tile choice of the GEMM entry points for this process: block_n in {32, 64, 128, 256} and

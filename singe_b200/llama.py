@@ -218,6 +218,29 @@ class LlamaConfig:
     page_size: int = 16
 
 
+def choose_decode_splits(rows: int, key_bound: int, bytes_per_key: int, sms: int) -> int:
+    """Split count for the flash-decode kernel on ``rows`` (sequence, KV head) rows of up to ``key_bound`` keys.
+
+    A small cost model, fitted to measurements of the kernel on B200: three CTAs are resident per SM; a CTA streams
+    at most about 16 GB/s (its shared-memory ring against the loaded memory latency) and all of them together about
+    5.3 TB/s; a CTA costs about 2 us before its first page arrives; CTAs run in waves of the resident count.  The
+    fixed 512-key split is right when the rows alone fill the machine several times; with few rows (tensor-parallel
+    shards, small batches) it picks the split that fills one wave instead of one and a half."""
+    slots = 3 * sms
+    finest = max(1, (key_bound + 127) // 128)
+    best, best_time = 1, float("inf")
+    for splits in range(1, min(finest, 64) + 1):
+        ctas = rows * splits
+        chunk = key_bound / splits * bytes_per_key
+        resident = min(ctas, slots)
+        rate = min(16e9, 5.3e12 / resident)
+        waves = -(-ctas // slots)
+        elapsed = waves * (2e-6 + chunk / rate) + 0.3e-6 * splits  # the combine reads one partial per split
+        if elapsed < best_time * 0.98:  # prefer fewer splits on a near tie
+            best, best_time = splits, elapsed
+    return best
+
+
 def rotary_tables(head_dim: int, theta: float, capacity: int):
     """cos/sin [capacity, head_dim/2] in f32: inv_freq = 1 / theta^(2i/D), angle = position * inv_freq, all in f32
     (singe/src/nn/layers/positional/rotary.rs:102-105,186-205)."""
@@ -352,12 +375,9 @@ class LlamaDecoder:
         fast = config.head_dim in (64, 128) and config.page_size == 16 and config.heads // config.kv_heads <= 8
         self.fast_decode = fast
         if max_splits <= 0:
-            max_splits = max(1, min(64, (self.stride * config.page_size + 511) // 512))
-            rows = sequences * self.kv_heads
-            wanted = 4 * torch.cuda.get_device_properties(0).multi_processor_count
-            if rows * max_splits < wanted:
-                finest = max(1, (self.stride * config.page_size + 127) // 128)
-                max_splits = min(finest, max(max_splits, (wanted + rows - 1) // rows))
+            max_splits = choose_decode_splits(sequences * self.kv_heads, self.stride * config.page_size,
+                                              2 * 2 * config.head_dim,
+                                              torch.cuda.get_device_properties(0).multi_processor_count)
         self.max_splits = max_splits
         self.attn_scratch = torch.empty((t, self.heads, max_splits, config.head_dim), dtype=torch.float32, device=dev)
         self.lse_scratch = torch.empty((t, self.heads, max_splits), dtype=torch.float32, device=dev)

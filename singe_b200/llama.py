@@ -221,22 +221,24 @@ class LlamaConfig:
 def choose_decode_splits(rows: int, key_bound: int, bytes_per_key: int, sms: int) -> int:
     """Split count for the flash-decode kernel on ``rows`` (sequence, KV head) rows of up to ``key_bound`` keys.
 
-    A small cost model, fitted to measurements of the kernel on B200: three CTAs are resident per SM; a CTA streams
-    at most about 16 GB/s (its shared-memory ring against the loaded memory latency) and all of them together about
-    5.3 TB/s; a CTA costs about 2 us before its first page arrives; CTAs run in waves of the resident count.  The
-    fixed 512-key split is right when the rows alone fill the machine several times; with few rows (tensor-parallel
-    shards, small batches) it picks the split that fills one wave instead of one and a half."""
+    A small cost model fitted to the kernel on B200 (64 sequences x 2048 keys, 1 / 2 / 4 / 8 KV heads, 2 - 12 splits):
+    three CTAs are resident per SM and run in waves; a CTA streams at most about 18 GB/s (its shared-memory ring
+    against the loaded memory latency) and all resident CTAs together about 6 TB/s; a wave costs about 2 us before
+    its first page arrives; a last, partly filled wave still costs a whole CTA's time.  The fixed 512-key split is
+    fine when the rows alone fill the machine several times; with few rows (tensor-parallel shards, small batches)
+    the model picks the split that just fills one wave (6 instead of 10 splits at one KV head: 15.5 us against 20.6)."""
     slots = 3 * sms
     finest = max(1, (key_bound + 127) // 128)
     best, best_time = 1, float("inf")
     for splits in range(1, min(finest, 64) + 1):
         ctas = rows * splits
         chunk = key_bound / splits * bytes_per_key
-        resident = min(ctas, slots)
-        rate = min(16e9, 5.3e12 / resident)
-        waves = -(-ctas // slots)
-        elapsed = waves * (2e-6 + chunk / rate) + 0.3e-6 * splits  # the combine reads one partial per split
-        if elapsed < best_time * 0.98:  # prefer fewer splits on a near tie
+        full, rest = divmod(ctas, slots)
+        elapsed = full * (2e-6 + chunk / min(18e9, 6.0e12 / slots))
+        if rest:
+            elapsed += 2e-6 + chunk / min(18e9, 6.0e12 / rest)
+        elapsed += 0.2e-6 * splits  # the combine reads one partial per split
+        if elapsed < best_time:
             best, best_time = splits, elapsed
     return best
 

@@ -143,3 +143,15 @@ def test_bulk_prompt_placement_equals_stepping_token_by_token():
     a.place_prompts([5, 0, 17])
     b.step([[1] * 5, [], [2] * 17])
     assert a.pages == b.pages and a.lengths == b.lengths and a.free == b.free
+
+
+def test_decode_split_choice_fills_one_wave_when_rows_are_few():
+    # 64 sequences x 2048 keys on 148 SMs (444 resident CTAs): with one KV head per rank six splits give 384 CTAs in
+    # one wave; seven would start a second wave.  With all eight KV heads the rows alone fill the machine.
+    from singe_b200.llama import choose_decode_splits
+
+    one_head = choose_decode_splits(64, 2112, 512, 148)
+    assert 64 * one_head <= 444 < 64 * (one_head + 2)
+    assert 1 <= choose_decode_splits(512, 2112, 512, 148) <= 8
+    assert choose_decode_splits(1, 16, 512, 148) == 1          # a single page cannot be split
+    assert choose_decode_splits(1, 65536, 512, 148) > 8        # one long sequence alone is cut finely

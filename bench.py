@@ -233,6 +233,19 @@ def run_decode(args, rank, world, group):
     total_bytes = sum_over_ranks(my_bytes, group)
     value = total_bytes * args.steps / seconds / 1e9
 
+    # ---- spread: five more replays of the same graph, each timed on its own (median and p10-p90, as the
+    # reference's Benches report, singe-testing/src/bench.rs:12-40) ----
+    repeats = []
+    for _ in range(5):
+        again_start, again_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        again_start.record(stream)
+        steps_graph.replay()
+        again_stop.record(stream)
+        torch.cuda.synchronize()
+        repeats.append(again_start.elapsed_time(again_stop) / args.steps)
+    spread = {"median": round(float(np.median(repeats)), 5), "p10": round(float(np.percentile(repeats, 10)), 5),
+              "p90": round(float(np.percentile(repeats, 90)), 5), "replays": len(repeats)}
+
     # ---- the same K steps launched one by one from the host, for comparison ----
     eager_start, eager_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
@@ -289,6 +302,7 @@ def run_decode(args, rank, world, group):
                    "algorithmic_bytes_per_step_per_gpu": int(my_bytes), "l2": "inputs (277 MB) larger than L2",
                    "launch_mode": "the K timed steps are one CUDA graph; e2e replays a one-step graph per step",
                    "eager_ms_per_step": round(eager_seconds / args.steps * 1e3, 5),
+                   "repeat_ms_per_step": spread,
                    "sharding": "by sequence, no collective"},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},

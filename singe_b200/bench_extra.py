@@ -101,10 +101,50 @@ def prefill_figures(peaks) -> dict:
             "causal_gflop": round(flops / 1e9, 1), "includes": "slot-mapped KV-cache write of all 15360 tokens"}
 
 
+def paged_attention_figures(peaks) -> dict:
+    """Config 2 through the Tensor-surface entry point (FlashInfer-style paging, base-2 LSE, status word)."""
+    import numpy as np
+
+    from . import kernel_sys as ks
+
+    case = workloads.paged_decode_case()
+    generator = torch.Generator(device="cuda").manual_seed(1)
+    shape = (case.physical_blocks, case.block_size, case.kv_heads, case.head_dim)
+    key_cache = torch.randn(shape, generator=generator, device="cuda").to(torch.bfloat16)
+    value_cache = torch.randn(shape, generator=generator, device="cuda").to(torch.bfloat16)
+    query = torch.randn((case.batch, case.heads, case.head_dim), generator=generator, device="cuda").to(torch.bfloat16)
+    blocks = (case.lens.astype(np.int64) + case.block_size - 1) // case.block_size
+    page_offsets = np.concatenate([[0], np.cumsum(blocks)]).astype(np.int64)
+    pages = np.concatenate([case.block_table[b, : blocks[b]] for b in range(case.batch)]).astype(np.int64)
+    last = (case.lens.astype(np.int64) - (blocks - 1) * case.block_size).astype(np.int64)
+    query_offsets = np.arange(case.batch + 1, dtype=np.int64)
+    d = lambda a: torch.from_numpy(a).cuda()
+    d_qo, d_po, d_pages, d_last = d(query_offsets), d(page_offsets), d(pages), d(last)
+    out = torch.empty_like(query)
+    lse = torch.empty((case.batch, case.heads), dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fn = ks.lib().singe_paged_attention_bf16
+
+    def call():
+        stream = int(torch.cuda.current_stream().cuda_stream)
+        code = fn(stream, out.data_ptr(), lse.data_ptr(), query.data_ptr(), key_cache.data_ptr(),
+                  value_cache.data_ptr(), d_qo.data_ptr(), d_po.data_ptr(), d_pages.data_ptr(), d_last.data_ptr(), 8,
+                  case.batch, case.heads, case.kv_heads, case.head_dim, case.block_size, case.physical_blocks,
+                  case.batch, pages.size, case.scale, 1, 0, status.data_ptr())
+        if code != ks.OK:
+            raise RuntimeError(f"paged_attention: status {code}")
+
+    seconds = graph_seconds(call)
+    moved = float(case.algorithmic_bytes())
+    return {"us": round(seconds * 1e6, 2), "gbs": round(moved / seconds / 1e9, 1),
+            "frac_of_hbm_peak": round(moved / seconds / 1e9 / peaks["hbm_gbs"], 4),
+            "status_word": int(status.item())}
+
+
 def run_all(peaks) -> dict:
     result = {}
     for name, fn in (("kv_cache_write_config4", cache_write_figures), ("gemm_config3", gemm_figures),
-                     ("prefill_config4", prefill_figures)):
+                     ("prefill_config4", prefill_figures), ("paged_attention_config2", paged_attention_figures)):
         try:
             result[name] = fn(peaks)
         except Exception as error:

@@ -4,6 +4,8 @@
 #include <mutex>
 
 #include "attention_general.cuh"
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace singe {
@@ -16,7 +18,8 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
                         const void *query, const void *key_cache, const void *value_cache,
                         const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch, size_t heads,
                         size_t kv_heads, size_t head_dim, size_t physical_blocks, size_t block_table_batch_stride,
-                        size_t max_splits, float scale, bool partials_only, uint32_t *status);
+                        size_t max_splits, float scale, bool partials_only, uint32_t *status,
+                        const RaggedDecode *ragged);
 // prefill_tcgen05.cu
 bool prefill_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t total_query_tokens, const void *query,
                        const void *key, const void *value, const void *out);
@@ -184,8 +187,10 @@ struct TensorPagedPolicy {
     const Index *last_page_lengths;
     int sequences, heads, kv_heads, head_dim, page_size, causal;
     long long tokens, cache_pages, table_len, window;
+    const int *skip_when_zero;  // the planning kernel's verdict: 0 = the tiled decode kernel serves this call
 
     __device__ int locate(size_t row, RowPlan<T> &plan) const {
+        if (skip_when_zero != nullptr && *skip_when_zero == 0) return 0;
         const long long token = static_cast<long long>(row / heads);
         const int head = static_cast<int>(row - static_cast<size_t>(token) * heads);
         int owner = -1;
@@ -239,24 +244,77 @@ struct TensorPagedPolicy {
 };
 
 // The whole-table refusal of check_paged_values: any sequence with bad offsets, pages or last length sets the status.
+// One warp per sequence; its lanes share the sequence's page list.
 template <typename Index>
 __global__ void check_paged_values_kernel(const Index *query_offsets, const Index *page_offsets, const Index *pages,
                                           const Index *last_page_lengths, int sequences, long long tokens,
                                           long long cache_pages, long long table_len, long long page_size,
                                           uint32_t *status) {
-    for (int s = blockIdx.x * blockDim.x + threadIdx.x; s < sequences; s += gridDim.x * blockDim.x) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int s = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; s < sequences; s += warps) {
         const long long qf = static_cast<long long>(query_offsets[s]), ql = static_cast<long long>(query_offsets[s + 1]);
         const long long pf = static_cast<long long>(page_offsets[s]), pl = static_cast<long long>(page_offsets[s + 1]);
         bool bad = !(0 <= qf && qf <= ql && ql <= tokens) || !(0 <= pf && pf <= pl && pl <= table_len);
         if (!bad && pf != pl) {
             const long long last = static_cast<long long>(last_page_lengths[s]);
             bad = last < 0 || last > page_size;
-            for (long long i = pf; i < pl && !bad; ++i) {
+            for (long long i = pf + lane; i < pl && !bad; i += 32) {
                 const long long page = static_cast<long long>(pages[i]);
                 bad = page < 0 || page >= cache_pages;
             }
         }
         if (bad) report_status(status, kStatusIndexOutOfBounds);
+    }
+}
+
+// Decides, on the device, whether a Tensor-surface call is a plain decode batch (sequence b owns exactly query
+// token b, every paging value is valid) and, if so, turns the paging tensors into what the tiled decode kernel
+// reads: lens[b], first[b] (index of the sequence's first page) and the tokens per split for `split_budget` splits
+// of the longest sequence.  control[0] = 0 hands the call to the tiled kernel, 1 to the general kernel.
+template <typename Index>
+__global__ void plan_paged_decode_kernel(const Index *query_offsets, const Index *page_offsets, const Index *pages,
+                                         const Index *last_page_lengths, int sequences, long long cache_pages,
+                                         long long table_len, long long page_size, int split_budget, int *lens,
+                                         long long *first, int *control) {
+    __shared__ int shared_bad;
+    __shared__ int shared_longest;
+    if (threadIdx.x == 0) {
+        shared_bad = 0;
+        shared_longest = 0;
+    }
+    __syncthreads();
+    int bad = 0;
+    int longest = 0;
+    for (int s = threadIdx.x; s < sequences; s += blockDim.x) {
+        const long long qf = static_cast<long long>(query_offsets[s]), ql = static_cast<long long>(query_offsets[s + 1]);
+        const long long pf = static_cast<long long>(page_offsets[s]), pl = static_cast<long long>(page_offsets[s + 1]);
+        long long keys = 0;
+        if (qf != s || ql != s + 1 || !(0 <= pf && pf <= pl && pl <= table_len)) {
+            bad = 1;
+        } else if (pf != pl) {
+            const long long last = static_cast<long long>(last_page_lengths[s]);
+            if (last < 0 || last > page_size) bad = 1;
+            keys = (pl - pf - 1) * page_size + last;
+            if (keys > 0x7ffffff0ll) bad = 1;
+        }
+        lens[s] = bad ? 0 : static_cast<int>(keys);
+        first[s] = bad ? 0 : pf;
+        longest = max(longest, bad ? 0 : static_cast<int>(keys));
+    }
+    // every page id the table holds must address the cache (the general kernel skips the rows of a bad one)
+    for (long long i = threadIdx.x; i < table_len; i += blockDim.x) {
+        const long long page = static_cast<long long>(pages[i]);
+        if (page < 0 || page >= cache_pages) bad = 1;
+    }
+    if (bad) atomicExch(&shared_bad, 1);
+    atomicMax(&shared_longest, longest);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        control[0] = shared_bad;
+        const long long per = (static_cast<long long>(shared_longest) + split_budget - 1) / split_budget;
+        const long long rounded = (per + page_size - 1) / page_size * page_size;
+        control[1] = static_cast<int>(rounded < page_size ? page_size : rounded);
     }
 }
 
@@ -339,6 +397,15 @@ int workspace_for(cudaStream_t stream, size_t floats, float **data) {
     return SINGE_OK;
 }
 
+// SINGE_TENSOR_DECODE_PATH=0 keeps the general kernel for every Tensor-surface call (comparison runs).
+bool tensor_decode_path_enabled() {
+    static const bool enabled = [] {
+        const char *value = getenv("SINGE_TENSOR_DECODE_PATH");
+        return value == nullptr || value[0] != '0';
+    }();
+    return enabled;
+}
+
 // Splits the drop-in decode uses when the caller gives no budget: ~512-token splits, more when few CTAs would run.
 size_t default_splits(size_t batch, size_t kv_heads, size_t bound_tokens) {
     size_t splits = (bound_tokens + 511) / 512;
@@ -391,7 +458,7 @@ int decode_half(cudaStream_t stream, int element, void *out, const void *query, 
         SINGE_TRY(workspace_for(stream, rows * (head_dim + 1), &scratch));
         return paged_decode_splitk(stream, element, out, scratch, scratch + rows * head_dim, query, key_cache,
                                    value_cache, lens, table, batch, heads, kv_heads, head_dim, physical_blocks, stride,
-                                   splits, scale, false, device_error_word());
+                                   splits, scale, false, device_error_word(), nullptr);
     }
     if (element == 0) {
         return decode_general<__nv_bfloat16>(stream, out, query, key_cache, value_cache, lens, table, batch, heads,
@@ -418,7 +485,7 @@ int decode_splitk_half(cudaStream_t stream, int element, void *out, float *attn_
     }
     return paged_decode_splitk(stream, element, out, attn_scratch, lse_scratch, query, key_cache, value_cache, lens,
                                table, batch, heads, kv_heads, head_dim, physical_blocks, stride, max_splits, scale,
-                               partials_only, device_error_word());
+                               partials_only, device_error_word(), nullptr);
 }
 
 template <typename T>
@@ -477,12 +544,59 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
     policy.cache_pages = static_cast<long long>(cache_pages);
     policy.table_len = static_cast<long long>(table_len);
     policy.window = static_cast<long long>(window);
+    policy.skip_when_zero = nullptr;
     if (status != nullptr) {
-        const unsigned blocks = static_cast<unsigned>((sequences + 127) / 128);
-        check_paged_values_kernel<Index><<<blocks > 64 ? 64 : blocks, 128, 0, stream>>>(
+        const unsigned blocks = static_cast<unsigned>((sequences + 3) / 4);  // four warps, one sequence each
+        check_paged_values_kernel<Index><<<blocks > 256 ? 256 : blocks, 128, 0, stream>>>(
             policy.query_offsets, policy.page_offsets, policy.pages, policy.last_page_lengths, policy.sequences,
             policy.tokens, policy.cache_pages, policy.table_len, static_cast<long long>(page_size), status);
         SINGE_TRY(launch_status());
+    }
+    // One query token per sequence, no window: possibly a plain decode batch.  Whether it is one depends on the
+    // paging tensors, which live on the device, so a planning kernel decides there: it either hands the call to
+    // the tiled flash-decode kernel (and the general kernel below finds nothing to do) or leaves it to the general
+    // kernel (and the tiled kernel's CTAs leave at once).
+    constexpr bool kHalfType = sizeof(T) == 2;
+    if (kHalfType && tensor_decode_path_enabled() && tokens == sequences && window == 0 && sequences <= 65535 &&
+        paged_decode_fast_path(heads, kv_heads, head_dim, page_size, key_cache, value_cache, query)) {
+        // split budget: ~512-key splits of a sequence twice the average length (the real lengths are device data)
+        const size_t average = table_len * page_size / sequences;
+        size_t guess = 2 * average;
+        if (guess < page_size) guess = page_size;
+        const size_t splits = default_splits(sequences, kv_heads, guess);
+        const size_t rows = tokens * heads * splits;
+        const size_t partial_floats = rows * (head_dim + 1);
+        const size_t plan_floats = 3 * sequences + 16;  // lens (int32), first (int64), control
+        float *scratch = nullptr;
+        const int grown = workspace_for(stream, partial_floats + plan_floats + 4, &scratch);
+        if (grown == SINGE_OK) {
+            // 8-byte aligned plan area behind the partials
+            uintptr_t plan_at = reinterpret_cast<uintptr_t>(scratch + partial_floats);
+            plan_at = (plan_at + 7u) & ~static_cast<uintptr_t>(7u);
+            long long *first = reinterpret_cast<long long *>(plan_at);
+            int *lens = reinterpret_cast<int *>(first + sequences);
+            int *control = lens + sequences;
+            plan_paged_decode_kernel<Index><<<1, 256, 0, stream>>>(
+                policy.query_offsets, policy.page_offsets, policy.pages, policy.last_page_lengths, policy.sequences,
+                policy.cache_pages, policy.table_len, static_cast<long long>(page_size), static_cast<int>(splits), lens,
+                first, control);
+            SINGE_TRY(launch_status());
+            RaggedDecode ragged;
+            ragged.pages = pages;
+            ragged.first = first;
+            ragged.control = control;
+            ragged.index_width = static_cast<int>(sizeof(Index));
+            ragged.lse_out = lse;
+            const int element = std::is_same<T, __nv_bfloat16>::value ? 0 : 1;
+            SINGE_TRY(paged_decode_splitk(stream, element, out, scratch, scratch + rows * head_dim, query, key_cache,
+                                          value_cache, lens, nullptr, sequences, heads, kv_heads, head_dim,
+                                          cache_pages, 1, splits, scale, false,
+                                          status != nullptr ? status : device_error_word(), &ragged));
+            policy.skip_when_zero = control;
+        } else if (grown != SINGE_ERR_AUTOTUNE_DURING_CAPTURE) {
+            return grown;
+        }
+        // (workspace growth refused under stream capture: the general kernel serves the call)
     }
     return launch_attention_general<T>(stream, policy, tokens * heads, head_dim, scale, LseKind::Base2, -INFINITY,
                                        status);

@@ -43,6 +43,16 @@ inline bool fits_i32(size_t value) { return value <= static_cast<size_t>(INT32_M
 
 inline int launch_status() { return cuda_status(cudaGetLastError()); }
 
+// What the Tensor-surface paged attention hands the tiled decode kernel when a call is a plain decode batch: the
+// page list as the caller gave it, and what the planning kernel of the same call wrote into the workspace.
+struct RaggedDecode {
+    const void *pages;         // [table_len] page ids, 32- or 64-bit
+    const long long *first;    // [sequences] index of each sequence's first page in `pages`
+    const int *control;        // [0] 0 = plain decode batch (tiled kernel runs), else the general kernel runs; [1] tokens per split
+    int index_width;           // 4 or 8
+    float *lse_out;            // [tokens, heads] base-2 LSE
+};
+
 // Programmatic dependent launch.  Every kernel of the decode path is launched with the attribute that lets it start
 // while the kernel before it on the stream is still draining: its CTAs do their private set-up (barriers, tensor
 // memory, tensor-map prefetch) and then block in grid_dependency_wait() until the earlier kernel has completed and

@@ -73,10 +73,13 @@ constexpr int decode_smem_bytes() {
     return kDecodeStages * decode_stage_bytes<HD>() + 2 * kDecodeWarps * 8 * 4 + 2 * kDecodeStages * 8 + 1024;
 }
 
-template <typename T, int HD>
-__global__ void __launch_bounds__(kDecodeThreads, 3)
-    paged_decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                        const DecodeParams p) {
+// RAGGED selects the Tensor-surface form: the pages of sequence b start at ragged.first[b] in ragged.pages (32- or 64-bit
+// entries), p.lens and ragged.control were written by the planning kernel of the same call (control[0] != 0: "not a plain
+// decode batch, the general kernel runs instead"; control[1] = tokens per split), and finished rows also get their
+// base-2 LSE in ragged.lse_out.  The classic form carries none of this code and never reads `ragged`.
+template <typename T, int HD, bool RAGGED>
+__device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, const CUtensorMap &v_map,
+                                                  const DecodeParams &p, const RaggedDecode &ragged) {
     constexpr int NHALF = HD / 64;
     constexpr int KSTEPS = HD / 16;
     constexpr int NTILES = HD / 8;
@@ -94,6 +97,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     const uint32_t bar_full = base + kDecodeStages * STAGE + 2 * kDecodeWarps * 8 * 4;
     const uint32_t bar_empty = bar_full + kDecodeStages * 8;
 
+    if (RAGGED && ragged.control[0] != 0) return;
     const int split = blockIdx.x;
     const int g = blockIdx.y;
     const int tid = threadIdx.x;
@@ -108,9 +112,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     // 5 % of the whole launch.  Split 0 almost always has work and keeps the early query loads below.
     if (split > 0) {
         int early = p.lens[b];
-        const int early_bound = p.table_stride * kPageTokens;
+        const int early_bound = RAGGED ? 0x7ffffff0 : p.table_stride * kPageTokens;
         early = early < 0 ? 0 : (early > early_bound ? early_bound : early);
-        if (split * p.split_tokens >= early && !p.partials_only) return;
+        if (RAGGED) {
+            if (static_cast<long long>(split) * ragged.control[1] >= early && !p.partials_only) return;
+        } else {
+            if (split * p.split_tokens >= early && !p.partials_only) return;
+        }
     }
     // Start the query-fragment loads before the length is known: their addresses depend only on the block
     // indices, so this global round trip overlaps the length read and the block-table read.
@@ -127,9 +135,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
         }
     }
     int len = p.lens[b];
-    const int bound = p.table_stride * kPageTokens;
+    const int bound = RAGGED ? 0x7ffffff0 : p.table_stride * kPageTokens;
     len = len < 0 ? 0 : (len > bound ? bound : len);
-    const int n_splits = (len + p.split_tokens - 1) / p.split_tokens;
+    const int n_splits =
+        RAGGED ? (len + ragged.control[1] - 1) / ragged.control[1] : (len + p.split_tokens - 1) / p.split_tokens;
 
     if (split >= n_splits) {
         // Nothing to attend.  Split 0 of an empty sequence still owns the row: zeros, as the reference writes.
@@ -140,6 +149,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
                 for (int d = tid; d < HD; d += kDecodeThreads) {
                     if (owns_row) {
                         static_cast<T *>(p.out)[row * HD + d] = from_float<T>(0.0f);
+                        if (RAGGED && d == 0) ragged.lse_out[row] = -INFINITY;
                     } else {
                         p.attn_partial[(row * p.max_splits + split) * HD + d] = 0.0f;
                     }
@@ -152,7 +162,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
         return;
     }
 
-    const int piece = p.split_tokens;
+    const int piece = RAGGED ? ragged.control[1] : p.split_tokens;
     const int tok_begin = split * piece;
     const int tok_end = min(len, tok_begin + piece);
     const int npages = tok_end > tok_begin ? (tok_end - tok_begin + kPageTokens - 1) / kPageTokens : 0;
@@ -176,9 +186,19 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
             prefetch_tensor_map(&v_map);
         }
         const uint32_t *table = p.table + static_cast<size_t>(b) * p.table_stride + first_page;
+        const long long ragged_at = RAGGED ? ragged.first[b] + first_page : 0;
         for (int chunk = 0; chunk < npages && !failed; chunk += 32) {
             const int mine = chunk + lane;
-            uint32_t page = mine < npages ? table[mine] : 0u;
+            uint32_t page = (!RAGGED && mine < npages) ? table[mine] : 0u;
+            if (RAGGED && mine < npages) {
+                if (ragged.index_width == 8) {
+                    const long long wide = static_cast<const long long *>(ragged.pages)[ragged_at + mine];
+                    page = (wide < 0 || wide > 0x7fffffffll) ? 0xffffffffu : static_cast<uint32_t>(wide);
+                } else {
+                    const int narrow = static_cast<const int *>(ragged.pages)[ragged_at + mine];
+                    page = narrow < 0 ? 0xffffffffu : static_cast<uint32_t>(narrow);
+                }
+            }
             if (page >= static_cast<uint32_t>(p.physical_blocks)) {
                 report_status(p.status, kStatusIndexOutOfBounds);
                 page = 0u;
@@ -340,6 +360,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
         const float result = value / total;
         if (direct) {
             static_cast<T *>(p.out)[head_row * HD + d] = from_float<T>(result);
+            if (RAGGED && d == 0) ragged.lse_out[head_row] = top + log2f(total);
         } else {
             p.attn_partial[(head_row * p.max_splits + split) * HD + d] = result;
             if (d == 0) {
@@ -350,13 +371,41 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     }
 }
 
+template <typename T, int HD>
+__global__ void __launch_bounds__(kDecodeThreads, 3)
+    paged_decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                        const DecodeParams p) {
+    RaggedDecode none;  // never read by the classic form
+    none.pages = nullptr;
+    none.first = nullptr;
+    none.control = nullptr;
+    none.index_width = 4;
+    none.lse_out = nullptr;
+    paged_decode_body<T, HD, false>(k_map, v_map, p, none);
+}
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(kDecodeThreads, 3)
+    paged_decode_ragged_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                               const DecodeParams p, const RaggedDecode ragged) {
+    paged_decode_body<T, HD, true>(k_map, v_map, p, ragged);
+}
+
 // Folds the split partials of every (sequence, head) row that needed more than one split.
 // Follows splitk_reduce_f32 (singe-kernel/src/cpu/attention.rs:2157-2193): out = sum_s exp(lse_s - M) attn_s / sum_s exp(lse_s - M).
-template <typename T>
+// RAGGED: the Tensor-surface form (split size and verdict from the planning kernel, base-2 LSE written too); the
+// classic form is a separate instantiation so that it carries none of that code (it measured 2 % slower with it).
+template <typename T, bool RAGGED>
 __global__ void decode_combine_kernel(T *out, const float *attn_partial, const float *lse_partial, const int32_t *lens,
-                                      int heads, int head_dim, int split_tokens, int max_splits, int bound) {
+                                      int heads, int head_dim, int split_tokens, int max_splits, int bound,
+                                      const int *ragged_control, float *lse_out) {
     grid_launch_dependents();
     grid_dependency_wait();
+    if (RAGGED) {
+        if (ragged_control[0] != 0) return;
+        split_tokens = ragged_control[1];
+        bound = 0x7ffffff0;
+    }
     const int b = blockIdx.y;
     const int head = blockIdx.x;
     int len = lens[b];
@@ -378,15 +427,24 @@ __global__ void decode_combine_kernel(T *out, const float *attn_partial, const f
         }
         out[row * head_dim + d] = from_float<T>(sum / denom);
     }
+    if (RAGGED && threadIdx.x == 0) {
+        lse_out[row] = (top + logf(denom)) * 1.4426950408889634f;  // natural log -> base 2
+    }
 }
 
-template <typename T, int HD>
-int launch_decode(cudaStream_t stream, const DecodeParams &params, const void *key_cache, const void *value_cache,
-                  size_t batch) {
+template <typename T, int HD, bool RAGGED>
+int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedDecode &shape, const void *key_cache,
+                  const void *value_cache, size_t batch) {
     static bool configured = false;
     constexpr int smem = decode_smem_bytes<HD>();
     if (!configured) {
-        SINGE_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (RAGGED) {
+            SINGE_CUDA_TRY(cudaFuncSetAttribute(paged_decode_ragged_kernel<T, HD>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        } else {
+            SINGE_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<T, HD>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        }
         configured = true;
     }
     CUtensorMap k_map, v_map;
@@ -402,9 +460,13 @@ int launch_decode(cudaStream_t stream, const DecodeParams &params, const void *k
                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B));
     dim3 grid(static_cast<unsigned>(params.max_splits), static_cast<unsigned>(params.kv_heads),
               static_cast<unsigned>(batch));
-    SINGE_CUDA_TRY(launch_dependent(paged_decode_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream, kLaunchDecode, 1, k_map,
-                                    v_map,
-                                    params));
+    if (RAGGED) {
+        SINGE_CUDA_TRY(launch_dependent(paged_decode_ragged_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,
+                                        kLaunchDecode, 1, k_map, v_map, params, shape));
+    } else {
+        SINGE_CUDA_TRY(launch_dependent(paged_decode_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,
+                                        kLaunchDecode, 1, k_map, v_map, params));
+    }
     return launch_status();
 }
 
@@ -433,8 +495,16 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
                         const void *query, const void *key_cache, const void *value_cache,
                         const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch, size_t heads,
                         size_t kv_heads, size_t head_dim, size_t physical_blocks, size_t block_table_batch_stride,
-                        size_t max_splits, float scale, bool partials_only, uint32_t *status) {
+                        size_t max_splits, float scale, bool partials_only, uint32_t *status,
+                        const RaggedDecode *ragged) {
     DecodeParams params;
+    RaggedDecode none;
+    none.pages = nullptr;
+    none.first = nullptr;
+    none.control = nullptr;
+    none.index_width = 4;
+    none.lse_out = nullptr;
+    const RaggedDecode &shape = ragged != nullptr ? *ragged : none;
     params.out = out;
     params.attn_partial = attn_scratch;
     params.lse_partial = lse_scratch;
@@ -458,29 +528,47 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
     }
     int result;
     if (element == 0) {
-        result = head_dim == 128 ? launch_decode<__nv_bfloat16, 128>(stream, params, key_cache, value_cache, batch)
-                                 : launch_decode<__nv_bfloat16, 64>(stream, params, key_cache, value_cache, batch);
+        if (ragged != nullptr) {
+            result = head_dim == 128
+                         ? launch_decode<__nv_bfloat16, 128, true>(stream, params, shape, key_cache, value_cache, batch)
+                         : launch_decode<__nv_bfloat16, 64, true>(stream, params, shape, key_cache, value_cache, batch);
+        } else {
+            result = head_dim == 128
+                         ? launch_decode<__nv_bfloat16, 128, false>(stream, params, shape, key_cache, value_cache, batch)
+                         : launch_decode<__nv_bfloat16, 64, false>(stream, params, shape, key_cache, value_cache, batch);
+        }
     } else {
-        result = head_dim == 128 ? launch_decode<__half, 128>(stream, params, key_cache, value_cache, batch)
-                                 : launch_decode<__half, 64>(stream, params, key_cache, value_cache, batch);
+        if (ragged != nullptr) {
+            result = head_dim == 128 ? launch_decode<__half, 128, true>(stream, params, shape, key_cache, value_cache, batch)
+                                     : launch_decode<__half, 64, true>(stream, params, shape, key_cache, value_cache, batch);
+        } else {
+            result = head_dim == 128 ? launch_decode<__half, 128, false>(stream, params, shape, key_cache, value_cache, batch)
+                                     : launch_decode<__half, 64, false>(stream, params, shape, key_cache, value_cache, batch);
+        }
     }
     SINGE_TRY(result);
     if (!partials_only && max_splits > 1) {
         dim3 grid(static_cast<unsigned>(heads), static_cast<unsigned>(batch));
         const int threads = head_dim >= 128 ? 128 : 64;
+#define SINGE_COMBINE(T, RAGGED_)                                                                                  \
+    SINGE_CUDA_TRY(launch_dependent(decode_combine_kernel<T, RAGGED_>, grid, dim3(threads), 0, stream, kLaunchCombine, \
+                                    1, static_cast<T *>(out), attn_scratch, lse_scratch, actual_seq_lens,            \
+                                    params.heads, static_cast<int>(head_dim), params.split_tokens,                   \
+                                    params.max_splits, static_cast<int>(bound), shape.control, shape.lse_out))
         if (element == 0) {
-            SINGE_CUDA_TRY(launch_dependent(decode_combine_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream,
-                                            kLaunchCombine, 1,
-                                            static_cast<__nv_bfloat16 *>(out), attn_scratch, lse_scratch,
-                                            actual_seq_lens, params.heads, static_cast<int>(head_dim),
-                                            params.split_tokens, params.max_splits, static_cast<int>(bound)));
+            if (ragged != nullptr) {
+                SINGE_COMBINE(__nv_bfloat16, true);
+            } else {
+                SINGE_COMBINE(__nv_bfloat16, false);
+            }
         } else {
-            SINGE_CUDA_TRY(launch_dependent(decode_combine_kernel<__half>, grid, dim3(threads), 0, stream,
-                                            kLaunchCombine, 1,
-                                            static_cast<__half *>(out), attn_scratch, lse_scratch, actual_seq_lens,
-                                            params.heads, static_cast<int>(head_dim), params.split_tokens,
-                                            params.max_splits, static_cast<int>(bound)));
+            if (ragged != nullptr) {
+                SINGE_COMBINE(__half, true);
+            } else {
+                SINGE_COMBINE(__half, false);
+            }
         }
+#undef SINGE_COMBINE
         return launch_status();
     }
     return SINGE_OK;
@@ -574,7 +662,7 @@ int singe_paged_kv_decode_attention_static_bf16(singe_stream_t stream, void *out
     // array has to start at zero; what an earlier call left behind is never read.
     return paged_decode_splitk(static_cast<cudaStream_t>(stream), 0, out, scratch, scratch + rows * head_dim, query,
                                key_cache, value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim,
-                               physical_blocks, block_table_batch_stride, splits, scale, false, device_error_word());
+                               physical_blocks, block_table_batch_stride, splits, scale, false, device_error_word(), nullptr);
 }
 
 }  // extern "C"

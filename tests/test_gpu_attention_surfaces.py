@@ -178,3 +178,70 @@ def test_tensor_paged_attention_mixes_prefill_and_decode_rows(dtype, bf16):
         else:
             assert_close_f32(host(out), ref_out, f"tensor paged out causal={causal} window={window}")
         assert_close_f32(host(lse), ref_lse, "tensor paged lse (base 2)", 2e-4)
+
+
+def _decode_batch(rng, lens, heads, kv_heads, page=16, head_dim=128, spare=3):
+    pages_per = [(n + page - 1) // page for n in lens]
+    pool = sum(pages_per) + spare
+    pages = rng.permutation(pool)[: sum(pages_per)].astype(np.int64)
+    page_offsets = np.concatenate([[0], np.cumsum(pages_per)]).astype(np.int64)
+    last = np.asarray([(n - 1) % page + 1 if n > 0 else 0 for n in lens], dtype=np.int64)
+    q = workloads.normal_bf16(rng, (len(lens), heads, head_dim))
+    kc = workloads.normal_bf16(rng, (pool, page, kv_heads, head_dim))
+    vc = workloads.normal_bf16(rng, (pool, page, kv_heads, head_dim))
+    return q, kc, vc, pages, page_offsets, last
+
+
+@pytest.mark.parametrize("index_dtype", [np.int64, np.int32])
+@pytest.mark.parametrize("lens", [[1, 700, 16, 0, 2049, 513], [4096, 128], [33] * 40])
+def test_a_plain_decode_batch_through_the_tensor_surface_takes_the_tiled_kernel_and_matches(lens, index_dtype):
+    # One query token per sequence, bf16, head_dim 128, 16-token pages: the planning kernel hands the call to the
+    # tiled flash-decode kernel (split-K for the long sequences, zeros and -inf for the empty one); out and the base-2
+    # LSE must match the CPU restatement of attend_paged like any other call.
+    rng = np.random.default_rng(31 + len(lens))
+    heads, kv_heads = 8, 2
+    q, kc, vc, pages, page_offsets, last = _decode_batch(rng, lens, heads, kv_heads)
+    query_offsets = np.arange(len(lens) + 1, dtype=np.int64)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cast = lambda a: dev(np.asarray(a, dtype=index_dtype))
+    scale = 1.0 / np.sqrt(128.0)
+    out, lse = ops.paged_attention(dev(q, torch.bfloat16), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16),
+                                   cast(query_offsets), cast(page_offsets), cast(pages), cast(last), scale=scale,
+                                   causal=True, status=status)
+    torch.cuda.synchronize()
+    code, ref_out, ref_lse = oracle.attend_paged_f32(q, kc, vc, query_offsets, page_offsets, pages, last, scale=scale,
+                                                     causal=True)
+    assert code == oracle.OK and int(status.item()) == 0 and ops.take_device_error() == 0
+    assert_close_bf16(host(out), ref_out, f"tensor-surface decode out lens={lens[:4]}")
+    got_lse, finite = host(lse), np.isfinite(ref_lse)
+    assert (np.isneginf(got_lse) == np.isneginf(ref_lse)).all()
+    assert np.abs(got_lse[finite] - ref_lse[finite]).max() < 5e-3
+
+
+def test_a_batch_that_only_looks_like_decode_is_left_to_the_general_kernel():
+    # tokens == sequences, but sequence 0 owns two query tokens and sequence 1 none: the planning kernel must not hand
+    # this to the tiled kernel.  Then a bad page id in an otherwise plain decode batch: status 1, no fault.
+    rng = np.random.default_rng(41)
+    heads, kv_heads = 8, 2
+    lens = [40, 0, 300]
+    q, kc, vc, pages, page_offsets, last = _decode_batch(rng, lens, heads, kv_heads)
+    query_offsets = np.asarray([0, 2, 2, 3], dtype=np.int64)
+    scale = 0.1
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, lse = ops.paged_attention(dev(q, torch.bfloat16), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16),
+                                   dev(query_offsets), dev(page_offsets), dev(pages), dev(last), scale=scale,
+                                   causal=True, status=status)
+    code, ref_out, ref_lse = oracle.attend_paged_f32(q, kc, vc, query_offsets, page_offsets, pages, last, scale=scale,
+                                                     causal=True)
+    assert code == oracle.OK and int(status.item()) == 0
+    assert_close_bf16(host(out), ref_out, "two queries in one sequence")
+    finite = np.isfinite(ref_lse)
+    assert np.abs(host(lse)[finite] - ref_lse[finite]).max() < 5e-3
+    bad = pages.copy()
+    bad[5] = kc.shape[0]  # one past the cache
+    status.zero_()
+    ops.paged_attention(dev(q, torch.bfloat16), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16),
+                        dev(np.arange(4, dtype=np.int64)), dev(page_offsets), dev(bad), dev(last), scale=scale,
+                        causal=True, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1

@@ -461,6 +461,10 @@ def run_only(args):
                                                              case.block_size, case.physical_blocks,
                                                              case.block_table_batch_stride, case.scale)
         call = lambda: ops.paged_kv_decode_attention(out, query, key_cache, value_cache, lens, table, config)
+    elif kind == "paged_attention":
+        from singe_b200 import bench_extra
+
+        call, _, _ = bench_extra.paged_attention_call()
     elif kind == "gemm":
         m, n, k = (int(v) for v in detail.split(","))
         x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
@@ -519,7 +523,7 @@ def main():
     parser.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                         help="how the decode step's two collectives per layer run at --gpus > 1")
     parser.add_argument("--only", default="", help="profiling aid: launch one kernel a few times and exit "
-                        "(decode | gemm:M,N,K | prefill[:len,len,...] | kvwrite | step:LAYERS[:TP])")
+                        "(decode | paged_attention | gemm:M,N,K | prefill[:len,len,...] | kvwrite | step:LAYERS[:TP])")
     args = parser.parse_args()
 
     if args.impl == "reference":

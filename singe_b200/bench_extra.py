@@ -101,8 +101,9 @@ def prefill_figures(peaks) -> dict:
             "causal_gflop": round(flops / 1e9, 1), "includes": "slot-mapped KV-cache write of all 15360 tokens"}
 
 
-def paged_attention_figures(peaks) -> dict:
-    """Config 2 through the Tensor-surface entry point (FlashInfer-style paging, base-2 LSE, status word)."""
+def paged_attention_call():
+    """Config 2 through the Tensor-surface entry point (FlashInfer-style paging, base-2 LSE, status word): returns
+    (call, case, status) with every buffer resident on the device."""
     import numpy as np
 
     from . import kernel_sys as ks
@@ -134,6 +135,11 @@ def paged_attention_figures(peaks) -> dict:
         if code != ks.OK:
             raise RuntimeError(f"paged_attention: status {code}")
 
+    return call, case, status
+
+
+def paged_attention_figures(peaks) -> dict:
+    call, case, status = paged_attention_call()
     seconds = graph_seconds(call)
     moved = float(case.algorithmic_bytes())
     return {"us": round(seconds * 1e6, 2), "gbs": round(moved / seconds / 1e9, 1),

@@ -26,7 +26,8 @@ bool prefill_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t to
 int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void *query, const void *key,
                          const void *value, const int32_t *lens_q, const int32_t *lens_kv, const int32_t *offsets,
                          size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads,
-                         size_t kv_heads, size_t head_dim, int causal, float scale);
+                         size_t kv_heads, size_t head_dim, int causal, float scale, const uint32_t *block_table,
+                         size_t table_stride, size_t cache_pages);
 // kv_cache_write.cu
 int kv_cache_write(cudaStream_t stream, void *key_cache, void *value_cache, const void *keys, const void *values,
                    const void *write_pages, const void *write_slots, int index_width, size_t tokens, size_t kv_heads,
@@ -877,6 +878,24 @@ int singe_paged_attention_f32(singe_stream_t stream, float *out, float *lse, con
                                      page_size, cache_pages, sequences, table_len, scale, causal, window, status);
 }
 
+// bf16, head_dim 128, 16-token pages: the tcgen05 prefill kernel gathers its K/V tiles through the block table.
+// Returns true when it took the call (its status is then in *status).
+static bool paged_prefill_tensor_core(bool is_bf16, singe_stream_t stream, void *out, float *lse, const void *query, const void *key_cache,
+                               const void *value_cache, const int32_t *lens_q, const int32_t *lens_kv,
+                               const int32_t *offsets, const uint32_t *block_table, size_t batch,
+                               size_t total_query_tokens, size_t heads, size_t kv_heads, size_t head_dim,
+                               size_t block_size, size_t physical_blocks, size_t stride, int causal, float scale,
+                               int *status) {
+    if (!is_bf16 || block_size != 16 ||
+        !prefill_fast_path(heads, kv_heads, head_dim, total_query_tokens, query, key_cache, value_cache, out)) {
+        return false;
+    }
+    *status = singe::prefill_tcgen05_bf16(static_cast<cudaStream_t>(stream), out, lse, query, key_cache, value_cache, lens_q,
+                                   lens_kv, offsets, batch, total_query_tokens, 0, heads, kv_heads, head_dim, causal,
+                                   scale, block_table, stride, physical_blocks);
+    return true;
+}
+
 #define SINGE_PAGED_PREFILL(NAME, T, POINTER)                                                                         \
     int NAME(singe_stream_t stream, POINTER *out, float *lse, const POINTER *query, const POINTER *key_cache,         \
              const POINTER *value_cache, const int32_t *actual_seq_lens_q, const int32_t *actual_seq_lens_kv,         \
@@ -889,6 +908,13 @@ int singe_paged_attention_f32(singe_stream_t stream, float *out, float *lse, con
             actual_seq_lens_q == nullptr || actual_seq_lens_kv == nullptr || actual_seq_offsets == nullptr ||         \
             block_table == nullptr) {                                                                                 \
             return SINGE_ERR_NULL_POINTER;                                                                            \
+        }                                                                                                             \
+        int tensor_core_status = SINGE_OK;                                                                            \
+        if (paged_prefill_tensor_core(std::is_same<T, __nv_bfloat16>::value, stream, out, lse, query, key_cache, value_cache, actual_seq_lens_q,          \
+                                         actual_seq_lens_kv, actual_seq_offsets, block_table, batch,                  \
+                                         total_query_tokens, heads, kv_heads, head_dim, block_size, physical_blocks,  \
+                                         block_table_batch_stride, causal, scale, &tensor_core_status)) {             \
+            return tensor_core_status;                                                                                \
         }                                                                                                             \
         return packed_prefill_general<T>(static_cast<cudaStream_t>(stream), out, lse, query, key_cache, value_cache,  \
                                          actual_seq_lens_q, actual_seq_lens_kv, actual_seq_offsets, block_table,      \
@@ -929,7 +955,7 @@ int singe_ragged_kv_prefill_attention_bf16(singe_stream_t stream, void *out, flo
     if (prefill_fast_path(heads, kv_heads, head_dim, total_query_tokens, query, key, value, out)) {
         return prefill_tcgen05_bf16(static_cast<cudaStream_t>(stream), out, lse, query, key, value, actual_seq_lens_q,
                                     actual_seq_lens_kv, actual_seq_offsets, batch, total_query_tokens,
-                                    total_kv_tokens, heads, kv_heads, head_dim, causal, scale);
+                                    total_kv_tokens, heads, kv_heads, head_dim, causal, scale, nullptr, 0, 0);
     }
     return packed_prefill_general<__nv_bfloat16>(static_cast<cudaStream_t>(stream), out, lse, query, key, value,
                                                  actual_seq_lens_q, actual_seq_lens_kv, actual_seq_offsets, nullptr,

@@ -49,6 +49,8 @@ constexpr int kChunk = 32;           // score columns taken out of tensor memory
 constexpr int kHeadDim = 128;
 constexpr int kHalfTileBytes = kTile * 128;       // one TMA box: 128 rows x 128 bytes
 constexpr int kTileBytes = 2 * kHalfTileBytes;    // 32 KB
+constexpr int kPageTokens = 16;                   // paged form: tokens per cache page
+constexpr int kPageBytes = kPageTokens * 128;     // one page box: 16 rows x 128 bytes
 constexpr int kMaxRankTiles = 1024;               // heaviest-first dispatch: sequences up to 256 Ki tokens
 constexpr float kRescaleThreshold = 8.0f;         // two-pass tiles: re-base when the max grew by 2^8 (log2 units)
 constexpr float kRebaseLimit = 65536.0f;          // single-pass tiles: re-base a row when its sum passes 2^16
@@ -70,6 +72,10 @@ struct PrefillParams {
     int kv_heads;
     int total_q;
     int total_kv;
+    // paged form: keys and values live in a cache [pages, 16, kv_heads, 128] behind a block table [batch, table_stride]
+    const uint32_t *block_table;
+    int table_stride;
+    int cache_pages;
     int causal;
     float scale_log2;
     uint32_t *error;
@@ -182,6 +188,7 @@ __device__ __forceinline__ void scale_o_row(uint32_t tmem_o, float factor) {
 struct Item {
     int head;
     int kv_head;
+    int seq;        // sequence index (row of the block table in the paged form)
     int offset;     // first packed row of the sequence
     int q0;         // sequence-local index of the first query row
     int len_q;
@@ -235,6 +242,7 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
         }
     }
     item.valid = false;
+    item.seq = seq < 0 ? 0 : seq;
     item.offset = 0;
     item.q0 = max(pair, 0) * kPair;
     item.len_q = 0;
@@ -245,7 +253,9 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
     item.len_q = max(p.lens_q[seq], 0);
     item.len_kv = max(p.lens_kv[seq], 0);
     item.offset = p.offsets[seq];
-    item.valid = item.offset >= 0 && item.offset + item.len_q <= p.total_q && item.offset + item.len_kv <= p.total_kv;
+    item.valid = item.offset >= 0 && item.offset + item.len_q <= p.total_q &&
+                 (p.block_table != nullptr ? item.len_kv <= p.table_stride * kPageTokens
+                                           : item.offset + item.len_kv <= p.total_kv);
     if (!item.valid) return item;
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
@@ -265,7 +275,9 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
 // last tile and epilogue.  Softmax is single-pass after an item's first key tile.
 // SAFE = true: the second launch, same grid and same shares: it leaves at once unless the flag above is raised, and
 // otherwise recomputes it with the exact row maximum on every tile.
-template <bool SAFE>
+// PAGED: K and V tiles are gathered from 16-token cache pages through the block table (eight page boxes per
+// 128-key tile and 64-wide half; the boxes land back to back, which is the layout one 128-row box would have).
+template <bool SAFE, bool PAGED>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
     prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                            const __grid_constant__ CUtensorMap v_map, const PrefillParams p) {
@@ -420,8 +432,30 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                     failed = true;
                     break;
                 }
-                if (lane == 0) {
-                    mbar_expect_tx(bar_k_full + stage * 8, kTileBytes);
+                // paged form: lanes 0-15 each own one (page, half) box of the tile; a page past the sequence's last
+                // one is replaced by the sequence's first page (finite data that the mask hides), a page id outside
+                // the cache likewise, with status 1
+                int32_t page = 0;
+                if (PAGED) {
+                    const int pages_of_sequence = (item.len_kv + kPageTokens - 1) / kPageTokens;
+                    const int wanted = j * (kTile / kPageTokens) + (lane & 7);
+                    const uint32_t *row = p.block_table + static_cast<size_t>(item.seq) * p.table_stride;
+                    uint32_t id = row[wanted < pages_of_sequence ? wanted : 0];
+                    if (id >= static_cast<uint32_t>(p.cache_pages)) {
+                        report_status(p.error, kStatusIndexOutOfBounds);
+                        id = 0u;
+                    }
+                    page = static_cast<int32_t>(id);
+                }
+                if (lane == 0) mbar_expect_tx(bar_k_full + stage * 8, kTileBytes);
+                __syncwarp();
+                if (PAGED) {
+                    if (lane < 16) {
+                        const int half = lane >> 3;
+                        tma_load_4d(k_smem + stage * kTileBytes + half * kHalfTileBytes + (lane & 7) * kPageBytes, &k_map,
+                                    bar_k_full + stage * 8, half * 64, item.kv_head, 0, page);
+                    }
+                } else if (lane == 0) {
                     tma_load_3d(k_smem + stage * kTileBytes, &k_map, bar_k_full + stage * 8, 0, item.kv_head, row0);
                     tma_load_3d(k_smem + stage * kTileBytes + kHalfTileBytes, &k_map, bar_k_full + stage * 8, 64,
                                 item.kv_head, row0);
@@ -430,8 +464,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                     failed = true;
                     break;
                 }
-                if (lane == 0) {
-                    mbar_expect_tx(bar_v_full + stage * 8, kTileBytes);
+                if (lane == 0) mbar_expect_tx(bar_v_full + stage * 8, kTileBytes);
+                __syncwarp();
+                if (PAGED) {
+                    if (lane < 16) {
+                        const int half = lane >> 3;
+                        tma_load_4d(v_smem + stage * kTileBytes + half * kHalfTileBytes + (lane & 7) * kPageBytes, &v_map,
+                                    bar_v_full + stage * 8, half * 64, item.kv_head, 0, page);
+                    }
+                } else if (lane == 0) {
                     tma_load_3d(v_smem + stage * kTileBytes, &v_map, bar_v_full + stage * 8, 0, item.kv_head, row0);
                     tma_load_3d(v_smem + stage * kTileBytes + kHalfTileBytes, &v_map, bar_v_full + stage * 8, 64,
                                 item.kv_head, row0);
@@ -727,18 +768,39 @@ bool prefill_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t to
     return head_dim == kHeadDim && heads % kv_heads == 0 && heads <= 65535 && (all & 15u) == 0;
 }
 
+namespace {
+
+template <bool PAGED>
+int launch_prefill(cudaStream_t stream, const CUtensorMap &q_map, const CUtensorMap &k_map, const CUtensorMap &v_map,
+                   const PrefillParams &params, unsigned persistent) {
+    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<false, PAGED>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
+    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<true, PAGED>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
+    prefill_tcgen05_kernel<false, PAGED><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map,
+                                                                                                params);
+    SINGE_TRY(launch_status());
+    // Redo pass over the same shares: a no-op while the device's out-of-range flag has never been raised.
+    prefill_tcgen05_kernel<true, PAGED><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map,
+                                                                                               params);
+    return launch_status();
+}
+
+}  // namespace
+
+// Packed queries over packed keys/values (block_table == nullptr: key/value are [total_kv_tokens, kv_heads, 128]) or
+// over a paged cache (key/value are [cache_pages, 16, kv_heads, 128], rows of block_table [batch, table_stride] list
+// each sequence's pages).
 int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void *query, const void *key,
                          const void *value, const int32_t *lens_q, const int32_t *lens_kv, const int32_t *offsets,
                          size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads,
-                         size_t kv_heads, size_t head_dim, int causal, float scale) {
+                         size_t kv_heads, size_t head_dim, int causal, float scale, const uint32_t *block_table,
+                         size_t table_stride, size_t cache_pages) {
     if (head_dim != kHeadDim) return SINGE_ERR_UNSUPPORTED_WIDTH;
-    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        kPrefillSmem));
-    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        kPrefillSmem));
     int device = 0, sms = 0;
     SINGE_CUDA_TRY(cudaGetDevice(&device));
     SINGE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const bool paged = block_table != nullptr;
     CUtensorMap q_map, k_map, v_map;
     const uint32_t box[3] = {64, 1, kTile};
     {
@@ -747,7 +809,15 @@ int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void 
         SINGE_TRY(encode_tensor_map(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, query, dims, strides, box,
                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
     }
-    {
+    if (paged) {
+        const uint64_t dims[4] = {kHeadDim, kv_heads, kPageTokens, cache_pages};
+        const uint64_t strides[3] = {kHeadDim * 2, kHeadDim * 2 * kv_heads, kHeadDim * 2 * kv_heads * kPageTokens};
+        const uint32_t page_box[4] = {64, 1, kPageTokens, 1};
+        SINGE_TRY(encode_tensor_map(&k_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, key, dims, strides, page_box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+        SINGE_TRY(encode_tensor_map(&v_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, value, dims, strides, page_box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+    } else {
         const uint64_t dims[3] = {kHeadDim, kv_heads, total_kv_tokens};
         const uint64_t strides[2] = {kHeadDim * 2, kHeadDim * 2 * kv_heads};
         SINGE_TRY(encode_tensor_map(&k_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, key, dims, strides, box,
@@ -766,6 +836,9 @@ int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void 
     params.kv_heads = static_cast<int>(kv_heads);
     params.total_q = static_cast<int>(total_query_tokens);
     params.total_kv = static_cast<int>(total_kv_tokens);
+    params.block_table = block_table;
+    params.table_stride = static_cast<int>(table_stride);
+    params.cache_pages = static_cast<int>(cache_pages);
     params.causal = causal ? 1 : 0;
     params.scale_log2 = scale * 1.4426950408889634f;
     params.error = device_error_word();
@@ -774,11 +847,8 @@ int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void 
     if (items > 0x7fffffffull) return SINGE_ERR_LENGTH_EXCEEDS_I32;
     if (items == 0) return SINGE_OK;
     const unsigned persistent = static_cast<unsigned>(items < static_cast<size_t>(sms) ? items : sms);
-    prefill_tcgen05_kernel<false><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
-    SINGE_TRY(launch_status());
-    // Redo pass over the same shares: a no-op while the device's out-of-range flag has never been raised.
-    prefill_tcgen05_kernel<true><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
-    return launch_status();
+    return paged ? launch_prefill<true>(stream, q_map, k_map, v_map, params, persistent)
+                 : launch_prefill<false>(stream, q_map, k_map, v_map, params, persistent);
 }
 
 }  // namespace singe

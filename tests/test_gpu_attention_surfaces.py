@@ -245,3 +245,42 @@ def test_a_batch_that_only_looks_like_decode_is_left_to_the_general_kernel():
                         causal=True, status=status)
     torch.cuda.synchronize()
     assert int(status.item()) == 1
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_paged_prefill_bf16_gathers_its_key_tiles_through_the_block_table(causal):
+    # bf16, head_dim 128, 16-token pages: the tensor-core prefill kernel reads K and V page by page from a permuted
+    # pool.  Sequences with more keys than queries, fewer keys than queries, no keys at all, and a ragged last page.
+    rng = np.random.default_rng(51)
+    heads, kv_heads, head_dim, block = 8, 2, 128, 16
+    lens_q = np.array([300, 1, 129, 40, 257], dtype=np.int32)
+    lens_kv = np.array([300, 517, 100, 0, 257], dtype=np.int32)
+    offsets = np.concatenate([[0], np.cumsum(lens_q)[:-1]]).astype(np.int32)
+    total = int(lens_q.sum())
+    stride = 40
+    pages_per = (lens_kv + block - 1) // block
+    pool = int(pages_per.sum()) + 5
+    perm = rng.permutation(pool).astype(np.uint32)
+    table = np.zeros((len(lens_q), stride), dtype=np.uint32)
+    at = 0
+    for b, n in enumerate(pages_per):
+        table[b, :n] = perm[at: at + n]
+        at += int(n)
+    q = workloads.normal_bf16(rng, (total, heads, head_dim))
+    kc = workloads.normal_bf16(rng, (pool, block, kv_heads, head_dim))
+    vc = workloads.normal_bf16(rng, (pool, block, kv_heads, head_dim))
+    scale = 1.0 / np.sqrt(128.0)
+    cfg = ops.PagedKvPrefillAttentionConfig(len(lens_q), total, heads, kv_heads, head_dim, block, pool, stride, causal,
+                                            scale)
+    out = torch.full((total, heads, head_dim), 7.0, dtype=torch.bfloat16, device="cuda")
+    lse = torch.full((total, heads), 7.0, device="cuda")
+    ops.paged_kv_prefill_attention(out, lse, dev(q, torch.bfloat16), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16),
+                                   dev(lens_q), dev(lens_kv), dev(offsets), dev_u32(table), cfg)
+    torch.cuda.synchronize()
+    assert ops.take_device_error() == 0
+    ref_out, ref_lse = oracle.paged_kv_prefill_attention_f32(
+        q, kc, vc, lens_q, lens_kv, offsets, table, batch=len(lens_q), total_query_tokens=total, heads=heads,
+        kv_heads=kv_heads, head_dim=head_dim, block_size=block, block_table_batch_stride=stride, causal=causal,
+        scale=scale)
+    assert_close_bf16(host(out), ref_out, f"paged prefill bf16 out causal={causal}")
+    assert_close_f32(host(lse), ref_lse, f"paged prefill bf16 lse causal={causal}", 2e-3)

@@ -5,6 +5,7 @@ device; every kernel is timed with CUDA events around a CUDA graph of repeated l
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from . import ops, workloads
@@ -96,9 +97,27 @@ def prefill_figures(peaks) -> dict:
                                                 cache_write=(key_cache, value_cache, pages, slots, status)),
         reps=3)
     flops = case.causal_flops()
-    return {"us": round(seconds * 1e6, 1), "tflops": round(flops / seconds / 1e12, 1),
-            "frac_of_bf16_peak": round(flops / seconds / 1e12 / peaks["bf16_tflops"], 4),
-            "causal_gflop": round(flops / 1e9, 1), "includes": "slot-mapped KV-cache write of all 15360 tokens"}
+    figures = {"us": round(seconds * 1e6, 1), "tflops": round(flops / seconds / 1e12, 1),
+               "frac_of_bf16_peak": round(flops / seconds / 1e12 / peaks["bf16_tflops"], 4),
+               "causal_gflop": round(flops / 1e9, 1), "includes": "slot-mapped KV-cache write of all 15360 tokens"}
+    # The same attention read back out of the cache the call above filled: K/V tiles gathered page by page.
+    table = torch.from_numpy(case.block_table.view(np.int32)).cuda()
+    paged_out = torch.empty_like(q)
+    paged_lse = torch.empty_like(lse)
+    paged = ops.PagedKvPrefillAttentionConfig(len(case.lens), total, case.heads, case.kv_heads, case.head_dim,
+                                              case.page_size, case.pages, case.block_table.shape[1], True, case.scale)
+    seconds = graph_seconds(
+        lambda: ops.paged_kv_prefill_attention(paged_out, paged_lse, q, key_cache, value_cache, lens, lens, offsets,
+                                               table, paged),
+        reps=3)
+    torch.cuda.synchronize()
+    if not torch.allclose(paged_out.float(), out.float(), atol=2e-2, rtol=1e-2):
+        raise RuntimeError("paged prefill differs from ragged prefill over the same keys and values")
+    figures["paged"] = {"us": round(seconds * 1e6, 1), "tflops": round(flops / seconds / 1e12, 1),
+                        "frac_of_bf16_peak": round(flops / seconds / 1e12 / peaks["bf16_tflops"], 4),
+                        "bit_identical_to_ragged": bool(torch.equal(paged_out, out)),
+                        "reads": "K/V from the 16-token cache pages through the block table"}
+    return figures
 
 
 def paged_attention_call():

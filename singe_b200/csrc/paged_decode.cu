@@ -6,7 +6,7 @@
 // the combine of splitk_reduce_f32 (singe-kernel/src/cpu/attention.rs:2157-2193).
 //
 // Structure (HBM-bound; 2 * kv_heads * head_dim * 2 bytes per cached token must cross HBM once):
-//   grid  = (max_splits, kv_heads, batch); one CTA owns up to `split_tokens` keys of one (sequence,
+//   grid  = (kv_heads, max_splits, batch); one CTA owns up to `split_tokens` keys of one (sequence,
 //           KV head) and ALL query heads of that KV head, so K and V are read once for the group.
 //   warp 4 (producer): reads the block table 32 entries at a time and issues one TMA tile load per
 //           (page, 64-wide half of the head) -- 16 rows x 128 bytes, SWIZZLE_128B -- for K and V into a
@@ -98,8 +98,8 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
     const uint32_t bar_empty = bar_full + kDecodeStages * 8;
 
     if (RAGGED && ragged.control[0] != 0) return;
-    const int split = blockIdx.x;
-    const int g = blockIdx.y;
+    const int g = blockIdx.x;
+    const int split = blockIdx.y;
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
@@ -107,21 +107,23 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
 
     const int b = blockIdx.z;
 
-    // A grid covers the longest possible sequence, so under mixed lengths many CTAs of split >= 1 have nothing to
-    // do (40 % on config 2): those read the length first and leave before touching anything else, which is worth
-    // 5 % of the whole launch.  Split 0 almost always has work and keeps the early query loads below.
-    if (split > 0) {
-        int early = p.lens[b];
-        const int early_bound = RAGGED ? 0x7ffffff0 : p.table_stride * kPageTokens;
-        early = early < 0 ? 0 : (early > early_bound ? early_bound : early);
-        if (RAGGED) {
-            if (static_cast<long long>(split) * ragged.control[1] >= early && !p.partials_only) return;
-        } else {
-            if (split * p.split_tokens >= early && !p.partials_only) return;
+    // The length and (classic form) this split's slice of the block-table row are read together, the table slice
+    // before the length says how much of it is live: one dependent round trip fewer before the first K/V boxes.
+    // The ragged form's page list hangs off two more device values and is read below.
+    int len = p.lens[b];
+    uint32_t early_page = 0u;
+    if (!RAGGED && warp == kDecodeWarps) {
+        const int at = split * (p.split_tokens / kPageTokens) + lane;
+        if (lane < p.split_tokens / kPageTokens && at < p.table_stride) {
+            early_page = p.table[static_cast<size_t>(b) * p.table_stride + at];
         }
     }
-    // Start the query-fragment loads before the length is known: their addresses depend only on the block
-    // indices, so this global round trip overlaps the length read and the block-table read.
+    // A grid covers the longest possible sequence, so under mixed lengths many CTAs of split >= 1 have nothing to
+    // do (40 % on config 2): those leave as soon as the length is here.
+    const int bound = RAGGED ? 0x7ffffff0 : p.table_stride * kPageTokens;
+    len = len < 0 ? 0 : (len > bound ? bound : len);
+    const int piece = RAGGED ? ragged.control[1] : p.split_tokens;
+    if (split > 0 && static_cast<long long>(split) * piece >= len && !p.partials_only) return;
     uint32_t qa[KSTEPS][2];
     if (warp < kDecodeWarps) {
         const int row = lane >> 2;
@@ -134,11 +136,16 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
             qa[ks][1] = row < p.group ? q32[ks * 8 + 4 + quad] : 0u;
         }
     }
-    int len = p.lens[b];
-    const int bound = RAGGED ? 0x7ffffff0 : p.table_stride * kPageTokens;
-    len = len < 0 ? 0 : (len > bound ? bound : len);
-    const int n_splits =
-        RAGGED ? (len + ragged.control[1] - 1) / ragged.control[1] : (len + p.split_tokens - 1) / p.split_tokens;
+    // The barriers are set up while the query reads are in flight.
+    if (tid == 0) {
+        for (int s = 0; s < kDecodeStages; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        mbar_init_fence();
+    }
+
+    const int n_splits = (len + piece - 1) / piece;
 
     if (split >= n_splits) {
         // Nothing to attend.  Split 0 of an empty sequence still owns the row: zeros, as the reference writes.
@@ -162,19 +169,10 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         return;
     }
 
-    const int piece = RAGGED ? ragged.control[1] : p.split_tokens;
     const int tok_begin = split * piece;
     const int tok_end = min(len, tok_begin + piece);
     const int npages = tok_end > tok_begin ? (tok_end - tok_begin + kPageTokens - 1) / kPageTokens : 0;
     const int first_page = tok_begin / kPageTokens;
-
-    if (tid == 0) {
-        for (int s = 0; s < kDecodeStages; ++s) {
-            mbar_init(bar_full + s * 8, 1);
-            mbar_init(bar_empty + s * 8, 1);
-        }
-        mbar_init_fence();
-    }
     __syncthreads();
 
     bool failed = false;
@@ -189,7 +187,8 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         const long long ragged_at = RAGGED ? ragged.first[b] + first_page : 0;
         for (int chunk = 0; chunk < npages && !failed; chunk += 32) {
             const int mine = chunk + lane;
-            uint32_t page = (!RAGGED && mine < npages) ? table[mine] : 0u;
+            uint32_t page = 0u;
+            if (!RAGGED && mine < npages) page = chunk == 0 ? early_page : table[mine];
             if (RAGGED && mine < npages) {
                 if (ragged.index_width == 8) {
                     const long long wide = static_cast<const long long *>(ragged.pages)[ragged_at + mine];
@@ -458,7 +457,8 @@ int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedD
                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B));
     SINGE_TRY(encode_tensor_map(&v_map, TensorMapType<T>::value, 4, value_cache, dims, strides, box,
                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B));
-    dim3 grid(static_cast<unsigned>(params.max_splits), static_cast<unsigned>(params.kv_heads),
+    // KV heads vary fastest: the CTAs that read the interleaved rows of the same cache pages start together.
+    dim3 grid(static_cast<unsigned>(params.kv_heads), static_cast<unsigned>(params.max_splits),
               static_cast<unsigned>(batch));
     if (RAGGED) {
         SINGE_CUDA_TRY(launch_dependent(paged_decode_ragged_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,

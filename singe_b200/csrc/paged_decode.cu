@@ -85,7 +85,6 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
     constexpr int NTILES = HD / 8;
     constexpr int STAGE = decode_stage_bytes<HD>();
 
-    grid_launch_dependents();
     grid_dependency_wait();  // the queries (and, in a decode step, the newest K/V rows) come from the kernel before
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -334,6 +333,9 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
             *reinterpret_cast<float2 *>(mine + nt * 8 + quad * 2) = make_float2(o[nt][0], o[nt][1]);
         }
     }
+    // Only now may the next kernel on the stream (the combine) take SM slots: its CTAs then arrive while this
+    // launch drains instead of competing with its last wave.  CTAs that left early count as having said so.
+    grid_launch_dependents();
     __syncthreads();
 
     // ---------------- merge the four warps and write ----------------
@@ -523,7 +525,7 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
     params.partials_only = partials_only ? 1 : 0;
     params.scale_log2 = scale * 1.4426950408889634f;
     params.status = status;
-    if (batch > 65535 || max_splits > 0x7fffffffull || kv_heads > 65535) {
+    if (batch > 65535 || max_splits > 65535 || kv_heads > 0x7fffffffull) {
         return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
     }
     int result;

@@ -247,13 +247,14 @@ struct TensorPagedPolicy {
 // The whole-table refusal of check_paged_values: any sequence with bad offsets, pages or last length sets the status.
 // One warp per sequence; its lanes share the sequence's page list.
 template <typename Index>
-__global__ void check_paged_values_kernel(const Index *query_offsets, const Index *page_offsets, const Index *pages,
-                                          const Index *last_page_lengths, int sequences, long long tokens,
-                                          long long cache_pages, long long table_len, long long page_size,
-                                          uint32_t *status) {
+__device__ __forceinline__ void check_paged_values_body(const Index *query_offsets, const Index *page_offsets,
+                                                        const Index *pages, const Index *last_page_lengths,
+                                                        int sequences, long long tokens, long long cache_pages,
+                                                        long long table_len, long long page_size, uint32_t *status,
+                                                        int block, int blocks) {
     const int lane = threadIdx.x & 31;
-    const int warps = (gridDim.x * blockDim.x) >> 5;
-    for (int s = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; s < sequences; s += warps) {
+    const int warps = (blocks * blockDim.x) >> 5;
+    for (int s = (block * blockDim.x + threadIdx.x) >> 5; s < sequences; s += warps) {
         const long long qf = static_cast<long long>(query_offsets[s]), ql = static_cast<long long>(query_offsets[s + 1]);
         const long long pf = static_cast<long long>(page_offsets[s]), pl = static_cast<long long>(page_offsets[s + 1]);
         bool bad = !(0 <= qf && qf <= ql && ql <= tokens) || !(0 <= pf && pf <= pl && pl <= table_len);
@@ -269,15 +270,25 @@ __global__ void check_paged_values_kernel(const Index *query_offsets, const Inde
     }
 }
 
+template <typename Index>
+__global__ void check_paged_values_kernel(const Index *query_offsets, const Index *page_offsets, const Index *pages,
+                                          const Index *last_page_lengths, int sequences, long long tokens,
+                                          long long cache_pages, long long table_len, long long page_size,
+                                          uint32_t *status) {
+    check_paged_values_body<Index>(query_offsets, page_offsets, pages, last_page_lengths, sequences, tokens, cache_pages,
+                                   table_len, page_size, status, blockIdx.x, gridDim.x);
+}
+
 // Decides, on the device, whether a Tensor-surface call is a plain decode batch (sequence b owns exactly query
 // token b, every paging value is valid) and, if so, turns the paging tensors into what the tiled decode kernel
 // reads: lens[b], first[b] (index of the sequence's first page) and the tokens per split for `split_budget` splits
 // of the longest sequence.  control[0] = 0 hands the call to the tiled kernel, 1 to the general kernel.
 template <typename Index>
-__global__ void plan_paged_decode_kernel(const Index *query_offsets, const Index *page_offsets, const Index *pages,
-                                         const Index *last_page_lengths, int sequences, long long cache_pages,
-                                         long long table_len, long long page_size, int split_budget, int *lens,
-                                         long long *first, int *control) {
+__device__ __forceinline__ void plan_paged_decode_body(const Index *query_offsets, const Index *page_offsets,
+                                                       const Index *pages, const Index *last_page_lengths,
+                                                       int sequences, long long cache_pages, long long table_len,
+                                                       long long page_size, int split_budget, int *lens,
+                                                       long long *first, int *control) {
     __shared__ int shared_bad;
     __shared__ int shared_longest;
     if (threadIdx.x == 0) {
@@ -316,6 +327,30 @@ __global__ void plan_paged_decode_kernel(const Index *query_offsets, const Index
         const long long per = (static_cast<long long>(shared_longest) + split_budget - 1) / split_budget;
         const long long rounded = (per + page_size - 1) / page_size * page_size;
         control[1] = static_cast<int>(rounded < page_size ? page_size : rounded);
+    }
+}
+
+template <typename Index>
+__global__ void plan_paged_decode_kernel(const Index *query_offsets, const Index *page_offsets, const Index *pages,
+                                         const Index *last_page_lengths, int sequences, long long cache_pages,
+                                         long long table_len, long long page_size, int split_budget, int *lens,
+                                         long long *first, int *control) {
+    plan_paged_decode_body<Index>(query_offsets, page_offsets, pages, last_page_lengths, sequences, cache_pages,
+                                  table_len, page_size, split_budget, lens, first, control);
+}
+
+// Both of the above in one launch: the last block plans, the others check (one launch gap fewer per call).
+template <typename Index>
+__global__ void check_and_plan_kernel(const Index *query_offsets, const Index *page_offsets, const Index *pages,
+                                      const Index *last_page_lengths, int sequences, long long tokens,
+                                      long long cache_pages, long long table_len, long long page_size,
+                                      uint32_t *status, int split_budget, int *lens, long long *first, int *control) {
+    if (blockIdx.x == gridDim.x - 1) {
+        plan_paged_decode_body<Index>(query_offsets, page_offsets, pages, last_page_lengths, sequences, cache_pages,
+                                      table_len, page_size, split_budget, lens, first, control);
+    } else {
+        check_paged_values_body<Index>(query_offsets, page_offsets, pages, last_page_lengths, sequences, tokens,
+                                       cache_pages, table_len, page_size, status, blockIdx.x, gridDim.x - 1);
     }
 }
 
@@ -546,13 +581,14 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
     policy.table_len = static_cast<long long>(table_len);
     policy.window = static_cast<long long>(window);
     policy.skip_when_zero = nullptr;
-    if (status != nullptr) {
+    bool checked = status == nullptr;  // no status word, no whole-table check
+    auto check_alone = [&]() -> int {
         const unsigned blocks = static_cast<unsigned>((sequences + 3) / 4);  // four warps, one sequence each
         check_paged_values_kernel<Index><<<blocks > 256 ? 256 : blocks, 128, 0, stream>>>(
             policy.query_offsets, policy.page_offsets, policy.pages, policy.last_page_lengths, policy.sequences,
             policy.tokens, policy.cache_pages, policy.table_len, static_cast<long long>(page_size), status);
-        SINGE_TRY(launch_status());
-    }
+        return launch_status();
+    };
     // One query token per sequence, no window: possibly a plain decode batch.  Whether it is one depends on the
     // paging tensors, which live on the device, so a planning kernel decides there: it either hands the call to
     // the tiled flash-decode kernel (and the general kernel below finds nothing to do) or leaves it to the general
@@ -577,10 +613,19 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
             long long *first = reinterpret_cast<long long *>(plan_at);
             int *lens = reinterpret_cast<int *>(first + sequences);
             int *control = lens + sequences;
-            plan_paged_decode_kernel<Index><<<1, 256, 0, stream>>>(
-                policy.query_offsets, policy.page_offsets, policy.pages, policy.last_page_lengths, policy.sequences,
-                policy.cache_pages, policy.table_len, static_cast<long long>(page_size), static_cast<int>(splits), lens,
-                first, control);
+            if (!checked) {
+                const unsigned blocks = static_cast<unsigned>((sequences + 7) / 8);  // eight warps, one sequence each
+                check_and_plan_kernel<Index><<<(blocks > 256 ? 256 : blocks) + 1, 256, 0, stream>>>(
+                    policy.query_offsets, policy.page_offsets, policy.pages, policy.last_page_lengths,
+                    policy.sequences, policy.tokens, policy.cache_pages, policy.table_len,
+                    static_cast<long long>(page_size), status, static_cast<int>(splits), lens, first, control);
+                checked = true;
+            } else {
+                plan_paged_decode_kernel<Index><<<1, 256, 0, stream>>>(
+                    policy.query_offsets, policy.page_offsets, policy.pages, policy.last_page_lengths,
+                    policy.sequences, policy.cache_pages, policy.table_len, static_cast<long long>(page_size),
+                    static_cast<int>(splits), lens, first, control);
+            }
             SINGE_TRY(launch_status());
             RaggedDecode ragged;
             ragged.pages = pages;
@@ -599,6 +644,7 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
         }
         // (workspace growth refused under stream capture: the general kernel serves the call)
     }
+    if (!checked) SINGE_TRY(check_alone());
     return launch_attention_general<T>(stream, policy, tokens * heads, head_dim, scale, LseKind::Base2, -INFINITY,
                                        status);
 }

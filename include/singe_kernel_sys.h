@@ -162,6 +162,8 @@ int singe_paged_kv_decode_attention_static_bf16(singe_stream_t stream, void *out
  * Split s of a sequence covers keys [s * split_tokens, (s+1) * split_tokens) where
  *   split_tokens = singe_paged_kv_decode_split_tokens(block_table_batch_stride * block_size, max_splits),
  * a multiple of block_size; splits past a sequence's length hold lse = -inf and zeros.
+ * The tiled kernel takes batch <= 65535 and max_splits <= 65535 (grid dimensions); beyond that the call
+ * returns SINGE_ERR_UNSUPPORTED_CONFIGURATION.
  * ================================================================================================= */
 
 /* Tokens per split for a key-length bound and a split budget (host arithmetic, no device work). */

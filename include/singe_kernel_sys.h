@@ -59,6 +59,18 @@ extern "C" {
 
 typedef void *singe_stream_t; /* CUstream / cudaStream_t */
 
+/* Hints a caller may give the entry points that take a `hints` argument.  They widen what a kernel may read BEFORE
+ * the kernels queued ahead of it on the stream have finished (all of this library's decode-path kernels are launched
+ * so that their set-up overlaps the kernel before); without a hint a kernel reads nothing early.
+ *   SINGE_HINT_STABLE_WEIGHTS : the weight operand is not written by any work still in flight when the call is
+ *                               enqueued (a layer parameter): its first tiles are fetched ahead of the wait.
+ *   SINGE_HINT_STABLE_PAGING  : lengths and block table are not written by work still in flight, and of the cache
+ *                               only each sequence's LAST key position may be (the row the step's cache write
+ *                               fills): everything else of the cache is fetched ahead of the wait.
+ * The reference has no counterpart: its launches serialise on the stream. */
+#define SINGE_HINT_STABLE_WEIGHTS 1u
+#define SINGE_HINT_STABLE_PAGING 2u
+
 /* Library version (major * 1000 + minor). */
 int singe_kernel_sys_version(void);
 
@@ -104,10 +116,13 @@ int singe_kv_cache_write_f32(singe_stream_t stream, void *key_cache, void *value
  *   block_table           : uint32 [batch, block_table_batch_stride]
  * The bf16/f16 entry points run the split-K flash-decode kernel (TMA-staged pages, tensor-core
  * tiles, log-sum-exp combine) when head_dim is 64 or 128, block_size is 16 and heads/kv_heads <= 8,
- * and a general one-warp-per-row kernel otherwise.  Their split-K partials live in a per-device
- * workspace the library grows on demand (never while the stream is capturing: that returns
+ * and a general one-warp-per-row kernel otherwise (also for batch > 65535).  Their split-K partials live in
+ * a per-device workspace the library grows on demand (never while the stream is capturing: that returns
  * SINGE_ERR_AUTOTUNE_DURING_CAPTURE; call once outside capture first, or use the *_splitk_reduce_*
- * entry points below with caller-owned scratch).
+ * entry points below with caller-owned scratch).  Every stream of a device shares that one workspace: calls
+ * whose kernels can overlap on the GPU (different streams, no event between them) race on it -- run them on
+ * one stream at a time or pass caller-owned scratch.  Growth never frees: a buffer that was handed out
+ * (and may be baked into a captured CUDA graph) stays allocated until singe_release_workspaces().
  * ================================================================================================= */
 int singe_paged_kv_decode_attention_bf16(singe_stream_t stream, void *out, const void *query,
                                          const void *key_cache, const void *value_cache,
@@ -198,6 +213,22 @@ int singe_paged_kv_decode_splitk_reduce_f16(singe_stream_t stream, void *out, fl
                                             size_t kv_heads, size_t head_dim, size_t block_size,
                                             size_t physical_blocks, size_t block_table_batch_stride,
                                             size_t max_splits, float scale);
+
+/* singe_paged_kv_decode_splitk_reduce_bf16 inside a decode step: same arguments and result plus a `hints` word.
+ * With SINGE_HINT_STABLE_PAGING the kernel reads lengths, block table and cache pages ahead of the kernels still
+ * running before it on the stream, except the page holding each sequence's last key position (the one row the
+ * step's cache write, queued just before, fills); the queries are read after those kernels finish.
+ * No reference counterpart (the reference's launches serialise). */
+int singe_paged_kv_decode_step_bf16(singe_stream_t stream, void *out, float *attn_scratch, float *lse_scratch,
+                                    const void *query, const void *key_cache, const void *value_cache,
+                                    const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch,
+                                    size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
+                                    size_t physical_blocks, size_t block_table_batch_stride, size_t max_splits,
+                                    float scale, unsigned hints);
+
+/* Pages beyond its shared-memory ring that each CTA of the hinted decode pulls into L2 ahead of its wait
+ * (0 = none, the default).  A tuning knob like singe_matmul_set_staging. */
+int singe_paged_kv_decode_set_prefetch(int pages);
 
 /* =================================================================================================
  * Tensor-surface paged attention (FlashInfer-style paging, decode and prefill rows mixed)
@@ -401,6 +432,14 @@ int singe_matmul_bf16_swiglu_bf16(singe_stream_t stream, void *out, const void *
                                   size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
                                   size_t output_row_stride);
 
+/* Linear::forward (singe/src/nn/layers/linear/mod.rs:49-70): out[rows, columns] = x[rows, reduction] . weight[columns,
+ * reduction]^T, bf16 in, f32 accumulate, bf16 out -- singe_matmul_bf16_bf16 with the layer's layout fixed and a `hints`
+ * word (SINGE_HINT_STABLE_WEIGHTS).  gated != 0: the SwiGLU epilogue of singe_matmul_bf16_swiglu_bf16 (out is
+ * columns / 2 wide). */
+int singe_linear_bf16(singe_stream_t stream, void *out, const void *x, const void *weight, size_t rows, size_t columns,
+                      size_t reduction, size_t x_row_stride, size_t weight_row_stride, size_t output_row_stride,
+                      int gated, unsigned hints);
+
 /* Explicit tile choice for the two GEMM entry points, process-wide: block_n in {32,64,128,256},
  * k_slices_per_stage in {1,2,4,8}; 0 = choose from the problem shape.
  * Replaces: TuningChoice::Explicit(MatmulTuning { tile, .. }) (singe-kernel/src/cuda/matmul.rs:58-77). */
@@ -412,10 +451,27 @@ int singe_matmul_set_tuning(int block_n, int k_slices_per_stage);
  * compile options only; this is a tuning knob of the same kind for this library's extra degree of freedom. */
 int singe_matmul_set_splits(int k_splits);
 
+/* Staging knobs of the same kind: shared memory one GEMM CTA may take (KB; 0 = choose), and how many KB of a stable
+ * weight operand each CTA pulls into L2 ahead of its dependency wait beyond what its ring holds (negative = choose). */
+int singe_matmul_set_staging(int shared_kb, int prefetch_kb);
+
+/* L2 warm-ahead: attaches the read-only range [pointer, pointer + bytes) (16-byte aligned) to the NEXT kernel this host
+ * thread enqueues through singe_linear_bf16 / singe_matmul_*, singe_paged_kv_decode_step_bf16 and the other
+ * *_splitk_* decode calls, singe_add_rms_norm_bf16, singe_rotary_cache_write_bf16 or singe_allreduce_add_rms_norm_bf16;
+ * that kernel asks the memory system to pull the range into L2 beside its own work, so that a later kernel (a weight
+ * matrix two launches ahead, say) finds it there.  The range must stay allocated until that kernel has finished; it is
+ * only read.  A hint: results never depend on it.  No reference counterpart. */
+int singe_warm_l2_with_next_launch(const void *pointer, size_t bytes);
+
+/* Frees the current device's decode workspaces (the live one and every one retired by growth) after a device
+ * synchronisation.  Only when no captured graph that used them will be replayed again.  No reference
+ * counterpart (the reference's operators take all scratch from the caller). */
+int singe_release_workspaces(void);
+
 /* Reads and clears the library's sticky device error word for the current device (synchronises the device).
  * 0 = no kernel-side failure; 2 = a bounded device-side wait ran out.  Plays the role of the planner's status
  * word read-back (singe/src/backend/cuda/kernel_plan/mod.rs:192-204) for entry points without a status argument. */
-int singe_debug_take_device_error(uint32_t *value);
+int singe_take_device_error(uint32_t *value);
 
 #ifdef __cplusplus
 }

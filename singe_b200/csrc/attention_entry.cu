@@ -19,7 +19,8 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
                         const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch, size_t heads,
                         size_t kv_heads, size_t head_dim, size_t physical_blocks, size_t block_table_batch_stride,
                         size_t max_splits, float scale, bool partials_only, uint32_t *status,
-                        const RaggedDecode *ragged);
+                        const RaggedDecode *ragged, unsigned hints);
+extern int g_decode_prefetch_pages;
 // prefill_tcgen05.cu
 bool prefill_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t total_query_tokens, const void *query,
                        const void *key, const void *value, const void *out);
@@ -398,18 +399,23 @@ struct DensePolicy {
 // ---------------------------------------------------------------------------------------------
 // Per-device split-K workspace of the drop-in decode entry points
 // ---------------------------------------------------------------------------------------------
+// The reference's scratch-less signatures leave the library to find split-K scratch.  One buffer per device, shared by
+// every stream: calls that use it must not overlap on the GPU (callers that run decode on several streams of one
+// device at once pass their own scratch through the *_splitk_reduce_* entry points).  Growth happens outside stream
+// capture only and never frees: a CUDA graph captured earlier has the old address baked in, so a buffer that was ever
+// handed out stays allocated until singe_release_workspaces() or process exit.
 struct Workspace {
     float *data = nullptr;
     size_t floats = 0;
+    float *retired[32] = {nullptr};
+    int retired_count = 0;
 };
-constexpr int kMaxDevices = 64;
 Workspace g_workspace[kMaxDevices];
 std::mutex g_workspace_mutex;
 
 int workspace_for(cudaStream_t stream, size_t floats, float **data) {
-    int device = 0;
-    SINGE_CUDA_TRY(cudaGetDevice(&device));
-    if (device < 0 || device >= kMaxDevices) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    const int device = device_slot();
+    if (device < 0) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
     std::lock_guard<std::mutex> guard(g_workspace_mutex);
     Workspace &space = g_workspace[device];
     if (space.floats < floats) {
@@ -418,28 +424,32 @@ int workspace_for(cudaStream_t stream, size_t floats, float **data) {
         if (capture != cudaStreamCaptureStatusNone) {
             return SINGE_ERR_AUTOTUNE_DURING_CAPTURE;
         }
-        // Work queued on the old buffer must finish before it is released.
-        SINGE_CUDA_TRY(cudaDeviceSynchronize());
-        if (space.data != nullptr) {
-            SINGE_CUDA_TRY(cudaFree(space.data));
-            space.data = nullptr;
-            space.floats = 0;
-        }
-        const size_t grown = floats + floats / 2;
-        SINGE_CUDA_TRY(cudaMalloc(&space.data, grown * sizeof(float)));
+        if (space.data != nullptr && space.retired_count >= 32) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+        // Doubling keeps the number of retired buffers logarithmic in the largest problem seen.
+        size_t grown = floats + floats / 2;
+        if (grown < 2 * space.floats) grown = 2 * space.floats;
+        float *fresh = nullptr;
+        SINGE_CUDA_TRY(cudaMalloc(&fresh, grown * sizeof(float)));
+        if (space.data != nullptr) space.retired[space.retired_count++] = space.data;
+        space.data = fresh;
         space.floats = grown;
     }
     *data = space.data;
     return SINGE_OK;
 }
 
-// SINGE_TENSOR_DECODE_PATH=0 keeps the general kernel for every Tensor-surface call (comparison runs).
-bool tensor_decode_path_enabled() {
-    static const bool enabled = [] {
-        const char *value = getenv("SINGE_TENSOR_DECODE_PATH");
-        return value == nullptr || value[0] != '0';
-    }();
-    return enabled;
+int release_workspaces() {
+    const int device = device_slot();
+    if (device < 0) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    std::lock_guard<std::mutex> guard(g_workspace_mutex);
+    Workspace &space = g_workspace[device];
+    SINGE_CUDA_TRY(cudaDeviceSynchronize());
+    for (int i = 0; i < space.retired_count; ++i) cudaFree(space.retired[i]);
+    space.retired_count = 0;
+    if (space.data != nullptr) cudaFree(space.data);
+    space.data = nullptr;
+    space.floats = 0;
+    return SINGE_OK;
 }
 
 // Splits the drop-in decode uses when the caller gives no budget: ~512-token splits, more when few CTAs would run.
@@ -487,14 +497,15 @@ int decode_half(cudaStream_t stream, int element, void *out, const void *query, 
         table == nullptr) {
         return SINGE_ERR_NULL_POINTER;
     }
-    if (paged_decode_fast_path(heads, kv_heads, head_dim, block_size, key_cache, value_cache, query)) {
+    // The tiled kernel puts the batch in a grid dimension of at most 65535; larger batches keep the general kernel.
+    if (batch <= 65535 && paged_decode_fast_path(heads, kv_heads, head_dim, block_size, key_cache, value_cache, query)) {
         const size_t splits = default_splits(batch, kv_heads, stride * block_size);
         float *scratch = nullptr;
         const size_t rows = batch * heads * splits;
         SINGE_TRY(workspace_for(stream, rows * (head_dim + 1), &scratch));
         return paged_decode_splitk(stream, element, out, scratch, scratch + rows * head_dim, query, key_cache,
                                    value_cache, lens, table, batch, heads, kv_heads, head_dim, physical_blocks, stride,
-                                   splits, scale, false, device_error_word(), nullptr);
+                                   splits, scale, false, device_error_word(), nullptr, 0u);
     }
     if (element == 0) {
         return decode_general<__nv_bfloat16>(stream, out, query, key_cache, value_cache, lens, table, batch, heads,
@@ -508,7 +519,7 @@ int decode_splitk_half(cudaStream_t stream, int element, void *out, float *attn_
                        const void *query, const void *key_cache, const void *value_cache, const int32_t *lens,
                        const uint32_t *table, size_t batch, size_t heads, size_t kv_heads, size_t head_dim,
                        size_t block_size, size_t physical_blocks, size_t stride, size_t max_splits, float scale,
-                       bool partials_only) {
+                       bool partials_only, unsigned hints = 0u) {
     SINGE_TRY(validate_paged_decode(batch, heads, kv_heads, head_dim, block_size, physical_blocks, stride, scale));
     if (max_splits == 0) return SINGE_ERR_INVALID_LENGTH;  // validate_fmha_decode_splitk_reduce_config, mod.rs:2553-2559
     if (!fits_i32(max_splits)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
@@ -521,7 +532,7 @@ int decode_splitk_half(cudaStream_t stream, int element, void *out, float *attn_
     }
     return paged_decode_splitk(stream, element, out, attn_scratch, lse_scratch, query, key_cache, value_cache, lens,
                                table, batch, heads, kv_heads, head_dim, physical_blocks, stride, max_splits, scale,
-                               partials_only, device_error_word(), nullptr);
+                               partials_only, device_error_word(), nullptr, hints);
 }
 
 template <typename T>
@@ -594,7 +605,7 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
     // the tiled flash-decode kernel (and the general kernel below finds nothing to do) or leaves it to the general
     // kernel (and the tiled kernel's CTAs leave at once).
     constexpr bool kHalfType = sizeof(T) == 2;
-    if (kHalfType && tensor_decode_path_enabled() && tokens == sequences && window == 0 && sequences <= 65535 &&
+    if (kHalfType && tokens == sequences && window == 0 && sequences <= 65535 &&
         paged_decode_fast_path(heads, kv_heads, head_dim, page_size, key_cache, value_cache, query)) {
         // split budget: ~512-key splits of a sequence twice the average length (the real lengths are device data)
         const size_t average = table_len * page_size / sequences;
@@ -637,7 +648,7 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
             SINGE_TRY(paged_decode_splitk(stream, element, out, scratch, scratch + rows * head_dim, query, key_cache,
                                           value_cache, lens, nullptr, sequences, heads, kv_heads, head_dim,
                                           cache_pages, 1, splits, scale, false,
-                                          status != nullptr ? status : device_error_word(), &ragged));
+                                          status != nullptr ? status : device_error_word(), &ragged, 0u));
             policy.skip_when_zero = control;
         } else if (grown != SINGE_ERR_AUTOTUNE_DURING_CAPTURE) {
             return grown;
@@ -757,7 +768,9 @@ using namespace singe;
 
 extern "C" {
 
-int singe_kernel_sys_version(void) { return 1000; }
+int singe_kernel_sys_version(void) { return 1001; }
+
+int singe_release_workspaces(void) { return release_workspaces(); }
 
 const char *singe_status_string(int status) {
     switch (status) {
@@ -863,6 +876,23 @@ int singe_paged_kv_decode_splitk_reduce_bf16(singe_stream_t stream, void *out, f
     return decode_splitk_half(static_cast<cudaStream_t>(stream), 0, out, attn_scratch, lse_scratch, query, key_cache,
                               value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim, block_size,
                               physical_blocks, block_table_batch_stride, max_splits, scale, false);
+}
+
+int singe_paged_kv_decode_step_bf16(singe_stream_t stream, void *out, float *attn_scratch, float *lse_scratch,
+                                    const void *query, const void *key_cache, const void *value_cache,
+                                    const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch,
+                                    size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
+                                    size_t physical_blocks, size_t block_table_batch_stride, size_t max_splits,
+                                    float scale, unsigned hints) {
+    return decode_splitk_half(static_cast<cudaStream_t>(stream), 0, out, attn_scratch, lse_scratch, query, key_cache,
+                              value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim, block_size,
+                              physical_blocks, block_table_batch_stride, max_splits, scale, false, hints);
+}
+
+int singe_paged_kv_decode_set_prefetch(int pages) {
+    if (pages < 0 || pages > 4096) return SINGE_ERR_INVALID_ARGUMENT;
+    g_decode_prefetch_pages = pages;
+    return SINGE_OK;
 }
 
 int singe_paged_kv_decode_splitk_reduce_f16(singe_stream_t stream, void *out, float *attn_scratch, float *lse_scratch,

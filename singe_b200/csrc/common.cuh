@@ -54,24 +54,35 @@ struct RaggedDecode {
 };
 
 // Programmatic dependent launch.  Every kernel of the decode path is launched with the attribute that lets it start
-// while the kernel before it on the stream is still draining: its CTAs do their private set-up (barriers, tensor
-// memory, tensor-map prefetch) and then block in grid_dependency_wait() until the earlier kernel has completed and
-// its writes are visible.  The wait is the first thing before any access to global memory another kernel may have
-// written or may still read, so stream order is preserved; without the attribute the wait returns at once.  A step
-// of eleven short launches per layer otherwise pays a launch ramp per kernel.  SINGE_PDL=0 turns the attribute off.
+// while the kernels before it on the stream are still running: its CTAs do whatever does not depend on earlier work
+// (barriers, tensor memory, tensor-map prefetch and -- where the caller has said that an operand is stable, see
+// SINGE_HINT_* -- the first loads of that operand) and then block in grid_dependency_wait() until the earlier kernels
+// have completed and their writes are visible.  The wait comes before any access to global memory that another kernel
+// may have written or may still read, so stream order is preserved; without the attribute the wait returns at once.
+// A step of nine short launches per layer otherwise pays a launch ramp and a cold pipeline per kernel.
 // Measured on B200 (config-2 decode and the Llama decode step): every kind gains.  The split-K combine does so only
 // because the decode kernel releases its dependents late, after its key loop: released at the top, the combine's
 // thousand small CTAs took warp slots from the decode kernel's last wave (-4 % on the headline).
-constexpr unsigned kDefaultDependentLaunchMask = 1u | 2u | 4u | 8u | 16u;
 enum LaunchKind : unsigned { kLaunchGlue = 1, kLaunchGemm = 2, kLaunchDecode = 4, kLaunchCombine = 8, kLaunchReduce = 16 };
 
-// Which kinds of kernels take the attribute (SINGE_PDL = a bit mask of LaunchKind; default: see the value below).
-inline unsigned dependent_launch_mask() {
-    static const unsigned mask = [] {
-        const char *value = getenv("SINGE_PDL");
-        return value == nullptr ? kDefaultDependentLaunchMask : static_cast<unsigned>(strtoul(value, nullptr, 0));
-    }();
-    return mask;
+constexpr int kMaxDevices = 64;
+
+// Index of the current device in the library's per-device tables, or -1.
+inline int device_slot() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return -1;
+    return device;
+}
+
+// Raises a kernel's dynamic shared-memory limit once per device (the attribute belongs to the device's copy of the
+// function, so a process that drives several GPUs sets it on each).  `done` is the launch site's own table.
+template <typename Kernel>
+inline cudaError_t ensure_dynamic_shared(Kernel kernel, int bytes, int (&done)[kMaxDevices]) {
+    const int slot = device_slot();
+    if (slot >= 0 && done[slot] >= bytes) return cudaSuccess;
+    const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (error == cudaSuccess && slot >= 0) done[slot] = bytes;
+    return error;
 }
 
 template <typename... Parameters, typename... Arguments>
@@ -84,11 +95,10 @@ inline cudaError_t launch_dependent(void (*kernel)(Parameters...), dim3 grid, di
     config.stream = stream;
     cudaLaunchAttribute attributes[2];
     unsigned count = 0;
-    if ((dependent_launch_mask() & kind) != 0) {
-        attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attributes[count].val.programmaticStreamSerializationAllowed = 1;
-        ++count;
-    }
+    (void)kind;
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
     if (cluster > 1) {
         attributes[count].id = cudaLaunchAttributeClusterDimension;
         attributes[count].val.clusterDim.x = cluster;
@@ -157,20 +167,34 @@ struct TensorMapType<float> {
     static constexpr CUtensorMapDataType value = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
 };
 
+// L2 warm-ahead.  A decode step is a chain of short kernels, each of which streams a weight matrix once; whatever a
+// kernel finds in L2 when its turn comes it does not have to wait for HBM for.  A caller that knows what the kernels
+// after the next one will read (singe_warm_l2_with_next_launch) attaches that range to the next launch: the kernel's
+// CTAs ask the memory system to pull it into L2 (cp.async.bulk.prefetch, no registers, no shared memory, no
+// completion to wait for) next to their own work.  The range must stay allocated until the kernel has finished and
+// is only read.
+struct WarmRange {
+    const void *pointer;
+    unsigned long long bytes;
+};
+// The range attached to this host thread's next launch (runtime.cu); taking it clears it.
+WarmRange take_pending_warm();
+
 // Device address of the library's sticky error word on the current device (runtime.cu): kernels record
 // their first internal failure there (2 = a bounded wait ran out).  nullptr if it cannot be resolved.
 uint32_t *device_error_word();
 
+// SM count of the current device (cached per device).
 inline int device_sm_count() {
-    static int count = [] {
-        int device = 0, value = 0;
-        if (cudaGetDevice(&device) != cudaSuccess ||
-            cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || value <= 0) {
-            value = 148;
-        }
-        return value;
-    }();
-    return count;
+    static int counts[kMaxDevices] = {0};
+    const int slot = device_slot();
+    if (slot >= 0 && counts[slot] > 0) return counts[slot];
+    int value = 0;
+    if (slot < 0 || cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, slot) != cudaSuccess || value <= 0) {
+        return 148;
+    }
+    counts[slot] = value;
+    return value;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -289,6 +313,30 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
+// Asks the memory system to bring a tile into L2; nothing lands in shared memory and nothing signals completion.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int32_t c0, int32_t c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap *map, int32_t c0, int32_t c1, int32_t c2, int32_t c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global [%0, {%1, %2, %3, %4}];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+
+// One warp of each CTA calls this: the CTAs of the grid split the range into 4 KB pieces.
+__device__ __forceinline__ void warm_l2(const WarmRange &range, unsigned cta, unsigned ctas, unsigned lane) {
+    constexpr unsigned long long kPiece = 4096;
+    if (range.bytes == 0) return;
+    const unsigned long long pieces = range.bytes / kPiece;
+    const char *start = static_cast<const char *>(range.pointer);
+    for (unsigned long long i = static_cast<unsigned long long>(lane) * ctas + cta; i < pieces; i += 32ull * ctas) {
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(start + i * kPiece), "r"(4096u) : "memory");
+    }
+}
+
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int32_t c0, int32_t c1) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1)
@@ -403,6 +451,12 @@ template <>
 __device__ __forceinline__ __half from_float<__half>(float value) {
     return __float2half_rn(value);
 }
+
+// silu(x) = x / (1 + exp(-x)) with the special-function unit's exponential and reciprocal (a handful of instructions;
+// the IEEE division it replaces costs about twenty, which shows in epilogues that run one warp per scheduler).  Every
+// kernel that applies the activation uses this one form, so fused and unfused paths agree bit for bit; against the
+// exact f32 value the error is a few ulp, far inside the bf16 rounding that follows.
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 __device__ __forceinline__ float warp_sum(float value) {
 #pragma unroll

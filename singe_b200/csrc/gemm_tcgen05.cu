@@ -18,6 +18,8 @@
 // short A box: rows past the box are stale shared memory, which only reaches output rows that are not stored.
 // Tiles are ordered in groups of eight M-tiles so that one wave of CTAs shares A and B tiles through L2.
 // Every mbarrier wait is bounded; a wait that runs out sets the device error word and the CTA leaves.
+#include <atomic>
+
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -39,10 +41,15 @@ struct GemmParams {
     int a_rows;       // rows of the A box (multiple of 8, <= 128)
     int stages;
     int stage_bytes;  // KPS * (a_rows * 128 + BN * 128)
+    int pad_bytes;    // behind the ring: what the MMA's read of 128 A rows may touch past the last stage's short A box
     int tiles_m, tiles_n, k_blocks;  // k_blocks counts stages: KPS 64-wide slices each
     int vector_store;  // 16-byte stores are legal (alignment and stride)
     int gated;         // 1: columns are (gate, up) pairs; the epilogue stores bf16(bf16(silu(gate)) * up), n / 2 wide
+    int stable_rhs;    // 1: the caller vouches that rhs (a weight matrix) is not written by work still in flight, so
+                       //    its first tiles are fetched before the wait on the preceding kernels
+    int prefetch_blocks;  // with stable_rhs: k-blocks beyond the ring whose rhs tiles are pulled into L2 before the wait
     uint32_t *error;   // sticky device error word (2 = a bounded wait ran out)
+    WarmRange warm;    // pulled into L2 by the epilogue warps while they have nothing else to do
 };
 
 // GatedMlp's activation-then-multiply (singe/src/nn/layers/feed_forward/mod.rs:58-66) on two accumulators, with the
@@ -50,7 +57,7 @@ struct GemmParams {
 __device__ __forceinline__ float gated_value(float gate_acc, float up_acc) {
     const float gate = __bfloat162float(__float2bfloat16_rn(gate_acc));
     const float up = __bfloat162float(__float2bfloat16_rn(up_acc));
-    const float activated = __bfloat162float(__float2bfloat16_rn(gate / (1.0f + __expf(-gate))));
+    const float activated = __bfloat162float(__float2bfloat16_rn(silu_fast(gate)));
     return activated * up;
 }
 
@@ -79,8 +86,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
-    // [stages x stage_bytes][16 KB over-read pad][barriers]
-    const uint32_t bars = base + p.stages * p.stage_bytes + kBlockM * 128;
+    // [stages x stage_bytes][over-read pad][barriers]
+    const uint32_t bars = base + p.stages * p.stage_bytes + p.pad_bytes;
     const uint32_t bar_full = bars;
     const uint32_t bar_empty = bars + kMaxStages * 8;
     const uint32_t bar_acc_full = bars + 2 * kMaxStages * 8;
@@ -113,7 +120,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_holder_ptr;
-    grid_dependency_wait();  // barriers and tensor memory are set up; the operands come from the kernel before
 
     bool failed = false;
 
@@ -123,6 +129,34 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             prefetch_tensor_map(&a_map);
             prefetch_tensor_map(&b_map);
         }
+        // A stable weight operand does not depend on the kernels before this one: the B halves of the first tile's
+        // first `stages` ring slots are requested now (and a few more k-blocks pulled into L2), so that they cross
+        // HBM while the preceding kernel is still running.  Each slot's barrier expects the bytes of both operands;
+        // the A halves follow after the wait.
+        int preloaded = 0;
+        if (p.stable_rhs && blockIdx.x < total_tiles) {
+            int tm, tn;
+            tile_coordinates(blockIdx.x, p.tiles_m, p.tiles_n, tm, tn);
+            preloaded = min(p.stages, p.k_blocks);
+            if (lane == 0) {
+                for (int kb = 0; kb < preloaded; ++kb) {
+                    const uint32_t stage = base + kb * p.stage_bytes;
+                    const uint32_t full = bar_full + kb * 8;
+                    mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
+#pragma unroll
+                    for (int sub = 0; sub < KPS; ++sub) {
+                        tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
+                                    tn * BN);
+                    }
+                }
+                const int last = min(p.k_blocks, preloaded + p.prefetch_blocks);
+                for (int kb = preloaded; kb < last; ++kb) {
+#pragma unroll
+                    for (int sub = 0; sub < KPS; ++sub) tma_prefetch_2d(&b_map, (kb * KPS + sub) * kBlockK, tn * BN);
+                }
+            }
+        }
+        grid_dependency_wait();  // the A operand comes from the kernel before
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
             int tm, tn;
@@ -130,8 +164,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                 const int s = it % p.stages;
                 const uint32_t phase = (it / p.stages) & 1;
+                const bool early = it < preloaded;  // slot armed and its B half requested before the wait
                 int ok = 1;
-                if (lane == 0) ok = mbar_wait(bar_empty + s * 8, phase ^ 1) ? 1 : 0;
+                if (lane == 0 && !early) ok = mbar_wait(bar_empty + s * 8, phase ^ 1) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) {
                     failed = true;
@@ -140,16 +175,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 if (lane == 0) {
                     const uint32_t stage = base + s * p.stage_bytes;
                     const uint32_t full = bar_full + s * 8;
-                    mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
+                    if (!early) mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
                         // slices past K are zero-filled by TMA and add nothing
                         tma_load_2d(stage + sub * a_bytes, &a_map, full, (kb * KPS + sub) * kBlockK, tm * kBlockM);
                     }
+                    if (!early) {
 #pragma unroll
-                    for (int sub = 0; sub < KPS; ++sub) {
-                        tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
-                                    tn * BN);
+                        for (int sub = 0; sub < KPS; ++sub) {
+                            tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full,
+                                        (kb * KPS + sub) * kBlockK, tn * BN);
+                        }
                     }
                 }
             }
@@ -200,6 +237,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
     } else {
         // ---------------- epilogue ----------------
+        if (warp == 2) warm_l2(p.warm, blockIdx.x, gridDim.x, lane);
+        grid_dependency_wait();  // nothing is stored while an earlier kernel may still read the output buffer
         const int quarter = warp & 3;  // tensor-memory lanes 32*quarter .. +31
         int local = 0;
         for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++local) {
@@ -301,10 +340,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
 // ---- split-K for one-M-tile problems whose N gives too few tiles to fill the machine ----
 // A thread-block cluster of `splits` CTAs owns one N tile; CTA r of the cluster streams K slice r (its own TMA ring,
-// its own accumulator in tensor memory), parks the f32 partial tile in its shared memory, and after a cluster
-// barrier every CTA sums a share of the tile's rows over all the cluster's partials through distributed shared
-// memory, in split order (so the result does not depend on timing), and stores them.  No workspace in global
-// memory, no atomics, nothing to reset between launches.
+// its own accumulator in tensor memory) and pushes each row of its f32 partial tile into the shared memory of the
+// cluster CTA that owns the row (distributed shared memory stores); after one cluster barrier every CTA sums its
+// rows' partials out of its own shared memory, in split order (so the result does not depend on timing), and stores
+// them.  No workspace in global memory, no atomics, nothing to reset between launches.  A timeline of the earlier
+// form (partials parked locally, owners pulling them with remote loads, a second barrier before leaving) showed
+// 2.2 - 2.6 us in the pull and 0.8 us in the closing barrier of a 10 us kernel.
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t value;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(value));
@@ -323,17 +364,6 @@ __device__ __forceinline__ void cluster_barrier() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ float4 load_cluster_shared(uint32_t local_address, uint32_t rank) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
-    float4 value;
-    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(value.x), "=f"(value.y), "=f"(value.z), "=f"(value.w)
-                 : "r"(remote)
-                 : "memory");
-    return value;
-}
-
 template <int BN, int KPS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_splitk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
@@ -341,27 +371,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     constexpr uint32_t kTmemColumns = BN < 32 ? 32 : BN;
     constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, 0, 0);
     constexpr int kBBytes = BN * 128;
-    constexpr int kPartialStride = BN + 4;  // floats per parked row: 16-byte stores of a warp spread over all banks
+    constexpr int kQuads = BN / 4;  // float4 groups per row
 
     grid_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
-    // [ring: stages x stage_bytes, reused for the parked partial tile][16 KB over-read pad][barriers]
-    const uint32_t ring_bytes = max(p.stages * p.stage_bytes, kBlockM * kPartialStride * 4);
-    const uint32_t bars = base + ring_bytes + kBlockM * 128;
+    const uint32_t rank = cluster_rank();
+    const uint32_t splits = cluster_size();
+    const int rows_per_cta = (p.m + static_cast<int>(splits) - 1) / static_cast<int>(splits);
+    // [ring: stages x stage_bytes, its start reused for the parked partial tile][over-read pad]
+    // [receive area: splits x rows_per_cta x BN floats][barriers]
+    const uint32_t slot_bytes = static_cast<uint32_t>(rows_per_cta) * BN * 4;  // one CTA's rows of one split's partial
+    const uint32_t recv = base + max(static_cast<uint32_t>(p.stages * p.stage_bytes), splits * slot_bytes) + p.pad_bytes;
+    const uint32_t bars = recv + splits * slot_bytes;
     const uint32_t bar_full = bars;
     const uint32_t bar_empty = bars + kMaxStages * 8;
     const uint32_t bar_acc_full = bars + 2 * kMaxStages * 8;
+    const uint32_t bar_recv = bar_acc_full + 8;
     const uint32_t tmem_holder = bar_acc_full + 16;
     volatile uint32_t *tmem_holder_ptr = reinterpret_cast<volatile uint32_t *>(smem_raw + (tmem_holder - raw));
-    float *partial = reinterpret_cast<float *>(smem_raw + (base - raw));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int a_bytes = p.a_rows * 128;
-    const uint32_t rank = cluster_rank();
-    const uint32_t splits = cluster_size();
     const int tn = blockIdx.x / splits;
     const int per_split = (p.k_blocks + splits - 1) / splits;
     const int kb_first = rank * per_split;
@@ -374,6 +407,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             mbar_init(bar_empty + s * 8, 1);
         }
         mbar_init(bar_acc_full, 1);
+        mbar_init(bar_recv, 1);
         mbar_init_fence();
     }
     if (warp == 1) {
@@ -384,7 +418,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_holder_ptr;
-    grid_dependency_wait();  // barriers and tensor memory are set up; the operands come from the kernel before
+    cluster_barrier();  // every CTA's receive barrier exists before anyone may complete bytes on it
 
     bool failed = false;
     if (warp == 0) {
@@ -393,12 +427,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             prefetch_tensor_map(&a_map);
             prefetch_tensor_map(&b_map);
         }
+        // Stable weights: the B halves of this CTA's first ring slots are requested before the wait (see
+        // gemm_bf16_kernel), a few more k-blocks are pulled into L2.
+        int preloaded = 0;
+        if (p.stable_rhs && has_work) {
+            preloaded = min(p.stages, kb_last - kb_first);
+            if (lane == 0) {
+                for (int i = 0; i < preloaded; ++i) {
+                    const int kb = kb_first + i;
+                    const uint32_t stage = base + i * p.stage_bytes;
+                    const uint32_t full = bar_full + i * 8;
+                    mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
+#pragma unroll
+                    for (int sub = 0; sub < KPS; ++sub) {
+                        tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
+                                    tn * BN);
+                    }
+                }
+                const int last = min(kb_last, kb_first + preloaded + p.prefetch_blocks);
+                for (int kb = kb_first + preloaded; kb < last; ++kb) {
+#pragma unroll
+                    for (int sub = 0; sub < KPS; ++sub) tma_prefetch_2d(&b_map, (kb * KPS + sub) * kBlockK, tn * BN);
+                }
+            }
+        }
+        grid_dependency_wait();  // the A operand comes from the kernel before
         int it = 0;
         for (int kb = kb_first; kb < kb_last; ++kb, ++it) {
             const int s = it % p.stages;
             const uint32_t phase = (it / p.stages) & 1;
+            const bool early = it < preloaded;
             int ok = 1;
-            if (lane == 0) ok = mbar_wait(bar_empty + s * 8, phase ^ 1) ? 1 : 0;
+            if (lane == 0 && !early) ok = mbar_wait(bar_empty + s * 8, phase ^ 1) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) {
                 failed = true;
@@ -407,14 +467,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (lane == 0) {
                 const uint32_t stage = base + s * p.stage_bytes;
                 const uint32_t full = bar_full + s * 8;
-                mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
+                if (!early) mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
 #pragma unroll
                 for (int sub = 0; sub < KPS; ++sub) {
                     tma_load_2d(stage + sub * a_bytes, &a_map, full, (kb * KPS + sub) * kBlockK, 0);
                 }
+                if (!early) {
 #pragma unroll
-                for (int sub = 0; sub < KPS; ++sub) {
-                    tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK, tn * BN);
+                    for (int sub = 0; sub < KPS; ++sub) {
+                        tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
+                                    tn * BN);
+                    }
                 }
             }
         }
@@ -450,117 +513,224 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             __syncwarp();
         }
     } else {
-        // ---------------- park the partial tile in shared memory ----------------
-        // The ring is free once the accumulator is complete: every MMA that read it has retired.
+        // ---------------- hand the partial tile to the CTAs that own its rows ----------------
+        // Row i of the tile belongs to cluster CTA i % splits.  The four warps park the CTA's f32 partial tile in its
+        // own shared memory grouped by owner ([owner][row / splits][BN], 16-byte groups XOR-swizzled by the row so the
+        // one-row-per-thread writes spread over the banks), then one thread sends each other owner its group with a
+        // single bulk copy into that CTA's receive area (slot = this CTA's rank), completing bytes on the owner's
+        // receive barrier.  An owner waits for the bytes of all live splits and sums its rows out of its own shared
+        // memory: no thread ever waits for a remote load.  (Stores of one row per thread straight into the owners'
+        // shared memory took 1.6 us for 24 KB per CTA: 4096 separate 16-byte transfers.)
+        if (warp == 2) warm_l2(p.warm, blockIdx.x, gridDim.x, lane);
+        grid_dependency_wait();  // these warps store the output: not while an earlier kernel may still read it
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
+        const int live = min(static_cast<int>(splits), (p.k_blocks + per_split - 1) / per_split);
         if (has_work && !__all_sync(0xffffffffu, mbar_wait(bar_acc_full, 0) ? 1 : 0)) failed = true;
         tcgen05_fence_after();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        if (has_work && !failed) {
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            const int owner = row % static_cast<int>(splits);
+            const int local_row = row / static_cast<int>(splits);
+            float *mine = reinterpret_cast<float *>(smem_raw + (base - raw)) +
+                          (static_cast<size_t>(owner) * rows_per_cta + local_row) * BN;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-            uint32_t r[32];
-            if (has_work && !failed) {
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
                 tmem_ld_x32(taddr + c, r);
                 tmem_wait_ld();
-            } else {
+                if (row < p.m) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = 0u;
+                    for (int j = 0; j < 32; j += 4) {
+                        const int quad = ((c + j) >> 2) ^ (row & (kQuads - 1));
+                        *reinterpret_cast<float4 *>(mine + quad * 4) =
+                            make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                        __uint_as_float(r[j + 3]));
+                    }
+                }
             }
-            if (row < p.m) {
-                float4 *dst = reinterpret_cast<float4 *>(partial + row * kPartialStride + c);
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    dst[j >> 2] = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            fence_proxy_async_shared();  // the bulk copies below read what these threads wrote
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps: the whole tile is parked
+        if (threadIdx.x == 64) {
+            // bytes this CTA will receive: one slot from every other live split
+            const int senders = live - (static_cast<int>(rank) < live ? 1 : 0);
+            mbar_expect_tx(bar_recv, static_cast<uint32_t>(senders) * slot_bytes);
+            if (has_work && !failed) {
+                for (uint32_t o = 0; o < splits; ++o) {
+                    if (o == rank) continue;
+                    uint32_t remote_slot, remote_bar;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                                 : "=r"(remote_slot)
+                                 : "r"(recv + rank * slot_bytes), "r"(o));
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(bar_recv), "r"(o));
+                    asm volatile(
+                        "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                        ::"r"(remote_slot), "r"(base + o * slot_bytes), "r"(slot_bytes), "r"(remote_bar)
+                        : "memory");
                 }
             }
         }
     }
+    // Every warp helps with the reduction (the producer and MMA warps have nothing left to do): all of them wait for
+    // the bytes addressed to this CTA.
+    if (!__all_sync(0xffffffffu, mbar_wait(bar_recv, 0) ? 1 : 0)) failed = true;
     if (failed && lane == 0) {
         report_status(p.error, kStatusWaitTimeout);
     }
-    tcgen05_fence_before();
-    cluster_barrier();  // all partial tiles of the cluster are parked
-    if (warp >= 2) {
-        // ---------------- reduce: CTA r takes rows r, r + splits, ... of the tile ----------------
-        const int t = threadIdx.x - 64;                    // 0 .. 127
-        constexpr int kQuads = BN / 4;                     // float4 groups per row
+    // Arrive: "everything addressed to this CTA has landed".  When all CTAs have said so, every bulk copy of the
+    // cluster has finished reading its source, and a CTA may leave (the matching wait is at the end).
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    {
+        // ---------------- reduce: CTA r owns rows r, r + splits, ... of the tile ----------------
+        if (warp < 2) grid_dependency_wait();  // (the other warps did before they parked the tile)
+        const int t = threadIdx.x;
         const int my_rows = (p.m - static_cast<int>(rank) + static_cast<int>(splits) - 1) / static_cast<int>(splits);
-        const uint32_t partial_address = base;
-        for (int index = t; index < my_rows * kQuads; index += 128) {
-            const int row = static_cast<int>(rank) + (index / kQuads) * static_cast<int>(splits);
-            const int quad = index % kQuads;
-            const int col = tn * BN + quad * 4;
-            if (col >= p.n) continue;
-            const uint32_t at = partial_address + (row * kPartialStride + quad * 4) * 4;
-            float4 sum = load_cluster_shared(at, 0);
-            for (uint32_t s = 1; s < splits; ++s) {
-                const float4 other = load_cluster_shared(at, s);
-                sum.x += other.x;
-                sum.y += other.y;
-                sum.z += other.z;
-                sum.w += other.w;
-            }
-            const float values[4] = {sum.x, sum.y, sum.z, sum.w};
-            if (p.gated) {
-                __nv_bfloat16 *dst =
-                    static_cast<__nv_bfloat16 *>(p.out) + static_cast<long long>(row) * p.ldo + col / 2;
-                if (col + 4 <= p.n) {
-                    *reinterpret_cast<uint32_t *>(dst) =
-                        pack2<__nv_bfloat16>(gated_value(sum.x, sum.y), gated_value(sum.z, sum.w));
-                } else if (col + 2 <= p.n) {
-                    dst[0] = __float2bfloat16_rn(gated_value(sum.x, sum.y));
-                }
-            } else if (p.out_f32) {
-                float *dst = static_cast<float *>(p.out) + static_cast<long long>(row) * p.ldo + col;
-                if (p.vector_store && col + 4 <= p.n) {
-                    *reinterpret_cast<float4 *>(dst) = sum;
-                } else {
-                    for (int j = 0; j < 4; ++j) {
-                        if (col + j < p.n) dst[j] = values[j];
+        const int live = min(static_cast<int>(splits), (p.k_blocks + per_split - 1) / per_split);
+        const float *received = reinterpret_cast<const float *>(smem_raw + (recv - raw));
+        const float *parked = reinterpret_cast<const float *>(smem_raw + (base - raw));
+        const int slot_floats = rows_per_cta * BN;
+        // One warp per scheduler runs here, so nothing hides an instruction's latency but the warp's own independent
+        // work: the shared-memory reads of a batch of items are issued together before any of them is summed.
+        constexpr int kBatch = 3;
+        const int items = my_rows * kQuads;
+        for (int first = t; first < items; first += kGemmThreads * kBatch) {
+            float4 part[kBatch][8];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int index = first + u * kGemmThreads;
+                const int local_row = index / kQuads;
+                const int quad = index % kQuads;
+                const int row = static_cast<int>(rank) + local_row * static_cast<int>(splits);
+                const int at = local_row * BN + ((quad ^ (row & (kQuads - 1))) << 2);
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    if (index < items && s < live) {
+                        // this CTA's own partial never left its parked tile (group `rank` there)
+                        const float *from = s == static_cast<int>(rank) ? parked + rank * slot_floats
+                                                                         : received + s * slot_floats;
+                        part[u][s] = *reinterpret_cast<const float4 *>(from + at);
                     }
                 }
-            } else {
-                __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.out) + static_cast<long long>(row) * p.ldo + col;
-                if (p.vector_store && col + 4 <= p.n) {
-                    *reinterpret_cast<uint2 *>(dst) =
-                        make_uint2(pack2<__nv_bfloat16>(sum.x, sum.y), pack2<__nv_bfloat16>(sum.z, sum.w));
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int index = first + u * kGemmThreads;
+                if (index >= items) continue;
+                const int local_row = index / kQuads;
+                const int row = static_cast<int>(rank) + local_row * static_cast<int>(splits);
+                const int quad = index % kQuads;
+                const int col = tn * BN + quad * 4;
+                if (col >= p.n) continue;
+                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (live > 0) sum = part[u][0];
+#pragma unroll
+                for (int s = 1; s < 8; ++s) {  // split order: the result does not depend on timing
+                    if (s < live) {
+                        sum.x += part[u][s].x;
+                        sum.y += part[u][s].y;
+                        sum.z += part[u][s].z;
+                        sum.w += part[u][s].w;
+                    }
+                }
+                const float values[4] = {sum.x, sum.y, sum.z, sum.w};
+                if (p.gated) {
+                    __nv_bfloat16 *dst =
+                        static_cast<__nv_bfloat16 *>(p.out) + static_cast<long long>(row) * p.ldo + col / 2;
+                    if (col + 4 <= p.n) {
+                        *reinterpret_cast<uint32_t *>(dst) =
+                            pack2<__nv_bfloat16>(gated_value(sum.x, sum.y), gated_value(sum.z, sum.w));
+                    } else if (col + 2 <= p.n) {
+                        dst[0] = __float2bfloat16_rn(gated_value(sum.x, sum.y));
+                    }
+                } else if (p.out_f32) {
+                    float *dst = static_cast<float *>(p.out) + static_cast<long long>(row) * p.ldo + col;
+                    if (p.vector_store && col + 4 <= p.n) {
+                        *reinterpret_cast<float4 *>(dst) = sum;
+                    } else {
+                        for (int j = 0; j < 4; ++j) {
+                            if (col + j < p.n) dst[j] = values[j];
+                        }
+                    }
                 } else {
-                    for (int j = 0; j < 4; ++j) {
-                        if (col + j < p.n) dst[j] = __float2bfloat16_rn(values[j]);
+                    __nv_bfloat16 *dst =
+                        static_cast<__nv_bfloat16 *>(p.out) + static_cast<long long>(row) * p.ldo + col;
+                    if (p.vector_store && col + 4 <= p.n) {
+                        *reinterpret_cast<uint2 *>(dst) =
+                            make_uint2(pack2<__nv_bfloat16>(sum.x, sum.y), pack2<__nv_bfloat16>(sum.z, sum.w));
+                    } else {
+                        for (int j = 0; j < 4; ++j) {
+                            if (col + j < p.n) dst[j] = __float2bfloat16_rn(values[j]);
+                        }
                     }
                 }
             }
         }
     }
-    cluster_barrier();  // nobody leaves while its shared memory is still being read
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // see the arrive above
+    tcgen05_fence_before();
+    __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, kTmemColumns);
     }
 }
 
+// Explicit tuning (the reference's TuningChoice::Explicit(MatmulTuning), singe-kernel/src/cuda/matmul.rs:58-77):
+// 0 = choose from the problem shape.  Atomics: calls on several host threads may race with a setter.
+std::atomic<int> g_tuning_block_n{0};
+std::atomic<int> g_tuning_slices{0};
+std::atomic<int> g_tuning_splits{0};       // 0 = choose, 1 = never split K
+std::atomic<int> g_tuning_shared_kb{0};    // 0 = choose; otherwise the dynamic shared memory a CTA may take, in KB
+std::atomic<int> g_tuning_prefetch_kb{-1};  // -1 = choose; KB of stable weights per CTA pulled into L2 before the wait
+
+// Dynamic shared memory a GEMM CTA may use.  One-M-tile problems with stable weights are the decode step's linears:
+// kept to half an SM so that the CTAs of the next linear can become resident beside them and fetch their own first
+// weight tiles while this one still runs; everything else takes the whole SM.
+int shared_limit(const GemmParams &params) {
+    const int forced = g_tuning_shared_kb.load(std::memory_order_relaxed);
+    if (forced > 0) return forced * 1024 > 227 * 1024 ? 227 * 1024 : forced * 1024;
+    return 227 * 1024;
+}
+
+// The MMA reads 128 rows of A from every stage although a short box fills only a_rows of them; what it reads past the
+// box lies inside the stage while the B tiles behind the last A tile are at least as large as the overhang.
+int over_read_pad(int a_rows, int stage_b_bytes) {
+    const int overhang = (kBlockM - a_rows) * 128 - stage_b_bytes;
+    return overhang > 0 ? (overhang + 1023) / 1024 * 1024 : 0;
+}
+
+int prefetch_blocks_for(const GemmParams &params, int block_b_bytes) {
+    if (!params.stable_rhs) return 0;
+    const int forced = g_tuning_prefetch_kb.load(std::memory_order_relaxed);
+    const int kb = forced >= 0 ? forced : 0;
+    return kb * 1024 / block_b_bytes;
+}
+
 template <int BN, int KPS>
 int launch_gemm_splitk(cudaStream_t stream, GemmParams params, const void *lhs, const void *rhs,
                        size_t lhs_row_stride, size_t rhs_row_stride, int splits) {
-    constexpr int kSmemLimit = 227 * 1024;
+    const int kSmemLimit = shared_limit(params);
     const int b_bytes = BN * 128;
     params.stage_bytes = KPS * (params.a_rows * 128 + b_bytes);
     params.k_blocks = (params.k + kBlockK * KPS - 1) / (kBlockK * KPS);
+    params.prefetch_blocks = prefetch_blocks_for(params, KPS * b_bytes);
     const int per_split = (params.k_blocks + splits - 1) / splits;
-    const int fixed = kBlockM * 128 + 2 * kMaxStages * 8 + 64 + 1024;
+    params.pad_bytes = over_read_pad(params.a_rows, KPS * b_bytes);
+    const int receive = splits * ((params.m + splits - 1) / splits) * BN * 4;  // every split's partial of the CTA's rows
+    const int fixed = params.pad_bytes + receive + 2 * kMaxStages * 8 + 64 + 1024;
+    // (the ring is at least as large as the parked tile, which reuses it: checked below)
     int stages = (kSmemLimit - fixed) / params.stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages > per_split + 1 && per_split + 1 >= 2) stages = per_split + 1;
-    if (stages < 2) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    if (stages < 2) stages = 2;  // the limit is a preference; two stages is the least the pipeline runs with
     params.stages = stages;
     params.tiles_n = (params.n + BN - 1) / BN;
-    const int parked = kBlockM * (BN + 4) * 4;
-    const int ring = stages * params.stage_bytes > parked ? stages * params.stage_bytes : parked;
+    const int ring = stages * params.stage_bytes > receive ? stages * params.stage_bytes : receive;
     const int smem = ring + fixed;
-    if (smem > kSmemLimit) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
-    SINGE_CUDA_TRY(cudaFuncSetAttribute(gemm_splitk_kernel<BN, KPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (smem > 227 * 1024) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    static int configured[kMaxDevices] = {0};
+    SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_splitk_kernel<BN, KPS>, smem, configured));
 
     CUtensorMap a_map, b_map;
     {
@@ -587,19 +757,23 @@ int launch_gemm_splitk(cudaStream_t stream, GemmParams params, const void *lhs, 
 template <int BN, int KPS>
 int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const void *rhs, size_t lhs_row_stride,
                 size_t rhs_row_stride) {
-    constexpr int kSmemLimit = 227 * 1024;
+    const int kSmemLimit = shared_limit(params);
     const int b_bytes = BN * 128;
     params.stage_bytes = KPS * (params.a_rows * 128 + b_bytes);
     params.k_blocks = (params.k + kBlockK * KPS - 1) / (kBlockK * KPS);
-    const int fixed = kBlockM * 128 + 2 * kMaxStages * 8 + 64 + 1024;
+    params.prefetch_blocks = prefetch_blocks_for(params, KPS * b_bytes);
+    params.pad_bytes = over_read_pad(params.a_rows, KPS * b_bytes);
+    const int fixed = params.pad_bytes + 2 * kMaxStages * 8 + 64 + 1024;
     int stages = (kSmemLimit - fixed) / params.stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages > params.k_blocks + 1 && params.k_blocks + 1 >= 2) stages = params.k_blocks + 1;
-    if (stages < 2) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    if (stages < 2) stages = 2;  // the limit is a preference; two stages is the least the pipeline runs with
     params.stages = stages;
     params.tiles_n = (params.n + BN - 1) / BN;
     const int smem = stages * params.stage_bytes + fixed;
-    SINGE_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_kernel<BN, KPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (smem > 227 * 1024) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    static int configured[kMaxDevices] = {0};
+    SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS>, smem, configured));
 
     CUtensorMap a_map, b_map;
     {
@@ -623,18 +797,12 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
     return launch_status();
 }
 
-// Explicit tuning (the reference's TuningChoice::Explicit(MatmulTuning), singe-kernel/src/cuda/matmul.rs:58-77):
-// 0 = choose from the problem shape.
-int g_tuning_block_n = 0;
-int g_tuning_slices = 0;
-int g_tuning_splits = 0;  // 0 = choose, 1 = never split K
-
 }  // namespace
 
 // validate_matmul (singe-kernel/src/cuda/matmul.rs:2977-3020), then the layout gate of the tensor-core path.
 int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, const void *rhs, size_t rows,
               size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
-              size_t output_row_stride, int transpose_lhs, int transpose_rhs, bool gated) {
+              size_t output_row_stride, int transpose_lhs, int transpose_rhs, bool gated, unsigned hints) {
     const size_t lhs_min = transpose_lhs ? rows : reduction;
     const size_t rhs_min = transpose_rhs ? reduction : columns;
     if (rows == 0 || columns == 0 || reduction == 0 || lhs_row_stride < lhs_min || rhs_row_stride < rhs_min ||
@@ -659,6 +827,9 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
     params.out = out;
     params.out_f32 = out_f32 ? 1 : 0;
     params.gated = gated ? 1 : 0;
+    params.stable_rhs = (hints & SINGE_HINT_STABLE_WEIGHTS) != 0 ? 1 : 0;
+    params.warm = take_pending_warm();
+    params.prefetch_blocks = 0;
     params.m = static_cast<int>(rows);
     params.n = static_cast<int>(columns);
     params.k = static_cast<int>(reduction);
@@ -704,7 +875,10 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
     // wave; 8 pays only when even 4 leave two thirds of the SMs idle (then with 64-wide tiles), and a split needs at
     // least three pipeline stages of K to amortise its fill and the reduction.
     int splits = 1;
-    if (params.m <= kBlockM && tiles(128) < (sms * 2) / 3 && g_tuning_splits != 1) {
+    const int forced_splits = g_tuning_splits.load(std::memory_order_relaxed);
+    const int forced_block_n = g_tuning_block_n.load(std::memory_order_relaxed);
+    const int forced_slices = g_tuning_slices.load(std::memory_order_relaxed);
+    if (params.m <= kBlockM && tiles(128) < (sms * 2) / 3 && forced_splits != 1) {
         int wide = 128;
         int wanted = 1;
         while (wanted < 4 && tiles(wide) * wanted * 2 <= sms) wanted <<= 1;
@@ -722,9 +896,14 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
             slices = 2;
         }
     }
-    if (g_tuning_splits != 0) splits = g_tuning_splits;
-    if (g_tuning_block_n != 0) bn = g_tuning_block_n;
-    if (g_tuning_slices != 0) slices = g_tuning_slices;
+    if (forced_splits != 0) splits = forced_splits;
+    if (forced_block_n != 0) bn = forced_block_n;
+    {
+        // two stages must fit the shared-memory limit of the call
+        const int room = shared_limit(params) - 20 * 1024;
+        while (slices > 1 && slices * (params.a_rows + bn) * 128 * 2 > room) slices >>= 1;
+    }
+    if (forced_slices != 0) slices = forced_slices;
     if (splits > 1) {
         if (params.m > kBlockM || (splits != 2 && splits != 4 && splits != 8)) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
 #define SINGE_SPLITK_CASE(BN_, KPS_)                                                                             \
@@ -732,6 +911,7 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
         return launch_gemm_splitk<BN_, KPS_>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride, splits);
         SINGE_SPLITK_CASE(128, 2)
         SINGE_SPLITK_CASE(128, 1)
+        SINGE_SPLITK_CASE(64, 1)
         SINGE_SPLITK_CASE(64, 2)
         SINGE_SPLITK_CASE(64, 4)
         SINGE_SPLITK_CASE(32, 8)
@@ -764,7 +944,7 @@ int singe_matmul_bf16_bf16(singe_stream_t stream, void *out, const void *lhs, co
                            size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
                            size_t output_row_stride, int transpose_lhs, int transpose_rhs) {
     return singe::gemm_bf16(static_cast<cudaStream_t>(stream), out, false, lhs, rhs, rows, columns, reduction,
-                            lhs_row_stride, rhs_row_stride, output_row_stride, transpose_lhs, transpose_rhs, false);
+                            lhs_row_stride, rhs_row_stride, output_row_stride, transpose_lhs, transpose_rhs, false, 0u);
 }
 
 // out[M, N/2] = bf16(bf16(silu(g)) * u) with g = bf16(lhs . rhs[2j]^T), u = bf16(lhs . rhs[2j+1]^T): the gate and up
@@ -774,14 +954,23 @@ int singe_matmul_bf16_swiglu_bf16(singe_stream_t stream, void *out, const void *
                                   size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
                                   size_t output_row_stride) {
     return singe::gemm_bf16(static_cast<cudaStream_t>(stream), out, false, lhs, rhs, rows, columns, reduction,
-                            lhs_row_stride, rhs_row_stride, output_row_stride, 0, 1, true);
+                            lhs_row_stride, rhs_row_stride, output_row_stride, 0, 1, true, 0u);
 }
 
 int singe_matmul_bf16_f32(singe_stream_t stream, float *out, const void *lhs, const void *rhs, size_t rows,
                           size_t columns, size_t reduction, size_t lhs_row_stride, size_t rhs_row_stride,
                           size_t output_row_stride, int transpose_lhs, int transpose_rhs) {
     return singe::gemm_bf16(static_cast<cudaStream_t>(stream), out, true, lhs, rhs, rows, columns, reduction,
-                            lhs_row_stride, rhs_row_stride, output_row_stride, transpose_lhs, transpose_rhs, false);
+                            lhs_row_stride, rhs_row_stride, output_row_stride, transpose_lhs, transpose_rhs, false, 0u);
+}
+
+// Linear::forward with the weight matrix as a parameter of the layer: out[M, N] = x[M, K] . weight[N, K]^T.  `hints`
+// may carry SINGE_HINT_STABLE_WEIGHTS; `gated` != 0 selects the SwiGLU epilogue of singe_matmul_bf16_swiglu_bf16.
+int singe_linear_bf16(singe_stream_t stream, void *out, const void *x, const void *weight, size_t rows,
+                      size_t columns, size_t reduction, size_t x_row_stride, size_t weight_row_stride,
+                      size_t output_row_stride, int gated, unsigned hints) {
+    return singe::gemm_bf16(static_cast<cudaStream_t>(stream), out, false, x, weight, rows, columns, reduction,
+                            x_row_stride, weight_row_stride, output_row_stride, 0, 1, gated != 0, hints);
 }
 
 // Overrides the tile choice of the GEMM entry points for this process: block_n in {32, 64, 128, 256} and
@@ -789,8 +978,8 @@ int singe_matmul_bf16_f32(singe_stream_t stream, float *out, const void *lhs, co
 // (singe-kernel/src/cuda/matmul.rs:58-77).  Unsupported pairs make the next call return
 // SINGE_ERR_UNSUPPORTED_CONFIGURATION.
 int singe_matmul_set_tuning(int block_n, int k_slices_per_stage) {
-    singe::g_tuning_block_n = block_n;
-    singe::g_tuning_slices = k_slices_per_stage;
+    singe::g_tuning_block_n.store(block_n);
+    singe::g_tuning_slices.store(k_slices_per_stage);
     return SINGE_OK;
 }
 
@@ -799,7 +988,16 @@ int singe_matmul_set_splits(int k_splits) {
     if (k_splits != 0 && k_splits != 1 && k_splits != 2 && k_splits != 4 && k_splits != 8) {
         return SINGE_ERR_INVALID_ARGUMENT;
     }
-    singe::g_tuning_splits = k_splits;
+    singe::g_tuning_splits.store(k_splits);
+    return SINGE_OK;
+}
+
+// Shared memory a GEMM CTA may take (KB, 0 = choose) and the amount of stable weights a CTA pulls into L2 ahead of
+// its dependency wait (KB, negative = choose).
+int singe_matmul_set_staging(int shared_kb, int prefetch_kb) {
+    if (shared_kb < 0 || shared_kb > 227) return SINGE_ERR_INVALID_ARGUMENT;
+    singe::g_tuning_shared_kb.store(shared_kb);
+    singe::g_tuning_prefetch_kb.store(prefetch_kb < 0 ? -1 : prefetch_kb);
     return SINGE_OK;
 }
 

@@ -88,8 +88,9 @@ constexpr int kHeld = 4;
 
 template <int VEC>
 __global__ void add_rms_norm_kernel(__nv_bfloat16 *hidden, const __nv_bfloat16 *delta, __nv_bfloat16 *normed,
-                                    const __nv_bfloat16 *weight, int width, float eps) {
+                                    const __nv_bfloat16 *weight, int width, float eps, const WarmRange warm) {
     grid_launch_dependents();
+    if (threadIdx.x < 32) warm_l2(warm, blockIdx.x, gridDim.x, threadIdx.x);
     grid_dependency_wait();
     __shared__ float scratch[32];
     const size_t base = static_cast<size_t>(blockIdx.x) * width;
@@ -175,8 +176,9 @@ __global__ void rotary_cache_write_kernel(__nv_bfloat16 *q_out, const __nv_bfloa
                                           __nv_bfloat16 *value_cache, const Index *write_pages,
                                           const Index *write_slots, int heads, int kv_heads, int head_dim,
                                           long long pages, long long page_size, long long capacity,
-                                          uint32_t *status) {
+                                          uint32_t *status, const WarmRange warm) {
     grid_launch_dependents();
+    if (threadIdx.x < 32) warm_l2(warm, blockIdx.x, gridDim.x, threadIdx.x);
     grid_dependency_wait();
     const int token = blockIdx.x;
     const int half = head_dim >> 1;
@@ -254,12 +256,12 @@ __global__ void silu_mul_kernel(__nv_bfloat16 *out, const __nv_bfloat16 *gate, c
         const Vec8 g = load8(gate + in_base + c), u = load8(up + in_base + c);
         Vec8 result;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) result.v[i] = round_bf16(g.v[i] / (1.0f + __expf(-g.v[i]))) * u.v[i];
+        for (int i = 0; i < 8; ++i) result.v[i] = round_bf16(silu_fast(g.v[i])) * u.v[i];
         store8(out + out_base + c, result);
     } else {
         const float g = __bfloat162float(gate[in_base + c]);
         const float u = __bfloat162float(up[in_base + c]);
-        out[out_base + c] = __float2bfloat16_rn(round_bf16(g / (1.0f + __expf(-g))) * u);
+        out[out_base + c] = __float2bfloat16_rn(round_bf16(silu_fast(g)) * u);
     }
 }
 
@@ -356,6 +358,7 @@ int singe_add_rms_norm_bf16(singe_stream_t stream, void *hidden, const void *del
         return SINGE_ERR_NULL_POINTER;
     }
     const bool wide = width % 8 == 0 && aligned16(hidden) && aligned16(delta) && aligned16(normed) && aligned16(weight);
+    const WarmRange warm = take_pending_warm();
     if (wide) {
         int threads = static_cast<int>((width / 8 + 31) / 32 * 32);
         if (threads > 512) threads = 512;
@@ -363,13 +366,13 @@ int singe_add_rms_norm_bf16(singe_stream_t stream, void *hidden, const void *del
                          static_cast<cudaStream_t>(stream), kLaunchGlue, 1,
             static_cast<__nv_bfloat16 *>(hidden), static_cast<const __nv_bfloat16 *>(delta),
             static_cast<__nv_bfloat16 *>(normed), static_cast<const __nv_bfloat16 *>(weight),
-            static_cast<int>(width), eps);
+            static_cast<int>(width), eps, warm);
     } else {
         launch_dependent(add_rms_norm_kernel<1>, dim3(static_cast<unsigned>(rows)), dim3(256), 0,
                          static_cast<cudaStream_t>(stream), kLaunchGlue, 1,
             static_cast<__nv_bfloat16 *>(hidden), static_cast<const __nv_bfloat16 *>(delta),
             static_cast<__nv_bfloat16 *>(normed), static_cast<const __nv_bfloat16 *>(weight),
-            static_cast<int>(width), eps);
+            static_cast<int>(width), eps, warm);
     }
     return launch_status();
 }
@@ -404,7 +407,8 @@ int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void
         static_cast<__nv_bfloat16 *>(key_cache), static_cast<__nv_bfloat16 *>(value_cache),                          \
         static_cast<const Index *>(write_pages), static_cast<const Index *>(write_slots), static_cast<int>(heads),   \
         static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<long long>(pages),                       \
-        static_cast<long long>(page_size), static_cast<long long>(capacity), status)
+        static_cast<long long>(page_size), static_cast<long long>(capacity), status, warm)
+    const WarmRange warm = take_pending_warm();
     if (index_width == 8) {
         if (wide) SINGE_ROTARY(long long, 8); else SINGE_ROTARY(long long, 1);
     } else {

@@ -191,12 +191,8 @@ int launch_write_bulk(cudaStream_t stream, void *key_cache, void *value_cache, c
     constexpr int kStages = 8;
     constexpr int kAhead = 4;
     const size_t smem = kBulkWarps * kStages * row_bytes + 2 * kBulkWarps * kStages * 8 + 128;
-    static bool configured = false;
-    if (!configured) {
-        SINGE_CUDA_TRY(cudaFuncSetAttribute(kv_cache_write_bulk_kernel<Index, kStages, kAhead>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-        configured = true;
-    }
+    static int configured[kMaxDevices] = {0};
+    SINGE_CUDA_TRY(ensure_dynamic_shared(kv_cache_write_bulk_kernel<Index, kStages, kAhead>, 100 * 1024, configured));
     const size_t units = tokens * static_cast<size_t>(tensors);
     size_t blocks = (units + kBulkWarps * 32 - 1) / (kBulkWarps * 32);
     const size_t resident = 227 * 1024 / smem;
@@ -214,16 +210,13 @@ template <typename Vector, typename Index>
 int launch_write(cudaStream_t stream, void *key_cache, void *value_cache, const void *keys, const void *values,
                  const void *write_pages, const void *write_slots, size_t tokens, size_t row_bytes, size_t pages,
                  size_t page_size, int tensors, uint32_t *status) {
-#ifndef SINGE_KVW_UNROLL
-#define SINGE_KVW_UNROLL 2
-#define SINGE_KVW_BLOCKS_PER_SM 8
-#endif
-    constexpr int kUnroll = SINGE_KVW_UNROLL;
+    constexpr int kUnroll = 2;
+    constexpr int kBlocksPerSm = 8;
     const size_t row_vectors = row_bytes / sizeof(Vector);
     const size_t total = tokens * row_vectors * static_cast<size_t>(tensors);
     const size_t per_block = 256 * kUnroll;
     size_t blocks = (total + per_block - 1) / per_block;
-    const size_t cap = static_cast<size_t>(device_sm_count()) * SINGE_KVW_BLOCKS_PER_SM;
+    const size_t cap = static_cast<size_t>(device_sm_count()) * kBlocksPerSm;
     if (blocks > cap) blocks = cap;
     if (blocks == 0) return SINGE_OK;
     kv_cache_write_kernel<Vector, Index, kUnroll><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
@@ -235,15 +228,6 @@ int launch_write(cudaStream_t stream, void *key_cache, void *value_cache, const 
 }
 
 bool aligned16(const void *pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
-
-// SINGE_KVW_BULK=0 keeps the register kernel for every shape (comparison runs).
-bool bulk_write_enabled() {
-    static const bool enabled = [] {
-        const char *value = getenv("SINGE_KVW_BULK");
-        return value == nullptr || value[0] != '0';
-    }();
-    return enabled;
-}
 
 }  // namespace
 
@@ -283,7 +267,7 @@ int kv_cache_write(cudaStream_t stream, void *key_cache, void *value_cache, cons
                                                   write_slots, tokens, row_bytes, pages, page_size, tensors, status))
     // Whole rows through the bulk-copy engine when a warp's ring of 8 rows fits (rows of 256 B .. 3 KB) and there are
     // enough rows to fill the machine; short or odd rows keep the register kernel.
-    if (wide && bulk_write_enabled() && row_bytes >= 256 && row_bytes <= 3072 &&
+    if (wide && row_bytes >= 256 && row_bytes <= 3072 &&
         tokens * static_cast<size_t>(tensors) >= 4096) {
         return index_width == 8
                    ? launch_write_bulk<long long>(stream, key_cache, value_target, keys, value_source, write_pages,

@@ -51,6 +51,12 @@ struct DecodeParams {
     int split_tokens;  // multiple of 16
     int max_splits;
     int partials_only;  // 1: every split slot is written, nothing goes to `out`
+    int stable_paging;  // 1: lengths, block table and every cached row but each sequence's last key position are not
+                        //    written by work still in flight (SINGE_HINT_STABLE_PAGING): they are read ahead of the
+                        //    wait on the preceding kernels
+    int early_release;  // 1: the grid fits the machine in one wave, so the next kernel may become resident at once
+    int prefetch_pages; // with stable_paging: pages beyond the ring pulled into L2 ahead of the wait
+    WarmRange warm;     // pulled into L2 beside the kernel's own work (classic form only)
     float scale_log2;   // scale * log2(e)
     uint32_t *status;
 };
@@ -85,7 +91,15 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
     constexpr int NTILES = HD / 8;
     constexpr int STAGE = decode_stage_bytes<HD>();
 
-    grid_dependency_wait();  // the queries (and, in a decode step, the newest K/V rows) come from the kernel before
+    // The queries (and, in a decode step, the newest K/V rows) come from the kernel before.  No global write of this
+    // kernel -- outputs, split partials -- may move above a thread's wait: an earlier kernel may still read them.
+    const bool stable = !RAGGED && p.stable_paging != 0;
+    if (!RAGGED && threadIdx.x < 32) {
+        warm_l2(p.warm, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                gridDim.x * gridDim.y * gridDim.z, threadIdx.x);
+    }
+    if (!stable) grid_dependency_wait();
+    if (!RAGGED && p.early_release) grid_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -124,7 +138,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
     const int piece = RAGGED ? ragged.control[1] : p.split_tokens;
     if (split > 0 && static_cast<long long>(split) * piece >= len && !p.partials_only) return;
     uint32_t qa[KSTEPS][2];
-    if (warp < kDecodeWarps) {
+    if (warp < kDecodeWarps && !stable) {
         const int row = lane >> 2;
         const int quad = lane & 3;
         const size_t head = static_cast<size_t>(b) * p.heads + g * p.group + row;
@@ -148,6 +162,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
 
     if (split >= n_splits) {
         // Nothing to attend.  Split 0 of an empty sequence still owns the row: zeros, as the reference writes.
+        if (stable) grid_dependency_wait();
         const bool owns_row = split == 0 && !p.partials_only;
         if (owns_row || p.partials_only) {
             for (int r = 0; r < p.group; ++r) {
@@ -184,6 +199,45 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         }
         const uint32_t *table = p.table + static_cast<size_t>(b) * p.table_stride + first_page;
         const long long ragged_at = RAGGED ? ragged.first[b] + first_page : 0;
+        // Stable paging: the ring's first pages are requested ahead of the wait, up to (not including) the page that
+        // holds the sequence's last key position, which the preceding kernel may still be writing.  `ahead` pages
+        // are in flight when the wait returns; the loop below starts behind them.
+        int ahead = 0;
+        if (stable) {
+            const int newest = (len - 1) / kPageTokens - first_page;  // relative index of the page still in flux
+            ahead = min(min(npages, kDecodeStages), newest);
+            if (ahead < 0) ahead = 0;
+            uint32_t page = 0u;
+            if (lane < ahead) page = early_page;  // kDecodeStages <= 32: the early read covers them
+            if (lane < ahead && page >= static_cast<uint32_t>(p.physical_blocks)) {
+                report_status(p.status, kStatusIndexOutOfBounds);
+                page = 0u;
+            }
+            for (int j = 0; j < ahead; ++j) {
+                const uint32_t pg = __shfl_sync(0xffffffffu, page, j);
+                const uint32_t full = bar_full + j * 8;
+                const uint32_t stage = base + j * STAGE;
+                if (lane == 0) mbar_expect_tx(full, STAGE);
+                __syncwarp();
+                if (lane < 2 * NHALF) {
+                    const int hf = lane % NHALF;
+                    const CUtensorMap *map = lane < NHALF ? &k_map : &v_map;
+                    tma_load_4d(stage + lane * kHalfBytes, map, full, hf * 64, g, 0, static_cast<int32_t>(pg));
+                }
+            }
+            const int far = min(min(npages, newest), ahead + p.prefetch_pages);
+            for (int i = ahead + (lane >> 2); i < far; i += 8) {
+                const uint32_t pg = table[i];
+                if (pg < static_cast<uint32_t>(p.physical_blocks)) {
+                    const int which = lane & 3;  // K low, K high, V low, V high (head_dim 64: K, V only)
+                    if (which < 2 * NHALF) {
+                        tma_prefetch_4d(which < NHALF ? &k_map : &v_map, (which % NHALF) * 64, g, 0,
+                                        static_cast<int32_t>(pg));
+                    }
+                }
+            }
+            grid_dependency_wait();
+        }
         for (int chunk = 0; chunk < npages && !failed; chunk += 32) {
             const int mine = chunk + lane;
             uint32_t page = 0u;
@@ -205,6 +259,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
             for (int j = 0; j < count; ++j) {
                 const uint32_t pg = __shfl_sync(0xffffffffu, page, j);
                 const int i = chunk + j;
+                if (i < ahead) continue;  // already in flight
                 const int s = i % kDecodeStages;
                 const int use = i / kDecodeStages;
                 if (use > 0) {
@@ -241,6 +296,16 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         // ---------------- consumers ----------------
         const int row = lane >> 2;   // query head within the group (rows >= group are zero padding)
         const int quad = lane & 3;
+        if (stable) {
+            grid_dependency_wait();
+            const size_t head = static_cast<size_t>(b) * p.heads + g * p.group + row;
+            const uint32_t *q32 = reinterpret_cast<const uint32_t *>(query + head * HD);
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                qa[ks][0] = row < p.group ? q32[ks * 8 + quad] : 0u;
+                qa[ks][1] = row < p.group ? q32[ks * 8 + 4 + quad] : 0u;
+            }
+        }
         float o[NTILES][4];
 #pragma unroll
         for (int nt = 0; nt < NTILES; ++nt) {
@@ -335,6 +400,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
     }
     // Only now may the next kernel on the stream (the combine) take SM slots: its CTAs then arrive while this
     // launch drains instead of competing with its last wave.  CTAs that left early count as having said so.
+    // (A one-wave grid has said so at its top.)
     grid_launch_dependents();
     __syncthreads();
 
@@ -436,17 +502,12 @@ __global__ void decode_combine_kernel(T *out, const float *attn_partial, const f
 template <typename T, int HD, bool RAGGED>
 int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedDecode &shape, const void *key_cache,
                   const void *value_cache, size_t batch) {
-    static bool configured = false;
+    static int configured[kMaxDevices] = {0};  // one table per instantiation, one entry per device
     constexpr int smem = decode_smem_bytes<HD>();
-    if (!configured) {
-        if (RAGGED) {
-            SINGE_CUDA_TRY(cudaFuncSetAttribute(paged_decode_ragged_kernel<T, HD>,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        } else {
-            SINGE_CUDA_TRY(cudaFuncSetAttribute(paged_decode_kernel<T, HD>,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        }
-        configured = true;
+    if (RAGGED) {
+        SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_ragged_kernel<T, HD>, smem, configured));
+    } else {
+        SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_kernel<T, HD>, smem, configured));
     }
     CUtensorMap k_map, v_map;
     const uint64_t dims[4] = {static_cast<uint64_t>(HD), static_cast<uint64_t>(params.kv_heads), kPageTokens,
@@ -474,6 +535,9 @@ int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedD
 
 }  // namespace
 
+// Pages beyond its ring that a CTA pulls into L2 ahead of its dependency wait under SINGE_HINT_STABLE_PAGING.
+int g_decode_prefetch_pages = 0;
+
 // True when the tensor-core flash-decode kernel takes this shape.
 bool paged_decode_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t block_size, const void *key_cache,
                             const void *value_cache, const void *query) {
@@ -498,7 +562,7 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
                         const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch, size_t heads,
                         size_t kv_heads, size_t head_dim, size_t physical_blocks, size_t block_table_batch_stride,
                         size_t max_splits, float scale, bool partials_only, uint32_t *status,
-                        const RaggedDecode *ragged) {
+                        const RaggedDecode *ragged, unsigned hints) {
     DecodeParams params;
     RaggedDecode none;
     none.pages = nullptr;
@@ -523,6 +587,11 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
     params.split_tokens = static_cast<int>(paged_decode_split_tokens(bound, max_splits, kPageTokens));
     params.max_splits = static_cast<int>(max_splits);
     params.partials_only = partials_only ? 1 : 0;
+    params.stable_paging = (ragged == nullptr && (hints & SINGE_HINT_STABLE_PAGING) != 0) ? 1 : 0;
+    // One wave: three CTAs are resident per SM.
+    params.early_release = kv_heads * max_splits * batch <= static_cast<size_t>(3 * device_sm_count()) ? 1 : 0;
+    params.prefetch_pages = g_decode_prefetch_pages;
+    params.warm = ragged == nullptr ? take_pending_warm() : WarmRange{nullptr, 0};
     params.scale_log2 = scale * 1.4426950408889634f;
     params.status = status;
     if (batch > 65535 || max_splits > 65535 || kv_heads > 0x7fffffffull) {
@@ -599,7 +668,6 @@ static __device__ __align__(256) float g_decode_static_scratch[kStaticScratchFlo
 // In host code the array's name is only a handle for the runtime, not a device address; the address the
 // kernels need is looked up once per device, with that device current.
 int static_scratch_address(float **address) {
-    constexpr int kMaxDevices = 64;
     static float *resolved[kMaxDevices] = {nullptr};
     int device = 0;
     SINGE_CUDA_TRY(cudaGetDevice(&device));
@@ -648,7 +716,10 @@ int singe_paged_kv_decode_attention_static_bf16(singe_stream_t stream, void *out
         return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
     }
     // One split needs batch * heads * (head_dim + 1) floats; a problem that does not fit even unsplit is refused.
-    const size_t per_split = batch * heads * (head_dim + 1);
+    size_t per_split = 0;
+    if (__builtin_mul_overflow(batch, heads, &per_split) || __builtin_mul_overflow(per_split, head_dim + 1, &per_split)) {
+        return SINGE_ERR_SIZE_OVERFLOW;
+    }
     if (per_split > kStaticScratchFloats) {
         return SINGE_ERR_STATIC_SCRATCH_EXCEEDED;
     }
@@ -664,7 +735,8 @@ int singe_paged_kv_decode_attention_static_bf16(singe_stream_t stream, void *out
     // array has to start at zero; what an earlier call left behind is never read.
     return paged_decode_splitk(static_cast<cudaStream_t>(stream), 0, out, scratch, scratch + rows * head_dim, query,
                                key_cache, value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim,
-                               physical_blocks, block_table_batch_stride, splits, scale, false, device_error_word(), nullptr);
+                               physical_blocks, block_table_batch_stride, splits, scale, false, device_error_word(), nullptr,
+                               0u);
 }
 
 }  // extern "C"

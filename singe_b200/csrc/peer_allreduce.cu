@@ -42,6 +42,7 @@ struct PeerParams {
     int world;
     int width;
     float eps;
+    WarmRange warm;  // pulled into L2 while the ranks wait for one another
 };
 
 __device__ __forceinline__ void store_release_system(uint32_t *address, uint32_t value) {
@@ -73,6 +74,7 @@ __global__ void __launch_bounds__(kReduceThreads)
     __shared__ float scratch[kReduceThreads / 32];
     const int tid = threadIdx.x;
     grid_launch_dependents();
+    if (tid < 32) warm_l2(p.warm, blockIdx.x, gridDim.x, tid);
     grid_dependency_wait();  // the GEMM before this launch has written this rank's partial rows
     if (tid == 0) {
         shared_epoch = p.state[0] + 1;
@@ -257,6 +259,7 @@ int singe_allreduce_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void 
     params.world = world;
     params.width = static_cast<int>(width);
     params.eps = eps;
+    params.warm = singe::take_pending_warm();
     SINGE_CUDA_TRY(singe::launch_dependent(singe::allreduce_add_rms_norm_kernel, dim3(static_cast<unsigned>(rows)),
                                            dim3(singe::kReduceThreads), 0, static_cast<cudaStream_t>(stream),
                                            singe::kLaunchReduce, 1,

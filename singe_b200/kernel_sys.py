@@ -31,6 +31,9 @@ ERR_CUDA_BASE = 1000
 STATUS_INDEX_OUT_OF_BOUNDS = 1
 STATUS_WAIT_TIMEOUT = 2
 
+HINT_STABLE_WEIGHTS = 1
+HINT_STABLE_PAGING = 2
+
 _p = ctypes.c_void_p
 _z = ctypes.c_size_t
 _i = ctypes.c_int
@@ -40,7 +43,9 @@ _f = ctypes.c_float
 SIGNATURES = {
     "singe_kernel_sys_version": [],
     "singe_status_string": [_i],
-    "singe_debug_take_device_error": [_p],
+    "singe_take_device_error": [_p],
+    "singe_release_workspaces": [],
+    "singe_warm_l2_with_next_launch": [_p, _z],
     "singe_kv_cache_write_bf16": [_p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _p],
     "singe_kv_cache_write_f16": [_p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _p],
     "singe_kv_cache_write_f32": [_p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _p],
@@ -56,6 +61,9 @@ SIGNATURES = {
                                                  _f],
     "singe_paged_kv_decode_splitk_reduce_f16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z,
                                                 _f],
+    "singe_paged_kv_decode_step_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z,
+                                        _f, ctypes.c_uint],
+    "singe_paged_kv_decode_set_prefetch": [_i],
     "singe_paged_attention_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _z, _z, _z, _f, _i,
                                    _z, _p],
     "singe_paged_attention_f32": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _z, _z, _z, _f, _i,
@@ -76,6 +84,8 @@ SIGNATURES = {
     "singe_matmul_bf16_swiglu_bf16": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z],
     "singe_matmul_set_tuning": [_i, _i],
     "singe_matmul_set_splits": [_i],
+    "singe_matmul_set_staging": [_i, _i],
+    "singe_linear_bf16": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _i, ctypes.c_uint],
     "singe_embedding_bf16": [_p, _p, _p, _p, _i, _z, _z, _z, _p],
     "singe_add_rms_norm_bf16": [_p, _p, _p, _p, _p, _z, _z, _f],
     "singe_rotary_cache_write_bf16": [_p, _p, _p, _z, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _z, _z,

@@ -296,7 +296,7 @@ class LlamaDecoder:
 
     def __init__(self, config: LlamaConfig, sequences: int, capacity: int, shard: Shard | None = None, seed: int = 4,
                  weights: dict | None = None, shard_lm_head: bool = True, max_splits: int = 0,
-                 collective: str = "peer", fuse_swiglu: bool = True):
+                 collective: str = "peer", fuse_swiglu: bool = True, overlap: bool = True, warm_mb: int = 32):
         import torch
 
         self.torch = torch
@@ -319,6 +319,13 @@ class LlamaDecoder:
             weights = random_weights(config, seed)
         # SwiGLU in the epilogue of the gate/up GEMM (one launch less per layer; same roundings as the separate ops)
         self.fuse_swiglu = fuse_swiglu
+        # Weights are parameters and the page table is uploaded before the step's kernels are enqueued, so the
+        # kernels may fetch them while the kernel before is still running (SINGE_HINT_*).
+        self.weight_hints = ks.HINT_STABLE_WEIGHTS if overlap else 0
+        self.paging_hints = ks.HINT_STABLE_PAGING if overlap else 0
+        # L2 warm-ahead: the light kernels of a layer (norm / collective, rotary) and the attention kernel also pull
+        # up to this many bytes of the weight matrix a later kernel of the layer streams into L2.
+        self.warm_bytes = (warm_mb << 20) if overlap else 0
         for full in weights["layers"]:
             cut = shard_layer_weights(full, config, self.shard, interleave_gate_up=fuse_swiglu)
             self.layers.append({k: self._device(v) for k, v in cut.items()})
@@ -422,6 +429,12 @@ class LlamaDecoder:
         self.d_lens.copy_(torch.from_numpy((step.positions + 1).astype(np.int32)))
         return step
 
+    def _warm(self, weight) -> None:
+        """Attaches (the first part of) a weight matrix to the next launch as an L2 warm-ahead range."""
+        if self.warm_bytes > 0:
+            size = min(weight.numel() * weight.element_size(), self.warm_bytes)
+            self._check(ks.lib().singe_warm_l2_with_next_launch(weight.data_ptr(), size), "warm")
+
     def _check(self, code: int, where: str) -> None:
         if code != ks.OK:
             raise RuntimeError(f"{where}: status {code} ({ks.status_string(code)})")
@@ -429,14 +442,16 @@ class LlamaDecoder:
     def _linear(self, out, x, weight, stream) -> None:
         m, k = x.shape
         n = weight.shape[0]
-        self._check(ks.lib().singe_matmul_bf16_bf16(stream, out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k,
-                                                    x.stride(0), weight.stride(0), out.stride(0), 0, 1), "linear")
+        self._check(ks.lib().singe_linear_bf16(stream, out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k,
+                                               x.stride(0), weight.stride(0), out.stride(0), 0, self.weight_hints),
+                    "linear")
 
     def _linear_raw(self, out_pointer: int, out_stride: int, x, weight, stream) -> None:
         m, k = x.shape
         n = weight.shape[0]
-        self._check(ks.lib().singe_matmul_bf16_bf16(stream, out_pointer, x.data_ptr(), weight.data_ptr(), m, n, k,
-                                                    x.stride(0), weight.stride(0), out_stride, 0, 1), "linear")
+        self._check(ks.lib().singe_linear_bf16(stream, out_pointer, x.data_ptr(), weight.data_ptr(), m, n, k,
+                                               x.stride(0), weight.stride(0), out_stride, 0, self.weight_hints),
+                    "linear")
 
     def close(self) -> None:
         """Releases the peer-mapped buffers (collective: every rank calls it)."""
@@ -460,22 +475,25 @@ class LlamaDecoder:
         for index, layer in enumerate(self.layers):
             keys, values = self.key_caches[index], self.value_caches[index]
             if self.peer is None or index == 0:
+                self._warm(layer["wqkv"])
                 self._check(lib.singe_add_rms_norm_bf16(stream, self.hidden.data_ptr(),
                                                         None if delta is None else delta.data_ptr(),
                                                         self.normed.data_ptr(), layer["attn_norm"].data_ptr(), t, w,
                                                         c.eps), "attn norm")
             self._linear(self.qkv, self.normed, layer["wqkv"], stream)
+            self._warm(layer["wo"])
             self._check(lib.singe_rotary_cache_write_bf16(
                 stream, self.query.data_ptr(), self.qkv.data_ptr(), self.qkv.stride(0), self.cos.data_ptr(),
                 self.sin.data_ptr(), self.d_positions.data_ptr(), keys.data_ptr(), values.data_ptr(),
                 self.d_pages.data_ptr(), self.d_slots.data_ptr(), 8, t, self.heads, self.kv_heads, d, keys.shape[0],
                 c.page_size, self.capacity, status), "rotary cache write")
             if self.fast_decode:
-                self._check(lib.singe_paged_kv_decode_splitk_reduce_bf16(
+                self._warm(layer["w_gate_up"])
+                self._check(lib.singe_paged_kv_decode_step_bf16(
                     stream, self.attended.data_ptr(), self.attn_scratch.data_ptr(), self.lse_scratch.data_ptr(),
                     self.query.data_ptr(), keys.data_ptr(), values.data_ptr(), self.d_lens.data_ptr(),
                     self.d_table.data_ptr(), t, self.heads, self.kv_heads, d, c.page_size, keys.shape[0], self.stride,
-                    self.max_splits, 1.0 / math.sqrt(d)), "decode attention")
+                    self.max_splits, 1.0 / math.sqrt(d), self.paging_hints), "decode attention")
             else:
                 self._check(lib.singe_paged_kv_decode_attention_bf16(
                     stream, self.attended.data_ptr(), self.query.data_ptr(), keys.data_ptr(), values.data_ptr(),
@@ -483,19 +501,21 @@ class LlamaDecoder:
                     keys.shape[0], self.stride, 1.0 / math.sqrt(d)), "decode attention")
             if self.peer is not None:
                 self._linear_raw(self.peer.partial_pointer(0), w, self.attended, layer["wo"], stream)
+                self._warm(layer["w_down"])
                 self.peer.reduce_add_norm(stream, 0, self.hidden.data_ptr(), self.normed.data_ptr(),
                                           layer["mlp_norm"].data_ptr(), c.eps, status)
             else:
                 self._linear(self.projected, self.attended, layer["wo"], stream)
                 self._all_reduce(self.projected)
+                self._warm(layer["w_down"])
                 self._check(lib.singe_add_rms_norm_bf16(stream, self.hidden.data_ptr(), self.projected.data_ptr(),
                                                         self.normed.data_ptr(), layer["mlp_norm"].data_ptr(), t, w,
                                                         c.eps), "mlp norm")
             if self.fuse_swiglu:
-                self._check(lib.singe_matmul_bf16_swiglu_bf16(
+                self._check(lib.singe_linear_bf16(
                     stream, self.activated.data_ptr(), self.normed.data_ptr(), layer["w_gate_up"].data_ptr(), t,
-                    2 * self.ffn, w, self.normed.stride(0), layer["w_gate_up"].stride(0), self.activated.stride(0)),
-                    "gate/up + swiglu")
+                    2 * self.ffn, w, self.normed.stride(0), layer["w_gate_up"].stride(0), self.activated.stride(0), 1,
+                    self.weight_hints), "gate/up + swiglu")
             else:
                 self._linear(self.gate_up, self.normed, layer["w_gate_up"], stream)
                 self._check(lib.singe_silu_mul_bf16(stream, self.activated.data_ptr(), self.gate_up.data_ptr(),
@@ -505,6 +525,7 @@ class LlamaDecoder:
                 # the down_proj collective also applies the norm that opens the next layer (or the final norm)
                 following = self.layers[index + 1]["attn_norm"] if index + 1 < len(self.layers) else self.final_norm
                 self._linear_raw(self.peer.partial_pointer(1), w, self.activated, layer["w_down"], stream)
+                self._warm(self.layers[index + 1]["wqkv"] if index + 1 < len(self.layers) else self.lm_head)
                 self.peer.reduce_add_norm(stream, 1, self.hidden.data_ptr(), self.normed.data_ptr(),
                                           following.data_ptr(), c.eps, status)
             else:
@@ -512,6 +533,7 @@ class LlamaDecoder:
                 self._all_reduce(self.projected)
                 delta = self.projected
         if self.peer is None:
+            self._warm(self.lm_head)
             self._check(lib.singe_add_rms_norm_bf16(stream, self.hidden.data_ptr(), delta.data_ptr(),
                                                     self.normed.data_ptr(), self.final_norm.data_ptr(), t, w, c.eps),
                         "final norm")

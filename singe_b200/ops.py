@@ -346,5 +346,5 @@ def take_device_error() -> int:
     import ctypes
 
     word = ctypes.c_uint32(0)
-    _check(ks.lib().singe_debug_take_device_error(ctypes.byref(word)), "take_device_error")
+    _check(ks.lib().singe_take_device_error(ctypes.byref(word)), "take_device_error")
     return int(word.value)

@@ -386,6 +386,89 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def decode_step_parity(rank, world, group, collective: str):
+    """Correctness of the tensor-parallel step on this very box, before anything is timed: two Llama-3-8B-wide layers,
+    64 sequences at context 512, the same weights, cache contents and tokens everywhere.  The step with the fused
+    peer-memory collective must agree with the step over NCCL's all-reduce, every rank must pick the same next tokens,
+    and the gathered logits must agree with the same two layers run unsharded on rank 0."""
+    import torch
+
+    from singe_b200 import llama
+
+    config = llama.LlamaConfig(layers=2)
+    sequences, context = 64, 512
+    weights = llama.random_weights(config, seed=11)          # same seed, same values on every rank
+    shard = llama.Shard(rank, world, group)
+    sharded = {kind: llama.LlamaDecoder(config, sequences, context + 16, shard=shard, weights=weights,
+                                        collective=kind) for kind in (collective, "nccl")}
+    whole = llama.LlamaDecoder(config, sequences, context + 16, weights=weights) if rank == 0 else None
+    generator = torch.Generator(device="cuda").manual_seed(12)
+    pages = sharded["nccl"].table.page_count()
+    g = config.kv_heads // world
+    for layer in range(config.layers):
+        for which in ("key_caches", "value_caches"):
+            full = torch.randn((pages, config.page_size, config.kv_heads, config.head_dim), generator=generator,
+                               device="cuda").to(torch.bfloat16)
+            for decoder in sharded.values():
+                getattr(decoder, which)[layer].copy_(full[:, :, rank * g:(rank + 1) * g])
+            if whole is not None:
+                getattr(whole, which)[layer].copy_(full)
+    tokens = np.random.default_rng(13).integers(0, config.vocab, size=sequences)
+    outcome = {}
+    logits = {}
+    for kind, decoder in list(sharded.items()) + ([("whole", whole)] if whole is not None else []):
+        decoder.table.place_prompts([context] * sequences)
+        decoder._refresh_block_table()
+        picked = decoder.step(tokens)
+        torch.cuda.synchronize()
+        logits[kind] = decoder.logits.float()
+        outcome[kind] = picked.clone()
+        if int(decoder.status.item()) != 0:
+            raise RuntimeError(f"decode step ({kind}): status word {int(decoder.status.item())}")
+    ours, nccl = logits[collective], logits["nccl"]
+    # Two bf16 layer stacks that round partial sums in different places drift apart by a little noise on every one of
+    # the 8 M logits (their standard deviation is about 1.3 here): the bound on a single logit leaves room for the
+    # tail of that noise; the root-mean-square error (about 1 % of the logits' own rms, measured) must stay under 3 %.
+    # A wrong sum -- a rank's partial rows missing or doubled -- is an error of order 1 on both counts.
+    tolerance = lambda expect: 1e-1 + 2e-2 * expect.abs()
+    relative_rms = lambda got, expect: float(((got - expect).pow(2).mean() / expect.pow(2).mean()).sqrt())
+    problems = []
+    versus_nccl = float((ours - nccl).abs().max())
+    if not bool(((ours - nccl).abs() <= tolerance(nccl)).all()) or relative_rms(ours, nccl) > 3e-2:
+        problems.append(f"logits differ from the NCCL step by {versus_nccl:.3e}")
+    everyone = [torch.empty_like(outcome[collective]) for _ in range(world)]
+    group.all_gather(everyone, outcome[collective])
+    if any(not torch.equal(everyone[0], other) for other in everyone[1:]):
+        problems.append("ranks picked different next tokens")
+    gathered = [torch.empty_like(sharded[collective].logits) for _ in range(world)]
+    group.all_gather(gathered, sharded[collective].logits)
+    versus_whole = rms_whole = None
+    if rank == 0:
+        full_logits = torch.cat(gathered, dim=1).float() if sharded[collective].shard_lm_head else gathered[0].float()
+        expect = logits["whole"]
+        versus_whole = float((full_logits - expect).abs().max())
+        rms_whole = relative_rms(full_logits, expect)
+        if not bool(((full_logits - expect).abs() <= tolerance(expect)).all()) or rms_whole > 3e-2:
+            problems.append(f"logits differ from the unsharded step by {versus_whole:.3e} (relative rms {rms_whole:.2e})")
+        top = torch.sort(expect, dim=1).values[:, -2:]
+        clear = (top[:, 1] - top[:, 0]) > 0.1
+        if not torch.equal(outcome[collective][clear], expect.argmax(dim=1)[clear]):
+            problems.append("next tokens differ from the unsharded step")
+    for decoder in sharded.values():
+        decoder.close()
+    del sharded, whole, weights
+    torch.cuda.empty_cache()
+    flag = torch.tensor([len(problems)], dtype=torch.int32, device="cuda")
+    group.all_reduce(flag)
+    return {"tp_parity": "ok" if int(flag.item()) == 0 else "FAILED: " + "; ".join(problems or ["on another rank"]),
+            "max_abs_vs_nccl_step": round(versus_nccl, 5),
+            "max_abs_vs_unsharded_step": None if versus_whole is None else round(versus_whole, 5),
+            "relative_rms_vs_unsharded_step": None if rms_whole is None else round(rms_whole, 6),
+            "checked": "2 layers of the Llama-3-8B shape, 64 sequences x 512 context, same weights/cache/tokens on "
+                       "every rank: fused collective vs NCCL all-reduce, every rank's next tokens, gathered logits "
+                       "vs the unsharded step on rank 0"}
+
+
 def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3, collective: str = "peer"):
     """Config 5: Llama-3-8B-shaped decode step, 64 sequences at context 2048, tensor-parallel over all ranks
     (KV heads and column/row-sharded linears, all-reduce after o_proj and down_proj).  Returns rank 0's figures."""
@@ -393,6 +476,14 @@ def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3, collec
 
     from singe_b200 import llama
 
+    parity = None
+    if world > 1:
+        try:
+            parity = decode_step_parity(rank, world, group, collective)
+        except Exception as error:
+            parity = {"tp_parity": "FAILED: " + repr(error)}
+        if parity["tp_parity"] != "ok":
+            return {"error": "the tensor-parallel step is wrong on this box, so it is not timed", **parity}
     config = llama.LlamaConfig()
     sequences, context = 64, 2048
     shard = llama.Shard(rank, world, group)
@@ -429,9 +520,13 @@ def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3, collec
     decoder.close()
     how = "none (one GPU)"
     if world > 1:
-        how = ("one kernel per collective: sum of the ranks' partial rows read from peer memory + residual add + "
-               "RMSNorm" if collective == "peer" else "NCCL all-reduce, then the add + RMSNorm kernel")
-    return {
+        how = {"oneshot": "one kernel per collective: every rank reads all ranks' partial rows from peer memory, then "
+                          "residual add + RMSNorm",
+               "twophase": "one kernel per collective: partial rows pushed to the rank that owns them, summed there, "
+                           "residual add + RMSNorm, normalised rows pushed to every rank",
+               "nccl": "NCCL all-reduce, then the add + RMSNorm kernel"}[decoder.collective]
+    figures = dict(parity or {})
+    figures.update({
         "collective": how,
         "tokens_per_s": round(sequences / seconds, 1), "ms_per_step": round(seconds * 1e3, 3),
         "e2e_tokens_per_s": round(sequences / e2e_seconds, 1), "tp": world,
@@ -440,7 +535,8 @@ def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3, collec
         "lm_head": "vocab-sharded + (max, argmax) gather" if decoder.shard_lm_head else "replicated",
         "collectives_per_step": 2 * config.layers if world > 1 else 0, "status_word": status,
         "config": "Llama-3-8B shape, random bf16 weights, 64 seqs x ctx 2048, page 16, CUDA-graph replay",
-    }
+    })
+    return figures
 
 
 def run_only(args):
@@ -520,7 +616,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-also", action="store_true", help="skip the secondary figures")
     parser.add_argument("--no-decode-step", action="store_true", help="skip the Llama-shaped decode step figure")
-    parser.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+    parser.add_argument("--collective", default="peer", choices=["peer", "oneshot", "twophase", "nccl"],
                         help="how the decode step's two collectives per layer run at --gpus > 1")
     parser.add_argument("--only", default="", help="profiling aid: launch one kernel a few times and exit "
                         "(decode | paged_attention | gemm:M,N,K | prefill[:len,len,...] | kvwrite | step:LAYERS[:TP])")

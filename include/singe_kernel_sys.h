@@ -423,6 +423,26 @@ int singe_allreduce_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void 
                                       const void *const *partials, uint32_t *const *flags, uint32_t *state, int rank,
                                       int world, size_t rows, size_t width, float eps, uint32_t *status);
 
+/* The same collective in two phases, for more ranks (the one-shot form reads world x rows x width per rank):
+ * rank r owns rows [r * rpr, (r + 1) * rpr), rpr = ceil(rows / world).  Every rank pushes its partial rows into their
+ * owners' receive buffers, an owner sums its rows (rank order, f32, rounded to bf16), adds them to ITS rows of the
+ * residual stream `hidden` (only the owner keeps a row of the residual up to date), normalises and pushes the
+ * normalised rows to every rank; when the kernel has finished, the local `normed` [rows, width] holds all rows.
+ * Data crosses NVLink as 8-byte packets {4 bytes data, 4-byte launch epoch}: no flags, fences or atomics.
+ *   partial          : local [rows, width], this rank's partial sums (read only)
+ *   receive, gather  : HOST arrays of `world` device pointers, entry r being rank r's buffer as mapped into this
+ *                      process; receive holds world * rpr * width * 4 bytes, gather rows * width * 4 bytes, both
+ *                      zero at first use and owned by the collective (packet format, not for the caller to read)
+ *   state            : local uint32[4], zero at first use; state[2] != 0 shortens every wait to state[2] * 1024
+ *                      clock cycles (the default is a few seconds).  The one-shot call reads state[2] the same way.
+ * rows <= 256, width % 8 == 0, width <= 8192.  A wait that runs out writes SINGE_STATUS_WAIT_TIMEOUT to *status, leaves
+ * the rows that depended on it unwritten, and the kernel ends.  No reference counterpart beyond the all-reduce itself
+ * (singe-nccl/src/communicator/operations/collectives.rs:99-134). */
+int singe_allreduce_two_phase_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void *normed, const void *weight,
+                                                const void *partial, void *const *receive, void *const *gather,
+                                                uint32_t *state, int rank, int world, size_t rows, size_t width,
+                                                float eps, uint32_t *status);
+
 /* The gate and up projections of GatedMlp (singe/src/nn/layers/feed_forward/mod.rs:58-66) and its activation in one
  * call: rhs [columns, reduction] holds the gate and up weight rows interleaved (row 2j = gate_j, row 2j+1 = up_j),
  * out [rows, columns / 2] = bf16(bf16(silu(g_j)) * u_j) with g, u the bf16-rounded projections: the same roundings as

@@ -458,6 +458,12 @@ __device__ __forceinline__ __half from_float<__half>(float value) {
 // exact f32 value the error is a few ulp, far inside the bf16 rounding that follows.
 __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
+// Sum of squares of a row, the way every RMSNorm in the library takes it, so that the fused and unfused paths agree
+// bit for bit: rows are cut into chunks of eight adjacent values; "virtual thread" t of 512 owns chunks t, t + 512, ...
+// and runs one fused-multiply-add chain over their values in order; the 32 virtual threads of a warp are folded with
+// the xor butterfly of warp_sum, and the warp totals are added in warp order.
+__device__ __forceinline__ float square_chain(float sum, float value) { return __fmaf_rn(value, value, sum); }
+
 __device__ __forceinline__ float warp_sum(float value) {
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) {

@@ -110,7 +110,7 @@ __global__ void add_rms_norm_kernel(__nv_bfloat16 *hidden, const __nv_bfloat16 *
                     store8(hidden + base + c, held[h]);
                 }
 #pragma unroll
-                for (int i = 0; i < 8; ++i) square += held[h].v[i] * held[h].v[i];
+                for (int i = 0; i < 8; ++i) square = square_chain(square, held[h].v[i]);
             }
         }
         for (int c = threadIdx.x * 8 + kHeld * stride; c < width; c += stride) {  // rows wider than the held part
@@ -122,7 +122,7 @@ __global__ void add_rms_norm_kernel(__nv_bfloat16 *hidden, const __nv_bfloat16 *
                 store8(hidden + base + c, value);
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) square += value.v[i] * value.v[i];
+            for (int i = 0; i < 8; ++i) square = square_chain(square, value.v[i]);
         }
         if (normed == nullptr) return;
         const float total = block_sum(square, scratch);
@@ -154,7 +154,7 @@ __global__ void add_rms_norm_kernel(__nv_bfloat16 *hidden, const __nv_bfloat16 *
             value = round_bf16(value + __bfloat162float(delta[base + c]));
             hidden[base + c] = __float2bfloat16_rn(value);
         }
-        square += value * value;
+        square = square_chain(square, value);
     }
     if (normed == nullptr) return;
     const float total = block_sum(square, scratch);

@@ -97,6 +97,7 @@ SIGNATURES = {
     "singe_peer_buffer_close": [_p],
     "singe_peer_buffer_destroy": [_p],
     "singe_allreduce_add_rms_norm_bf16": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _z, _z, _f, _p],
+    "singe_allreduce_two_phase_add_rms_norm_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _z, _z, _f, _p],
 }
 
 _RESTYPES = {

@@ -364,13 +364,22 @@ class LlamaDecoder:
         self.projected = torch.empty((t, w), dtype=bf16, device=dev)
         # The two collectives of a layer: "peer" = one kernel per collective that sums the ranks' partial rows out
         # of peer memory and applies the residual add + RMSNorm that follows; "nccl" = all-reduce, then the norm.
-        if collective not in ("peer", "nccl"):
-            raise ValueError("collective must be 'peer' or 'nccl'")
+        if collective not in ("peer", "oneshot", "twophase", "nccl"):
+            raise ValueError("collective must be 'peer', 'oneshot', 'twophase' or 'nccl'")
+        if collective == "peer":
+            # one-shot: every rank pulls all partial rows (little to pull with two ranks); two-phase: rows are
+            # reduced by their owners and pushed back
+            collective = "oneshot" if tp <= 2 else "twophase"
+        self.collective = collective
         self.peer = None
-        if tp > 1 and collective == "peer":
+        if tp > 1 and collective == "oneshot":
             from .peer import PeerAllReduce
 
             self.peer = PeerAllReduce(self.shard.group, self.shard.rank, tp, t, w)
+        elif tp > 1 and collective == "twophase":
+            from .peer import TwoPhaseAllReduce
+
+            self.peer = TwoPhaseAllReduce(self.shard.group, self.shard.rank, tp, t, w)
         self.gate_up = torch.empty((t, 2 * self.ffn), dtype=bf16, device=dev)
         self.activated = torch.empty((t, self.ffn), dtype=bf16, device=dev)
         self.logits = torch.empty((t, self.lm_head.shape[0]), dtype=bf16, device=dev)

@@ -59,6 +59,42 @@ class PeerBuffer:
             self.local = 0
 
 
+class TwoPhaseAllReduce:
+    """Buffers of the two-phase collective (``singe_allreduce_two_phase_add_rms_norm_bf16``): the packet buffer the
+    peers push their partial rows into, the packet buffer every owner pushes its normalised rows into, and the local
+    epoch state.  The GEMMs write their partial sums into ordinary local memory (``partial_pointer(which)``) and the
+    normalised rows come out in an ordinary local tensor."""
+
+    def __init__(self, group, rank: int, world: int, rows: int, width: int, wait_limit_kcycles: int = 0):
+        import torch
+
+        if world > 8:
+            raise ValueError("the fused all-reduce serves one NVSwitch domain: at most 8 ranks")
+        self.group, self.rank, self.world, self.rows, self.width = group, rank, world, rows, width
+        self.rpr = (rows + world - 1) // world
+        self.receive = PeerBuffer(group, rank, world, world * self.rpr * width * 4)
+        self.gather = PeerBuffer(group, rank, world, rows * width * 4)
+        self.state = torch.zeros(4, dtype=torch.int32, device="cuda")
+        if wait_limit_kcycles:
+            self.state[2] = wait_limit_kcycles
+        self.partials = [torch.empty((rows, width), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+
+    def partial_pointer(self, which: int) -> int:
+        return self.partials[which].data_ptr()
+
+    def reduce_add_norm(self, stream: int, which: int, hidden: int, normed: int, weight: int, eps: float,
+                        status: int) -> None:
+        code = ks.lib().singe_allreduce_two_phase_add_rms_norm_bf16(
+            stream, hidden, normed, weight, self.partials[which].data_ptr(), self.receive.array, self.gather.array,
+            self.state.data_ptr(), self.rank, self.world, self.rows, self.width, eps, status)
+        if code != ks.OK:
+            raise RuntimeError(f"two-phase all-reduce: status {code} ({ks.status_string(code)})")
+
+    def close(self) -> None:
+        for buffer in (self.receive, self.gather):
+            buffer.close(self.group)
+
+
 class PeerAllReduce:
     """The buffers one decode step needs: two partial buffers [rows, width] bf16 that alternate between the
     o_proj and down_proj collectives, the flag arrays, and the local epoch state."""

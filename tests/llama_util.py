@@ -7,6 +7,8 @@ from singe_b200.llama import LlamaConfig
 TINY = LlamaConfig(layers=2, hidden=64, heads=4, kv_heads=2, head_dim=16, ffn=128, vocab=97, page_size=4)
 # head_dim 128 and 16-token pages: the tiled decode kernel and the tensor-core GEMM are on this path
 MEDIUM = LlamaConfig(layers=2, hidden=512, heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=512, page_size=16)
+# eight KV heads: shards across 2, 4 or 8 ranks
+WIDE = LlamaConfig(layers=2, hidden=512, heads=16, kv_heads=8, head_dim=128, ffn=1024, vocab=512, page_size=16)
 
 
 def make_weights(config: LlamaConfig, seed: int = 4) -> dict:

@@ -157,8 +157,8 @@ def sum_over_ranks(value: float, group) -> float:
 # headline: config 2 paged decode
 # ----------------------------------------------------------------------------------------------------------
 
-# DRAM bytes one launch of paged_decode_kernel moves on the config-2 workload (seed 1), from the ncu capture summarised
-# in profiles/paged_decode_kernel_config2.md: 277.40 MB read + 8.50 MB written (the split-K partials).
+# DRAM bytes one launch of paged_decode_kernel moves on the config-2 workload (seed 1), from an ncu capture of this
+# very command (dram__bytes_read.sum + dram__bytes_write.sum): 277.40 MB read + 8.50 MB written (the split-K partials).
 DECODE_DRAM_TRAFFIC = 285_900_000
 
 
@@ -218,17 +218,26 @@ def run_decode(args, rank, world, group):
             for _ in range(args.steps):
                 step(side)
     torch.cuda.synchronize()
-    for _ in range(2):
-        steps_graph.replay()  # untimed: the replay path itself warms up
+    probe_start, probe_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps_graph.replay()  # untimed: the replay path itself warms up
+    probe_start.record(stream)
+    steps_graph.replay()
+    probe_stop.record(stream)
+    torch.cuda.synchronize()
+    # The K-step graph is replayed back to back until the timed region is at least 50 ms long (K steps alone are
+    # about a millisecond, too short for the clock sampler to see), and the time is divided by the replays.
+    replays = max(1, int(math.ceil(50.0 / max(probe_start.elapsed_time(probe_stop), 1e-3))))
+    replays = int(max_over_ranks(float(replays), group))
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(torch.cuda.current_device())
     with sampler:
         barrier_sync(group)
         start.record(stream)
-        steps_graph.replay()
+        for _ in range(replays):
+            steps_graph.replay()
         stop.record(stream)
         barrier_sync(group)
-    seconds = max_over_ranks(start.elapsed_time(stop) * 1e-3, group)
+    seconds = max_over_ranks(start.elapsed_time(stop) * 1e-3 / replays, group)
     my_bytes = float(case.algorithmic_bytes())
     total_bytes = sum_over_ranks(my_bytes, group)
     value = total_bytes * args.steps / seconds / 1e9
@@ -258,7 +267,7 @@ def run_decode(args, rank, world, group):
 
     # ---- kernel duration for the roofline: this rank's own K launches inside the timed region (the step's two
     # kernels back to back; the small combine kernel is counted against the decode kernel) ----
-    launch_seconds = start.elapsed_time(stop) * 1e-3 / args.steps
+    launch_seconds = start.elapsed_time(stop) * 1e-3 / replays / args.steps
     peaks = measured_peaks()
     achieved = my_bytes / launch_seconds / 1e9
 
@@ -301,17 +310,18 @@ def run_decode(args, rank, world, group):
         "config": {"workload": WORKLOAD, "sequences_per_gpu": case.batch, "tokens_per_gpu": case.total_tokens,
                    "algorithmic_bytes_per_step_per_gpu": int(my_bytes), "l2": "inputs (277 MB) larger than L2",
                    "launch_mode": "the K timed steps are one CUDA graph; e2e replays a one-step graph per step",
+                   "timed_replays": replays,
                    "eager_ms_per_step": round(eager_seconds / args.steps * 1e3, 5),
                    "repeat_ms_per_step": spread,
                    "sharding": "by sequence, no collective"},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": 2 * args.steps * replays,
         "clocks": sampler.summary(),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": DECODE_DRAM_TRAFFIC,
                      "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum of "
-                                     "paged_decode_kernel on this workload, profiles/paged_decode_kernel_config2.md)",
+                                     "paged_decode_kernel on this workload)",
                      "algorithmic_bytes": int(my_bytes),
                      "peak_source": peaks["source"], "launch_us": round(launch_seconds * 1e6, 2),
                      "kernels": "paged_decode_kernel + decode_combine_kernel"},
@@ -350,7 +360,9 @@ def run_reference(args):
     if rank != 0:
         return
     case = workloads.paged_decode_case(seed=1)
-    threads = oracle.max_threads()
+    # every core this process may run on (torchrun exports OMP_NUM_THREADS=1 to its ranks, which would otherwise
+    # leave the reference on one thread)
+    threads = max(oracle.max_threads(), len(os.sched_getaffinity(0)))
     rng = np.random.default_rng(1)
     q = workloads.normal_bf16(rng, (case.batch, case.heads, case.head_dim))
     shape = (case.physical_blocks, case.block_size, case.kv_heads, case.head_dim)
@@ -364,8 +376,10 @@ def run_reference(args):
                                              block_size=case.block_size,
                                              block_table_batch_stride=case.block_table_batch_stride, scale=case.scale)
 
-    warmup = min(max(args.warmup, 1), 3)
-    steps = min(args.steps, 20)
+    # one step = the whole config-2 batch (about 0.1 s on 16 threads): the run stays within minutes at any --steps
+    # the driver uses; beyond 200 steps it is cut short and the line says so
+    warmup = args.warmup
+    steps = min(args.steps, 200)
     for _ in range(warmup):
         step()
     begin = time.perf_counter()
@@ -541,7 +555,7 @@ def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3, collec
 
 def run_only(args):
     """Launches one kernel of the path `--steps` times after `--warmup` launches and exits: the small, bounded
-    command the ncu captures under profiles/ are taken from."""
+    command the ncu captures of this repository are taken from."""
     import torch
 
     from singe_b200 import llama, ops, workloads
@@ -558,7 +572,7 @@ def run_only(args):
                                                              case.block_table_batch_stride, case.scale)
         call = lambda: ops.paged_kv_decode_attention(out, query, key_cache, value_cache, lens, table, config)
     elif kind == "paged_attention":
-        from singe_b200 import bench_extra
+        import bench_extra
 
         call, _, _ = bench_extra.paged_attention_call()
     elif kind == "gemm":
@@ -650,7 +664,7 @@ def main():
         line["also"] = {}
         if not args.no_also:
             try:
-                from singe_b200 import bench_extra
+                import bench_extra
 
                 line["also"] = bench_extra.run_all(measured_peaks())
             except Exception as error:  # secondary figures never take the headline down

@@ -2,7 +2,7 @@
 import numpy as np
 import torch
 
-# BASELINE tolerances: bf16 outputs within 2e-2 max-abs and 1e-2 relative of the f32 reference; f32 within 1e-4.
+# Tolerances of the parity tests: bf16 outputs within 2e-2 max-abs and 1e-2 relative of the f32 reference; f32 within 1e-4.
 BF16_ABS = 2e-2
 BF16_REL = 1e-2
 F32_ABS = 1e-4

@@ -122,6 +122,30 @@ def test_config3_full_size_gemm_through_linearity():
     assert torch.equal(y_half * 2.0, y32)  # scaling by a power of two commutes with every rounding
 
 
+@pytest.mark.parametrize("m,n,k", [(4096, 14336, 4096), (4096, 4096, 14336), (16, 14336, 4096), (128, 14336, 4096),
+                                   (16, 4096, 14336), (128, 4096, 14336), (1, 4096, 14336), (16, 4096, 4096),
+                                   (128, 4096, 4096), (1, 4096, 4096)])
+def test_config3_remaining_shapes_by_sampled_rows_and_linearity(m, n, k):
+    # The wide shapes of config 3 take the scalar oracle minutes in full, so: sampled rows against it (every row when
+    # M <= 16), and the whole product through linearity in X, which holds exactly for a power-of-two factor.
+    x, w = _case(m, n, k)
+    y32 = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    ops.matmul_bf16(y32, x, w, ops.MatmulConfig.row_major_transposed_rhs(m, n, k))
+    y = ops.linear(x, w)
+    rows = sorted({0, 1, m // 2, m - 1, min(127, m - 1), min(128, m - 1)}) if m > 16 else list(range(m))
+    rows = rows[:4] if n * k > 4096 * 4096 else rows      # the oracle needs ~0.1 s per row of a 14336-wide product
+    ref = oracle.linear_bf16_f32(_bits(x[rows]), _bits(w), m=len(rows), n=n, k=k)
+    assert_close_bf16(host(y32[rows]), ref, f"config 3 {m}x{n}x{k} sampled rows (f32 out)")
+    assert_close_bf16(host(y[rows]), oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(ref)),
+                      f"config 3 {m}x{n}x{k} sampled rows (bf16 out)")
+    half = (x.float() * 0.5).to(torch.bfloat16)
+    y_half = torch.empty_like(y32)
+    ops.matmul_bf16(y_half, half, w, ops.MatmulConfig.row_major_transposed_rhs(m, n, k))
+    torch.cuda.synchronize()
+    assert ops.take_device_error() == 0
+    assert torch.equal(y_half * 2.0, y32)
+
+
 def test_strided_operands_and_output():
     m, n, k = 96, 160, 192
     x_full, w_full = _case(m, n + 8, k + 64)

@@ -266,11 +266,14 @@ int singe_paged_attention_f32(singe_stream_t stream, float *out, float *lse, con
  *   mod.rs:97-123,746-882), CPU meaning singe-kernel/src/cpu/attention.rs:1248-1420.
  *   query, out : [total_query_tokens, heads, head_dim]; lse : f32 [total_query_tokens, heads], natural
  *   log, -1.0e20 for a row that sees no key.  Sequence b owns query tokens
- *   [offsets[b], offsets[b] + lens_q[b]) and keys 0..lens_kv[b]; causal hides key_index > query_index
- *   with sequence-local indices (singe-kernel/src/cpu/attention.rs:1282,1377).
+ *   [offsets[b], offsets[b] + lens_q[b]) and keys 0..lens_kv[b]; causal == 1 hides key_index > query_index
+ *   with sequence-local indices (singe-kernel/src/cpu/attention.rs:1282,1377).  causal == 2 (an addition, for
+ *   prompt chunks behind an earlier context): the queries are the sequence's LAST tokens, query i sits at position
+ *   lens_kv[b] - lens_q[b] + i (clamped at 0) and sees the keys up to it -- the mask of Tensor::paged_attention
+ *   (singe/src/backend/cpu/normalization/attention.rs:481-483).
  *   ragged: key, value [total_kv_tokens, kv_heads, head_dim], key k of sequence b at row offsets[b] + k.
- * The bf16 ragged entry point runs the tcgen05/TMEM flash-attention kernel when head_dim == 128;
- * other shapes, the paged form and f32 run the general kernel.
+ * The bf16 entry points run the tcgen05/TMEM flash-attention kernel when head_dim == 128 (the paged form with
+ * 16-token pages: its key tiles are gathered through the block table); other shapes and f32 run the general kernel.
  * ================================================================================================= */
 int singe_paged_kv_prefill_attention_bf16(singe_stream_t stream, void *out, float *lse, const void *query,
                                           const void *key_cache, const void *value_cache,

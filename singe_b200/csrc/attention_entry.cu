@@ -152,7 +152,13 @@ struct PackedPrefillPolicy {
             if (static_cast<long long>(offsets[owner]) + keys > total_kv_tokens) return -1;
         }
         long long end = keys;
-        if (causal && local + 1 < end) end = local + 1;
+        if (causal == 1 && local + 1 < end) end = local + 1;
+        if (causal == 2) {
+            // the queries are the sequence's last tokens (attend_paged, backend/cpu/normalization/attention.rs:481-483)
+            long long position = keys + local - static_cast<long long>(lens_q[owner]);
+            if (position < 0) position = 0;
+            if (position + 1 < end) end = position + 1;
+        }
         plan.query = query + row * head_dim;
         plan.out = out + row * head_dim;
         plan.lse = lse + row;
@@ -556,7 +562,7 @@ int packed_prefill_general(cudaStream_t stream, void *out, float *lse, const voi
     policy.kv_heads = static_cast<int>(kv_heads);
     policy.head_dim = static_cast<int>(head_dim);
     policy.block_size = static_cast<int>(block_size);
-    policy.causal = causal ? 1 : 0;
+    policy.causal = causal == 2 ? 2 : (causal ? 1 : 0);
     policy.physical_blocks = static_cast<long long>(physical_blocks);
     policy.stride = static_cast<long long>(stride);
     policy.total_query_tokens = static_cast<long long>(total_q);

@@ -76,7 +76,8 @@ struct PrefillParams {
     const uint32_t *block_table;
     int table_stride;
     int cache_pages;
-    int causal;
+    int causal;     // 0: none; 1: key index > query index hidden (sequence-local, the kernel surface's mask);
+                    // 2: the queries are the sequence's last tokens (query i sits at position len_kv - len_q + i)
     float scale_log2;
     uint32_t *error;
 };
@@ -193,6 +194,8 @@ struct Item {
     int q0;         // sequence-local index of the first query row
     int len_q;
     int len_kv;
+    int shift;      // causal mask: query row i sees keys 0 .. max(i + shift, 0); 0 for the sequence-local mask,
+                    // len_kv - len_q when the queries are the sequence's last tokens
     int tiles[2];   // key tiles tile A / tile B need (0: no real row, or no visible key)
     int key_tiles;  // max of the two
     bool valid;     // false: the sequence's offsets leave the packed tensors
@@ -247,6 +250,7 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
     item.q0 = max(pair, 0) * kPair;
     item.len_q = 0;
     item.len_kv = 0;
+    item.shift = 0;
     item.tiles[0] = item.tiles[1] = 0;
     item.key_tiles = 0;
     if (seq < 0) return item;
@@ -257,12 +261,13 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
                  (p.block_table != nullptr ? item.len_kv <= p.table_stride * kPageTokens
                                            : item.offset + item.len_kv <= p.total_kv);
     if (!item.valid) return item;
+    item.shift = p.causal == 2 ? item.len_kv - item.len_q : 0;
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         const int first = item.q0 + x * kTile;
         const int real = min(max(item.len_q - first, 0), kTile);
         int visible = real > 0 ? item.len_kv : 0;
-        if (p.causal && real > 0) visible = min(visible, first + real);
+        if (p.causal && real > 0) visible = min(visible, max(first + real - 1 + item.shift, 0) + 1);
         item.tiles[x] = (visible + kTile - 1) / kTile;
     }
     item.key_tiles = max(item.tiles[0], item.tiles[1]);
@@ -657,7 +662,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                 tcgen05_fence_after();  // S(j) is ready, and with it every earlier MMA of this tile: O holds P V up to j-1
                 // number of keys of this key tile the row may see
                 int limit = item.len_kv - j * kTile;
-                if (p.causal) limit = min(limit, row + 1 - j * kTile);
+                if (p.causal) limit = min(limit, max(row + item.shift, 0) + 1 - j * kTile);
                 limit = real ? limit : 0;
                 const bool partial = __any_sync(0xffffffffu, limit < kTile);
 
@@ -839,7 +844,7 @@ int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void 
     params.block_table = block_table;
     params.table_stride = static_cast<int>(table_stride);
     params.cache_pages = static_cast<int>(cache_pages);
-    params.causal = causal ? 1 : 0;
+    params.causal = causal == 2 ? 2 : (causal ? 1 : 0);
     params.scale_log2 = scale * 1.4426950408889634f;
     params.error = device_error_word();
     // Upper bound on the items: every sequence can add one partial 256-row pair.

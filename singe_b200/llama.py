@@ -559,6 +559,98 @@ class LlamaDecoder:
         else:
             self.next_tokens.copy_(self.best_index)
 
+    # ---- steps of any shape: prompts, prompt chunks behind a context, idle rows ----
+
+    def step_tokens(self, tokens):
+        """Extends each sequence with its ``tokens`` (an empty list leaves a row idle) and returns the logits of each
+        sequence's last token, [sequences, vocab] -- ``Decoder::step`` of the reference (singe/src/generation/mod.rs:25-36,
+        ``CachedDecoder::step`` :715-744).  A step of one token per sequence takes the decode path (``step``); anything
+        else is a prompt step: every new token's K/V go into the cache first, then the packed causal prefill kernel
+        attends each sequence's new tokens over all of its cached keys (``causal = 2``: the queries are the sequence's
+        last tokens).  A step that cannot get its pages raises before anything changed."""
+        torch, lib, c = self.torch, ks.lib(), self.config
+        if all(len(t) == 1 for t in tokens):
+            self.step([t[0] for t in tokens])
+            return self._full_logits(self.logits)
+        step = self.table.step([[int(v) for v in t] for t in tokens])
+        stream = int(torch.cuda.current_stream().cuda_stream)
+        dev, bf16 = "cuda", torch.bfloat16
+        t, s, w, d = len(step.tokens), self.sequences, c.hidden, c.head_dim
+        to_device = lambda array, dtype: torch.from_numpy(np.ascontiguousarray(array)).to(dev).to(dtype)
+        d_tokens, d_positions = to_device(step.tokens, torch.int64), to_device(step.positions, torch.int64)
+        d_pages, d_slots = to_device(step.write_pages, torch.int64), to_device(step.write_slots, torch.int64)
+        lens_q = np.diff(step.query_offsets).astype(np.int32)
+        page_counts = np.diff(step.page_offsets)
+        lens_kv = ((page_counts - 1) * c.page_size + step.last_page_lengths).astype(np.int32)
+        stride = max(int(page_counts.max()), 1)
+        table = np.zeros((s, stride), dtype=np.uint32)
+        for b in range(s):
+            table[b, : page_counts[b]] = step.pages[step.page_offsets[b]: step.page_offsets[b + 1]]
+        d_lens_q, d_lens_kv = to_device(lens_q, torch.int32), to_device(lens_kv, torch.int32)
+        d_offsets = to_device(step.query_offsets[:-1].astype(np.int32), torch.int32)
+        d_table = to_device(table.view(np.int32), torch.int32)
+        d_last = to_device(step.last_rows, torch.int64)
+        status = self.status.data_ptr()
+        hidden = torch.empty((t, w), dtype=bf16, device=dev)
+        normed = torch.empty((t, w), dtype=bf16, device=dev)
+        qkv = torch.empty((t, (self.heads + 2 * self.kv_heads) * d), dtype=bf16, device=dev)
+        query = torch.empty((t, self.heads, d), dtype=bf16, device=dev)
+        attended = torch.empty((t, self.heads * d), dtype=bf16, device=dev)
+        lse = torch.empty((t, self.heads), dtype=torch.float32, device=dev)
+        projected = torch.empty((t, w), dtype=bf16, device=dev)
+        activated = torch.empty((t, self.ffn), dtype=bf16, device=dev)
+        gate_up = None if self.fuse_swiglu else torch.empty((t, 2 * self.ffn), dtype=bf16, device=dev)
+        self._check(lib.singe_embedding_bf16(stream, hidden.data_ptr(), self.embed.data_ptr(), d_tokens.data_ptr(), 8,
+                                             t, w, c.vocab, status), "embedding")
+        delta = None
+        for index, layer in enumerate(self.layers):
+            keys, values = self.key_caches[index], self.value_caches[index]
+            self._check(lib.singe_add_rms_norm_bf16(stream, hidden.data_ptr(),
+                                                    None if delta is None else delta.data_ptr(), normed.data_ptr(),
+                                                    layer["attn_norm"].data_ptr(), t, w, c.eps), "attn norm")
+            self._linear(qkv, normed, layer["wqkv"], stream)
+            self._check(lib.singe_rotary_cache_write_bf16(
+                stream, query.data_ptr(), qkv.data_ptr(), qkv.stride(0), self.cos.data_ptr(), self.sin.data_ptr(),
+                d_positions.data_ptr(), keys.data_ptr(), values.data_ptr(), d_pages.data_ptr(), d_slots.data_ptr(), 8,
+                t, self.heads, self.kv_heads, d, keys.shape[0], c.page_size, self.capacity, status),
+                "rotary cache write")
+            self._check(lib.singe_paged_kv_prefill_attention_bf16(
+                stream, attended.data_ptr(), lse.data_ptr(), query.data_ptr(), keys.data_ptr(), values.data_ptr(),
+                d_lens_q.data_ptr(), d_lens_kv.data_ptr(), d_offsets.data_ptr(), d_table.data_ptr(), s, t, self.heads,
+                self.kv_heads, d, c.page_size, keys.shape[0], stride, 2, 1.0 / math.sqrt(d)), "prompt attention")
+            self._linear(projected, attended, layer["wo"], stream)
+            self._all_reduce(projected)
+            self._check(lib.singe_add_rms_norm_bf16(stream, hidden.data_ptr(), projected.data_ptr(), normed.data_ptr(),
+                                                    layer["mlp_norm"].data_ptr(), t, w, c.eps), "mlp norm")
+            if self.fuse_swiglu:
+                self._check(lib.singe_linear_bf16(
+                    stream, activated.data_ptr(), normed.data_ptr(), layer["w_gate_up"].data_ptr(), t, 2 * self.ffn, w,
+                    normed.stride(0), layer["w_gate_up"].stride(0), activated.stride(0), 1, self.weight_hints),
+                    "gate/up + swiglu")
+            else:
+                self._linear(gate_up, normed, layer["w_gate_up"], stream)
+                self._check(lib.singe_silu_mul_bf16(stream, activated.data_ptr(), gate_up.data_ptr(),
+                                                    gate_up.data_ptr() + self.ffn * 2, gate_up.stride(0), t, self.ffn),
+                            "swiglu")
+            self._linear(projected, activated, layer["w_down"], stream)
+            self._all_reduce(projected)
+            delta = projected
+        self._check(lib.singe_add_rms_norm_bf16(stream, hidden.data_ptr(), delta.data_ptr(), normed.data_ptr(),
+                                                self.final_norm.data_ptr(), t, w, c.eps), "final norm")
+        last = normed.index_select(0, d_last).contiguous()   # CausalLm::forward_embedded keeps the last rows only
+        logits = torch.empty((s, self.lm_head.shape[0]), dtype=bf16, device=dev)
+        self._linear(logits, last, self.lm_head, stream)
+        return self._full_logits(logits)
+
+    def _full_logits(self, logits):
+        """[sequences, vocab] on every rank (the LM head may be sharded by vocabulary)."""
+        if not self.shard_lm_head:
+            return logits
+        torch = self.torch
+        pieces = [torch.empty_like(logits) for _ in range(self.shard.world)]
+        self.shard.group.all_gather(pieces, logits.contiguous())
+        return torch.cat(pieces, dim=1)
+
     def capture(self) -> None:
         """Captures ``forward`` into a CUDA graph that later steps replay (the reference replays a captured
         step the same way, singe/src/generation/mod.rs:529-579)."""
@@ -581,6 +673,34 @@ class LlamaDecoder:
         else:
             self.forward()
         return self.next_tokens
+
+
+class CachedDecoder:
+    """``LlamaDecoder`` behind the reference's ``Decoder`` trait (singe/src/generation/mod.rs:25-52), which is what
+    ``singe_b200.generation`` drives: ``sequences()``, ``step(tokens)``, ``reset()``, ``release(row)``,
+    ``largest_chunk()``.  Prompt steps read at most the largest prompt chunk of extra tokens (16, 64, 256, ... 1024,
+    ``PromptChunks``, :367-417)."""
+
+    def __init__(self, model: LlamaDecoder, prompt_chunks=None):
+        from .generation import PromptChunks
+
+        self.model = model
+        self.chunks = (prompt_chunks or PromptChunks.STANDARD).sizes(model.capacity)
+
+    def sequences(self) -> int:
+        return self.model.sequences
+
+    def step(self, tokens):
+        return self.model.step_tokens(tokens)
+
+    def reset(self) -> None:
+        self.model.table.reset()
+
+    def release(self, sequence: int) -> None:
+        self.model.table.release(sequence)
+
+    def largest_chunk(self):
+        return self.chunks[-1] if self.chunks else 0
 
 
 def random_weights(config: LlamaConfig, seed: int = 4) -> dict:

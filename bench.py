@@ -538,6 +538,8 @@ def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3, collec
                           "residual add + RMSNorm",
                "twophase": "one kernel per collective: partial rows pushed to the rank that owns them, summed there, "
                            "residual add + RMSNorm, normalised rows pushed to every rank",
+               "pushall": "one kernel per collective: every partial row pushed to every rank, summed there, residual "
+                          "add + RMSNorm",
                "nccl": "NCCL all-reduce, then the add + RMSNorm kernel"}[decoder.collective]
     figures = dict(parity or {})
     figures.update({
@@ -630,7 +632,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-also", action="store_true", help="skip the secondary figures")
     parser.add_argument("--no-decode-step", action="store_true", help="skip the Llama-shaped decode step figure")
-    parser.add_argument("--collective", default="peer", choices=["peer", "oneshot", "twophase", "nccl"],
+    parser.add_argument("--collective", default="peer", choices=["peer", "oneshot", "twophase", "pushall", "nccl"],
                         help="how the decode step's two collectives per layer run at --gpus > 1")
     parser.add_argument("--only", default="", help="profiling aid: launch one kernel a few times and exit "
                         "(decode | paged_attention | gemm:M,N,K | prefill[:len,len,...] | kvwrite | step:LAYERS[:TP])")

@@ -218,13 +218,62 @@ int singe_paged_kv_decode_splitk_reduce_f16(singe_stream_t stream, void *out, fl
  * With SINGE_HINT_STABLE_PAGING the kernel reads lengths, block table and cache pages ahead of the kernels still
  * running before it on the stream, except the page holding each sequence's last key position (the one row the
  * step's cache write, queued just before, fills); the queries are read after those kernels finish.
+ * tickets: uint32 [batch * kv_heads], zero at first use and left zero by every call, or NULL.  With tickets the
+ * split that finishes a (sequence, KV head) row last folds the row's partials inside the decode kernel and no
+ * combine kernel is launched -- one launch less per layer; pass them when batch * kv_heads * max_splits CTAs fit the
+ * machine in one wave (3 per SM), NULL otherwise (with several waves the separate combine kernel is faster).
  * No reference counterpart (the reference's launches serialise). */
 int singe_paged_kv_decode_step_bf16(singe_stream_t stream, void *out, float *attn_scratch, float *lse_scratch,
                                     const void *query, const void *key_cache, const void *value_cache,
                                     const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch,
                                     size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
                                     size_t physical_blocks, size_t block_table_batch_stride, size_t max_splits,
-                                    float scale, unsigned hints);
+                                    float scale, unsigned hints, uint32_t *tickets);
+
+/* Paged decode that rotates its queries itself: `query` holds the projections BEFORE the rotary embedding, the kernel
+ * applies the half-split rotation at positions[b] (cos / sin tables [capacity, head_dim / 2] in bf16; a negative
+ * position wraps by capacity, one still outside is reported through the device error word and treated as 0) --
+ * optionally after a per-head RMSNorm with gain query_norm_weight [head_dim] (NULL: no gain) -- and then attends as
+ * singe_paged_kv_decode_step_bf16 does.  Same rounding as singe_rotary_cache_write_bf16 followed by the decode call.
+ * Only the shapes of the tiled kernel (head_dim 64 / 128, block_size 16, heads / kv_heads <= 8).
+ * Replaces: singe_rotary_paged_attention and its QueryRotation
+ * (singe/src/backend/cuda/kernel_plan/source/paged_attention.rs:535-542,881-977). */
+int singe_rotary_paged_kv_decode_attention_bf16(singe_stream_t stream, void *out, float *attn_scratch,
+                                                float *lse_scratch, const void *query, const void *key_cache,
+                                                const void *value_cache, const int32_t *actual_seq_lens,
+                                                const uint32_t *block_table, const void *cos_table,
+                                                const void *sin_table, const void *positions, int index_width,
+                                                size_t batch, size_t heads, size_t kv_heads, size_t head_dim,
+                                                size_t block_size, size_t physical_blocks,
+                                                size_t block_table_batch_stride, size_t max_splits, size_t capacity,
+                                                float scale, int normalise_query, const void *query_norm_weight,
+                                                float eps, unsigned hints);
+
+/* The attention part of a decode step in ONE launch (plus the combine, unless tickets are given): rotary embedding of
+ * the queries and of the step's new key, the slot-mapped write of the new key and value rows into the cache, and paged
+ * attention over the cached keys and the new one.
+ *   qkv       : [batch, qkv_row_stride] bf16, one new token per sequence: heads * head_dim query projections, then
+ *               kv_heads * head_dim key and kv_heads * head_dim value projections, all BEFORE the rotary embedding
+ *   actual_seq_lens[b] counts the keys INCLUDING the new token (its position + 1); write_pages / write_slots [batch]
+ *               say where its K and V rows go (negative values wrap, anything still outside is dropped and reported
+ *               through `status`); positions [batch] index the cos / sin tables [capacity, head_dim / 2]
+ * The new rows are written by this kernel and not read back from the cache by it, so under SINGE_HINT_STABLE_PAGING
+ * every cache page it streams may be requested ahead of the kernels before it.  Same rounding as
+ * singe_rotary_cache_write_bf16 followed by the decode call, except that the new key's score is a plain f32 dot
+ * product instead of a tensor-core tile (same products, another summation order).
+ * Replaces: the fused rotary_cache_write module followed by singe_rotary_paged_attention
+ * (singe/src/backend/cuda/kernel_plan/source/rotary_cache.rs:238-427, paged_attention.rs:881-977; recognised in
+ * singe/src/compiled/plan/fusion/module.rs:28-74), i.e. GroupedQueryAttention::decode between its projections
+ * (singe/src/nn/layers/attention/grouped.rs:92-115). */
+int singe_decode_step_attention_bf16(singe_stream_t stream, void *out, float *attn_scratch, float *lse_scratch,
+                                     const void *qkv, size_t qkv_row_stride, void *key_cache, void *value_cache,
+                                     const int32_t *actual_seq_lens, const uint32_t *block_table,
+                                     const void *cos_table, const void *sin_table, const void *positions,
+                                     const void *write_pages, const void *write_slots, int index_width, size_t batch,
+                                     size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
+                                     size_t physical_blocks, size_t block_table_batch_stride, size_t max_splits,
+                                     size_t capacity, float scale, unsigned hints, uint32_t *tickets,
+                                     uint32_t *status);
 
 /* Pages beyond its shared-memory ring that each CTA of the hinted decode pulls into L2 ahead of its wait
  * (0 = none, the default).  A tuning knob like singe_matmul_set_staging. */
@@ -257,6 +306,23 @@ int singe_paged_attention_f32(singe_stream_t stream, float *out, float *lse, con
                               int index_width, size_t tokens, size_t heads, size_t kv_heads, size_t head_dim,
                               size_t page_size, size_t cache_pages, size_t sequences, size_t table_len, float scale,
                               int causal, size_t window, uint32_t *status);
+
+/* The same with the remaining AttentionOptions field of the path, the cap on the scaled scores
+ * (singe/src/tensor/neural.rs:26-32; CPU: score = cap * tanh(score / cap) before the softmax,
+ * singe/src/backend/cpu/normalization/attention.rs:445,500; CUDA: paged_attention.rs:112,662-672).  softcap == 0: none.
+ * Plain decode batches keep the tiled flash-decode kernel (tanh.approx on the score path). */
+int singe_paged_attention_options_bf16(singe_stream_t stream, void *out, float *lse, const void *query,
+                                       const void *key_cache, const void *value_cache, const void *query_offsets,
+                                       const void *page_offsets, const void *pages, const void *last_page_lengths,
+                                       int index_width, size_t tokens, size_t heads, size_t kv_heads, size_t head_dim,
+                                       size_t page_size, size_t cache_pages, size_t sequences, size_t table_len,
+                                       float scale, int causal, size_t window, float softcap, uint32_t *status);
+int singe_paged_attention_options_f32(singe_stream_t stream, float *out, float *lse, const float *query,
+                                      const float *key_cache, const float *value_cache, const void *query_offsets,
+                                      const void *page_offsets, const void *pages, const void *last_page_lengths,
+                                      int index_width, size_t tokens, size_t heads, size_t kv_heads, size_t head_dim,
+                                      size_t page_size, size_t cache_pages, size_t sequences, size_t table_len,
+                                      float scale, int causal, size_t window, float softcap, uint32_t *status);
 
 /* =================================================================================================
  * Packed variable-length prefill attention
@@ -336,6 +402,13 @@ int singe_scaled_dot_product_attention_f32(singe_stream_t stream, float *out, co
                                            size_t query_len, size_t key_len, size_t head_dim, float scale,
                                            int causal, size_t window);
 
+/* Tensor::attend with all of its options: singe_scaled_dot_product_attention_f32 plus the score cap (softcap == 0:
+ * none) and per-head sink logits, sinks [heads] or NULL -- a sink takes part in its rows' softmax and weighs no value
+ * (singe/src/backend/cpu/normalization/attention.rs:250-263). */
+int singe_attend_f32(singe_stream_t stream, float *out, const float *query, const float *key, const float *value,
+                     size_t batch, size_t heads, size_t kv_heads, size_t query_len, size_t key_len, size_t head_dim,
+                     float scale, int causal, size_t window, float softcap, const float *sinks);
+
 /* =================================================================================================
  * Linear-layer GEMM
  * Replaces: singe_kernel::cuda::matmul::{matmul_bf16_f32, matmul_mma_bf16_f32} + MatmulConfig
@@ -390,6 +463,19 @@ int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void
                                   size_t kv_heads, size_t head_dim, size_t pages, size_t page_size, size_t capacity,
                                   uint32_t *status);
 
+/* The same with the per-head RMSNorm a model applies to its query and / or key heads before rotating them
+ * (RotationNorm, query_norm / key_norm of RotaryCacheInputs,
+ * singe/src/backend/cuda/kernel_plan/source/rotary_cache.rs:25-52): every head's head_dim values are scaled by
+ * 1 / sqrt(mean(x^2) + eps) and by the gain [head_dim] (NULL: no gain), rounded to bf16 as the separate RmsNorm op
+ * returns them, and then rotated.  head_dim / 2 (head_dim / 16 on the 16-byte path) must be a power of two <= 32. */
+int singe_rotary_norm_cache_write_bf16(singe_stream_t stream, void *q_out, const void *qkv, size_t qkv_row_stride,
+                                       const void *cos_table, const void *sin_table, const void *positions,
+                                       void *key_cache, void *value_cache, const void *write_pages,
+                                       const void *write_slots, int index_width, size_t tokens, size_t heads,
+                                       size_t kv_heads, size_t head_dim, size_t pages, size_t page_size,
+                                       size_t capacity, int normalise_query, const void *query_norm_weight,
+                                       int normalise_key, const void *key_norm_weight, float eps, uint32_t *status);
+
 /* GatedMlp activation (singe/src/nn/layers/feed_forward/mod.rs:58-66): out = bf16(bf16(silu(gate)) * up);
  * gate and up are [rows, width] views with row stride input_row_stride (halves of a fused gate/up projection). */
 int singe_silu_mul_bf16(singe_stream_t stream, void *out, const void *gate, const void *up, size_t input_row_stride,
@@ -438,13 +524,17 @@ int singe_allreduce_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void 
  *                      zero at first use and owned by the collective (packet format, not for the caller to read)
  *   state            : local uint32[4], zero at first use; state[2] != 0 shortens every wait to state[2] * 1024
  *                      clock cycles (the default is a few seconds).  The one-shot call reads state[2] the same way.
+ *   replicated       : 0 as described.  1: every rank owns every row -- each partial row is pushed to ALL ranks, every
+ *                      rank sums and normalises all rows itself and keeps the whole residual stream; one NVLink trip
+ *                      instead of two at world x the bytes, which pays for two ranks.  receive then holds
+ *                      world * rows * width * 4 bytes and gather is unused (pass the same pointers).
  * rows <= 256, width % 8 == 0, width <= 8192.  A wait that runs out writes SINGE_STATUS_WAIT_TIMEOUT to *status, leaves
  * the rows that depended on it unwritten, and the kernel ends.  No reference counterpart beyond the all-reduce itself
  * (singe-nccl/src/communicator/operations/collectives.rs:99-134). */
 int singe_allreduce_two_phase_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void *normed, const void *weight,
                                                 const void *partial, void *const *receive, void *const *gather,
                                                 uint32_t *state, int rank, int world, size_t rows, size_t width,
-                                                float eps, uint32_t *status);
+                                                float eps, int replicated, uint32_t *status);
 
 /* The gate and up projections of GatedMlp (singe/src/nn/layers/feed_forward/mod.rs:58-66) and its activation in one
  * call: rhs [columns, reduction] holds the gate and up weight rows interleaved (row 2j = gate_j, row 2j+1 = up_j),

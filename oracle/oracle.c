@@ -341,7 +341,51 @@ void oracle_splitk_reduce_f32(float *out, const float *attn, const float *lse, s
 /* singe/src/backend/cpu/normalization/attention.rs:191-276  execute_scaled_dot_product_attention
  * Dense [B, H, L, D] queries over [B, H, S, D] keys/values (the caller has already repeated KV heads,
  * :20-130).  causal: end = min(S, i + 1); window (0 = none): start = (i + 1) saturating_sub window.
- * Mask, sinks, softcap and key_lengths are not on the hot path and are not restated. */
+ * softcap (0 = none): score = tanh(score / cap) * cap after the scale (:250).  sinks (NULL = none): one logit per
+ * head, batch_head % heads, which joins the row's max and its sum of exponentials and weighs no value (:253-263).
+ * Mask and key_lengths are not on the hot path and are not restated. */
+void oracle_attend_options_f32(float *out, const float *query, const float *key, const float *value,
+                               size_t batch_heads, size_t query_len, size_t key_len, size_t head_dim,
+                               size_t value_dim, float scale, int causal, size_t window, float softcap,
+                               const float *sinks, size_t heads) {
+#pragma omp parallel for schedule(dynamic, 8)
+    for (size_t row = 0; row < batch_heads * query_len; ++row) {
+        size_t batch_head = row / query_len;
+        size_t qi = row % query_len;
+        const float *q = query + row * head_dim;
+        const float *keys = key + batch_head * key_len * head_dim;
+        const float *values = value + batch_head * key_len * value_dim;
+        size_t end = causal ? (qi + 1 < key_len ? qi + 1 : key_len) : key_len;
+        size_t start = window ? (qi + 1 > window ? qi + 1 - window : 0) : 0;
+        if (end < start) end = start;
+        size_t count = end - start;
+        float *o = out + row * value_dim;
+        for (size_t f = 0; f < value_dim; ++f) o[f] = 0.0f;
+        if (count == 0) continue;
+        float *scores = (float *)malloc(count * sizeof(float));
+        float max_score = -INFINITY;
+        for (size_t k = 0; k < count; ++k) {
+            const float *kp = keys + (start + k) * head_dim;
+            float score = 0.0f;
+            for (size_t d = 0; d < head_dim; ++d) score = fmaf(q[d], kp[d], score);
+            score *= scale;
+            if (softcap > 0.0f) score = tanhf(score / softcap) * softcap;
+            scores[k] = score;
+            max_score = fmaxf(max_score, score);
+        }
+        if (sinks) max_score = fmaxf(max_score, sinks[batch_head % (heads ? heads : 1)]);
+        float score_sum = 0.0f;
+        for (size_t k = 0; k < count; ++k) score_sum += expf(scores[k] - max_score);
+        if (sinks) score_sum += expf(sinks[batch_head % (heads ? heads : 1)] - max_score);
+        for (size_t k = 0; k < count; ++k) {
+            const float *vp = values + (start + k) * value_dim;
+            float weight = expf(scores[k] - max_score) / score_sum;
+            for (size_t f = 0; f < value_dim; ++f) o[f] = fmaf(weight, vp[f], o[f]);
+        }
+        free(scores);
+    }
+}
+
 void oracle_scaled_dot_product_attention_f32(float *out, const float *query, const float *key, const float *value,
                                              size_t batch_heads, size_t query_len, size_t key_len, size_t head_dim,
                                              size_t value_dim, float scale, int causal, size_t window) {
@@ -400,14 +444,33 @@ int oracle_check_paged_values(const int64_t *query_offsets, const int64_t *page_
 /* singe/src/backend/cpu/normalization/attention.rs:424-540  attend_paged (f32)
  * query/out [T, H, D], caches [P, S, G, D], FlashInfer-style paging; queries are the LAST tokens of
  * their sequence (position = keys - queries + i, :481-483); lse [T, H] is base 2 and -inf for a row
- * that sees no key (:459, :513-515).  window 0 = none.  Softcap is not restated.
+ * that sees no key (:459, :513-515).  window 0 = none.  softcap 0 = none, else score = tanh(score / cap) * cap
+ * after the scale (:445, :500).
  * Note the accumulation here is `out = fma(weight/total, value, out)` per key (:519-523), and the
  * weights are exp(score - largest) kept un-normalised until that division. */
+int oracle_attend_paged_options_f32(float *out, float *lse, const float *query, const float *key_cache,
+                                    const float *value_cache, const int64_t *query_offsets,
+                                    const int64_t *page_offsets, const int64_t *pages, size_t table_len,
+                                    const int64_t *last_page_lengths, size_t sequences, size_t tokens, size_t heads,
+                                    size_t kv_heads, size_t head_dim, size_t page_size, size_t cache_pages,
+                                    float scale, int causal, size_t window, float softcap);
+
 int oracle_attend_paged_f32(float *out, float *lse, const float *query, const float *key_cache,
                             const float *value_cache, const int64_t *query_offsets, const int64_t *page_offsets,
                             const int64_t *pages, size_t table_len, const int64_t *last_page_lengths,
                             size_t sequences, size_t tokens, size_t heads, size_t kv_heads, size_t head_dim,
                             size_t page_size, size_t cache_pages, float scale, int causal, size_t window) {
+    return oracle_attend_paged_options_f32(out, lse, query, key_cache, value_cache, query_offsets, page_offsets, pages,
+                                           table_len, last_page_lengths, sequences, tokens, heads, kv_heads, head_dim,
+                                           page_size, cache_pages, scale, causal, window, 0.0f);
+}
+
+int oracle_attend_paged_options_f32(float *out, float *lse, const float *query, const float *key_cache,
+                                    const float *value_cache, const int64_t *query_offsets,
+                                    const int64_t *page_offsets, const int64_t *pages, size_t table_len,
+                                    const int64_t *last_page_lengths, size_t sequences, size_t tokens, size_t heads,
+                                    size_t kv_heads, size_t head_dim, size_t page_size, size_t cache_pages,
+                                    float scale, int causal, size_t window, float softcap) {
     int status = oracle_check_paged_values(query_offsets, page_offsets, pages, table_len, last_page_lengths,
                                            sequences, (int64_t)tokens, (int64_t)cache_pages, (int64_t)page_size);
     if (status != ORACLE_OK) return status;
@@ -442,6 +505,7 @@ int oracle_attend_paged_f32(float *out, float *lse, const float *query, const fl
                     float score = 0.0f;
                     for (size_t d = 0; d < head_dim; ++d) score = fmaf(row[d], kp[d], score);
                     scores[k] = score * scale;
+                    if (softcap > 0.0f) scores[k] = tanhf(scores[k] / softcap) * softcap;
                     largest = fmaxf(largest, scores[k]);
                 }
                 float total = 0.0f;

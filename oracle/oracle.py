@@ -172,6 +172,19 @@ def scaled_dot_product_attention_f32(query, key, value, *, scale, causal, window
     return out
 
 
+def attend_options_f32(query, key, value, *, scale, causal, window=0, softcap=0.0, sinks=None):
+    """Dense [B, H, L, D] attention with the score cap and per-head sink logits of ``Tensor::attend``."""
+    query, key, value = _f32(query), _f32(key), _f32(value)
+    b, h, l, d = query.shape
+    s, dv = key.shape[2], value.shape[3]
+    out = np.zeros((b, h, l, dv), dtype=np.float32)
+    sink_values = None if sinks is None else _f32(sinks)
+    lib().oracle_attend_options_f32(
+        _ptr(out), _ptr(query), _ptr(key), _ptr(value), _sz(b * h), _sz(l), _sz(s), _sz(d), _sz(dv), _f(scale),
+        _i(int(causal)), _sz(window), _f(softcap), None if sink_values is None else _ptr(sink_values), _sz(h))
+    return out
+
+
 def check_paged_values(query_offsets, page_offsets, pages, last_page_lengths, *, tokens, cache_pages, page_size):
     qo = np.ascontiguousarray(query_offsets, dtype=np.int64)
     po = np.ascontiguousarray(page_offsets, dtype=np.int64)
@@ -183,7 +196,7 @@ def check_paged_values(query_offsets, page_offsets, pages, last_page_lengths, *,
 
 
 def attend_paged_f32(query, key_cache, value_cache, query_offsets, page_offsets, pages, last_page_lengths, *, scale,
-                     causal=True, window=0):
+                     causal=True, window=0, softcap=0.0):
     """Tensor-surface paged attention: returns (status, out [T, H, D], lse [T, H] base 2)."""
     query, key_cache, value_cache = _f32(query), _f32(key_cache), _f32(value_cache)
     tokens, heads, head_dim = query.shape
@@ -194,10 +207,10 @@ def attend_paged_f32(query, key_cache, value_cache, query_offsets, page_offsets,
     lp = np.ascontiguousarray(last_page_lengths, dtype=np.int64)
     out = np.zeros((tokens, heads, head_dim), dtype=np.float32)
     lse = np.zeros((tokens, heads), dtype=np.float32)
-    status = lib().oracle_attend_paged_f32(
+    status = lib().oracle_attend_paged_options_f32(
         _ptr(out), _ptr(lse), _ptr(query), _ptr(key_cache), _ptr(value_cache), _ptr(qo), _ptr(po), _ptr(pg),
         _sz(pg.size), _ptr(lp), _sz(lp.size), _sz(tokens), _sz(heads), _sz(kv_heads), _sz(head_dim), _sz(page_size),
-        _sz(cache_pages), _f(scale), _i(int(causal)), _sz(window))
+        _sz(cache_pages), _f(scale), _i(int(causal)), _sz(window), _f(softcap))
     return int(status), out, lse
 
 

@@ -19,7 +19,8 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
                         const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch, size_t heads,
                         size_t kv_heads, size_t head_dim, size_t physical_blocks, size_t block_table_batch_stride,
                         size_t max_splits, float scale, bool partials_only, uint32_t *status,
-                        const RaggedDecode *ragged, unsigned hints);
+                        const RaggedDecode *ragged, unsigned hints, const QueryRotation *rotation, uint32_t *tickets,
+                        const FusedStep *fused);
 extern int g_decode_prefetch_pages;
 // prefill_tcgen05.cu
 bool prefill_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t total_query_tokens, const void *query,
@@ -294,8 +295,8 @@ template <typename Index>
 __device__ __forceinline__ void plan_paged_decode_body(const Index *query_offsets, const Index *page_offsets,
                                                        const Index *pages, const Index *last_page_lengths,
                                                        int sequences, long long cache_pages, long long table_len,
-                                                       long long page_size, int split_budget, int *lens,
-                                                       long long *first, int *control) {
+                                                       long long page_size, int split_budget, int min_piece,
+                                                       int *lens, long long *first, int *control) {
     __shared__ int shared_bad;
     __shared__ int shared_longest;
     if (threadIdx.x == 0) {
@@ -331,7 +332,10 @@ __device__ __forceinline__ void plan_paged_decode_body(const Index *query_offset
     __syncthreads();
     if (threadIdx.x == 0) {
         control[0] = shared_bad;
-        const long long per = (static_cast<long long>(shared_longest) + split_budget - 1) / split_budget;
+        // The budget bounds the grid; pieces are not made shorter than 512 keys for its sake (the split size the
+        // kernel-surface decode uses), so a batch whose longest sequence needs fewer splits leaves the rest unused.
+        long long per = (static_cast<long long>(shared_longest) + split_budget - 1) / split_budget;
+        if (per < min_piece) per = min_piece;
         const long long rounded = (per + page_size - 1) / page_size * page_size;
         control[1] = static_cast<int>(rounded < page_size ? page_size : rounded);
     }
@@ -340,10 +344,10 @@ __device__ __forceinline__ void plan_paged_decode_body(const Index *query_offset
 template <typename Index>
 __global__ void plan_paged_decode_kernel(const Index *query_offsets, const Index *page_offsets, const Index *pages,
                                          const Index *last_page_lengths, int sequences, long long cache_pages,
-                                         long long table_len, long long page_size, int split_budget, int *lens,
-                                         long long *first, int *control) {
+                                         long long table_len, long long page_size, int split_budget, int min_piece,
+                                         int *lens, long long *first, int *control) {
     plan_paged_decode_body<Index>(query_offsets, page_offsets, pages, last_page_lengths, sequences, cache_pages,
-                                  table_len, page_size, split_budget, lens, first, control);
+                                  table_len, page_size, split_budget, min_piece, lens, first, control);
 }
 
 // Both of the above in one launch: the last block plans, the others check (one launch gap fewer per call).
@@ -351,10 +355,11 @@ template <typename Index>
 __global__ void check_and_plan_kernel(const Index *query_offsets, const Index *page_offsets, const Index *pages,
                                       const Index *last_page_lengths, int sequences, long long tokens,
                                       long long cache_pages, long long table_len, long long page_size,
-                                      uint32_t *status, int split_budget, int *lens, long long *first, int *control) {
+                                      uint32_t *status, int split_budget, int min_piece, int *lens, long long *first,
+                                      int *control) {
     if (blockIdx.x == gridDim.x - 1) {
         plan_paged_decode_body<Index>(query_offsets, page_offsets, pages, last_page_lengths, sequences, cache_pages,
-                                      table_len, page_size, split_budget, lens, first, control);
+                                      table_len, page_size, split_budget, min_piece, lens, first, control);
     } else {
         check_paged_values_body<Index>(query_offsets, page_offsets, pages, last_page_lengths, sequences, tokens,
                                        cache_pages, table_len, page_size, status, blockIdx.x, gridDim.x - 1);
@@ -376,6 +381,7 @@ struct DensePolicy {
     long long q_batch, q_head, q_row;     // element strides of query/out
     long long k_batch, k_head, k_row;     // element strides of key/value
     long long lse_batch, lse_head, lse_row;
+    const T *sinks;  // [heads] one sink logit per head, or nullptr
 
     __device__ int locate(size_t row, RowPlan<T> &plan) const {
         const long long i = static_cast<long long>(row % query_len);
@@ -395,6 +401,7 @@ struct DensePolicy {
         plan.end = static_cast<int>(end);
         plan.kv_head = static_cast<int>(head / (heads / kv_heads));
         plan.handle = b * k_batch + plan.kv_head * k_head;
+        if (sinks != nullptr) plan.sink = to_float<T>(sinks[head]);
         return 1;
     }
     __device__ long long key_offset(const RowPlan<T> &plan, int pos) const { return plan.handle + pos * k_row; }
@@ -511,7 +518,7 @@ int decode_half(cudaStream_t stream, int element, void *out, const void *query, 
         SINGE_TRY(workspace_for(stream, rows * (head_dim + 1), &scratch));
         return paged_decode_splitk(stream, element, out, scratch, scratch + rows * head_dim, query, key_cache,
                                    value_cache, lens, table, batch, heads, kv_heads, head_dim, physical_blocks, stride,
-                                   splits, scale, false, device_error_word(), nullptr, 0u);
+                                   splits, scale, false, device_error_word(), nullptr, 0u, nullptr, nullptr, nullptr);
     }
     if (element == 0) {
         return decode_general<__nv_bfloat16>(stream, out, query, key_cache, value_cache, lens, table, batch, heads,
@@ -525,7 +532,8 @@ int decode_splitk_half(cudaStream_t stream, int element, void *out, float *attn_
                        const void *query, const void *key_cache, const void *value_cache, const int32_t *lens,
                        const uint32_t *table, size_t batch, size_t heads, size_t kv_heads, size_t head_dim,
                        size_t block_size, size_t physical_blocks, size_t stride, size_t max_splits, float scale,
-                       bool partials_only, unsigned hints = 0u) {
+                       bool partials_only, unsigned hints = 0u, const QueryRotation *rotation = nullptr,
+                       uint32_t *tickets = nullptr, const FusedStep *fused = nullptr, uint32_t *status = nullptr) {
     SINGE_TRY(validate_paged_decode(batch, heads, kv_heads, head_dim, block_size, physical_blocks, stride, scale));
     if (max_splits == 0) return SINGE_ERR_INVALID_LENGTH;  // validate_fmha_decode_splitk_reduce_config, mod.rs:2553-2559
     if (!fits_i32(max_splits)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
@@ -538,7 +546,8 @@ int decode_splitk_half(cudaStream_t stream, int element, void *out, float *attn_
     }
     return paged_decode_splitk(stream, element, out, attn_scratch, lse_scratch, query, key_cache, value_cache, lens,
                                table, batch, heads, kv_heads, head_dim, physical_blocks, stride, max_splits, scale,
-                               partials_only, device_error_word(), nullptr, hints);
+                               partials_only, status != nullptr ? status : device_error_word(), nullptr, hints, rotation,
+                               tickets, fused);
 }
 
 template <typename T>
@@ -576,7 +585,7 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
                  const void *value_cache, const void *query_offsets, const void *page_offsets, const void *pages,
                  const void *last_page_lengths, size_t tokens, size_t heads, size_t kv_heads, size_t head_dim,
                  size_t page_size, size_t cache_pages, size_t sequences, size_t table_len, float scale, int causal,
-                 size_t window, uint32_t *status) {
+                 size_t window, uint32_t *status, float softcap) {
     TensorPagedPolicy<T, Index> policy;
     policy.query = static_cast<const T *>(query);
     policy.out = static_cast<T *>(out);
@@ -618,6 +627,10 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
         size_t guess = 2 * average;
         if (guess < page_size) guess = page_size;
         const size_t splits = default_splits(sequences, kv_heads, guess);
+        // pieces of at least 512 keys when that still gives the machine enough CTAs (what default_splits assumes)
+        const int min_piece = sequences * kv_heads * ((guess + 511) / 512) >= static_cast<size_t>(device_sm_count()) * 4
+                                  ? 512
+                                  : 128;
         const size_t rows = tokens * heads * splits;
         const size_t partial_floats = rows * (head_dim + 1);
         const size_t plan_floats = 3 * sequences + 16;  // lens (int32), first (int64), control
@@ -635,13 +648,13 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
                 check_and_plan_kernel<Index><<<(blocks > 256 ? 256 : blocks) + 1, 256, 0, stream>>>(
                     policy.query_offsets, policy.page_offsets, policy.pages, policy.last_page_lengths,
                     policy.sequences, policy.tokens, policy.cache_pages, policy.table_len,
-                    static_cast<long long>(page_size), status, static_cast<int>(splits), lens, first, control);
+                    static_cast<long long>(page_size), status, static_cast<int>(splits), min_piece, lens, first, control);
                 checked = true;
             } else {
                 plan_paged_decode_kernel<Index><<<1, 256, 0, stream>>>(
                     policy.query_offsets, policy.page_offsets, policy.pages, policy.last_page_lengths,
                     policy.sequences, policy.cache_pages, policy.table_len, static_cast<long long>(page_size),
-                    static_cast<int>(splits), lens, first, control);
+                    static_cast<int>(splits), min_piece, lens, first, control);
             }
             SINGE_TRY(launch_status());
             RaggedDecode ragged;
@@ -650,11 +663,13 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
             ragged.control = control;
             ragged.index_width = static_cast<int>(sizeof(Index));
             ragged.lse_out = lse;
+            ragged.softcap = softcap;
             const int element = std::is_same<T, __nv_bfloat16>::value ? 0 : 1;
             SINGE_TRY(paged_decode_splitk(stream, element, out, scratch, scratch + rows * head_dim, query, key_cache,
                                           value_cache, lens, nullptr, sequences, heads, kv_heads, head_dim,
                                           cache_pages, 1, splits, scale, false,
-                                          status != nullptr ? status : device_error_word(), &ragged, 0u));
+                                          status != nullptr ? status : device_error_word(), &ragged, 0u, nullptr,
+                                          nullptr, nullptr));
             policy.skip_when_zero = control;
         } else if (grown != SINGE_ERR_AUTOTUNE_DURING_CAPTURE) {
             return grown;
@@ -663,7 +678,7 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
     }
     if (!checked) SINGE_TRY(check_alone());
     return launch_attention_general<T>(stream, policy, tokens * heads, head_dim, scale, LseKind::Base2, -INFINITY,
-                                       status);
+                                       status, softcap);
 }
 
 template <typename T>
@@ -671,7 +686,9 @@ int tensor_paged_entry(singe_stream_t stream, void *out, float *lse, const void 
                        const void *value_cache, const void *query_offsets, const void *page_offsets,
                        const void *pages, const void *last_page_lengths, int index_width, size_t tokens, size_t heads,
                        size_t kv_heads, size_t head_dim, size_t page_size, size_t cache_pages, size_t sequences,
-                       size_t table_len, float scale, int causal, size_t window, uint32_t *status) {
+                       size_t table_len, float scale, int causal, size_t window, uint32_t *status,
+                       float softcap = 0.0f) {
+    if (!(softcap >= 0.0f) || !finite(softcap)) return SINGE_ERR_INVALID_ARGUMENT;
     // paged_attention_problem (singe/src/backend/spec/neural/attention.rs:337-361)
     if (heads == 0 || kv_heads == 0 || head_dim == 0 || page_size == 0 || heads % kv_heads != 0 || !finite(scale)) {
         return SINGE_ERR_INVALID_ARGUMENT;
@@ -691,17 +708,17 @@ int tensor_paged_entry(singe_stream_t stream, void *out, float *lse, const void 
     if (index_width == 8) {
         return tensor_paged<T, long long>(s, out, lse, query, key_cache, value_cache, query_offsets, page_offsets,
                                           pages, last_page_lengths, tokens, heads, kv_heads, head_dim, page_size,
-                                          cache_pages, sequences, table_len, scale, causal, window, status);
+                                          cache_pages, sequences, table_len, scale, causal, window, status, softcap);
     }
     return tensor_paged<T, int>(s, out, lse, query, key_cache, value_cache, query_offsets, page_offsets, pages,
                                 last_page_lengths, tokens, heads, kv_heads, head_dim, page_size, cache_pages, sequences,
-                                table_len, scale, causal, window, status);
+                                table_len, scale, causal, window, status, softcap);
 }
 
 template <typename T>
 int dense_entry(cudaStream_t stream, T *out, float *lse, const T *query, const T *key, const T *value, size_t batch,
                 size_t heads, size_t kv_heads, size_t query_len, size_t key_len, size_t head_dim, float scale,
-                int causal, size_t window, bool bshd) {
+                int causal, size_t window, bool bshd, float softcap = 0.0f, const T *sinks = nullptr) {
     if (batch == 0 || heads == 0 || kv_heads == 0 || query_len == 0 || key_len == 0 || head_dim == 0 ||
         heads % kv_heads != 0 || !finite(scale)) {
         return SINGE_ERR_INVALID_LENGTH;
@@ -710,7 +727,9 @@ int dense_entry(cudaStream_t stream, T *out, float *lse, const T *query, const T
         return SINGE_ERR_LENGTH_EXCEEDS_I32;
     }
     if (out == nullptr || query == nullptr || key == nullptr || value == nullptr) return SINGE_ERR_NULL_POINTER;
+    if (!(softcap >= 0.0f) || !finite(softcap)) return SINGE_ERR_INVALID_ARGUMENT;
     DensePolicy<T> policy;
+    policy.sinks = sinks;
     policy.query = query;
     policy.out = out;
     policy.lse = lse;
@@ -743,7 +762,7 @@ int dense_entry(cudaStream_t stream, T *out, float *lse, const T *query, const T
     policy.lse_head = static_cast<long long>(query_len);
     policy.lse_row = 1;
     return launch_attention_general<T>(stream, policy, batch * heads * query_len, head_dim, scale,
-                                       lse == nullptr ? LseKind::None : LseKind::Natural, -INFINITY, nullptr);
+                                       lse == nullptr ? LseKind::None : LseKind::Natural, -INFINITY, nullptr, softcap);
 }
 
 // splitk_reduce_f32 (singe-kernel/src/cpu/attention.rs:2157-2193) with SplitKReduceConfig strides.
@@ -889,10 +908,83 @@ int singe_paged_kv_decode_step_bf16(singe_stream_t stream, void *out, float *att
                                     const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch,
                                     size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
                                     size_t physical_blocks, size_t block_table_batch_stride, size_t max_splits,
-                                    float scale, unsigned hints) {
+                                    float scale, unsigned hints, uint32_t *tickets) {
     return decode_splitk_half(static_cast<cudaStream_t>(stream), 0, out, attn_scratch, lse_scratch, query, key_cache,
                               value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim, block_size,
-                              physical_blocks, block_table_batch_stride, max_splits, scale, false, hints);
+                              physical_blocks, block_table_batch_stride, max_splits, scale, false, hints, nullptr,
+                              tickets);
+}
+
+int singe_rotary_paged_kv_decode_attention_bf16(singe_stream_t stream, void *out, float *attn_scratch,
+                                                float *lse_scratch, const void *query, const void *key_cache,
+                                                const void *value_cache, const int32_t *actual_seq_lens,
+                                                const uint32_t *block_table, const void *cos_table,
+                                                const void *sin_table, const void *positions, int index_width,
+                                                size_t batch, size_t heads, size_t kv_heads, size_t head_dim,
+                                                size_t block_size, size_t physical_blocks,
+                                                size_t block_table_batch_stride, size_t max_splits, size_t capacity,
+                                                float scale, int normalise_query, const void *query_norm_weight,
+                                                float eps, unsigned hints) {
+    if (cos_table == nullptr || sin_table == nullptr || positions == nullptr) return SINGE_ERR_NULL_POINTER;
+    if (index_width != 4 && index_width != 8) return SINGE_ERR_INVALID_ARGUMENT;
+    if (capacity == 0) return SINGE_ERR_INVALID_LENGTH;
+    if (!fits_i32(capacity)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    if (((reinterpret_cast<uintptr_t>(cos_table) | reinterpret_cast<uintptr_t>(sin_table) |
+          reinterpret_cast<uintptr_t>(query_norm_weight)) & 3u) != 0) {
+        return SINGE_ERR_INVALID_ARGUMENT;
+    }
+    QueryRotation rotation;
+    rotation.cos = cos_table;
+    rotation.sin = sin_table;
+    rotation.positions = positions;
+    rotation.index_width = index_width;
+    rotation.capacity = static_cast<int>(capacity);
+    rotation.gain = query_norm_weight;
+    rotation.normalise = normalise_query != 0 ? 1 : 0;
+    rotation.eps = eps;
+    return decode_splitk_half(static_cast<cudaStream_t>(stream), 0, out, attn_scratch, lse_scratch, query, key_cache,
+                              value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim, block_size,
+                              physical_blocks, block_table_batch_stride, max_splits, scale, false, hints, &rotation);
+}
+
+int singe_decode_step_attention_bf16(singe_stream_t stream, void *out, float *attn_scratch, float *lse_scratch,
+                                     const void *qkv, size_t qkv_row_stride, void *key_cache, void *value_cache,
+                                     const int32_t *actual_seq_lens, const uint32_t *block_table,
+                                     const void *cos_table, const void *sin_table, const void *positions,
+                                     const void *write_pages, const void *write_slots, int index_width, size_t batch,
+                                     size_t heads, size_t kv_heads, size_t head_dim, size_t block_size,
+                                     size_t physical_blocks, size_t block_table_batch_stride, size_t max_splits,
+                                     size_t capacity, float scale, unsigned hints, uint32_t *tickets,
+                                     uint32_t *status) {
+    if (qkv == nullptr || cos_table == nullptr || sin_table == nullptr || positions == nullptr ||
+        write_pages == nullptr || write_slots == nullptr) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    if (index_width != 4 && index_width != 8) return SINGE_ERR_INVALID_ARGUMENT;
+    if (capacity == 0 || qkv_row_stride < (heads + 2 * kv_heads) * head_dim) return SINGE_ERR_INVALID_LENGTH;
+    if (!fits_i32(capacity) || !fits_i32(qkv_row_stride)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    if (((reinterpret_cast<uintptr_t>(cos_table) | reinterpret_cast<uintptr_t>(sin_table) |
+          reinterpret_cast<uintptr_t>(qkv)) & 3u) != 0 || qkv_row_stride % 2 != 0) {
+        return SINGE_ERR_INVALID_ARGUMENT;
+    }
+    QueryRotation rotation;
+    rotation.cos = cos_table;
+    rotation.sin = sin_table;
+    rotation.positions = positions;
+    rotation.index_width = index_width;
+    rotation.capacity = static_cast<int>(capacity);
+    rotation.gain = nullptr;
+    rotation.normalise = 0;
+    rotation.eps = 0.0f;
+    FusedStep fused;
+    fused.qkv = qkv;
+    fused.qkv_stride = static_cast<long long>(qkv_row_stride);
+    fused.write_pages = write_pages;
+    fused.write_slots = write_slots;
+    return decode_splitk_half(static_cast<cudaStream_t>(stream), 0, out, attn_scratch, lse_scratch, qkv, key_cache,
+                              value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim, block_size,
+                              physical_blocks, block_table_batch_stride, max_splits, scale, false, hints, &rotation,
+                              tickets, &fused, status);
 }
 
 int singe_paged_kv_decode_set_prefetch(int pages) {
@@ -958,6 +1050,39 @@ int singe_paged_attention_f32(singe_stream_t stream, float *out, float *lse, con
     return tensor_paged_entry<float>(stream, out, lse, query, key_cache, value_cache, query_offsets, page_offsets,
                                      pages, last_page_lengths, index_width, tokens, heads, kv_heads, head_dim,
                                      page_size, cache_pages, sequences, table_len, scale, causal, window, status);
+}
+
+// Tensor::paged_attention with every AttentionOptions field the path has: window and softcap.
+int singe_paged_attention_options_bf16(singe_stream_t stream, void *out, float *lse, const void *query,
+                                       const void *key_cache, const void *value_cache, const void *query_offsets,
+                                       const void *page_offsets, const void *pages, const void *last_page_lengths,
+                                       int index_width, size_t tokens, size_t heads, size_t kv_heads, size_t head_dim,
+                                       size_t page_size, size_t cache_pages, size_t sequences, size_t table_len,
+                                       float scale, int causal, size_t window, float softcap, uint32_t *status) {
+    return tensor_paged_entry<__nv_bfloat16>(stream, out, lse, query, key_cache, value_cache, query_offsets,
+                                             page_offsets, pages, last_page_lengths, index_width, tokens, heads,
+                                             kv_heads, head_dim, page_size, cache_pages, sequences, table_len, scale,
+                                             causal, window, status, softcap);
+}
+
+int singe_paged_attention_options_f32(singe_stream_t stream, float *out, float *lse, const float *query,
+                                      const float *key_cache, const float *value_cache, const void *query_offsets,
+                                      const void *page_offsets, const void *pages, const void *last_page_lengths,
+                                      int index_width, size_t tokens, size_t heads, size_t kv_heads, size_t head_dim,
+                                      size_t page_size, size_t cache_pages, size_t sequences, size_t table_len,
+                                      float scale, int causal, size_t window, float softcap, uint32_t *status) {
+    return tensor_paged_entry<float>(stream, out, lse, query, key_cache, value_cache, query_offsets, page_offsets,
+                                     pages, last_page_lengths, index_width, tokens, heads, kv_heads, head_dim,
+                                     page_size, cache_pages, sequences, table_len, scale, causal, window, status,
+                                     softcap);
+}
+
+// Tensor::attend with window, softcap and sinks.
+int singe_attend_f32(singe_stream_t stream, float *out, const float *query, const float *key, const float *value,
+                     size_t batch, size_t heads, size_t kv_heads, size_t query_len, size_t key_len, size_t head_dim,
+                     float scale, int causal, size_t window, float softcap, const float *sinks) {
+    return dense_entry<float>(static_cast<cudaStream_t>(stream), out, nullptr, query, key, value, batch, heads,
+                              kv_heads, query_len, key_len, head_dim, scale, causal, window, false, softcap, sinks);
 }
 
 // bf16, head_dim 128, 16-token pages: the tcgen05 prefill kernel gathers its K/V tiles through the block table.

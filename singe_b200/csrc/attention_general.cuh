@@ -25,6 +25,8 @@ struct RowPlan {
     int kv_head;
     long long handle;  // policy-specific (sequence index, table offset, ...)
     long long aux;
+    float sink;        // a logit that takes part in the row's softmax and weighs no value, or -inf for none
+                       // (sinks of Tensor::attend, singe/src/backend/cpu/normalization/attention.rs:253-263)
 };
 
 constexpr int kMaxPerLane = 8;  // head_dim <= 256
@@ -32,13 +34,18 @@ constexpr int kMaxPerLane = 8;  // head_dim <= 256
 template <typename T, typename Policy>
 __global__ void __launch_bounds__(128) attention_general_kernel(Policy policy, size_t rows, int head_dim, float scale,
                                                                 LseKind lse_kind, float empty_lse,
-                                                                uint32_t *status) {
+                                                                uint32_t *status, float softcap) {
+    // Launched as a programmatic dependent: its CTAs may become resident while the kernel before still runs, and
+    // read or write nothing before that kernel has finished.
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31;
     const size_t row = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) {
         return;
     }
     RowPlan<T> plan;
+    plan.sink = -INFINITY;
     const int located = policy.locate(row, plan);
     if (located == 0) {
         return;  // the row belongs to no sequence: nothing is written
@@ -56,8 +63,9 @@ __global__ void __launch_bounds__(128) attention_general_kernel(Policy policy, s
         q[i] = (i < per_lane && d < head_dim) ? to_float<T>(plan.query[d]) * scale : 0.0f;
         acc[i] = 0.0f;
     }
-    float running_max = -INFINITY;
-    float running_sum = 0.0f;
+    // a sink starts the online softmax as one key of weight exp(sink - sink) = 1 and value zero
+    float running_max = plan.sink;
+    float running_sum = plan.sink == -INFINITY ? 0.0f : 1.0f;
     bool failed = false;
     for (int pos = plan.start; pos < plan.end; pos += 4) {
         float score[4];
@@ -88,6 +96,9 @@ __global__ void __launch_bounds__(128) attention_general_kernel(Policy policy, s
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             score[j] = warp_sum(score[j]);
+            // AttentionOptions::softcap: the scaled score is capped as cap * tanh(score / cap)
+            // (singe/src/backend/cpu/normalization/attention.rs:250,500)
+            if (softcap > 0.0f) score[j] = softcap * tanhf(score[j] / softcap);
             if (pos + j >= plan.end) score[j] = -INFINITY;
         }
         const float tile_max = fmaxf(fmaxf(score[0], score[1]), fmaxf(score[2], score[3]));
@@ -124,7 +135,7 @@ __global__ void __launch_bounds__(128) attention_general_kernel(Policy policy, s
         if (lane == 0) report_status(status, kStatusIndexOutOfBounds);
         return;
     }
-    const bool empty = plan.end <= plan.start;
+    const bool empty = plan.end <= plan.start && plan.sink == -INFINITY;
     const float inverse = empty ? 0.0f : 1.0f / running_sum;
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; ++i) {
@@ -144,7 +155,7 @@ __global__ void __launch_bounds__(128) attention_general_kernel(Policy policy, s
 
 template <typename T, typename Policy>
 int launch_attention_general(cudaStream_t stream, const Policy &policy, size_t rows, size_t head_dim, float scale,
-                             LseKind lse_kind, float empty_lse, uint32_t *status) {
+                             LseKind lse_kind, float empty_lse, uint32_t *status, float softcap = 0.0f) {
     if (head_dim > 32 * kMaxPerLane) {
         return SINGE_ERR_UNSUPPORTED_WIDTH;
     }
@@ -155,8 +166,9 @@ int launch_attention_general(cudaStream_t stream, const Policy &policy, size_t r
     if (blocks > 0x7fffffffull) {
         return SINGE_ERR_LENGTH_EXCEEDS_I32;
     }
-    attention_general_kernel<T, Policy><<<static_cast<unsigned>(blocks), 128, 0, stream>>>(
-        policy, rows, static_cast<int>(head_dim), scale, lse_kind, empty_lse, status);
+    SINGE_CUDA_TRY(launch_dependent(attention_general_kernel<T, Policy>, dim3(static_cast<unsigned>(blocks)), dim3(128), 0,
+                                    stream, kLaunchGlue, 1, policy, rows, static_cast<int>(head_dim), scale, lse_kind,
+                                    empty_lse, status, softcap));
     return launch_status();
 }
 

@@ -51,6 +51,29 @@ struct RaggedDecode {
     const int *control;        // [0] 0 = plain decode batch (tiled kernel runs), else the general kernel runs; [1] tokens per split
     int index_width;           // 4 or 8
     float *lse_out;            // [tokens, heads] base-2 LSE
+    float softcap;             // 0: none; else the scaled scores are capped as softcap * tanh(score / softcap)
+};
+
+// What the tiled decode kernel needs to rotate its queries itself (singe_rotary_paged_kv_decode_attention_bf16).
+struct QueryRotation {
+    const void *cos;        // [capacity, head_dim / 2] in the cache dtype
+    const void *sin;
+    const void *positions;  // [batch], int32 or int64
+    int index_width;
+    int capacity;
+    const void *gain;       // per-head RMSNorm gain [head_dim] or nullptr
+    int normalise;
+    float eps;
+};
+
+// What the tiled decode kernel needs to take a whole decode step's attention part (see FUSED in paged_decode.cu):
+// the step's un-rotated projections and where the new K/V rows go.  Index width and capacity come with the
+// QueryRotation of the same call.
+struct FusedStep {
+    const void *qkv;          // [batch, qkv_stride]
+    long long qkv_stride;     // elements
+    const void *write_pages;  // [batch]
+    const void *write_slots;  // [batch]
 };
 
 // Programmatic dependent launch.  Every kernel of the decode path is launched with the attribute that lets it start

@@ -169,6 +169,18 @@ __global__ void add_rms_norm_kernel(__nv_bfloat16 *hidden, const __nv_bfloat16 *
 // (write_pages[t], write_slots[t]); V is copied into the cache.  Rounding follows the tensor-op chain of
 // rotate_pairs: first' = bf16(bf16(first*cos) - bf16(second*sin)), second' = bf16(bf16(second*cos) + bf16(first*sin)).
 // With VEC = 8 a thread rotates eight adjacent pairs (head_dim/2 is then a multiple of eight).
+// Per-head RMSNorm before the rotation (RotationNorm, query_norm / key_norm of RotaryCacheInputs,
+// singe/src/backend/cuda/kernel_plan/source/rotary_cache.rs:25-52): each head's D values are scaled by
+// 1 / sqrt(mean(x^2) + eps) and its gain, rounded to bf16 as the separate RmsNorm op would return them, then rotated.
+// The threads of one head are adjacent lanes of one warp, so the head's sum of squares is a few shuffles.
+struct HeadNorms {
+    const __nv_bfloat16 *query_weight;  // [head_dim] gain, or nullptr for none
+    const __nv_bfloat16 *key_weight;
+    int query;                          // 1: normalise the query heads
+    int key;                            // 1: normalise the key heads
+    float eps;
+};
+
 template <typename Index, int VEC>
 __global__ void rotary_cache_write_kernel(__nv_bfloat16 *q_out, const __nv_bfloat16 *qkv, long long qkv_stride,
                                           const __nv_bfloat16 *cos_table, const __nv_bfloat16 *sin_table,
@@ -176,7 +188,7 @@ __global__ void rotary_cache_write_kernel(__nv_bfloat16 *q_out, const __nv_bfloa
                                           __nv_bfloat16 *value_cache, const Index *write_pages,
                                           const Index *write_slots, int heads, int kv_heads, int head_dim,
                                           long long pages, long long page_size, long long capacity,
-                                          uint32_t *status, const WarmRange warm) {
+                                          uint32_t *status, const WarmRange warm, const HeadNorms norms) {
     grid_launch_dependents();
     if (threadIdx.x < 32) warm_l2(warm, blockIdx.x, gridDim.x, threadIdx.x);
     grid_dependency_wait();
@@ -197,21 +209,57 @@ __global__ void rotary_cache_write_kernel(__nv_bfloat16 *q_out, const __nv_bfloa
     const __nv_bfloat16 *sin_row = sin_table + static_cast<size_t>(position) * half;
     const size_t cache_row = (static_cast<size_t>(page) * page_size + slot) * kv_heads * head_dim;
     const int rotated_heads = heads + kv_heads;
-    const int per_head = half / VEC;
-    for (int item = threadIdx.x; item < rotated_heads * per_head; item += blockDim.x) {
-        const int head = item / per_head;
-        const int i = (item - head * per_head) * VEC;
+    const int per_head = half / VEC;   // threads of one head: adjacent lanes (a power of two <= 32 when a norm is asked for)
+    const bool any_norm = norms.query != 0 || norms.key != 0;
+    const int items = rotated_heads * per_head;
+    // With a norm every lane of a warp must reach the shuffles: the loop runs in whole warps.
+    const int bound = any_norm ? (items + 31) / 32 * 32 : items;
+    for (int item = threadIdx.x; item < bound; item += blockDim.x) {
+        const bool live = item < items;
+        const int head = live ? item / per_head : 0;
+        const int i = live ? (item - head * per_head) * VEC : 0;
         const __nv_bfloat16 *source = row + static_cast<size_t>(head) * head_dim;
         __nv_bfloat16 *target = nullptr;
-        if (head < heads) {
+        if (live && head < heads) {
             target = q_out + (static_cast<size_t>(token) * heads + head) * head_dim;
-        } else if (slot_ok) {
+        } else if (live && slot_ok) {
             target = key_cache + cache_row + static_cast<size_t>(head - heads) * head_dim;
         }
-        if (target == nullptr) continue;
+        const bool normalise = live && (head < heads ? norms.query != 0 : norms.key != 0);
+        const __nv_bfloat16 *gain = head < heads ? norms.query_weight : norms.key_weight;
         if (VEC == 8) {
+            Vec8 first, second;
+            if (live) {
+                first = load8(source + i);
+                second = load8(source + i + half);
+            }
+            if (any_norm) {
+                float squares = 0.0f;
+                if (normalise) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) squares += first.v[e] * first.v[e] + second.v[e] * second.v[e];
+                }
+                for (int offset = 1; offset < per_head; offset <<= 1) {
+                    squares += __shfl_xor_sync(0xffffffffu, squares, offset);
+                }
+                if (normalise) {
+                    const float scale = 1.0f / sqrtf(squares / static_cast<float>(head_dim) + norms.eps);
+                    Vec8 gain_first, gain_second;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) gain_first.v[e] = gain_second.v[e] = 1.0f;
+                    if (gain != nullptr) {
+                        gain_first = load8(gain + i);
+                        gain_second = load8(gain + i + half);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        first.v[e] = round_bf16(first.v[e] * scale * gain_first.v[e]);
+                        second.v[e] = round_bf16(second.v[e] * scale * gain_second.v[e]);
+                    }
+                }
+            }
+            if (target == nullptr) continue;
             const Vec8 c = load8(cos_row + i), s = load8(sin_row + i);
-            const Vec8 first = load8(source + i), second = load8(source + i + half);
             Vec8 out_first, out_second;
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -221,10 +269,24 @@ __global__ void rotary_cache_write_kernel(__nv_bfloat16 *q_out, const __nv_bfloa
             store8(target + i, out_first);
             store8(target + i + half, out_second);
         } else {
+            float first = live ? __bfloat162float(source[i]) : 0.0f;
+            float second = live ? __bfloat162float(source[i + half]) : 0.0f;
+            if (any_norm) {
+                float squares = normalise ? first * first + second * second : 0.0f;
+                for (int offset = 1; offset < per_head; offset <<= 1) {
+                    squares += __shfl_xor_sync(0xffffffffu, squares, offset);
+                }
+                if (normalise) {
+                    const float scale = 1.0f / sqrtf(squares / static_cast<float>(head_dim) + norms.eps);
+                    const float g_first = gain != nullptr ? __bfloat162float(gain[i]) : 1.0f;
+                    const float g_second = gain != nullptr ? __bfloat162float(gain[i + half]) : 1.0f;
+                    first = round_bf16(first * scale * g_first);
+                    second = round_bf16(second * scale * g_second);
+                }
+            }
+            if (target == nullptr) continue;
             const float c = __bfloat162float(cos_row[i]);
             const float s = __bfloat162float(sin_row[i]);
-            const float first = __bfloat162float(source[i]);
-            const float second = __bfloat162float(source[i + half]);
             target[i] = __float2bfloat16_rn(round_bf16(first * c) - round_bf16(second * s));
             target[i + half] = __float2bfloat16_rn(round_bf16(second * c) + round_bf16(first * s));
         }
@@ -377,12 +439,11 @@ int singe_add_rms_norm_bf16(singe_stream_t stream, void *hidden, const void *del
     return launch_status();
 }
 
-int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void *qkv, size_t qkv_row_stride,
-                                  const void *cos_table, const void *sin_table, const void *positions,
-                                  void *key_cache, void *value_cache, const void *write_pages,
-                                  const void *write_slots, int index_width, size_t tokens, size_t heads,
-                                  size_t kv_heads, size_t head_dim, size_t pages, size_t page_size, size_t capacity,
-                                  uint32_t *status) {
+static int rotary_cache_write(singe_stream_t stream, void *q_out, const void *qkv, size_t qkv_row_stride,
+                              const void *cos_table, const void *sin_table, const void *positions, void *key_cache,
+                              void *value_cache, const void *write_pages, const void *write_slots, int index_width,
+                              size_t tokens, size_t heads, size_t kv_heads, size_t head_dim, size_t pages,
+                              size_t page_size, size_t capacity, uint32_t *status, const HeadNorms &norms) {
     if (tokens == 0 || heads == 0 || kv_heads == 0 || head_dim == 0 || head_dim % 2 != 0 || pages == 0 ||
         page_size == 0 || capacity == 0 || qkv_row_stride < (heads + 2 * kv_heads) * head_dim) {
         return SINGE_ERR_INVALID_LENGTH;
@@ -398,7 +459,15 @@ int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void
     if (index_width != 4 && index_width != 8) return SINGE_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool wide = (head_dim / 2) % 8 == 0 && qkv_row_stride % 8 == 0 && aligned16(q_out) && aligned16(qkv) &&
-                      aligned16(cos_table) && aligned16(sin_table) && aligned16(key_cache) && aligned16(value_cache);
+                      aligned16(cos_table) && aligned16(sin_table) && aligned16(key_cache) && aligned16(value_cache) &&
+                      aligned16(norms.query_weight) && aligned16(norms.key_weight);
+    if (norms.query != 0 || norms.key != 0) {
+        // a head's threads must be adjacent lanes of one warp
+        const size_t per_head = wide ? head_dim / 16 : head_dim / 2;
+        if (per_head > 32 || (per_head & (per_head - 1)) != 0 || !(norms.eps == norms.eps)) {
+            return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+        }
+    }
 #define SINGE_ROTARY(Index, VEC)                                                                                     \
     launch_dependent(rotary_cache_write_kernel<Index, VEC>, dim3(static_cast<unsigned>(tokens)), dim3(256), 0, s, kLaunchGlue, 1, \
         static_cast<__nv_bfloat16 *>(q_out), static_cast<const __nv_bfloat16 *>(qkv),                                \
@@ -407,7 +476,7 @@ int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void
         static_cast<__nv_bfloat16 *>(key_cache), static_cast<__nv_bfloat16 *>(value_cache),                          \
         static_cast<const Index *>(write_pages), static_cast<const Index *>(write_slots), static_cast<int>(heads),   \
         static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<long long>(pages),                       \
-        static_cast<long long>(page_size), static_cast<long long>(capacity), status, warm)
+        static_cast<long long>(page_size), static_cast<long long>(capacity), status, warm, norms)
     const WarmRange warm = take_pending_warm();
     if (index_width == 8) {
         if (wide) SINGE_ROTARY(long long, 8); else SINGE_ROTARY(long long, 1);
@@ -416,6 +485,33 @@ int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void
     }
 #undef SINGE_ROTARY
     return launch_status();
+}
+
+int singe_rotary_cache_write_bf16(singe_stream_t stream, void *q_out, const void *qkv, size_t qkv_row_stride,
+                                  const void *cos_table, const void *sin_table, const void *positions,
+                                  void *key_cache, void *value_cache, const void *write_pages,
+                                  const void *write_slots, int index_width, size_t tokens, size_t heads,
+                                  size_t kv_heads, size_t head_dim, size_t pages, size_t page_size, size_t capacity,
+                                  uint32_t *status) {
+    const HeadNorms none = {nullptr, nullptr, 0, 0, 0.0f};
+    return rotary_cache_write(stream, q_out, qkv, qkv_row_stride, cos_table, sin_table, positions, key_cache,
+                              value_cache, write_pages, write_slots, index_width, tokens, heads, kv_heads, head_dim,
+                              pages, page_size, capacity, status, none);
+}
+
+int singe_rotary_norm_cache_write_bf16(singe_stream_t stream, void *q_out, const void *qkv, size_t qkv_row_stride,
+                                       const void *cos_table, const void *sin_table, const void *positions,
+                                       void *key_cache, void *value_cache, const void *write_pages,
+                                       const void *write_slots, int index_width, size_t tokens, size_t heads,
+                                       size_t kv_heads, size_t head_dim, size_t pages, size_t page_size,
+                                       size_t capacity, int normalise_query, const void *query_norm_weight,
+                                       int normalise_key, const void *key_norm_weight, float eps, uint32_t *status) {
+    const HeadNorms norms = {static_cast<const __nv_bfloat16 *>(query_norm_weight),
+                             static_cast<const __nv_bfloat16 *>(key_norm_weight), normalise_query != 0 ? 1 : 0,
+                             normalise_key != 0 ? 1 : 0, eps};
+    return rotary_cache_write(stream, q_out, qkv, qkv_row_stride, cos_table, sin_table, positions, key_cache,
+                              value_cache, write_pages, write_slots, index_width, tokens, heads, kv_heads, head_dim,
+                              pages, page_size, capacity, status, norms);
 }
 
 int singe_silu_mul_bf16(singe_stream_t stream, void *out, const void *gate, const void *up, size_t input_row_stride,

@@ -57,14 +57,110 @@ struct DecodeParams {
     int early_release;  // 1: the grid fits the machine in one wave, so the next kernel may become resident at once
     int prefetch_pages; // with stable_paging: pages beyond the ring pulled into L2 ahead of the wait
     WarmRange warm;     // pulled into L2 beside the kernel's own work (classic form only)
+    // Fused step form (FUSED): the kernel reads the step's un-rotated projections itself, rotates Q and the new K row,
+    // writes the new K/V rows into the cache and attends over the cached keys plus the new one.
+    const void *qkv;          // [batch, qkv_stride]: heads*D query | kv_heads*D key | kv_heads*D value projections
+    long long qkv_stride;     // elements
+    void *key_rows;           // the caches as plain pointers, for the one row this step adds per sequence and KV head
+    void *value_rows;
+    const void *write_pages;  // [batch] int32 / int64 (rope_index_width)
+    const void *write_slots;
+    uint32_t *tickets;  // [batch, kv_heads], zero between launches, or nullptr.  With tickets the split that finishes
+                        // a row last folds the row's partials itself and no combine kernel follows (classic form)
+    // Rotation of the queries inside the kernel (rope_cos == nullptr: the queries arrive rotated)
+    const void *rope_cos;        // [capacity, head_dim / 2] in the cache dtype
+    const void *rope_sin;
+    const void *rope_positions;  // [batch] position of each sequence's query token, int32 or int64
+    int rope_index_width;        // 4 or 8
+    int rope_capacity;
+    const void *query_gain;      // per-head RMSNorm before the rotation: gain [head_dim] or nullptr
+    int query_norm;              // 1: normalise
+    float query_norm_eps;
     float scale_log2;   // scale * log2(e)
     uint32_t *status;
 };
+
+__device__ __forceinline__ float fast_tanh(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// Rotates (and first, if asked, RMS-normalises) the query fragments a lane holds, in registers.  A lane of row
+// `row` (a query head of the group) and quad q holds, for every 16-wide k step ks, the elements ks*16 + 2q, +1
+// (qa[ks][0]) and ks*16 + 8 + 2q, +1 (qa[ks][1]): an element of the head's first half and its partner half a head
+// further on sit in the same slot of steps ks and ks + KSTEPS/2, so the half-split rotation needs no exchange.
+// Rounding follows the tensor-op chain of the separate kernel (singe_rotary_cache_write_bf16): every product and every
+// sum is rounded to the cache dtype, so attention over queries rotated here equals attention over queries rotated there.
+// Replaces the query stage of singe_rotary_paged_attention
+// (singe/src/backend/cuda/kernel_plan/source/paged_attention.rs:881-977, QueryRotation).
+template <typename T, int HD>
+__device__ __forceinline__ void rotate_query_fragments(uint32_t (&qa)[HD / 16][2], const DecodeParams &p, int b, int row,
+                                                       int quad, bool may_normalise = true) {
+    constexpr int KSTEPS = HD / 16;
+    constexpr int HALF_STEPS = KSTEPS / 2;
+    long long position = p.rope_index_width == 8 ? static_cast<const long long *>(p.rope_positions)[b]
+                                                 : static_cast<long long>(static_cast<const int *>(p.rope_positions)[b]);
+    if (position < 0) position += p.rope_capacity;
+    if (position < 0 || position >= p.rope_capacity) {
+        report_status(p.status, kStatusIndexOutOfBounds);
+        position = 0;
+    }
+    auto low = [](uint32_t word) {
+        T value;
+        *reinterpret_cast<uint16_t *>(&value) = static_cast<uint16_t>(word & 0xffffu);
+        return to_float<T>(value);
+    };
+    auto high = [](uint32_t word) {
+        T value;
+        *reinterpret_cast<uint16_t *>(&value) = static_cast<uint16_t>(word >> 16);
+        return to_float<T>(value);
+    };
+    auto rounded = [](float value) { return to_float<T>(from_float<T>(value)); };
+    if (p.query_norm && may_normalise) {
+        float squares = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) squares += low(qa[ks][j]) * low(qa[ks][j]) + high(qa[ks][j]) * high(qa[ks][j]);
+        }
+        squares += __shfl_xor_sync(0xffffffffu, squares, 1);
+        squares += __shfl_xor_sync(0xffffffffu, squares, 2);
+        const float scale = 1.0f / sqrtf(squares / static_cast<float>(HD) + p.query_norm_eps);
+        const uint32_t *gain = static_cast<const uint32_t *>(p.query_gain);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t g = gain != nullptr ? gain[ks * 8 + j * 4 + quad] : 0u;
+                const float g_low = gain != nullptr ? low(g) : 1.0f;
+                const float g_high = gain != nullptr ? high(g) : 1.0f;
+                qa[ks][j] = pack2<T>(low(qa[ks][j]) * scale * g_low, high(qa[ks][j]) * scale * g_high);
+            }
+        }
+    }
+    const uint32_t *cos_row = static_cast<const uint32_t *>(p.rope_cos) + position * (HD / 4);
+    const uint32_t *sin_row = static_cast<const uint32_t *>(p.rope_sin) + position * (HD / 4);
+    (void)row;
+#pragma unroll
+    for (int ks = 0; ks < HALF_STEPS; ++ks) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t c = cos_row[ks * 8 + j * 4 + quad];   // pairs ks*16 + 8j + 2q, +1
+            const uint32_t s = sin_row[ks * 8 + j * 4 + quad];
+            const uint32_t first = qa[ks][j], second = qa[ks + HALF_STEPS][j];
+            const float f0 = low(first), f1 = high(first), s0 = low(second), s1 = high(second);
+            qa[ks][j] = pack2<T>(rounded(f0 * low(c)) - rounded(s0 * low(s)), rounded(f1 * high(c)) - rounded(s1 * high(s)));
+            qa[ks + HALF_STEPS][j] =
+                pack2<T>(rounded(s0 * low(c)) + rounded(f0 * low(s)), rounded(s1 * high(c)) + rounded(f1 * high(s)));
+        }
+    }
 }
 
 template <int HD>
@@ -83,9 +179,16 @@ constexpr int decode_smem_bytes() {
 // entries), p.lens and ragged.control were written by the planning kernel of the same call (control[0] != 0: "not a plain
 // decode batch, the general kernel runs instead"; control[1] = tokens per split), and finished rows also get their
 // base-2 LSE in ragged.lse_out.  The classic form carries none of this code and never reads `ragged`.
-template <typename T, int HD, bool RAGGED>
+// FUSED (classic form only) is the whole attention part of a decode step in one launch: lens[b] counts the keys
+// INCLUDING the token this step adds; the CTA whose split holds that last position takes the token's K and V
+// projections straight from the qkv buffer (they never come out of the cache in this step), rotates K, writes both
+// rows into the cache for later steps and folds the new key into its online softmax as one more key; every CTA
+// rotates its own queries.  No rotary / cache-write kernel precedes the launch, so nothing this kernel streams from
+// the cache is written by the kernel before it, and with stable paging every page may be requested ahead of the wait.
+template <typename T, int HD, bool RAGGED, bool FUSED = false>
 __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, const CUtensorMap &v_map,
                                                   const DecodeParams &p, const RaggedDecode &ragged) {
+    static_assert(!(RAGGED && FUSED), "the fused step form is a classic-form kernel");
     constexpr int NHALF = HD / 64;
     constexpr int KSTEPS = HD / 16;
     constexpr int NTILES = HD / 8;
@@ -142,12 +245,16 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         const int row = lane >> 2;
         const int quad = lane & 3;
         const size_t head = static_cast<size_t>(b) * p.heads + g * p.group + row;
-        const uint32_t *q32 = reinterpret_cast<const uint32_t *>(query + head * HD);
+        const uint32_t *q32 =
+            FUSED ? reinterpret_cast<const uint32_t *>(static_cast<const T *>(p.qkv) + static_cast<size_t>(b) * p.qkv_stride +
+                                                       static_cast<size_t>(g * p.group + row) * HD)
+                  : reinterpret_cast<const uint32_t *>(query + head * HD);
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
             qa[ks][0] = row < p.group ? q32[ks * 8 + quad] : 0u;
             qa[ks][1] = row < p.group ? q32[ks * 8 + 4 + quad] : 0u;
         }
+        if (!RAGGED && p.rope_cos != nullptr) rotate_query_fragments<T, HD>(qa, p, b, row, quad);
     }
     // The barriers are set up while the query reads are in flight.
     if (tid == 0) {
@@ -184,7 +291,9 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
     }
 
     const int tok_begin = split * piece;
-    const int tok_end = min(len, tok_begin + piece);
+    // FUSED: the sequence's last key is not in the cache yet; the split that holds its position adds it from registers
+    const bool adds_new = FUSED && (len - 1) / piece == split;
+    const int tok_end = min(adds_new ? len - 1 : len, tok_begin + piece);
     const int npages = tok_end > tok_begin ? (tok_end - tok_begin + kPageTokens - 1) / kPageTokens : 0;
     const int first_page = tok_begin / kPageTokens;
     __syncthreads();
@@ -204,7 +313,8 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         // are in flight when the wait returns; the loop below starts behind them.
         int ahead = 0;
         if (stable) {
-            const int newest = (len - 1) / kPageTokens - first_page;  // relative index of the page still in flux
+            // relative index of the page still in flux (FUSED: none, this kernel writes the new row itself)
+            const int newest = FUSED ? npages : (len - 1) / kPageTokens - first_page;
             ahead = min(min(npages, kDecodeStages), newest);
             if (ahead < 0) ahead = 0;
             uint32_t page = 0u;
@@ -299,12 +409,17 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         if (stable) {
             grid_dependency_wait();
             const size_t head = static_cast<size_t>(b) * p.heads + g * p.group + row;
-            const uint32_t *q32 = reinterpret_cast<const uint32_t *>(query + head * HD);
+            const uint32_t *q32 =
+                FUSED ? reinterpret_cast<const uint32_t *>(static_cast<const T *>(p.qkv) +
+                                                           static_cast<size_t>(b) * p.qkv_stride +
+                                                           static_cast<size_t>(g * p.group + row) * HD)
+                      : reinterpret_cast<const uint32_t *>(query + head * HD);
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) {
                 qa[ks][0] = row < p.group ? q32[ks * 8 + quad] : 0u;
                 qa[ks][1] = row < p.group ? q32[ks * 8 + 4 + quad] : 0u;
             }
+            if (p.rope_cos != nullptr) rotate_query_fragments<T, HD>(qa, p, b, row, quad);
         }
         float o[NTILES][4];
 #pragma unroll
@@ -345,6 +460,15 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
             }
             // Row `row` of this lane: keys t0, t0+1 (tile 0) and t0+8, t0+9 (tile 1).
             const int t0 = tok_begin + i * kPageTokens + quad * 2;
+            if (RAGGED && ragged.softcap > 0.0f) {
+                // AttentionOptions::softcap: cap * tanh(scaled score / cap), then into the base-2 domain
+                const float inward = p.scale_log2 * 0.6931471805599453f / ragged.softcap;
+                const float outward = ragged.softcap * 1.4426950408889634f;
+                s0[0] = outward * fast_tanh(s0[0] * inward) / p.scale_log2;
+                s0[1] = outward * fast_tanh(s0[1] * inward) / p.scale_log2;
+                s1[0] = outward * fast_tanh(s1[0] * inward) / p.scale_log2;
+                s1[1] = outward * fast_tanh(s1[1] * inward) / p.scale_log2;
+            }
             float x00 = t0 < tok_end ? s0[0] * p.scale_log2 : -INFINITY;
             float x01 = t0 + 1 < tok_end ? s0[1] * p.scale_log2 : -INFINITY;
             float x10 = t0 + 8 < tok_end ? s1[0] * p.scale_log2 : -INFINITY;
@@ -384,6 +508,71 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         }
         if (failed && lane == 0) {
             report_status(p.status, kStatusWaitTimeout);
+        }
+        if (FUSED && adds_new && warp == 0) {
+            // ---- the key and value this step adds: rotate K, put both rows into the cache, attend the new key ----
+            const T *projections = static_cast<const T *>(p.qkv) + static_cast<size_t>(b) * p.qkv_stride;
+            const uint32_t *k32 = reinterpret_cast<const uint32_t *>(projections + static_cast<size_t>(p.heads + g) * HD);
+            const uint32_t *v32 =
+                reinterpret_cast<const uint32_t *>(projections + static_cast<size_t>(p.heads + p.kv_heads + g) * HD);
+            long long page = p.rope_index_width == 8 ? static_cast<const long long *>(p.write_pages)[b]
+                                                     : static_cast<long long>(static_cast<const int *>(p.write_pages)[b]);
+            long long slot = p.rope_index_width == 8 ? static_cast<const long long *>(p.write_slots)[b]
+                                                     : static_cast<long long>(static_cast<const int *>(p.write_slots)[b]);
+            if (page < 0) page += p.physical_blocks;
+            if (slot < 0) slot += kPageTokens;
+            const bool slot_ok = page >= 0 && page < p.physical_blocks && slot >= 0 && slot < kPageTokens;
+            if (!slot_ok && lane == 0) report_status(p.status, kStatusIndexOutOfBounds);
+            const size_t cache_row = ((static_cast<size_t>(slot_ok ? page : 0) * kPageTokens + (slot_ok ? slot : 0)) *
+                                          p.kv_heads + g) * HD;
+            uint32_t *k_out = reinterpret_cast<uint32_t *>(static_cast<T *>(p.key_rows) + cache_row);
+            uint32_t *v_out = reinterpret_cast<uint32_t *>(static_cast<T *>(p.value_rows) + cache_row);
+            uint32_t kf[KSTEPS][2];
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                kf[ks][0] = k32[ks * 8 + quad];
+                kf[ks][1] = k32[ks * 8 + 4 + quad];
+            }
+            rotate_query_fragments<T, HD>(kf, p, b, row, quad, false);   // the same rotation, without the query's norm
+            auto low = [](uint32_t word) {
+                T value;
+                *reinterpret_cast<uint16_t *>(&value) = static_cast<uint16_t>(word & 0xffffu);
+                return to_float<T>(value);
+            };
+            auto high = [](uint32_t word) {
+                T value;
+                *reinterpret_cast<uint16_t *>(&value) = static_cast<uint16_t>(word >> 16);
+                return to_float<T>(value);
+            };
+            float dot = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    dot = fmaf(low(qa[ks][j]), low(kf[ks][j]), dot);
+                    dot = fmaf(high(qa[ks][j]), high(kf[ks][j]), dot);
+                    if (row == 0 && slot_ok) k_out[ks * 8 + j * 4 + quad] = kf[ks][j];   // lanes 0-3 hold the whole row
+                }
+            }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            if (slot_ok && lane < HD / 2) v_out[lane] = v32[lane];   // HD / 2 words
+            if (HD / 2 > 32 && slot_ok) v_out[lane + 32] = v32[lane + 32];
+            const float x = dot * p.scale_log2;
+            const float next_max = fmaxf(run_max, x);
+            const float correction = fast_exp2(run_max - next_max);
+            const float weight = fast_exp2(x - next_max);
+            run_max = next_max;
+            run_sum = run_sum * correction + (quad == 0 ? weight : 0.0f);   // the quad's sums are added up below
+            // the weight takes the rounding the tensor-core path gives P
+            T packed_weight = from_float<T>(weight);
+            const float rounded_weight = to_float<T>(packed_weight);
+#pragma unroll
+            for (int nt = 0; nt < NTILES; ++nt) {
+                const uint32_t value = v32[nt * 4 + quad];   // columns nt*8 + 2*quad, +1
+                o[nt][0] = o[nt][0] * correction + rounded_weight * low(value);
+                o[nt][1] = o[nt][1] * correction + rounded_weight * high(value);
+            }
         }
         run_sum += __shfl_xor_sync(0xffffffffu, run_sum, 1);
         run_sum += __shfl_xor_sync(0xffffffffu, run_sum, 2);
@@ -436,6 +625,41 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
             }
         }
     }
+    if (RAGGED || p.tickets == nullptr || direct || p.partials_only) return;
+    // ---------------- the last split of the row to finish folds the row ----------------
+    // Every split of a (sequence, KV head) row takes a ticket once its partials are written and visible; the one
+    // that draws the last ticket reads all of them back (through L2: they were written by other SMs) and writes the
+    // row with the arithmetic of decode_combine_kernel, then puts the counter back to zero for the next launch.
+    // Worth it when the grid is one wave (a tensor-parallel shard, a small batch): the folding CTA holds no slot
+    // another CTA is waiting for, and the step saves a launch.  With several waves it measured slower than the
+    // separate kernel, which is why the caller decides by passing tickets or not.
+    __shared__ int shared_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t *ticket = p.tickets + static_cast<size_t>(b) * p.kv_heads + g;
+        const uint32_t drawn = atomicAdd(ticket, 1u);
+        shared_last = drawn == static_cast<uint32_t>(n_splits - 1) ? 1 : 0;
+        if (shared_last) *ticket = 0u;  // every other split of the row has drawn already
+    }
+    __syncthreads();
+    if (shared_last == 0) return;
+    __threadfence();
+    for (int item = tid; item < p.group * HD; item += kDecodeThreads) {
+        const int r = item / HD;
+        const int d = item - r * HD;
+        const size_t head_row = static_cast<size_t>(b) * p.heads + g * p.group + r;
+        const float *lse = p.lse_partial + head_row * p.max_splits;
+        float top = -INFINITY;
+        for (int s2 = 0; s2 < n_splits; ++s2) top = fmaxf(top, __ldcg(lse + s2));
+        float denom = 0.0f;
+        for (int s2 = 0; s2 < n_splits; ++s2) denom += expf(__ldcg(lse + s2) - top);
+        float sum = 0.0f;
+        for (int s2 = 0; s2 < n_splits; ++s2) {
+            sum = fmaf(expf(__ldcg(lse + s2) - top), __ldcg(p.attn_partial + (head_row * p.max_splits + s2) * HD + d), sum);
+        }
+        static_cast<T *>(p.out)[head_row * HD + d] = from_float<T>(sum / denom);
+    }
 }
 
 template <typename T, int HD>
@@ -448,7 +672,22 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     none.control = nullptr;
     none.index_width = 4;
     none.lse_out = nullptr;
+    none.softcap = 0.0f;
     paged_decode_body<T, HD, false>(k_map, v_map, p, none);
+}
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(kDecodeThreads, 3)
+    paged_decode_fused_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                              const DecodeParams p) {
+    RaggedDecode none;  // never read by this form
+    none.pages = nullptr;
+    none.first = nullptr;
+    none.control = nullptr;
+    none.index_width = 4;
+    none.lse_out = nullptr;
+    none.softcap = 0.0f;
+    paged_decode_body<T, HD, false, true>(k_map, v_map, p, none);
 }
 
 template <typename T, int HD>
@@ -504,8 +743,12 @@ int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedD
                   const void *value_cache, size_t batch) {
     static int configured[kMaxDevices] = {0};  // one table per instantiation, one entry per device
     constexpr int smem = decode_smem_bytes<HD>();
+    const bool fused = !RAGGED && params.qkv != nullptr;
     if (RAGGED) {
         SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_ragged_kernel<T, HD>, smem, configured));
+    } else if (fused) {
+        static int configured_fused[kMaxDevices] = {0};
+        SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_fused_kernel<T, HD>, smem, configured_fused));
     } else {
         SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_kernel<T, HD>, smem, configured));
     }
@@ -526,6 +769,9 @@ int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedD
     if (RAGGED) {
         SINGE_CUDA_TRY(launch_dependent(paged_decode_ragged_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,
                                         kLaunchDecode, 1, k_map, v_map, params, shape));
+    } else if (fused) {
+        SINGE_CUDA_TRY(launch_dependent(paged_decode_fused_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,
+                                        kLaunchDecode, 1, k_map, v_map, params));
     } else {
         SINGE_CUDA_TRY(launch_dependent(paged_decode_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,
                                         kLaunchDecode, 1, k_map, v_map, params));
@@ -562,14 +808,44 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
                         const int32_t *actual_seq_lens, const uint32_t *block_table, size_t batch, size_t heads,
                         size_t kv_heads, size_t head_dim, size_t physical_blocks, size_t block_table_batch_stride,
                         size_t max_splits, float scale, bool partials_only, uint32_t *status,
-                        const RaggedDecode *ragged, unsigned hints) {
+                        const RaggedDecode *ragged, unsigned hints, const QueryRotation *rotation, uint32_t *tickets,
+                        const FusedStep *fused) {
     DecodeParams params;
+    params.tickets = ragged == nullptr && !partials_only ? tickets : nullptr;
+    params.qkv = nullptr;
+    params.qkv_stride = 0;
+    params.key_rows = params.value_rows = nullptr;
+    params.write_pages = params.write_slots = nullptr;
+    if (fused != nullptr && ragged == nullptr && rotation != nullptr && element == 0 && !partials_only) {
+        params.qkv = fused->qkv;
+        params.qkv_stride = fused->qkv_stride;
+        params.key_rows = const_cast<void *>(key_cache);
+        params.value_rows = const_cast<void *>(value_cache);
+        params.write_pages = fused->write_pages;
+        params.write_slots = fused->write_slots;
+    }
+    params.rope_cos = params.rope_sin = params.rope_positions = params.query_gain = nullptr;
+    params.rope_index_width = 8;
+    params.rope_capacity = 0;
+    params.query_norm = 0;
+    params.query_norm_eps = 0.0f;
+    if (rotation != nullptr && ragged == nullptr) {
+        params.rope_cos = rotation->cos;
+        params.rope_sin = rotation->sin;
+        params.rope_positions = rotation->positions;
+        params.rope_index_width = rotation->index_width;
+        params.rope_capacity = rotation->capacity;
+        params.query_gain = rotation->gain;
+        params.query_norm = rotation->normalise;
+        params.query_norm_eps = rotation->eps;
+    }
     RaggedDecode none;
     none.pages = nullptr;
     none.first = nullptr;
     none.control = nullptr;
     none.index_width = 4;
     none.lse_out = nullptr;
+    none.softcap = 0.0f;
     const RaggedDecode &shape = ragged != nullptr ? *ragged : none;
     params.out = out;
     params.attn_partial = attn_scratch;
@@ -618,7 +894,7 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
         }
     }
     SINGE_TRY(result);
-    if (!partials_only && max_splits > 1) {
+    if (!partials_only && max_splits > 1 && params.tickets == nullptr) {
         dim3 grid(static_cast<unsigned>(heads), static_cast<unsigned>(batch));
         const int threads = head_dim >= 128 ? 128 : 64;
 #define SINGE_COMBINE(T, RAGGED_)                                                                                  \
@@ -736,7 +1012,7 @@ int singe_paged_kv_decode_attention_static_bf16(singe_stream_t stream, void *out
     return paged_decode_splitk(static_cast<cudaStream_t>(stream), 0, out, scratch, scratch + rows * head_dim, query,
                                key_cache, value_cache, actual_seq_lens, block_table, batch, heads, kv_heads, head_dim,
                                physical_blocks, block_table_batch_stride, splits, scale, false, device_error_word(), nullptr,
-                               0u);
+                               0u, nullptr, nullptr, nullptr);
 }
 
 }  // extern "C"

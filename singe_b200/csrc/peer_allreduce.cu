@@ -218,6 +218,8 @@ struct TwoPhaseParams {
     const __nv_bfloat16 *weight;
     uint32_t *status;
     int rank, world, rows, rpr, width;
+    int replicated;  // 1: every rank owns every row -- each partial row is pushed to all ranks, every rank sums and
+                     // normalises all rows itself, and there is no second phase (one NVLink trip; for two ranks)
     float eps;
     WarmRange warm;
 };
@@ -271,21 +273,28 @@ __global__ void __launch_bounds__(kTwoPhaseThreads)
     const int quads = p.width >> 2;            // 16-byte packet pairs per row (4 values each)
     constexpr int kHeld = 2;                   // rows up to 1024 * 2 * 4 = 8192 wide
 
-    // ---- phase 1: row c of this rank's partial goes to its owner ----
+    // ---- phase 1: row c of this rank's partial goes to its owner (replicated: to every rank) ----
     {
-        const int owner = c / p.rpr;
-        uint4 *target = p.receive[owner] + (static_cast<size_t>(p.rank) * p.rpr + (c - owner * p.rpr)) * quads;
+        const int owner = p.replicated ? 0 : c / p.rpr;
+        const size_t at = (static_cast<size_t>(p.rank) * p.rpr + (c - owner * p.rpr)) * quads;
         const uint2 *source = reinterpret_cast<const uint2 *>(p.partial + static_cast<size_t>(c) * p.width);
         for (int q = tid; q < quads; q += kTwoPhaseThreads) {
             uint2 value;
             asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(value.x), "=r"(value.y) : "l"(source + q));
-            store_packets(target + q, value.x, value.y, epoch);
+            if (p.replicated) {
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; ++r) {
+                    if (r < p.world) store_packets(p.receive[r] + at + q, value.x, value.y, epoch);
+                }
+            } else {
+                store_packets(p.receive[owner] + at + q, value.x, value.y, epoch);
+            }
         }
     }
 
     // ---- phase 2: the first `owned` CTAs each finish one owned row ----
-    const int first_owned = p.rank * p.rpr;
-    const int owned = max(0, min(p.rows, first_owned + p.rpr) - first_owned);
+    const int first_owned = p.replicated ? 0 : p.rank * p.rpr;
+    const int owned = p.replicated ? p.rows : max(0, min(p.rows, first_owned + p.rpr) - first_owned);
     if (c < owned) {
         const int row = first_owned + c;
         float held[kHeld][4];
@@ -373,10 +382,15 @@ __global__ void __launch_bounds__(kTwoPhaseThreads)
                                                                 held[h][1] * scale * __uint_as_float(gain.x & 0xffff0000u));
                     const uint32_t second = pack2<__nv_bfloat16>(held[h][2] * scale * __uint_as_float(gain.y << 16),
                                                                  held[h][3] * scale * __uint_as_float(gain.y & 0xffff0000u));
+                    if (p.replicated) {
+                        *reinterpret_cast<uint2 *>(p.normed + static_cast<size_t>(row) * p.width + q * 4) =
+                            make_uint2(first, second);
+                    } else {
 #pragma unroll
-                    for (int r = 0; r < kMaxPeers; ++r) {
-                        if (r < p.world) {
-                            store_packets(p.gather[r] + static_cast<size_t>(row) * quads + q, first, second, epoch);
+                        for (int r = 0; r < kMaxPeers; ++r) {
+                            if (r < p.world) {
+                                store_packets(p.gather[r] + static_cast<size_t>(row) * quads + q, first, second, epoch);
+                            }
                         }
                     }
                 }
@@ -385,7 +399,7 @@ __global__ void __launch_bounds__(kTwoPhaseThreads)
     }
 
     // ---- phase 3: unpack normalised row c ----
-    {
+    if (!p.replicated) {
         bool ok = true;
         for (int q = tid; q < quads; q += kTwoPhaseThreads) {
             if (shared_failed != 0) break;  // an owner's wait ran out on this rank: do not sit through another one
@@ -499,7 +513,7 @@ int singe_allreduce_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void 
 int singe_allreduce_two_phase_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void *normed, const void *weight,
                                                 const void *partial, void *const *receive, void *const *gather,
                                                 uint32_t *state, int rank, int world, size_t rows, size_t width,
-                                                float eps, uint32_t *status) {
+                                                float eps, int replicated, uint32_t *status) {
     if (hidden == nullptr || normed == nullptr || weight == nullptr || partial == nullptr || receive == nullptr ||
         gather == nullptr || state == nullptr) {
         return SINGE_ERR_NULL_POINTER;
@@ -534,7 +548,9 @@ int singe_allreduce_two_phase_add_rms_norm_bf16(singe_stream_t stream, void *hid
     params.rank = rank;
     params.world = world;
     params.rows = static_cast<int>(rows);
-    params.rpr = static_cast<int>((rows + static_cast<size_t>(world) - 1) / static_cast<size_t>(world));
+    params.replicated = replicated != 0 ? 1 : 0;
+    params.rpr = params.replicated ? static_cast<int>(rows)
+                                   : static_cast<int>((rows + static_cast<size_t>(world) - 1) / static_cast<size_t>(world));
     params.width = static_cast<int>(width);
     params.eps = eps;
     params.warm = singe::take_pending_warm();

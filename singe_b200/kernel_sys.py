@@ -62,12 +62,21 @@ SIGNATURES = {
     "singe_paged_kv_decode_splitk_reduce_f16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z,
                                                 _f],
     "singe_paged_kv_decode_step_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z,
-                                        _f, ctypes.c_uint],
+                                        _f, ctypes.c_uint, _p],
     "singe_paged_kv_decode_set_prefetch": [_i],
+    "singe_decode_step_attention_bf16": [_p, _p, _p, _p, _p, _z, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z,
+                                         _z, _z, _z, _z, _z, _f, ctypes.c_uint, _p, _p],
+    "singe_rotary_paged_kv_decode_attention_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z,
+                                                    _z, _z, _z, _z, _z, _f, _i, _p, _f, ctypes.c_uint],
     "singe_paged_attention_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _z, _z, _z, _f, _i,
                                    _z, _p],
     "singe_paged_attention_f32": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _z, _z, _z, _f, _i,
                                   _z, _p],
+    "singe_paged_attention_options_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _z, _z, _z,
+                                           _f, _i, _z, _f, _p],
+    "singe_paged_attention_options_f32": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _z, _z, _z,
+                                          _f, _i, _z, _f, _p],
+    "singe_attend_f32": [_p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _f, _i, _z, _f, _p],
     "singe_paged_kv_prefill_attention_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z,
                                               _i, _f],
     "singe_paged_kv_prefill_attention_f32": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z,
@@ -90,6 +99,8 @@ SIGNATURES = {
     "singe_add_rms_norm_bf16": [_p, _p, _p, _p, _p, _z, _z, _f],
     "singe_rotary_cache_write_bf16": [_p, _p, _p, _z, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _z, _z,
                                       _p],
+    "singe_rotary_norm_cache_write_bf16": [_p, _p, _p, _z, _p, _p, _p, _p, _p, _p, _p, _i, _z, _z, _z, _z, _z, _z, _z,
+                                           _i, _p, _i, _p, _f, _p],
     "singe_silu_mul_bf16": [_p, _p, _p, _p, _z, _z, _z],
     "singe_argmax_bf16": [_p, _p, _p, _p, _z, _z, _z, ctypes.c_int64],
     "singe_peer_buffer_create": [_z, ctypes.POINTER(ctypes.c_void_p), _p],
@@ -97,7 +108,7 @@ SIGNATURES = {
     "singe_peer_buffer_close": [_p],
     "singe_peer_buffer_destroy": [_p],
     "singe_allreduce_add_rms_norm_bf16": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _z, _z, _f, _p],
-    "singe_allreduce_two_phase_add_rms_norm_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _z, _z, _f, _p],
+    "singe_allreduce_two_phase_add_rms_norm_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _z, _z, _f, _i, _p],
 }
 
 _RESTYPES = {

@@ -296,7 +296,8 @@ class LlamaDecoder:
 
     def __init__(self, config: LlamaConfig, sequences: int, capacity: int, shard: Shard | None = None, seed: int = 4,
                  weights: dict | None = None, shard_lm_head: bool = True, max_splits: int = 0,
-                 collective: str = "peer", fuse_swiglu: bool = True, overlap: bool = True, warm_mb: int = 32):
+                 collective: str = "peer", fuse_swiglu: bool = True, overlap: bool = True, warm_mb: int = 0,
+                 fold_in_kernel: bool = True, fuse_attention: bool = True):
         import torch
 
         self.torch = torch
@@ -326,13 +327,17 @@ class LlamaDecoder:
         # L2 warm-ahead: the light kernels of a layer (norm / collective, rotary) and the attention kernel also pull
         # up to this many bytes of the weight matrix a later kernel of the layer streams into L2.
         self.warm_bytes = (warm_mb << 20) if overlap else 0
+        if "gate_up_interleaved" in weights and bool(weights["gate_up_interleaved"]) != bool(fuse_swiglu):
+            raise ValueError("the checkpoint's gate/up layout does not match fuse_swiglu")
         for full in weights["layers"]:
-            cut = shard_layer_weights(full, config, self.shard, interleave_gate_up=fuse_swiglu)
+            # a layer that already carries the fused shards (singe_b200.checkpoint.load_llama) is taken as it is
+            cut = full if "wqkv" in full else shard_layer_weights(full, config, self.shard,
+                                                                  interleave_gate_up=fuse_swiglu)
             self.layers.append({k: self._device(v) for k, v in cut.items()})
         self.embed = self._device(weights["embed"])
         self.final_norm = self._device(weights["final_norm"])
         head = weights["lm_head"]
-        if self.shard_lm_head:
+        if self.shard_lm_head and not weights.get("lm_head_is_cut", False):
             head = head[self.shard.slice(config.vocab)]
         self.lm_head = self._device(head)
         self.vocab_offset = self.shard.slice(config.vocab).start if self.shard_lm_head else 0
@@ -364,8 +369,8 @@ class LlamaDecoder:
         self.projected = torch.empty((t, w), dtype=bf16, device=dev)
         # The two collectives of a layer: "peer" = one kernel per collective that sums the ranks' partial rows out
         # of peer memory and applies the residual add + RMSNorm that follows; "nccl" = all-reduce, then the norm.
-        if collective not in ("peer", "oneshot", "twophase", "nccl"):
-            raise ValueError("collective must be 'peer', 'oneshot', 'twophase' or 'nccl'")
+        if collective not in ("peer", "oneshot", "twophase", "pushall", "nccl"):
+            raise ValueError("collective must be 'peer', 'oneshot', 'twophase', 'pushall' or 'nccl'")
         if collective == "peer":
             # one-shot: every rank pulls all partial rows (little to pull with two ranks); two-phase: rows are
             # reduced by their owners and pushed back
@@ -376,10 +381,11 @@ class LlamaDecoder:
             from .peer import PeerAllReduce
 
             self.peer = PeerAllReduce(self.shard.group, self.shard.rank, tp, t, w)
-        elif tp > 1 and collective == "twophase":
+        elif tp > 1 and collective in ("twophase", "pushall"):
             from .peer import TwoPhaseAllReduce
 
-            self.peer = TwoPhaseAllReduce(self.shard.group, self.shard.rank, tp, t, w)
+            self.peer = TwoPhaseAllReduce(self.shard.group, self.shard.rank, tp, t, w,
+                                          replicated=collective == "pushall")
         self.gate_up = torch.empty((t, 2 * self.ffn), dtype=bf16, device=dev)
         self.activated = torch.empty((t, self.ffn), dtype=bf16, device=dev)
         self.logits = torch.empty((t, self.lm_head.shape[0]), dtype=bf16, device=dev)
@@ -392,6 +398,8 @@ class LlamaDecoder:
         # split-K scratch owned by the caller (this class), so the step allocates nothing and can be graph-captured
         fast = config.head_dim in (64, 128) and config.page_size == 16 and config.heads // config.kv_heads <= 8
         self.fast_decode = fast
+        # rotary embedding, cache write and attention of a decode step in one launch (singe_decode_step_attention_bf16)
+        self.fuse_attention = fuse_attention and fast
         if max_splits <= 0:
             max_splits = choose_decode_splits(sequences * self.kv_heads, self.stride * config.page_size,
                                               2 * 2 * config.head_dim,
@@ -399,6 +407,10 @@ class LlamaDecoder:
         self.max_splits = max_splits
         self.attn_scratch = torch.empty((t, self.heads, max_splits, config.head_dim), dtype=torch.float32, device=dev)
         self.lse_scratch = torch.empty((t, self.heads, max_splits), dtype=torch.float32, device=dev)
+        # One wave of decode CTAs (three fit an SM): the last split of a row folds the row inside the decode kernel
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        self.tickets = (torch.zeros(t * self.kv_heads, dtype=i32, device=dev)
+                        if fold_in_kernel and t * self.kv_heads * max_splits <= 3 * sms else None)
         self.graph = None
 
     def _device(self, array):
@@ -491,23 +503,34 @@ class LlamaDecoder:
                                                         c.eps), "attn norm")
             self._linear(self.qkv, self.normed, layer["wqkv"], stream)
             self._warm(layer["wo"])
-            self._check(lib.singe_rotary_cache_write_bf16(
-                stream, self.query.data_ptr(), self.qkv.data_ptr(), self.qkv.stride(0), self.cos.data_ptr(),
-                self.sin.data_ptr(), self.d_positions.data_ptr(), keys.data_ptr(), values.data_ptr(),
-                self.d_pages.data_ptr(), self.d_slots.data_ptr(), 8, t, self.heads, self.kv_heads, d, keys.shape[0],
-                c.page_size, self.capacity, status), "rotary cache write")
-            if self.fast_decode:
-                self._warm(layer["w_gate_up"])
-                self._check(lib.singe_paged_kv_decode_step_bf16(
+            if self.fuse_attention:
+                self._check(lib.singe_decode_step_attention_bf16(
                     stream, self.attended.data_ptr(), self.attn_scratch.data_ptr(), self.lse_scratch.data_ptr(),
-                    self.query.data_ptr(), keys.data_ptr(), values.data_ptr(), self.d_lens.data_ptr(),
-                    self.d_table.data_ptr(), t, self.heads, self.kv_heads, d, c.page_size, keys.shape[0], self.stride,
-                    self.max_splits, 1.0 / math.sqrt(d), self.paging_hints), "decode attention")
+                    self.qkv.data_ptr(), self.qkv.stride(0), keys.data_ptr(), values.data_ptr(),
+                    self.d_lens.data_ptr(), self.d_table.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
+                    self.d_positions.data_ptr(), self.d_pages.data_ptr(), self.d_slots.data_ptr(), 8, t, self.heads,
+                    self.kv_heads, d, c.page_size, keys.shape[0], self.stride, self.max_splits, self.capacity,
+                    1.0 / math.sqrt(d), self.paging_hints,
+                    None if self.tickets is None else self.tickets.data_ptr(), status), "decode step attention")
             else:
-                self._check(lib.singe_paged_kv_decode_attention_bf16(
-                    stream, self.attended.data_ptr(), self.query.data_ptr(), keys.data_ptr(), values.data_ptr(),
-                    self.d_lens.data_ptr(), self.d_table.data_ptr(), t, self.heads, self.kv_heads, d, c.page_size,
-                    keys.shape[0], self.stride, 1.0 / math.sqrt(d)), "decode attention")
+                self._check(lib.singe_rotary_cache_write_bf16(
+                    stream, self.query.data_ptr(), self.qkv.data_ptr(), self.qkv.stride(0), self.cos.data_ptr(),
+                    self.sin.data_ptr(), self.d_positions.data_ptr(), keys.data_ptr(), values.data_ptr(),
+                    self.d_pages.data_ptr(), self.d_slots.data_ptr(), 8, t, self.heads, self.kv_heads, d,
+                    keys.shape[0], c.page_size, self.capacity, status), "rotary cache write")
+                if self.fast_decode:
+                    self._warm(layer["w_gate_up"])
+                    self._check(lib.singe_paged_kv_decode_step_bf16(
+                        stream, self.attended.data_ptr(), self.attn_scratch.data_ptr(), self.lse_scratch.data_ptr(),
+                        self.query.data_ptr(), keys.data_ptr(), values.data_ptr(), self.d_lens.data_ptr(),
+                        self.d_table.data_ptr(), t, self.heads, self.kv_heads, d, c.page_size, keys.shape[0],
+                        self.stride, self.max_splits, 1.0 / math.sqrt(d), self.paging_hints,
+                        None if self.tickets is None else self.tickets.data_ptr()), "decode attention")
+                else:
+                    self._check(lib.singe_paged_kv_decode_attention_bf16(
+                        stream, self.attended.data_ptr(), self.query.data_ptr(), keys.data_ptr(), values.data_ptr(),
+                        self.d_lens.data_ptr(), self.d_table.data_ptr(), t, self.heads, self.kv_heads, d, c.page_size,
+                        keys.shape[0], self.stride, 1.0 / math.sqrt(d)), "decode attention")
             if self.peer is not None:
                 self._linear_raw(self.peer.partial_pointer(0), w, self.attended, layer["wo"], stream)
                 self._warm(layer["w_down"])

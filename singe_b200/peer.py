@@ -65,15 +65,18 @@ class TwoPhaseAllReduce:
     epoch state.  The GEMMs write their partial sums into ordinary local memory (``partial_pointer(which)``) and the
     normalised rows come out in an ordinary local tensor."""
 
-    def __init__(self, group, rank: int, world: int, rows: int, width: int, wait_limit_kcycles: int = 0):
+    def __init__(self, group, rank: int, world: int, rows: int, width: int, wait_limit_kcycles: int = 0,
+                 replicated: bool = False):
         import torch
 
         if world > 8:
             raise ValueError("the fused all-reduce serves one NVSwitch domain: at most 8 ranks")
         self.group, self.rank, self.world, self.rows, self.width = group, rank, world, rows, width
-        self.rpr = (rows + world - 1) // world
+        # replicated: every rank receives every partial row and reduces all rows itself (one NVLink trip, for two ranks)
+        self.replicated = replicated
+        self.rpr = rows if replicated else (rows + world - 1) // world
         self.receive = PeerBuffer(group, rank, world, world * self.rpr * width * 4)
-        self.gather = PeerBuffer(group, rank, world, rows * width * 4)
+        self.gather = self.receive if replicated else PeerBuffer(group, rank, world, rows * width * 4)
         self.state = torch.zeros(4, dtype=torch.int32, device="cuda")
         if wait_limit_kcycles:
             self.state[2] = wait_limit_kcycles
@@ -86,12 +89,12 @@ class TwoPhaseAllReduce:
                         status: int) -> None:
         code = ks.lib().singe_allreduce_two_phase_add_rms_norm_bf16(
             stream, hidden, normed, weight, self.partials[which].data_ptr(), self.receive.array, self.gather.array,
-            self.state.data_ptr(), self.rank, self.world, self.rows, self.width, eps, status)
+            self.state.data_ptr(), self.rank, self.world, self.rows, self.width, eps, int(self.replicated), status)
         if code != ks.OK:
             raise RuntimeError(f"two-phase all-reduce: status {code} ({ks.status_string(code)})")
 
     def close(self) -> None:
-        for buffer in (self.receive, self.gather):
+        for buffer in ((self.receive,) if self.replicated else (self.receive, self.gather)):
             buffer.close(self.group)
 
 

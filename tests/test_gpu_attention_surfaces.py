@@ -284,3 +284,66 @@ def test_paged_prefill_bf16_gathers_its_key_tiles_through_the_block_table(causal
         scale=scale)
     assert_close_bf16(host(out), ref_out, f"paged prefill bf16 out causal={causal}")
     assert_close_f32(host(lse), ref_lse, f"paged prefill bf16 lse causal={causal}", 2e-3)
+
+
+def test_attend_with_a_score_cap_and_per_head_sinks():
+    # AttentionOptions::softcap and the sinks of Tensor::attend (singe/src/tensor/neural.rs:26-32,114-175; CPU meaning
+    # singe/src/backend/cpu/normalization/attention.rs:250-263)
+    from singe_b200 import kernel_sys as ks
+
+    rng = np.random.default_rng(61)
+    b, h, g, l, s, d = 2, 4, 2, 19, 23, 32
+    q = rng.standard_normal((b, h, l, d), dtype=np.float32)
+    k = rng.standard_normal((b, g, s, d), dtype=np.float32)
+    v = rng.standard_normal((b, g, s, d), dtype=np.float32)
+    sinks = rng.standard_normal(h).astype(np.float32)
+    rep = lambda x: np.repeat(x, h // g, axis=1)
+    d_q, d_k, d_v, d_sinks = dev(q), dev(k), dev(v), dev(sinks)
+    out = torch.empty((b, h, l, d), device="cuda")
+    stream = int(torch.cuda.current_stream().cuda_stream)
+    for causal, window, softcap, with_sinks in [(True, 0, 1.5, False), (False, 0, 0.0, True), (True, 6, 0.7, True)]:
+        code = ks.lib().singe_attend_f32(stream, out.data_ptr(), d_q.data_ptr(), d_k.data_ptr(), d_v.data_ptr(), b, h,
+                                         g, l, s, d, 0.4, int(causal), window, softcap,
+                                         d_sinks.data_ptr() if with_sinks else None)
+        torch.cuda.synchronize()
+        assert code == ks.OK
+        ref = oracle.attend_options_f32(q, rep(k), rep(v), scale=0.4, causal=causal, window=window, softcap=softcap,
+                                        sinks=sinks if with_sinks else None)
+        assert_close_f32(host(out), ref, f"attend causal={causal} window={window} cap={softcap} sinks={with_sinks}")
+    assert ks.lib().singe_attend_f32(stream, out.data_ptr(), d_q.data_ptr(), d_k.data_ptr(), d_v.data_ptr(), b, h, g,
+                                     l, s, d, 0.4, 1, 0, -1.0, None) == ks.ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("plain_decode", [True, False])
+def test_tensor_paged_attention_with_a_score_cap(plain_decode):
+    # softcap on the paged surface: a plain decode batch stays on the tiled kernel (tanh.approx on the score path),
+    # a mixed batch runs the general kernel; both against attend_paged with the cap
+    from singe_b200 import kernel_sys as ks
+
+    rng = np.random.default_rng(62)
+    heads, kv_heads, softcap = 8, 2, 2.0
+    lens = [1, 700, 16, 0, 2049, 513]
+    q, kc, vc, pages, page_offsets, last = _decode_batch(rng, lens, heads, kv_heads)
+    if plain_decode:
+        query_offsets = np.arange(len(lens) + 1, dtype=np.int64)
+    else:
+        query_offsets = np.asarray([0, 1, 3, 4, 4, 5, 6], dtype=np.int64)   # sequence 1 owns two query tokens
+    scale = 0.25    # large scaled scores, so the cap matters
+    d_q, d_k, d_v = dev(q, torch.bfloat16), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16)
+    out = torch.full((len(lens), heads, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty((len(lens), heads), device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    d_qo, d_po, d_pages, d_last = dev(query_offsets), dev(page_offsets), dev(pages), dev(last)
+    code = ks.lib().singe_paged_attention_options_bf16(
+        int(torch.cuda.current_stream().cuda_stream), out.data_ptr(), lse.data_ptr(), d_q.data_ptr(), d_k.data_ptr(),
+        d_v.data_ptr(), d_qo.data_ptr(), d_po.data_ptr(), d_pages.data_ptr(), d_last.data_ptr(), 8, len(lens), heads,
+        kv_heads, 128, 16, kc.shape[0], len(lens), pages.size, scale, 1, 0, softcap, status.data_ptr())
+    torch.cuda.synchronize()
+    assert code == ks.OK and int(status.item()) == 0 and ops.take_device_error() == 0
+    ref_code, ref_out, ref_lse = oracle.attend_paged_f32(q, kc, vc, query_offsets, page_offsets, pages, last,
+                                                         scale=scale, causal=True, softcap=softcap)
+    uncapped = oracle.attend_paged_f32(q, kc, vc, query_offsets, page_offsets, pages, last, scale=scale, causal=True)[1]
+    assert ref_code == oracle.OK and np.abs(uncapped - ref_out).max() > 0.1      # the cap changes the answer
+    assert_close_bf16(host(out), ref_out, f"paged attention with a score cap (decode={plain_decode})")
+    finite = np.isfinite(ref_lse)
+    assert np.abs(host(lse)[finite] - ref_lse[finite]).max() < 5e-3

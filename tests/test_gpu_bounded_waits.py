@@ -75,7 +75,7 @@ def test_two_phase_all_reduce_gives_up_when_the_other_rank_never_pushes():
     stream = int(torch.cuda.current_stream().cuda_stream)
     code = lib.singe_allreduce_two_phase_add_rms_norm_bf16(
         stream, hidden.data_ptr(), normed.data_ptr(), weight.data_ptr(), partial.data_ptr(), _pointers(receive),
-        _pointers(gather), state.data_ptr(), 0, 2, ROWS, WIDTH, EPS, status.data_ptr())
+        _pointers(gather), state.data_ptr(), 0, 2, ROWS, WIDTH, EPS, 0, status.data_ptr())
     assert code == ks.OK
     torch.cuda.synchronize()
     assert int(status.item()) == ks.STATUS_WAIT_TIMEOUT
@@ -89,7 +89,7 @@ def test_two_phase_all_reduce_gives_up_when_the_other_rank_never_pushes():
     lone_state = torch.zeros(4, dtype=torch.int32, device="cuda")
     code = lib.singe_allreduce_two_phase_add_rms_norm_bf16(
         stream, hidden.data_ptr(), normed.data_ptr(), weight.data_ptr(), partial.data_ptr(),
-        _pointers([packets(ROWS)]), _pointers([packets(ROWS)]), lone_state.data_ptr(), 0, 1, ROWS, WIDTH, EPS,
+        _pointers([packets(ROWS)]), _pointers([packets(ROWS)]), lone_state.data_ptr(), 0, 1, ROWS, WIDTH, EPS, 0,
         status.data_ptr())
     assert code == ks.OK
     torch.cuda.synchronize()

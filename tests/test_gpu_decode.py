@@ -159,3 +159,158 @@ def test_validation_mirrors_the_reference_config_checks():
         ops.paged_kv_decode_attention(short, dev(q, torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16),
                                       dev(case.lens), dev_u32(case.block_table), _config(case))
     assert caught.value.code == ks.ERR_LENGTH_TOO_SHORT
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(32, 8, 128), (16, 2, 64)])
+@pytest.mark.parametrize("normalise", [False, True])
+@pytest.mark.parametrize("hinted", [False, True])
+def test_decode_that_rotates_its_own_queries(heads, kv_heads, head_dim, normalise, hinted):
+    # singe_rotary_paged_attention (kernel_plan/source/paged_attention.rs:535-542,881-977): the attention kernel takes the
+    # query projections before the rotary embedding.  Without the norm the result must EQUAL the separate rotation
+    # followed by the plain decode call (same rounding chain); with the per-head RMSNorm it is checked against the CPU
+    # restatement: RmsNorm per head -> rotate_pairs -> paged_kv_decode_attention.
+    from oracle import llama_ref
+    from singe_b200.llama import rotary_tables
+
+    lens = [1, 300, 16, 2049, 0, 777]
+    case = workloads.paged_decode_case(seed=21, heads=heads, kv_heads=kv_heads, head_dim=head_dim, lens=lens)
+    q, k, v = _inputs(case, seed=22)
+    rng = np.random.default_rng(23)
+    capacity, eps, splits = 4096, 1e-6, 6
+    positions = np.array([0, 299, 15, 2048, 5, -1], dtype=np.int64)          # -1 wraps to capacity - 1
+    cos, sin = rotary_tables(head_dim, 500000.0, capacity)
+    gain = llama_ref.bf16(1.0 + 0.1 * rng.standard_normal(head_dim).astype(np.float32))
+    lib = ks.lib()
+    stream = int(torch.cuda.current_stream().cuda_stream)
+    d_q, d_k, d_v = dev(q, torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16)
+    d_lens, d_table = dev(case.lens), dev_u32(case.block_table)
+    d_cos, d_sin, d_positions = dev(cos, torch.bfloat16), dev(sin, torch.bfloat16), dev(positions)
+    d_gain = dev(gain, torch.bfloat16)
+    scratch = torch.empty((case.batch, heads, splits, head_dim + 1), dtype=torch.float32, device="cuda")
+    attn_scratch, lse_scratch = scratch[..., :head_dim].contiguous(), scratch[..., head_dim].contiguous()
+    out = torch.full((case.batch, heads, head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+    hints = ks.HINT_STABLE_PAGING if hinted else 0
+    code = lib.singe_rotary_paged_kv_decode_attention_bf16(
+        stream, out.data_ptr(), attn_scratch.data_ptr(), lse_scratch.data_ptr(), d_q.data_ptr(), d_k.data_ptr(),
+        d_v.data_ptr(), d_lens.data_ptr(), d_table.data_ptr(), d_cos.data_ptr(), d_sin.data_ptr(),
+        d_positions.data_ptr(), 8, case.batch, heads, kv_heads, head_dim, case.block_size, case.physical_blocks,
+        case.block_table_batch_stride, splits, capacity, case.scale, int(normalise),
+        d_gain.data_ptr() if normalise else None, eps, hints)
+    torch.cuda.synchronize()
+    assert code == ks.OK and ops.take_device_error() == 0
+    wrapped = np.where(positions < 0, positions + capacity, positions)
+    c, s = llama_ref.bf16(cos)[wrapped], llama_ref.bf16(sin)[wrapped]
+    prepared = llama_ref.rms_norm(q.reshape(-1, head_dim), gain, eps).reshape(q.shape) if normalise else q
+    rotated = llama_ref.rotate(prepared, c, s)
+    assert_close_bf16(host(out), _oracle(case, rotated, k, v), "decode over queries rotated in the kernel")
+    if not normalise:
+        # the separate path: rotate on the host exactly as the rotary kernel rounds, then the plain split-K decode call
+        separate = torch.full_like(out, float("nan"))
+        code = lib.singe_paged_kv_decode_splitk_reduce_bf16(
+            stream, separate.data_ptr(), attn_scratch.data_ptr(), lse_scratch.data_ptr(),
+            dev(rotated, torch.bfloat16).data_ptr(), d_k.data_ptr(), d_v.data_ptr(), d_lens.data_ptr(),
+            d_table.data_ptr(), case.batch, heads, kv_heads, head_dim, case.block_size, case.physical_blocks,
+            case.block_table_batch_stride, splits, case.scale)
+        torch.cuda.synchronize()
+        assert code == ks.OK and torch.equal(out, separate)
+
+
+@pytest.mark.parametrize("hinted", [False, True])
+def test_the_last_split_of_a_row_folds_it_inside_the_decode_kernel(hinted):
+    # With a ticket array the decode kernel needs no combine launch: whichever split of a (sequence, KV head) row
+    # finishes last reads the row's partials back and writes the row, with the combine kernel's arithmetic -- so the
+    # result must EQUAL the two-launch path -- and leaves the tickets at zero for the next call.
+    lens = [1, 300, 16, 2049, 0, 777, 4096, 513]
+    case = workloads.paged_decode_case(seed=41, heads=16, kv_heads=4, head_dim=128, lens=lens)
+    q, k, v = _inputs(case, seed=42)
+    lib = ks.lib()
+    stream = int(torch.cuda.current_stream().cuda_stream)
+    d_q, d_k, d_v = dev(q, torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16)
+    d_lens, d_table = dev(case.lens), dev_u32(case.block_table)
+    splits = 7
+    attn = torch.empty((case.batch, case.heads, splits, case.head_dim), dtype=torch.float32, device="cuda")
+    lse = torch.empty((case.batch, case.heads, splits), dtype=torch.float32, device="cuda")
+    tickets = torch.zeros(case.batch * case.kv_heads, dtype=torch.int32, device="cuda")
+    hints = ks.HINT_STABLE_PAGING if hinted else 0
+
+    def run(out, with_tickets):
+        return lib.singe_paged_kv_decode_step_bf16(
+            stream, out.data_ptr(), attn.data_ptr(), lse.data_ptr(), d_q.data_ptr(), d_k.data_ptr(), d_v.data_ptr(),
+            d_lens.data_ptr(), d_table.data_ptr(), case.batch, case.heads, case.kv_heads, case.head_dim,
+            case.block_size, case.physical_blocks, case.block_table_batch_stride, splits, case.scale, hints,
+            tickets.data_ptr() if with_tickets else None)
+
+    two_launches = torch.full((case.batch, case.heads, case.head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert run(two_launches, False) == ks.OK
+    torch.cuda.synchronize()
+    for _ in range(3):   # repeated calls: the tickets reset themselves
+        folded = torch.full_like(two_launches, float("nan"))
+        assert run(folded, True) == ks.OK
+        torch.cuda.synchronize()
+        assert torch.equal(folded, two_launches)
+        assert int(tickets.abs().sum().item()) == 0
+    assert ops.take_device_error() == 0
+    assert_close_bf16(host(two_launches), _oracle(case, q, k, v), "decode with a split budget of 7")
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(32, 8, 128), (16, 2, 64), (4, 4, 128)])
+@pytest.mark.parametrize("hinted,folded", [(False, False), (True, True)])
+def test_the_fused_decode_step_attention_equals_rotation_cache_write_and_decode(heads, kv_heads, head_dim, hinted, folded):
+    # singe_decode_step_attention_bf16: rotary embedding of Q and of the new K, the slot-mapped write of the new K / V rows
+    # and paged attention over cached + new keys in one launch, against the three-kernel chain it replaces (rotation
+    # + cache write kernel, then the split-K decode): caches bit-identical, outputs within the bf16 tolerance of each
+    # other and of the CPU restatement (the new key's score is summed in another order).
+    from oracle import llama_ref
+    from singe_b200.llama import rotary_tables
+
+    lens = [1, 300, 16, 2049, 17, 777, 512, 513]     # lengths INCLUDING the new token: the last key's position + 1
+    case = workloads.paged_decode_case(seed=51, heads=heads, kv_heads=kv_heads, head_dim=head_dim, lens=lens)
+    _, k, v = _inputs(case, seed=52)
+    rng = np.random.default_rng(53)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = workloads.normal_bf16(rng, (case.batch, width + 8))[:, :width]      # a row stride wider than the row
+    capacity, splits = 4096, 6
+    positions = np.asarray(lens, dtype=np.int64) - 1
+    write_pages = np.asarray([case.block_table[b, (n - 1) // 16] for b, n in enumerate(lens)], dtype=np.int64)
+    write_slots = (positions % 16).astype(np.int64)
+    cos, sin = rotary_tables(head_dim, 500000.0, capacity)
+    lib = ks.lib()
+    stream = int(torch.cuda.current_stream().cuda_stream)
+    d_qkv_full = dev(np.pad(qkv, ((0, 0), (0, 8))), torch.bfloat16)
+    d_lens, d_table = dev(case.lens), dev_u32(case.block_table)
+    d_cos, d_sin = dev(cos, torch.bfloat16), dev(sin, torch.bfloat16)
+    d_positions, d_pages, d_slots = dev(positions), dev(write_pages), dev(write_slots)
+    attn = torch.empty((case.batch, heads, splits, head_dim), dtype=torch.float32, device="cuda")
+    lse = torch.empty((case.batch, heads, splits), dtype=torch.float32, device="cuda")
+    tickets = torch.zeros(case.batch * kv_heads, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    hints = ks.HINT_STABLE_PAGING if hinted else 0
+    # fused
+    fused_k, fused_v = dev(k, torch.bfloat16), dev(v, torch.bfloat16)
+    fused_out = torch.full((case.batch, heads, head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+    code = lib.singe_decode_step_attention_bf16(
+        stream, fused_out.data_ptr(), attn.data_ptr(), lse.data_ptr(), d_qkv_full.data_ptr(), width + 8,
+        fused_k.data_ptr(), fused_v.data_ptr(), d_lens.data_ptr(), d_table.data_ptr(), d_cos.data_ptr(),
+        d_sin.data_ptr(), d_positions.data_ptr(), d_pages.data_ptr(), d_slots.data_ptr(), 8, case.batch, heads,
+        kv_heads, head_dim, 16, case.physical_blocks, case.block_table_batch_stride, splits, capacity, case.scale,
+        hints, tickets.data_ptr() if folded else None, status.data_ptr())
+    torch.cuda.synchronize()
+    assert code == ks.OK and int(status.item()) == 0 and ops.take_device_error() == 0
+    # the chain it replaces
+    chain_k, chain_v = dev(k, torch.bfloat16), dev(v, torch.bfloat16)
+    rotated_q = torch.empty((case.batch, heads, head_dim), dtype=torch.bfloat16, device="cuda")
+    assert lib.singe_rotary_cache_write_bf16(
+        stream, rotated_q.data_ptr(), d_qkv_full.data_ptr(), width + 8, d_cos.data_ptr(), d_sin.data_ptr(),
+        d_positions.data_ptr(), chain_k.data_ptr(), chain_v.data_ptr(), d_pages.data_ptr(), d_slots.data_ptr(), 8,
+        case.batch, heads, kv_heads, head_dim, case.physical_blocks, 16, capacity, status.data_ptr()) == ks.OK
+    chain_out = torch.full_like(fused_out, float("nan"))
+    assert lib.singe_paged_kv_decode_splitk_reduce_bf16(
+        stream, chain_out.data_ptr(), attn.data_ptr(), lse.data_ptr(), rotated_q.data_ptr(), chain_k.data_ptr(),
+        chain_v.data_ptr(), d_lens.data_ptr(), d_table.data_ptr(), case.batch, heads, kv_heads, head_dim, 16,
+        case.physical_blocks, case.block_table_batch_stride, splits, case.scale) == ks.OK
+    torch.cuda.synchronize()
+    assert torch.equal(fused_k, chain_k) and torch.equal(fused_v, chain_v)     # the same rows in the same slots
+    assert_close_bf16(host(fused_out), host(chain_out), "fused step attention vs the three-kernel chain")
+    assert_close_bf16(host(fused_out), _oracle(case, host(rotated_q), host(chain_k), host(chain_v)),
+                      "fused step attention vs the CPU restatement")
+    assert int(tickets.abs().sum().item()) == 0

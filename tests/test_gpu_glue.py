@@ -98,6 +98,52 @@ def test_rotary_cache_write(heads, kv_heads, head_dim):
     assert np.array_equal(host(d_k), expect_k)
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 128), (4, 2, 16), (2, 1, 64)])
+@pytest.mark.parametrize("which", ["both", "query with a gain", "key without a gain"])
+def test_rotary_cache_write_with_per_head_rms_norm(heads, kv_heads, head_dim, which):
+    # query_norm / key_norm of the reference's fused kernel (kernel_plan/source/rotary_cache.rs:25-52): RmsNorm over
+    # each head, rounded to bf16 as the separate op returns it, then the rotation's rounding chain
+    rng = np.random.default_rng(head_dim + len(which))
+    tokens, pages, page_size, capacity, eps = 5, 4, 4, 32, 1e-6
+    qkv = workloads.normal_bf16(rng, (tokens, (heads + 2 * kv_heads) * head_dim))
+    positions = np.array([0, 3, 31, 7, 12], dtype=np.int64)
+    write_pages, write_slots = np.array([0, 1, 2, 3, 1], dtype=np.int64), np.array([0, 1, 2, 3, 0], dtype=np.int64)
+    cos, sin = rotary_tables(head_dim, 10000.0, capacity)
+    gain_q = llama_ref.bf16(1.0 + 0.1 * rng.standard_normal(head_dim).astype(np.float32))
+    gain_k = llama_ref.bf16(1.0 + 0.1 * rng.standard_normal(head_dim).astype(np.float32))
+    norm_q, norm_k = which != "key without a gain", which != "query with a gain"
+    use_gain_k = which == "both"
+    d_k = torch.zeros((pages, page_size, kv_heads, head_dim), dtype=torch.bfloat16, device="cuda")
+    d_v = torch.zeros_like(d_k)
+    q_out = torch.empty((tokens, heads, head_dim), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    d_qkv, cos_d, sin_d = dev(qkv, torch.bfloat16), dev(cos, torch.bfloat16), dev(sin, torch.bfloat16)
+    d_positions, d_pages, d_slots = dev(positions), dev(write_pages), dev(write_slots)
+    d_gq, d_gk = dev(gain_q, torch.bfloat16), dev(gain_k, torch.bfloat16)
+    code = ks.lib().singe_rotary_norm_cache_write_bf16(
+        _stream(), q_out.data_ptr(), d_qkv.data_ptr(), qkv.shape[1], cos_d.data_ptr(), sin_d.data_ptr(),
+        d_positions.data_ptr(), d_k.data_ptr(), d_v.data_ptr(), d_pages.data_ptr(), d_slots.data_ptr(), 8, tokens,
+        heads, kv_heads, head_dim, pages, page_size, capacity, int(norm_q), d_gq.data_ptr() if norm_q else None,
+        int(norm_k), d_gk.data_ptr() if use_gain_k else None, eps, status.data_ptr())
+    torch.cuda.synchronize()
+    assert code == ks.OK and int(status.item()) == 0
+    c, s = llama_ref.bf16(cos)[positions], llama_ref.bf16(sin)[positions]
+    q = qkv[:, : heads * head_dim].reshape(tokens, heads, head_dim)
+    k = qkv[:, heads * head_dim: (heads + kv_heads) * head_dim].reshape(tokens, kv_heads, head_dim)
+    ones = np.ones(head_dim, dtype=np.float32)
+
+    def normalised(x, gain):
+        return llama_ref.rms_norm(x.reshape(-1, head_dim), gain, eps).reshape(x.shape)
+
+    expect_q = llama_ref.rotate(normalised(q, gain_q) if norm_q else q, c, s)
+    expect_k = llama_ref.rotate(normalised(k, gain_k if use_gain_k else ones) if norm_k else k, c, s)
+    assert_close_bf16(host(q_out), expect_q, f"normalised + rotated queries ({which})")
+    written = host(d_k)[write_pages, write_slots]
+    assert_close_bf16(written, expect_k, f"normalised + rotated keys ({which})")
+    if not norm_q:
+        assert np.array_equal(host(q_out), expect_q)   # heads without a norm keep the exact rounding chain
+
+
 @pytest.mark.parametrize("width", [4096, 50])
 def test_embedding_and_argmax(width):
     rng = np.random.default_rng(width)

@@ -76,7 +76,10 @@ def _reduce_rank(rank, world, port, results, kind):
     lib = ks.lib()
     rows, width, eps = 64, 4096, 1e-5
     two_phase = kind == "twophase"
-    peer = (TwoPhaseAllReduce if two_phase else PeerAllReduce)(dist, rank, world, rows, width)
+    if kind == "oneshot":
+        peer = PeerAllReduce(dist, rank, world, rows, width)
+    else:
+        peer = TwoPhaseAllReduce(dist, rank, world, rows, width, replicated=kind == "pushall")
     generator = torch.Generator(device="cuda").manual_seed(100 + rank)
     shared = torch.Generator(device="cuda").manual_seed(7)  # the residual stream and the gain are replicated
     weight = (1.0 + 0.05 * torch.randn(width, generator=shared, device="cuda")).to(torch.bfloat16)
@@ -154,7 +157,7 @@ def ctypes_copy(target_pointer, source, stream=None):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("kind", ["oneshot", "twophase"])
+@pytest.mark.parametrize("kind", ["oneshot", "twophase", "pushall"])
 def test_fused_peer_all_reduce_matches_the_rank_ordered_sum_then_norm_bit_for_bit(kind, world):
     import torch.multiprocessing as mp
 
@@ -167,7 +170,7 @@ def test_fused_peer_all_reduce_matches_the_rank_ordered_sum_then_norm_bit_for_bi
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("collective", ["oneshot", "twophase", "nccl"])
+@pytest.mark.parametrize("collective", ["oneshot", "twophase", "pushall", "nccl"])
 def test_tensor_parallel_decode_step_matches_the_reference_path(collective, world):
     import torch.multiprocessing as mp
 

@@ -220,8 +220,9 @@ int singe_paged_kv_decode_splitk_reduce_f16(singe_stream_t stream, void *out, fl
  * step's cache write, queued just before, fills); the queries are read after those kernels finish.
  * tickets: uint32 [batch * kv_heads], zero at first use and left zero by every call, or NULL.  With tickets the
  * split that finishes a (sequence, KV head) row last folds the row's partials inside the decode kernel and no
- * combine kernel is launched -- one launch less per layer; pass them when batch * kv_heads * max_splits CTAs fit the
- * machine in one wave (3 per SM), NULL otherwise (with several waves the separate combine kernel is faster).
+ * combine kernel is launched.  Measured on B200 this is SLOWER than the separate combine kernel even when the grid is
+ * one wave (+6 us on a 17 us decode: every CTA pays a device-wide fence and an atomic on its way out), so callers
+ * normally pass NULL; the path exists for hosts where a launch costs more than that.
  * No reference counterpart (the reference's launches serialise). */
 int singe_paged_kv_decode_step_bf16(singe_stream_t stream, void *out, float *attn_scratch, float *lse_scratch,
                                     const void *query, const void *key_cache, const void *value_cache,

@@ -630,9 +630,8 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
     // Every split of a (sequence, KV head) row takes a ticket once its partials are written and visible; the one
     // that draws the last ticket reads all of them back (through L2: they were written by other SMs) and writes the
     // row with the arithmetic of decode_combine_kernel, then puts the counter back to zero for the next launch.
-    // Worth it when the grid is one wave (a tensor-parallel shard, a small batch): the folding CTA holds no slot
-    // another CTA is waiting for, and the step saves a launch.  With several waves it measured slower than the
-    // separate kernel, which is why the caller decides by passing tickets or not.
+    // It saves a launch, but measured slower than the separate combine kernel on B200 even for one-wave grids (every
+    // CTA pays the device-wide fence and the atomic on its way out): the caller decides by passing tickets or not.
     __shared__ int shared_last;
     __threadfence();
     __syncthreads();

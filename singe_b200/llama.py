@@ -297,7 +297,7 @@ class LlamaDecoder:
     def __init__(self, config: LlamaConfig, sequences: int, capacity: int, shard: Shard | None = None, seed: int = 4,
                  weights: dict | None = None, shard_lm_head: bool = True, max_splits: int = 0,
                  collective: str = "peer", fuse_swiglu: bool = True, overlap: bool = True, warm_mb: int = 0,
-                 fold_in_kernel: bool = True, fuse_attention: bool = True):
+                 fold_in_kernel: bool = False, fuse_attention: bool = True):
         import torch
 
         self.torch = torch
@@ -407,7 +407,9 @@ class LlamaDecoder:
         self.max_splits = max_splits
         self.attn_scratch = torch.empty((t, self.heads, max_splits, config.head_dim), dtype=torch.float32, device=dev)
         self.lse_scratch = torch.empty((t, self.heads, max_splits), dtype=torch.float32, device=dev)
-        # One wave of decode CTAs (three fit an SM): the last split of a row folds the row inside the decode kernel
+        # Optional: with one wave of decode CTAs (three fit an SM) the last split of a row can fold the row inside the
+        # decode kernel instead of a combine launch.  Measured slower on B200 (+6 us per layer at the 8-way shard's
+        # shapes: the fence and the ticket sit on every CTA's exit path), so it is off unless asked for.
         sms = torch.cuda.get_device_properties(0).multi_processor_count
         self.tickets = (torch.zeros(t * self.kv_heads, dtype=i32, device=dev)
                         if fold_in_kernel and t * self.kv_heads * max_splits <= 3 * sms else None)

@@ -28,6 +28,10 @@ namespace singe {
 namespace {
 
 constexpr int kGemmThreads = 192;
+// The split-K kernel carries six more warps that do nothing but join its last phase: adding up the CTA's rows and
+// applying the epilogue is a few hundred dependent instructions, and with one warp per scheduler every one of them
+// waits out its own latency.
+constexpr int kSplitKThreads = 384;
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;
 constexpr int kMaxStages = 16;
@@ -365,7 +369,7 @@ __device__ __forceinline__ void cluster_barrier() {
 }
 
 template <int BN, int KPS>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kSplitKThreads, 1)
     gemm_splitk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                        const GemmParams p) {
     constexpr uint32_t kTmemColumns = BN < 32 ? 32 : BN;
@@ -512,7 +516,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (lane == 0) tcgen05_commit(bar_acc_full);
             __syncwarp();
         }
-    } else {
+    } else if (warp < 6) {
         // ---------------- hand the partial tile to the CTAs that own its rows ----------------
         // Row i of the tile belongs to cluster CTA i % splits.  The four warps park the CTA's f32 partial tile in its
         // own shared memory grouped by owner ([owner][row / splits][BN], 16-byte groups XOR-swizzled by the row so the
@@ -583,7 +587,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     {
         // ---------------- reduce: CTA r owns rows r, r + splits, ... of the tile ----------------
-        if (warp < 2) grid_dependency_wait();  // (the other warps did before they parked the tile)
+        if (warp < 2 || warp >= 6) grid_dependency_wait();  // (warps 2-5 did before they parked the tile)
         const int t = threadIdx.x;
         const int my_rows = (p.m - static_cast<int>(rank) + static_cast<int>(splits) - 1) / static_cast<int>(splits);
         const int live = min(static_cast<int>(splits), (p.k_blocks + per_split - 1) / per_split);
@@ -592,13 +596,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int slot_floats = rows_per_cta * BN;
         // One warp per scheduler runs here, so nothing hides an instruction's latency but the warp's own independent
         // work: the shared-memory reads of a batch of items are issued together before any of them is summed.
-        constexpr int kBatch = 3;
+        constexpr int kBatch = 2;
         const int items = my_rows * kQuads;
-        for (int first = t; first < items; first += kGemmThreads * kBatch) {
+        for (int first = t; first < items; first += kSplitKThreads * kBatch) {
             float4 part[kBatch][8];
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-                const int index = first + u * kGemmThreads;
+                const int index = first + u * kSplitKThreads;
                 const int local_row = index / kQuads;
                 const int quad = index % kQuads;
                 const int row = static_cast<int>(rank) + local_row * static_cast<int>(splits);
@@ -615,7 +619,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             }
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-                const int index = first + u * kGemmThreads;
+                const int index = first + u * kSplitKThreads;
                 if (index >= items) continue;
                 const int local_row = index / kQuads;
                 const int row = static_cast<int>(rank) + local_row * static_cast<int>(splits);
@@ -748,7 +752,7 @@ int launch_gemm_splitk(cudaStream_t stream, GemmParams params, const void *lhs, 
                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
     }
     SINGE_CUDA_TRY(launch_dependent(gemm_splitk_kernel<BN, KPS>, dim3(static_cast<unsigned>(params.tiles_n * splits)),
-                                    dim3(kGemmThreads), smem, stream, kLaunchGemm, static_cast<unsigned>(splits), a_map,
+                                    dim3(kSplitKThreads), smem, stream, kLaunchGemm, static_cast<unsigned>(splits), a_map,
                                     b_map,
                                     params));
     return launch_status();

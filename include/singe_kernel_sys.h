@@ -339,8 +339,10 @@ int singe_paged_attention_options_f32(singe_stream_t stream, float *out, float *
  *   lens_kv[b] - lens_q[b] + i (clamped at 0) and sees the keys up to it -- the mask of Tensor::paged_attention
  *   (singe/src/backend/cpu/normalization/attention.rs:481-483).
  *   ragged: key, value [total_kv_tokens, kv_heads, head_dim], key k of sequence b at row offsets[b] + k.
- * The bf16 entry points run the tcgen05/TMEM flash-attention kernel when head_dim == 128 (the paged form with
- * 16-token pages: its key tiles are gathered through the block table); other shapes and f32 run the general kernel.
+ * The bf16 and f16 entry points (paged.rs:313-421,479-582) run the tcgen05/TMEM flash-attention kernel when
+ * head_dim == 128 (the paged form with 16-token pages: its key tiles are gathered through the block table); f16
+ * takes the exact row maximum on every key tile so that the probabilities stay inside the half range.  Other
+ * shapes and f32 run the general kernel.
  * ================================================================================================= */
 int singe_paged_kv_prefill_attention_bf16(singe_stream_t stream, void *out, float *lse, const void *query,
                                           const void *key_cache, const void *value_cache,
@@ -349,6 +351,13 @@ int singe_paged_kv_prefill_attention_bf16(singe_stream_t stream, void *out, floa
                                           size_t batch, size_t total_query_tokens, size_t heads, size_t kv_heads,
                                           size_t head_dim, size_t block_size, size_t physical_blocks,
                                           size_t block_table_batch_stride, int causal, float scale);
+int singe_paged_kv_prefill_attention_f16(singe_stream_t stream, void *out, float *lse, const void *query,
+                                         const void *key_cache, const void *value_cache,
+                                         const int32_t *actual_seq_lens_q, const int32_t *actual_seq_lens_kv,
+                                         const int32_t *actual_seq_offsets, const uint32_t *block_table,
+                                         size_t batch, size_t total_query_tokens, size_t heads, size_t kv_heads,
+                                         size_t head_dim, size_t block_size, size_t physical_blocks,
+                                         size_t block_table_batch_stride, int causal, float scale);
 int singe_paged_kv_prefill_attention_f32(singe_stream_t stream, float *out, float *lse, const float *query,
                                          const float *key_cache, const float *value_cache,
                                          const int32_t *actual_seq_lens_q, const int32_t *actual_seq_lens_kv,
@@ -361,6 +370,11 @@ int singe_ragged_kv_prefill_attention_bf16(singe_stream_t stream, void *out, flo
                                            const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
                                            size_t batch, size_t total_query_tokens, size_t total_kv_tokens,
                                            size_t heads, size_t kv_heads, size_t head_dim, int causal, float scale);
+int singe_ragged_kv_prefill_attention_f16(singe_stream_t stream, void *out, float *lse, const void *query,
+                                          const void *key, const void *value, const int32_t *actual_seq_lens_q,
+                                          const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
+                                          size_t batch, size_t total_query_tokens, size_t total_kv_tokens,
+                                          size_t heads, size_t kv_heads, size_t head_dim, int causal, float scale);
 int singe_ragged_kv_prefill_attention_f32(singe_stream_t stream, float *out, float *lse, const float *query,
                                           const float *key, const float *value, const int32_t *actual_seq_lens_q,
                                           const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
@@ -379,16 +393,20 @@ int singe_ragged_kv_prefill_attention_cache_write_bf16(
     int index_width, size_t pages, size_t page_size, uint32_t *status);
 
 /* Dense prefill with log-sum-exp.
- * Replaces: fmha_prefill_lse_{f32,bf16} + FmhaPrefillConfig (singe-kernel/src/cuda/attention/fmha.rs:48-790,
+ * Replaces: fmha_prefill_lse_{f32,f16,bf16} + FmhaPrefillConfig (singe-kernel/src/cuda/attention/fmha.rs:48-790,
  *   mod.rs:253-274,1602-1756), CPU meaning fmha_prefill_lse_f32 (singe-kernel/src/cpu/attention.rs:1758-1833).
  *   query, out [batch, query_len, heads, head_dim]; key, value [batch, key_len, kv_heads, head_dim];
- *   lse f32 [batch, heads, query_len], natural log. */
+ *   lse f32 [batch, heads, query_len], natural log.  The 16-bit entry points with head_dim == 128 run the
+ *   tcgen05 prefill kernel in its dense form (uniform lengths, sequences back to back). */
 int singe_fmha_prefill_lse_f32(singe_stream_t stream, float *out, float *lse, const float *query, const float *key,
                                const float *value, size_t batch, size_t query_len, size_t key_len, size_t heads,
                                size_t kv_heads, size_t head_dim, float scale, int causal);
 int singe_fmha_prefill_lse_bf16(singe_stream_t stream, void *out, float *lse, const void *query, const void *key,
                                 const void *value, size_t batch, size_t query_len, size_t key_len, size_t heads,
                                 size_t kv_heads, size_t head_dim, float scale, int causal);
+int singe_fmha_prefill_lse_f16(singe_stream_t stream, void *out, float *lse, const void *query, const void *key,
+                               const void *value, size_t batch, size_t query_len, size_t key_len, size_t heads,
+                               size_t kv_heads, size_t head_dim, float scale, int causal);
 
 /* =================================================================================================
  * Dense scaled-dot-product attention (Tensor::attend)
@@ -419,10 +437,11 @@ int singe_attend_f32(singe_stream_t stream, float *out, const float *query, cons
  *   singe_tcgen05_matmul in kernel_plan/source/tcgen05.rs:137-266, singe_dot_product in dot_product.rs:133-243).
  *   CPU meaning: singe-kernel/src/cpu/matmul/mod.rs:12-45, blocked.rs:27-95,
  *   singe/src/backend/cpu/binary/matmul.rs:18-43 (bf16 widened to f32, one rounding of the result).
- * out[rows, columns] = lhs . rhs with f32 accumulation.  The tensor-core path needs the linear-layer
- * layout (transpose_lhs == 0, transpose_rhs == 1: rhs is a weight [columns, reduction]) with
- * reduction a multiple of 8 (16-byte rows for TMA); other layouts return
- * SINGE_ERR_UNSUPPORTED_CONFIGURATION.  `_bf16` rounds the result once to bf16 (Tensor surface);
+ * out[rows, columns] = lhs . rhs with f32 accumulation.  lhs is [rows, reduction] (transpose_lhs == 0);
+ * rhs is either a linear layer's weight [columns, reduction] (transpose_rhs == 1, MatmulConfig::
+ * row_major_transposed_rhs) or a row-major [reduction, columns] operand (transpose_rhs == 0,
+ * MatmulConfig::row_major :190-202), whose tiles the tensor core reads MN-major.  Row strides and start
+ * addresses are multiples of 16 bytes (TMA); a transposed lhs returns SINGE_ERR_UNSUPPORTED_CONFIGURATION.  `_bf16` rounds the result once to bf16 (Tensor surface);
  * `_f32` keeps f32 (singe-kernel surface).
  * ================================================================================================= */
 int singe_matmul_bf16_bf16(singe_stream_t stream, void *out, const void *lhs, const void *rhs, size_t rows,

@@ -30,6 +30,11 @@ int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void 
                          size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads,
                          size_t kv_heads, size_t head_dim, int causal, float scale, const uint32_t *block_table,
                          size_t table_stride, size_t cache_pages);
+int prefill_tcgen05(cudaStream_t stream, bool is_f16, void *out, float *lse, const void *query, const void *key,
+                    const void *value, const int32_t *lens_q, const int32_t *lens_kv, const int32_t *offsets,
+                    size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads, size_t kv_heads,
+                    size_t head_dim, int causal, float scale, const uint32_t *block_table, size_t table_stride,
+                    size_t cache_pages, size_t uniform_q, size_t uniform_kv);
 // kv_cache_write.cu
 int kv_cache_write(cudaStream_t stream, void *key_cache, void *value_cache, const void *keys, const void *values,
                    const void *write_pages, const void *write_slots, int index_width, size_t tokens, size_t kv_heads,
@@ -1085,21 +1090,21 @@ int singe_attend_f32(singe_stream_t stream, float *out, const float *query, cons
                               kv_heads, query_len, key_len, head_dim, scale, causal, window, false, softcap, sinks);
 }
 
-// bf16, head_dim 128, 16-token pages: the tcgen05 prefill kernel gathers its K/V tiles through the block table.
-// Returns true when it took the call (its status is then in *status).
-static bool paged_prefill_tensor_core(bool is_bf16, singe_stream_t stream, void *out, float *lse, const void *query, const void *key_cache,
+// bf16 / f16, head_dim 128, 16-token pages: the tcgen05 prefill kernel gathers its K/V tiles through the block table.
+// Returns true when it took the call (its status is then in *status).  kind: 0 f32, 1 bf16, 2 f16.
+static bool paged_prefill_tensor_core(int kind, singe_stream_t stream, void *out, float *lse, const void *query, const void *key_cache,
                                const void *value_cache, const int32_t *lens_q, const int32_t *lens_kv,
                                const int32_t *offsets, const uint32_t *block_table, size_t batch,
                                size_t total_query_tokens, size_t heads, size_t kv_heads, size_t head_dim,
                                size_t block_size, size_t physical_blocks, size_t stride, int causal, float scale,
                                int *status) {
-    if (!is_bf16 || block_size != 16 ||
+    if (kind == 0 || block_size != 16 ||
         !prefill_fast_path(heads, kv_heads, head_dim, total_query_tokens, query, key_cache, value_cache, out)) {
         return false;
     }
-    *status = singe::prefill_tcgen05_bf16(static_cast<cudaStream_t>(stream), out, lse, query, key_cache, value_cache, lens_q,
-                                   lens_kv, offsets, batch, total_query_tokens, 0, heads, kv_heads, head_dim, causal,
-                                   scale, block_table, stride, physical_blocks);
+    *status = singe::prefill_tcgen05(static_cast<cudaStream_t>(stream), kind == 2, out, lse, query, key_cache,
+                                     value_cache, lens_q, lens_kv, offsets, batch, total_query_tokens, 0, heads,
+                                     kv_heads, head_dim, causal, scale, block_table, stride, physical_blocks, 0, 0);
     return true;
 }
 
@@ -1117,7 +1122,7 @@ static bool paged_prefill_tensor_core(bool is_bf16, singe_stream_t stream, void 
             return SINGE_ERR_NULL_POINTER;                                                                            \
         }                                                                                                             \
         int tensor_core_status = SINGE_OK;                                                                            \
-        if (paged_prefill_tensor_core(std::is_same<T, __nv_bfloat16>::value, stream, out, lse, query, key_cache, value_cache, actual_seq_lens_q,          \
+        if (paged_prefill_tensor_core(std::is_same<T, __nv_bfloat16>::value ? 1 : (std::is_same<T, __half>::value ? 2 : 0), stream, out, lse, query, key_cache, value_cache, actual_seq_lens_q,          \
                                          actual_seq_lens_kv, actual_seq_offsets, block_table, batch,                  \
                                          total_query_tokens, heads, kv_heads, head_dim, block_size, physical_blocks,  \
                                          block_table_batch_stride, causal, scale, &tensor_core_status)) {             \
@@ -1130,6 +1135,7 @@ static bool paged_prefill_tensor_core(bool is_bf16, singe_stream_t stream, void 
     }
 
 SINGE_PAGED_PREFILL(singe_paged_kv_prefill_attention_bf16, __nv_bfloat16, void)
+SINGE_PAGED_PREFILL(singe_paged_kv_prefill_attention_f16, __half, void)
 SINGE_PAGED_PREFILL(singe_paged_kv_prefill_attention_f32, float, float)
 #undef SINGE_PAGED_PREFILL
 
@@ -1149,25 +1155,51 @@ int singe_ragged_kv_prefill_attention_f32(singe_stream_t stream, float *out, flo
                                          causal, scale);
 }
 
-int singe_ragged_kv_prefill_attention_bf16(singe_stream_t stream, void *out, float *lse, const void *query,
-                                           const void *key, const void *value, const int32_t *actual_seq_lens_q,
-                                           const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
-                                           size_t batch, size_t total_query_tokens, size_t total_kv_tokens,
-                                           size_t heads, size_t kv_heads, size_t head_dim, int causal, float scale) {
+}  // extern "C"
+
+template <typename T>
+static int ragged_prefill_16bit(singe_stream_t stream, void *out, float *lse, const void *query, const void *key,
+                                const void *value, const int32_t *actual_seq_lens_q,
+                                const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets, size_t batch,
+                                size_t total_query_tokens, size_t total_kv_tokens, size_t heads, size_t kv_heads,
+                                size_t head_dim, int causal, float scale) {
     SINGE_TRY(validate_ragged_prefill(batch, total_query_tokens, total_kv_tokens, heads, kv_heads, head_dim, scale));
     if (out == nullptr || lse == nullptr || query == nullptr || key == nullptr || value == nullptr ||
         actual_seq_lens_q == nullptr || actual_seq_lens_kv == nullptr || actual_seq_offsets == nullptr) {
         return SINGE_ERR_NULL_POINTER;
     }
     if (prefill_fast_path(heads, kv_heads, head_dim, total_query_tokens, query, key, value, out)) {
-        return prefill_tcgen05_bf16(static_cast<cudaStream_t>(stream), out, lse, query, key, value, actual_seq_lens_q,
-                                    actual_seq_lens_kv, actual_seq_offsets, batch, total_query_tokens,
-                                    total_kv_tokens, heads, kv_heads, head_dim, causal, scale, nullptr, 0, 0);
+        return prefill_tcgen05(static_cast<cudaStream_t>(stream), std::is_same<T, __half>::value, out, lse, query, key,
+                               value, actual_seq_lens_q, actual_seq_lens_kv, actual_seq_offsets, batch,
+                               total_query_tokens, total_kv_tokens, heads, kv_heads, head_dim, causal, scale, nullptr,
+                               0, 0, 0, 0);
     }
-    return packed_prefill_general<__nv_bfloat16>(static_cast<cudaStream_t>(stream), out, lse, query, key, value,
-                                                 actual_seq_lens_q, actual_seq_lens_kv, actual_seq_offsets, nullptr,
-                                                 batch, total_query_tokens, total_kv_tokens, heads, kv_heads,
-                                                 head_dim, 1, 1, 1, causal, scale);
+    return packed_prefill_general<T>(static_cast<cudaStream_t>(stream), out, lse, query, key, value,
+                                     actual_seq_lens_q, actual_seq_lens_kv, actual_seq_offsets, nullptr, batch,
+                                     total_query_tokens, total_kv_tokens, heads, kv_heads, head_dim, 1, 1, 1, causal,
+                                     scale);
+}
+
+extern "C" {
+
+int singe_ragged_kv_prefill_attention_bf16(singe_stream_t stream, void *out, float *lse, const void *query,
+                                           const void *key, const void *value, const int32_t *actual_seq_lens_q,
+                                           const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
+                                           size_t batch, size_t total_query_tokens, size_t total_kv_tokens,
+                                           size_t heads, size_t kv_heads, size_t head_dim, int causal, float scale) {
+    return ragged_prefill_16bit<__nv_bfloat16>(stream, out, lse, query, key, value, actual_seq_lens_q,
+                                               actual_seq_lens_kv, actual_seq_offsets, batch, total_query_tokens,
+                                               total_kv_tokens, heads, kv_heads, head_dim, causal, scale);
+}
+
+int singe_ragged_kv_prefill_attention_f16(singe_stream_t stream, void *out, float *lse, const void *query,
+                                          const void *key, const void *value, const int32_t *actual_seq_lens_q,
+                                          const int32_t *actual_seq_lens_kv, const int32_t *actual_seq_offsets,
+                                          size_t batch, size_t total_query_tokens, size_t total_kv_tokens,
+                                          size_t heads, size_t kv_heads, size_t head_dim, int causal, float scale) {
+    return ragged_prefill_16bit<__half>(stream, out, lse, query, key, value, actual_seq_lens_q, actual_seq_lens_kv,
+                                        actual_seq_offsets, batch, total_query_tokens, total_kv_tokens, heads,
+                                        kv_heads, head_dim, causal, scale);
 }
 
 int singe_ragged_kv_prefill_attention_cache_write_bf16(
@@ -1194,15 +1226,44 @@ int singe_fmha_prefill_lse_f32(singe_stream_t stream, float *out, float *lse, co
                               query_len, key_len, head_dim, scale, causal, 0, true);
 }
 
+}  // extern "C"
+
+// fmha_prefill_lse over 16-bit floats: [B, L, H, 128] queries over [B, S, G, 128] keys and values are the packed
+// prefill's dense form (uniform lengths, sequences back to back) on the tensor core; other widths, an empty key axis
+// and unaligned tensors take the general kernel.
+template <typename T>
+static int dense_prefill_16bit(singe_stream_t stream, void *out, float *lse, const void *query, const void *key,
+                               const void *value, size_t batch, size_t query_len, size_t key_len, size_t heads,
+                               size_t kv_heads, size_t head_dim, float scale, int causal) {
+    if (lse == nullptr) return SINGE_ERR_NULL_POINTER;
+    const size_t total_q = batch * query_len, total_kv = batch * key_len;
+    if (out != nullptr && query != nullptr && key != nullptr && value != nullptr && batch > 0 && query_len > 0 &&
+        key_len > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && finite(scale) &&
+        total_q <= 0x7fffffffull && total_kv <= 0x7fffffffull &&
+        prefill_fast_path(heads, kv_heads, head_dim, total_q, query, key, value, out)) {
+        return prefill_tcgen05(static_cast<cudaStream_t>(stream), std::is_same<T, __half>::value, out, lse, query, key,
+                               value, nullptr, nullptr, nullptr, batch, total_q, total_kv, heads, kv_heads, head_dim,
+                               causal ? 1 : 0, scale, nullptr, 0, 0, query_len, key_len);
+    }
+    return dense_entry<T>(static_cast<cudaStream_t>(stream), static_cast<T *>(out), lse, static_cast<const T *>(query),
+                          static_cast<const T *>(key), static_cast<const T *>(value), batch, heads, kv_heads,
+                          query_len, key_len, head_dim, scale, causal, 0, true);
+}
+
+extern "C" {
+
 int singe_fmha_prefill_lse_bf16(singe_stream_t stream, void *out, float *lse, const void *query, const void *key,
                                 const void *value, size_t batch, size_t query_len, size_t key_len, size_t heads,
                                 size_t kv_heads, size_t head_dim, float scale, int causal) {
-    if (lse == nullptr) return SINGE_ERR_NULL_POINTER;
-    return dense_entry<__nv_bfloat16>(static_cast<cudaStream_t>(stream), static_cast<__nv_bfloat16 *>(out), lse,
-                                      static_cast<const __nv_bfloat16 *>(query),
-                                      static_cast<const __nv_bfloat16 *>(key),
-                                      static_cast<const __nv_bfloat16 *>(value), batch, heads, kv_heads, query_len,
-                                      key_len, head_dim, scale, causal, 0, true);
+    return dense_prefill_16bit<__nv_bfloat16>(stream, out, lse, query, key, value, batch, query_len, key_len, heads,
+                                              kv_heads, head_dim, scale, causal);
+}
+
+int singe_fmha_prefill_lse_f16(singe_stream_t stream, void *out, float *lse, const void *query, const void *key,
+                               const void *value, size_t batch, size_t query_len, size_t key_len, size_t heads,
+                               size_t kv_heads, size_t head_dim, float scale, int causal) {
+    return dense_prefill_16bit<__half>(stream, out, lse, query, key, value, batch, query_len, key_len, heads,
+                                       kv_heads, head_dim, scale, causal);
 }
 
 int singe_scaled_dot_product_attention_f32(singe_stream_t stream, float *out, const float *query, const float *key,

@@ -301,6 +301,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     return true;
 }
 
+// After a bounded wait has run out, copies that were issued may still be landing in the CTA's shared memory.  The
+// threads that gave up stay for a bounded while (about half a millisecond) before the CTA ends, so that the memory is
+// not handed to another CTA with those copies still in flight.
+__device__ __forceinline__ void linger_after_timeout() {
+    const long long start = clock64();
+    while (clock64() - start < (1ll << 20)) {
+    }
+}
+
 __device__ __forceinline__ void fence_proxy_async_shared() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -52,6 +52,8 @@ struct GemmParams {
     int stable_rhs;    // 1: the caller vouches that rhs (a weight matrix) is not written by work still in flight, so
                        //    its first tiles are fetched before the wait on the preceding kernels
     int prefetch_blocks;  // with stable_rhs: k-blocks beyond the ring whose rhs tiles are pulled into L2 before the wait
+    int rhs_kn;        // 1: rhs is stored [K, N] (transpose_rhs == 0): its tiles are staged N-contiguous and the MMA
+                       //    reads them as an MN-major operand; 0: [N, K], K-major (a linear layer's weight)
     uint32_t *error;   // sticky device error word (2 = a bounded wait ran out)
     WarmRange warm;    // pulled into L2 by the epilogue warps while they have nothing else to do
 };
@@ -63,6 +65,33 @@ __device__ __forceinline__ float gated_value(float gate_acc, float up_acc) {
     const float up = __bfloat162float(__float2bfloat16_rn(up_acc));
     const float activated = __bfloat162float(__float2bfloat16_rn(silu_fast(gate)));
     return activated * up;
+}
+
+// One 64-wide K slice of the B operand into shared memory (BN x 128 bytes either way).  [N, K] weights: one box of BN
+// rows x 64 K-elements.  [K, N] right operands: BN / 64 boxes of 64 K-rows x 64 N-elements, 8 KB apart, which the MMA
+// reads MN-major (leading byte offset 8 KB to the next 64 columns, 1 KB to the next eight K-rows, 2 KB per 16-wide k step).
+template <int BN>
+__device__ __forceinline__ void load_b_slice(uint32_t dst, const CUtensorMap *map, uint32_t bar, int k0, int n0, int rhs_kn) {
+    if (!rhs_kn) {
+        tma_load_2d(dst, map, bar, k0, n0);
+    } else {
+#pragma unroll
+        for (int h = 0; h < BN / 64; ++h) tma_load_2d(dst + h * 8192, map, bar, n0 + h * 64, k0);
+    }
+}
+
+template <int BN>
+__device__ __forceinline__ void prefetch_b_slice(const CUtensorMap *map, int k0, int n0, int rhs_kn) {
+    if (!rhs_kn) {
+        tma_prefetch_2d(map, k0, n0);
+    } else {
+#pragma unroll
+        for (int h = 0; h < BN / 64; ++h) tma_prefetch_2d(map, n0 + h * 64, k0);
+    }
+}
+
+__device__ __forceinline__ uint64_t b_descriptor(uint32_t slice, int ks, int rhs_kn) {
+    return rhs_kn ? make_smem_desc(slice + ks * 2048, 8192, 1024) : make_smem_desc(slice, 16, 1024) + 2 * ks;
 }
 
 __device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tiles_n, int &tm, int &tn) {
@@ -84,6 +113,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                      const GemmParams p) {
     constexpr uint32_t kTmemColumns = 2 * BN < 32 ? 32 : 2 * BN;
     constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, 0, 0);
+    constexpr uint32_t kIdescKN = make_instr_desc(kBlockM, BN, true, 0, 1);  // B read MN-major
     constexpr int kBBytes = BN * 128;
 
     grid_launch_dependents();
@@ -149,14 +179,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
-                        tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
-                                    tn * BN);
+                        load_b_slice<BN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
+                                         tn * BN, p.rhs_kn);
                     }
                 }
                 const int last = min(p.k_blocks, preloaded + p.prefetch_blocks);
                 for (int kb = preloaded; kb < last; ++kb) {
 #pragma unroll
-                    for (int sub = 0; sub < KPS; ++sub) tma_prefetch_2d(&b_map, (kb * KPS + sub) * kBlockK, tn * BN);
+                    for (int sub = 0; sub < KPS; ++sub) prefetch_b_slice<BN>(&b_map, (kb * KPS + sub) * kBlockK, tn * BN, p.rhs_kn);
                 }
             }
         }
@@ -188,8 +218,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     if (!early) {
 #pragma unroll
                         for (int sub = 0; sub < KPS; ++sub) {
-                            tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full,
-                                        (kb * KPS + sub) * kBlockK, tn * BN);
+                            load_b_slice<BN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full,
+                                             (kb * KPS + sub) * kBlockK, tn * BN, p.rhs_kn);
                         }
                     }
                 }
@@ -221,12 +251,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
                         const uint64_t a_desc = make_smem_desc(stage + sub * a_bytes, 16, 1024);
-                        const uint64_t b_desc = make_smem_desc(stage + KPS * a_bytes + sub * kBBytes, 16, 1024);
+                        const uint32_t b_slice = stage + KPS * a_bytes + sub * kBBytes;
 #pragma unroll
                         for (int ks = 0; ks < kBlockK / 16; ++ks) {
                             // 16 bf16 of K = 32 bytes = 2 descriptor address units
-                            umma_ss(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kIdesc,
-                                    (kb > 0 || sub > 0 || ks > 0) ? 1u : 0u);
+                            umma_ss(tmem_d, a_desc + 2 * ks, b_descriptor(b_slice, ks, p.rhs_kn),
+                                    p.rhs_kn ? kIdescKN : kIdesc, (kb > 0 || sub > 0 || ks > 0) ? 1u : 0u);
                         }
                     }
                     tcgen05_commit(bar_empty + s * 8);
@@ -334,6 +364,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (failed && lane == 0) {
         report_status(p.error, kStatusWaitTimeout);
     }
+    if (failed) linger_after_timeout();
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -374,6 +405,7 @@ __global__ void __launch_bounds__(kSplitKThreads, 1)
                        const GemmParams p) {
     constexpr uint32_t kTmemColumns = BN < 32 ? 32 : BN;
     constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, 0, 0);
+    constexpr uint32_t kIdescKN = make_instr_desc(kBlockM, BN, true, 0, 1);  // B read MN-major
     constexpr int kBBytes = BN * 128;
     constexpr int kQuads = BN / 4;  // float4 groups per row
 
@@ -444,14 +476,14 @@ __global__ void __launch_bounds__(kSplitKThreads, 1)
                     mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
-                        tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
-                                    tn * BN);
+                        load_b_slice<BN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
+                                         tn * BN, p.rhs_kn);
                     }
                 }
                 const int last = min(kb_last, kb_first + preloaded + p.prefetch_blocks);
                 for (int kb = kb_first + preloaded; kb < last; ++kb) {
 #pragma unroll
-                    for (int sub = 0; sub < KPS; ++sub) tma_prefetch_2d(&b_map, (kb * KPS + sub) * kBlockK, tn * BN);
+                    for (int sub = 0; sub < KPS; ++sub) prefetch_b_slice<BN>(&b_map, (kb * KPS + sub) * kBlockK, tn * BN, p.rhs_kn);
                 }
             }
         }
@@ -479,8 +511,8 @@ __global__ void __launch_bounds__(kSplitKThreads, 1)
                 if (!early) {
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
-                        tma_load_2d(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
-                                    tn * BN);
+                        load_b_slice<BN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
+                                         tn * BN, p.rhs_kn);
                     }
                 }
             }
@@ -501,11 +533,11 @@ __global__ void __launch_bounds__(kSplitKThreads, 1)
 #pragma unroll
                 for (int sub = 0; sub < KPS; ++sub) {
                     const uint64_t a_desc = make_smem_desc(stage + sub * a_bytes, 16, 1024);
-                    const uint64_t b_desc = make_smem_desc(stage + KPS * a_bytes + sub * kBBytes, 16, 1024);
+                    const uint32_t b_slice = stage + KPS * a_bytes + sub * kBBytes;
 #pragma unroll
                     for (int ks = 0; ks < kBlockK / 16; ++ks) {
-                        umma_ss(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, kIdesc,
-                                (kb > kb_first || sub > 0 || ks > 0) ? 1u : 0u);
+                        umma_ss(tmem_base, a_desc + 2 * ks, b_descriptor(b_slice, ks, p.rhs_kn),
+                                p.rhs_kn ? kIdescKN : kIdesc, (kb > kb_first || sub > 0 || ks > 0) ? 1u : 0u);
                     }
                 }
                 tcgen05_commit(bar_empty + s * 8);
@@ -582,6 +614,7 @@ __global__ void __launch_bounds__(kSplitKThreads, 1)
     if (failed && lane == 0) {
         report_status(p.error, kStatusWaitTimeout);
     }
+    if (failed) linger_after_timeout();
     // Arrive: "everything addressed to this CTA has landed".  When all CTAs have said so, every bulk copy of the
     // cluster has finished reading its source, and a CTA may leave (the matching wait is at the end).
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -744,7 +777,13 @@ int launch_gemm_splitk(cudaStream_t stream, GemmParams params, const void *lhs, 
         SINGE_TRY(encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, lhs, dims, strides, box,
                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
     }
-    {
+    if (params.rhs_kn) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(params.n), static_cast<uint64_t>(params.k)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(rhs_row_stride) * 2};
+        const uint32_t box[2] = {64, kBlockK};
+        SINGE_TRY(encode_tensor_map(&b_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rhs, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+    } else {
         const uint64_t dims[2] = {static_cast<uint64_t>(params.k), static_cast<uint64_t>(params.n)};
         const uint64_t strides[1] = {static_cast<uint64_t>(rhs_row_stride) * 2};
         const uint32_t box[2] = {kBlockK, static_cast<uint32_t>(BN)};
@@ -787,7 +826,13 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
         SINGE_TRY(encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, lhs, dims, strides, box,
                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
     }
-    {
+    if (params.rhs_kn) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(params.n), static_cast<uint64_t>(params.k)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(rhs_row_stride) * 2};
+        const uint32_t box[2] = {64, kBlockK};
+        SINGE_TRY(encode_tensor_map(&b_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rhs, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+    } else {
         const uint64_t dims[2] = {static_cast<uint64_t>(params.k), static_cast<uint64_t>(params.n)};
         const uint64_t strides[1] = {static_cast<uint64_t>(rhs_row_stride) * 2};
         const uint32_t box[2] = {kBlockK, static_cast<uint32_t>(BN)};
@@ -823,7 +868,8 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
     // Tensor-core path: linear-layer layout, 16-byte aligned rows for TMA.
     const bool aligned = ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15u) == 0 &&
                          lhs_row_stride % 8 == 0 && rhs_row_stride % 8 == 0;
-    if (transpose_lhs || !transpose_rhs || !aligned) {
+    // lhs must be [M, K]; rhs may be [N, K] (a linear layer's weight, transpose_rhs != 0) or [K, N]
+    if (transpose_lhs || !aligned || (gated && !transpose_rhs)) {
         return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
     }
     GemmParams params;
@@ -833,6 +879,7 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
     params.gated = gated ? 1 : 0;
     params.stable_rhs = (hints & SINGE_HINT_STABLE_WEIGHTS) != 0 ? 1 : 0;
     params.warm = take_pending_warm();
+    params.rhs_kn = transpose_rhs ? 0 : 1;
     params.prefetch_blocks = 0;
     params.m = static_cast<int>(rows);
     params.n = static_cast<int>(columns);
@@ -902,6 +949,11 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
     }
     if (forced_splits != 0) splits = forced_splits;
     if (forced_block_n != 0) bn = forced_block_n;
+    if (params.rhs_kn && bn < 64) {
+        // [K, N] tiles are staged in boxes of 64 columns
+        bn = 64;
+        slices = slices > 4 ? 4 : slices;
+    }
     {
         // two stages must fit the shared-memory limit of the call
         const int room = shared_limit(params) - 20 * 1024;

@@ -180,7 +180,10 @@ __global__ void __launch_bounds__(kBulkWarps * 32)
     if (lane == 0) {
         while (stored < issued && !failed) store_oldest();
         asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // the stores have landed before the CTA leaves
-        if (failed) report_status(status, kStatusWaitTimeout);
+        if (failed) {
+            report_status(status, kStatusWaitTimeout);
+            linger_after_timeout();
+        }
     }
 }
 

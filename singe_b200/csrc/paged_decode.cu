@@ -402,6 +402,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         if (failed && lane == 0) {
             report_status(p.status, kStatusWaitTimeout);
         }
+        if (failed) linger_after_timeout();
     } else {
         // ---------------- consumers ----------------
         const int row = lane >> 2;   // query head within the group (rows >= group are zero padding)
@@ -509,6 +510,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         if (failed && lane == 0) {
             report_status(p.status, kStatusWaitTimeout);
         }
+        if (failed) linger_after_timeout();   // before this warp's first stage is reused as its merge buffer
         if (FUSED && adds_new && warp == 0) {
             // ---- the key and value this step adds: rotate K, put both rows into the cache, attend the new key ----
             const T *projections = static_cast<const T *>(p.qkv) + static_cast<size_t>(b) * p.qkv_stride;

@@ -1,4 +1,4 @@
-// Packed variable-length flash-attention prefill on the tcgen05 tensor core (bf16, head_dim 128, GQA).
+// Packed variable-length flash-attention prefill on the tcgen05 tensor core (bf16 or f16, head_dim 128, GQA).
 //
 // Meaning: ragged_kv_prefill_attention (singe-kernel/src/cpu/attention.rs:1343-1420): sequence b owns query
 // tokens [offsets[b], offsets[b] + lens_q[b]) and key rows [offsets[b], offsets[b] + lens_kv[b]) of the packed
@@ -35,6 +35,8 @@
 // Shared memory: Q_A, Q_B, 2 x K, 2 x V tiles of 32 KB = 192 KB.
 // Under a causal mask tile A sees one key tile less than tile B; CTAs are dispatched heaviest-first.
 // Every mbarrier wait is bounded; on a timeout the CTA records status 2, frees tensor memory and leaves.
+#include <type_traits>
+
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -46,7 +48,6 @@ constexpr int kPrefillThreads = 320;
 constexpr int kTile = 128;           // rows of one query tile, and keys per key tile
 constexpr int kPair = 2 * kTile;     // query rows per CTA
 constexpr int kChunk = 32;           // score columns taken out of tensor memory at a time
-constexpr int kHeadDim = 128;
 constexpr int kHalfTileBytes = kTile * 128;       // one TMA box: 128 rows x 128 bytes
 constexpr int kTileBytes = 2 * kHalfTileBytes;    // 32 KB
 constexpr int kPageTokens = 16;                   // paged form: tokens per cache page
@@ -62,11 +63,16 @@ constexpr int kRedoCapacity = 2048;               // marked items one CTA lists;
 __device__ unsigned g_out_of_range_seen = 0;
 
 struct PrefillParams {
-    __nv_bfloat16 *out;
+    void *out;
     float *lse;
-    const int32_t *lens_q;
-    const int32_t *lens_kv;
+    const int32_t *lens_q;    // nullptr: the dense form, every sequence has uniform_q queries and uniform_kv keys,
+    const int32_t *lens_kv;   //          sequence b starts at row b * uniform_q (queries) / b * uniform_kv (keys)
     const int32_t *offsets;
+    int uniform_q;
+    int uniform_kv;
+    int lse_rows;   // 0: LSE is [total_q, heads] (packed forms); > 0: [batch, heads, lse_rows] (fmha_prefill_lse)
+    int exact;      // 1: the exact-maximum launch walks every item (16-bit floats whose range the single-pass
+                    // softmax would leave); 0: it only redoes what the first launch marked
     int batch;
     int heads;
     int kv_heads;
@@ -81,6 +87,11 @@ struct PrefillParams {
     float scale_log2;
     uint32_t *error;
 };
+
+__device__ __forceinline__ int seq_len_q(const PrefillParams &p, int b) { return p.lens_q != nullptr ? p.lens_q[b] : p.uniform_q; }
+__device__ __forceinline__ int seq_len_kv(const PrefillParams &p, int b) { return p.lens_q != nullptr ? p.lens_kv[b] : p.uniform_kv; }
+__device__ __forceinline__ int seq_offset_q(const PrefillParams &p, int b) { return p.lens_q != nullptr ? p.offsets[b] : b * p.uniform_q; }
+__device__ __forceinline__ int seq_offset_kv(const PrefillParams &p, int b) { return p.lens_q != nullptr ? p.offsets[b] : b * p.uniform_kv; }
 
 __device__ __forceinline__ float exp2_approx(float x) {
     float y;
@@ -122,7 +133,7 @@ __device__ __forceinline__ void chunk_max(const uint32_t (&sc)[kChunk], int limi
 // columns at `tmem_p`), the unrounded values are added to two running f32x2 sums.  Scores are handled as f32x2
 // pairs.  (Evaluating part of the exponentials as a polynomial on the FMA pipe was measured slower at every ratio:
 // with one softmax warp per scheduler the extra instructions cost more than the special-function unit saves.)
-template <bool MASKED>
+template <typename T, bool MASKED>
 __device__ __forceinline__ void chunk_exp_store(const uint32_t (&sc)[kChunk], uint32_t tmem_p, float2 scale2,
                                                 float2 bias2, int limit, float2 (&sum)[2]) {
     uint32_t packed[kChunk / 2];
@@ -137,14 +148,14 @@ __device__ __forceinline__ void chunk_exp_store(const uint32_t (&sc)[kChunk], ui
             e.y = (i + 1 < limit) ? e.y : 0.0f;
         }
         sum[(i >> 1) & 1] = __fadd2_rn(sum[(i >> 1) & 1], e);
-        packed[i >> 1] = pack2<__nv_bfloat16>(e.x, e.y);
+        packed[i >> 1] = pack2<T>(e.x, e.y);
     }
     tmem_st_x16(tmem_p, packed);
 }
 
 // One row of one key tile: S (128 f32 columns at `tmem_s`) -> P (64 packed columns over the same place), chunk by
 // chunk with the next chunk's load in flight.
-template <bool MASKED>
+template <typename T, bool MASKED>
 __device__ __forceinline__ void tile_exp(uint32_t tmem_s, float2 scale2, float2 bias2, int limit, float2 (&sum)[2]) {
     uint32_t buf[2][kChunk];
     tmem_ld_x32(tmem_s, buf[0]);
@@ -152,7 +163,7 @@ __device__ __forceinline__ void tile_exp(uint32_t tmem_s, float2 scale2, float2 
     for (int c = 0; c < kTile / kChunk; ++c) {
         tmem_wait_ld_into(buf[c & 1]);
         if (c + 1 < kTile / kChunk) tmem_ld_x32(tmem_s + (c + 1) * kChunk, buf[(c + 1) & 1]);
-        chunk_exp_store<MASKED>(buf[c & 1], tmem_s + c * (kChunk / 2), scale2, bias2, limit - c * kChunk, sum);
+        chunk_exp_store<T, MASKED>(buf[c & 1], tmem_s + c * (kChunk / 2), scale2, bias2, limit - c * kChunk, sum);
     }
 }
 
@@ -171,10 +182,11 @@ __device__ __forceinline__ float tile_max(uint32_t tmem_s, int limit, float sign
     return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
 }
 
-// Multiplies this thread's row of O (128 f32 columns of tensor memory) by `factor`.
+// Multiplies this thread's row of O (HD f32 columns of tensor memory) by `factor`.
+template <int HD>
 __device__ __forceinline__ void scale_o_row(uint32_t tmem_o, float factor) {
 #pragma unroll 1
-    for (int c = 0; c < kHeadDim; c += 32) {
+    for (int c = 0; c < HD; c += 32) {
         uint32_t r[32];
         tmem_ld_x32(tmem_o + c, r);
         tmem_wait_ld_into(r);
@@ -190,7 +202,8 @@ struct Item {
     int head;
     int kv_head;
     int seq;        // sequence index (row of the block table in the paged form)
-    int offset;     // first packed row of the sequence
+    int offset;     // first packed query row of the sequence
+    int offset_kv;  // first packed key row of the sequence (the same row except in the dense form)
     int q0;         // sequence-local index of the first query row
     int len_q;
     int len_kv;
@@ -235,7 +248,7 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
     int seq = -1;
     for (int first = 0; first < p.batch && seq < 0 && pair >= 0; first += 32) {
         const int b = first + lane;
-        const bool has = b < p.batch && pairs_of(p.lens_q[b]) > pair;
+        const bool has = b < p.batch && pairs_of(seq_len_q(p, b)) > pair;
         const unsigned mask = __ballot_sync(kFull, has);
         const int n = __popc(mask);
         if (rank < n) {
@@ -247,6 +260,7 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
     item.valid = false;
     item.seq = seq < 0 ? 0 : seq;
     item.offset = 0;
+    item.offset_kv = 0;
     item.q0 = max(pair, 0) * kPair;
     item.len_q = 0;
     item.len_kv = 0;
@@ -254,12 +268,13 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
     item.tiles[0] = item.tiles[1] = 0;
     item.key_tiles = 0;
     if (seq < 0) return item;
-    item.len_q = max(p.lens_q[seq], 0);
-    item.len_kv = max(p.lens_kv[seq], 0);
-    item.offset = p.offsets[seq];
+    item.len_q = max(seq_len_q(p, seq), 0);
+    item.len_kv = max(seq_len_kv(p, seq), 0);
+    item.offset = seq_offset_q(p, seq);
+    item.offset_kv = seq_offset_kv(p, seq);
     item.valid = item.offset >= 0 && item.offset + item.len_q <= p.total_q &&
                  (p.block_table != nullptr ? item.len_kv <= p.table_stride * kPageTokens
-                                           : item.offset + item.len_kv <= p.total_kv);
+                                           : item.offset_kv + item.len_kv <= p.total_kv);
     if (!item.valid) return item;
     item.shift = p.causal == 2 ? item.len_kv - item.len_q : 0;
 #pragma unroll
@@ -282,7 +297,8 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
 // otherwise recomputes it with the exact row maximum on every tile.
 // PAGED: K and V tiles are gathered from 16-token cache pages through the block table (eight page boxes per
 // 128-key tile and 64-wide half; the boxes land back to back, which is the layout one 128-row box would have).
-template <bool SAFE, bool PAGED>
+// HD = 128 or 64: with 64 a tile is a single 128-byte-wide box (the second half of every 32 KB buffer stays unused).
+template <typename T, int HD, bool SAFE, bool PAGED>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
     prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                            const __grid_constant__ CUtensorMap v_map, const PrefillParams p) {
@@ -293,6 +309,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     const uint32_t k_smem = base + 2 * kTileBytes;       // [2 stages]
     const uint32_t v_smem = base + 4 * kTileBytes;       // [2 stages]
     const uint32_t bars = base + 6 * kTileBytes;
+    constexpr int kHalves = HD / 64;                       // 128-byte-wide boxes per tile
+    constexpr int kLoadBytes = kHalves * kHalfTileBytes;   // bytes one tile load delivers
     const uint32_t bar_q_full = bars;         // [2 tiles]
     const uint32_t bar_q_empty = bars + 16;   // [2 tiles]
     const uint32_t bar_k_full = bars + 32;    // [2 stages]
@@ -314,18 +332,18 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    if (SAFE && *reinterpret_cast<volatile unsigned *>(&g_out_of_range_seen) == 0u) {
+    if (SAFE && !p.exact && *reinterpret_cast<volatile unsigned *>(&g_out_of_range_seen) == 0u) {
         return;  // no first launch on this device has ever marked a row
     }
 
     // ---- the table behind the heaviest-first item order ----
     {
         int tmax = 0;
-        for (int b = 0; b < p.batch; ++b) tmax = max(tmax, pairs_of(p.lens_q[b]));
+        for (int b = 0; b < p.batch; ++b) tmax = max(tmax, pairs_of(seq_len_q(p, b)));
         tmax = min(tmax, kMaxRankTiles);
         for (int t = tid; t < tmax; t += kPrefillThreads) {
             int count = 0;
-            for (int b = 0; b < p.batch; ++b) count += pairs_of(p.lens_q[b]) > t ? 1 : 0;
+            for (int b = 0; b < p.batch; ++b) count += pairs_of(seq_len_q(p, b)) > t ? 1 : 0;
             counts[t] = count;
         }
         __syncthreads();
@@ -345,8 +363,15 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const long long index = first + ((round & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
         return index < total_items ? static_cast<int>(index) : -1;
     };
+    // where the LSE of (item, sequence-local query row) lives
+    auto lse_at = [&](const Item &item, int row) -> float * {
+        if (p.lse_rows > 0) {
+            return p.lse + (static_cast<size_t>(item.seq) * p.heads + item.head) * p.lse_rows + row;
+        }
+        return p.lse + (static_cast<size_t>(item.offset) + row) * p.heads + item.head;
+    };
     int listed = -1;  // SAFE: number of marked items in redo_list, or -1 = walk the whole share
-    if (SAFE) {
+    if (SAFE && !p.exact) {
         // The first launch leaves a NaN as the LSE of every row it could not finish in range: list the marked items.
         int found = 0;
         bool overflow = false;
@@ -356,7 +381,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             const Item item = decode_item(p, counts, tmax, index, lane);
             const int row = item.q0 + tid;
             const bool marked = item.valid && item.key_tiles > 0 && tid < kPair && row < item.len_q &&
-                                isnan(p.lse[(static_cast<size_t>(item.offset) + row) * p.heads + item.head]);
+                                isnan(*lse_at(item, row));
             if (__syncthreads_or(marked ? 1 : 0) != 0) {
                 if (found < kRedoCapacity) {
                     if (tid == 0) redo_list[found] = index;
@@ -423,16 +448,18 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                 }
                 ++q_loads[x];
                 if (lane == 0) {
-                    mbar_expect_tx(bar_q_full + x * 8, kTileBytes);
+                    mbar_expect_tx(bar_q_full + x * 8, kLoadBytes);
                     const int row0 = item.offset + item.q0 + x * kTile;
                     tma_load_3d(q_smem + x * kTileBytes, &q_map, bar_q_full + x * 8, 0, item.head, row0);
-                    tma_load_3d(q_smem + x * kTileBytes + kHalfTileBytes, &q_map, bar_q_full + x * 8, 64, item.head,
-                                row0);
+                    if (kHalves == 2) {
+                        tma_load_3d(q_smem + x * kTileBytes + kHalfTileBytes, &q_map, bar_q_full + x * 8, 64,
+                                    item.head, row0);
+                    }
                 }
             }
             for (int j = 0; j < item.key_tiles && !failed; ++j, ++g) {
                 const int stage = g & 1;
-                const int row0 = item.offset + j * kTile;
+                const int row0 = item.offset_kv + j * kTile;
                 if (g >= 2 && !wait_lane0(bar_k_empty + stage * 8, ((g >> 1) - 1) & 1)) {
                     failed = true;
                     break;
@@ -452,42 +479,47 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                     }
                     page = static_cast<int32_t>(id);
                 }
-                if (lane == 0) mbar_expect_tx(bar_k_full + stage * 8, kTileBytes);
+                if (lane == 0) mbar_expect_tx(bar_k_full + stage * 8, kLoadBytes);
                 __syncwarp();
                 if (PAGED) {
-                    if (lane < 16) {
+                    if (lane < 8 * kHalves) {
                         const int half = lane >> 3;
                         tma_load_4d(k_smem + stage * kTileBytes + half * kHalfTileBytes + (lane & 7) * kPageBytes, &k_map,
                                     bar_k_full + stage * 8, half * 64, item.kv_head, 0, page);
                     }
                 } else if (lane == 0) {
                     tma_load_3d(k_smem + stage * kTileBytes, &k_map, bar_k_full + stage * 8, 0, item.kv_head, row0);
-                    tma_load_3d(k_smem + stage * kTileBytes + kHalfTileBytes, &k_map, bar_k_full + stage * 8, 64,
-                                item.kv_head, row0);
+                    if (kHalves == 2) {
+                        tma_load_3d(k_smem + stage * kTileBytes + kHalfTileBytes, &k_map, bar_k_full + stage * 8, 64,
+                                    item.kv_head, row0);
+                    }
                 }
                 if (g >= 2 && !wait_lane0(bar_v_empty + stage * 8, ((g >> 1) - 1) & 1)) {
                     failed = true;
                     break;
                 }
-                if (lane == 0) mbar_expect_tx(bar_v_full + stage * 8, kTileBytes);
+                if (lane == 0) mbar_expect_tx(bar_v_full + stage * 8, kLoadBytes);
                 __syncwarp();
                 if (PAGED) {
-                    if (lane < 16) {
+                    if (lane < 8 * kHalves) {
                         const int half = lane >> 3;
                         tma_load_4d(v_smem + stage * kTileBytes + half * kHalfTileBytes + (lane & 7) * kPageBytes, &v_map,
                                     bar_v_full + stage * 8, half * 64, item.kv_head, 0, page);
                     }
                 } else if (lane == 0) {
                     tma_load_3d(v_smem + stage * kTileBytes, &v_map, bar_v_full + stage * 8, 0, item.kv_head, row0);
-                    tma_load_3d(v_smem + stage * kTileBytes + kHalfTileBytes, &v_map, bar_v_full + stage * 8, 64,
-                                item.kv_head, row0);
+                    if (kHalves == 2) {
+                        tma_load_3d(v_smem + stage * kTileBytes + kHalfTileBytes, &v_map, bar_v_full + stage * 8, 64,
+                                    item.kv_head, row0);
+                    }
                 }
             }
         }
     } else if (warp == 8) {
         // ---------------- MMA issuer ----------------
-        constexpr uint32_t kIdescQK = make_instr_desc(kTile, kTile, true, 0, 0);      // A, B K-major
-        constexpr uint32_t kIdescPV = make_instr_desc(kTile, kHeadDim, true, 0, 1);   // B (V) MN-major
+        constexpr bool kIsBf16 = std::is_same<T, __nv_bfloat16>::value;
+        constexpr uint32_t kIdescQK = make_instr_desc(kTile, kTile, kIsBf16, 0, 0);      // A, B K-major
+        constexpr uint32_t kIdescPV = make_instr_desc(kTile, HD, kIsBf16, 0, 1);   // B (V) MN-major
         auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {
             return __all_sync(0xffffffffu, mbar_wait(bar, parity) ? 1 : 0) != 0;
         };
@@ -497,7 +529,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                 const uint32_t q_tile = q_smem + x * kTileBytes;
                 const uint32_t k_tile = k_smem + stage * kTileBytes;
 #pragma unroll
-                for (int ks = 0; ks < kHeadDim / 16; ++ks) {
+                for (int ks = 0; ks < HD / 16; ++ks) {
                     const uint32_t within = (ks >> 2) * kHalfTileBytes + (ks & 3) * 32;
                     umma_ss(tmem_base + x * kTile, make_smem_desc(q_tile + within, 16, 1024),
                             make_smem_desc(k_tile + within, 16, 1024), kIdescQK, ks > 0 ? 1u : 0u);
@@ -514,7 +546,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                 const uint32_t v_tile = v_smem + stage * kTileBytes;
 #pragma unroll
                 for (int ks = 0; ks < kTile / 16; ++ks) {
-                    umma_ts(tmem_base + 2 * kTile + x * kHeadDim, tmem_base + x * kTile + ks * 8,
+                    umma_ts(tmem_base + 2 * kTile + x * HD, tmem_base + x * kTile + ks * 8,
                             make_smem_desc(v_tile + ks * 2048, kHalfTileBytes, 1024), kIdescPV,
                             (accumulate || ks > 0) ? 1u : 0u);
                 }
@@ -624,7 +656,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         const int local_row = quarter * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t tmem_s = tmem_base + x * kTile + lane_base;
-        const uint32_t tmem_o = tmem_base + 2 * kTile + x * kHeadDim + lane_base;
+        const uint32_t tmem_o = tmem_base + 2 * kTile + x * HD + lane_base;
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
         const float sign = p.scale_log2 < 0.0f ? -1.0f : 1.0f;
         int s_uses = 0;   // score tiles consumed so far, over all items
@@ -640,14 +672,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             const int row = item.q0 + x * kTile + local_row;    // sequence-local query index
             const bool real = row < item.len_q;
             const size_t token = static_cast<size_t>(item.offset) + (real ? row : 0);
-            __nv_bfloat16 *dst = p.out + (token * p.heads + item.head) * kHeadDim;
+            T *dst = static_cast<T *>(p.out) + (token * p.heads + item.head) * HD;
             const int my_tiles = x == 0 ? item.tiles[0] : item.tiles[1];
             if (my_tiles == 0) {
                 // No key is visible to this tile's rows: zeros and LSE -1e20.
                 if (real) {
 #pragma unroll
-                    for (int i = 0; i < kHeadDim / 8; ++i) reinterpret_cast<uint4 *>(dst)[i] = make_uint4(0u, 0u, 0u, 0u);
-                    p.lse[token * p.heads + item.head] = -1.0e20f;
+                    for (int i = 0; i < HD / 8; ++i) reinterpret_cast<uint4 *>(dst)[i] = make_uint4(0u, 0u, 0u, 0u);
+                    *lse_at(item, row) = -1.0e20f;
                 }
                 continue;
             }
@@ -677,7 +709,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                         if (j > 0) {
                             const float factor = exp2_approx(base_log2 - wanted);
                             row_sum *= factor;
-                            scale_o_row(tmem_o, factor);
+                            scale_o_row<HD>(tmem_o, factor);
                         }
                         base_log2 = wanted;
                     }
@@ -687,14 +719,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                     const float factor = __int_as_float((127 - exponent) << 23);
                     row_sum *= factor;
                     base_log2 += static_cast<float>(exponent);
-                    scale_o_row(tmem_o, factor);
+                    scale_o_row<HD>(tmem_o, factor);
                 }
                 const float2 bias2 = make_float2(-base_log2, -base_log2);
                 float2 sum[2] = {make_float2(row_sum, 0.0f), make_float2(0.0f, 0.0f)};
                 if (partial) {
-                    tile_exp<true>(tmem_s, scale2, bias2, limit, sum);
+                    tile_exp<T, true>(tmem_s, scale2, bias2, limit, sum);
                 } else {
-                    tile_exp<false>(tmem_s, scale2, bias2, limit, sum);
+                    tile_exp<T, false>(tmem_s, scale2, bias2, limit, sum);
                 }
                 row_sum = (sum[0].x + sum[0].y) + (sum[1].x + sum[1].y);
                 tmem_wait_st();
@@ -716,11 +748,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             const bool empty = row_sum == 0.0f;
             const float inverse = empty ? 0.0f : 1.0f / row_sum;
 #pragma unroll 1
-            for (int c = 0; c < kHeadDim; c += 32) {
+            for (int c = 0; c < HD; c += 32) {
                 uint32_t r[32];
                 tmem_ld_x32(tmem_o + c, r);
                 tmem_wait_ld_into(r);
-                if (c + 32 == kHeadDim) {
+                if (c + 32 == HD) {
                     // O is out of tensor memory: the next item's first P V may overwrite it
                     tcgen05_fence_before();
                     __syncwarp();
@@ -730,10 +762,10 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint4 word;
-                        word.x = pack2<__nv_bfloat16>(__uint_as_float(r[i]) * inverse, __uint_as_float(r[i + 1]) * inverse);
-                        word.y = pack2<__nv_bfloat16>(__uint_as_float(r[i + 2]) * inverse, __uint_as_float(r[i + 3]) * inverse);
-                        word.z = pack2<__nv_bfloat16>(__uint_as_float(r[i + 4]) * inverse, __uint_as_float(r[i + 5]) * inverse);
-                        word.w = pack2<__nv_bfloat16>(__uint_as_float(r[i + 6]) * inverse, __uint_as_float(r[i + 7]) * inverse);
+                        word.x = pack2<T>(__uint_as_float(r[i]) * inverse, __uint_as_float(r[i + 1]) * inverse);
+                        word.y = pack2<T>(__uint_as_float(r[i + 2]) * inverse, __uint_as_float(r[i + 3]) * inverse);
+                        word.z = pack2<T>(__uint_as_float(r[i + 4]) * inverse, __uint_as_float(r[i + 5]) * inverse);
+                        word.w = pack2<T>(__uint_as_float(r[i + 6]) * inverse, __uint_as_float(r[i + 7]) * inverse);
                         if (empty) word = make_uint4(0u, 0u, 0u, 0u);
                         *reinterpret_cast<uint4 *>(dst + c + i) = word;
                     }
@@ -745,13 +777,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                     value = __int_as_float(0x7fc00000);  // has the second launch redo the item
                     atomicExch(&g_out_of_range_seen, 1u);
                 }
-                p.lse[token * p.heads + item.head] = value;
+                *lse_at(item, row) = value;
             }
         }
     }
     if (failed && lane == 0) {
         report_status(p.error, kStatusWaitTimeout);
     }
+    if (failed) linger_after_timeout();
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 8) {
@@ -770,24 +803,27 @@ bool prefill_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t to
     if (total_query_tokens / kPair + 1 > kMaxRankTiles) return false;
     const uintptr_t all = reinterpret_cast<uintptr_t>(query) | reinterpret_cast<uintptr_t>(key) |
                           reinterpret_cast<uintptr_t>(value) | reinterpret_cast<uintptr_t>(out);
-    return head_dim == kHeadDim && heads % kv_heads == 0 && heads <= 65535 && (all & 15u) == 0;
+    return (head_dim == 128 || head_dim == 64) && heads % kv_heads == 0 && heads <= 65535 && (all & 15u) == 0;
 }
 
 namespace {
 
-template <bool PAGED>
+template <typename T, int HD, bool PAGED>
 int launch_prefill(cudaStream_t stream, const CUtensorMap &q_map, const CUtensorMap &k_map, const CUtensorMap &v_map,
                    const PrefillParams &params, unsigned persistent) {
-    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<false, PAGED>,
+    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<T, HD, true, PAGED>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
-    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<true, PAGED>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
-    prefill_tcgen05_kernel<false, PAGED><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map,
-                                                                                                params);
-    SINGE_TRY(launch_status());
-    // Redo pass over the same shares: a no-op while the device's out-of-range flag has never been raised.
-    prefill_tcgen05_kernel<true, PAGED><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map,
-                                                                                               params);
+    if (std::is_same<T, __nv_bfloat16>::value) {
+        SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<__nv_bfloat16, HD, false, PAGED>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
+        prefill_tcgen05_kernel<__nv_bfloat16, HD, false, PAGED>
+            <<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
+        SINGE_TRY(launch_status());
+    }
+    // bf16: the redo pass over the same shares, a no-op while the device's out-of-range flag has never been raised.
+    // f16 (params.exact): the only pass.  P must stay below 65504 there, so every tile takes its exact row maximum.
+    prefill_tcgen05_kernel<T, HD, true, PAGED><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map,
+                                                                                                  params);
     return launch_status();
 }
 
@@ -795,47 +831,54 @@ int launch_prefill(cudaStream_t stream, const CUtensorMap &q_map, const CUtensor
 
 // Packed queries over packed keys/values (block_table == nullptr: key/value are [total_kv_tokens, kv_heads, 128]) or
 // over a paged cache (key/value are [cache_pages, 16, kv_heads, 128], rows of block_table [batch, table_stride] list
-// each sequence's pages).
-int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void *query, const void *key,
-                         const void *value, const int32_t *lens_q, const int32_t *lens_kv, const int32_t *offsets,
-                         size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads,
-                         size_t kv_heads, size_t head_dim, int causal, float scale, const uint32_t *block_table,
-                         size_t table_stride, size_t cache_pages) {
-    if (head_dim != kHeadDim) return SINGE_ERR_UNSUPPORTED_WIDTH;
+// each sequence's pages).  lens_q == nullptr selects the dense form: `uniform_q` queries and `uniform_kv` keys per
+// sequence, back to back, and an LSE laid out [batch, heads, uniform_q].  is_f16: IEEE half instead of bf16.
+int prefill_tcgen05(cudaStream_t stream, bool is_f16, void *out, float *lse, const void *query, const void *key,
+                    const void *value, const int32_t *lens_q, const int32_t *lens_kv, const int32_t *offsets,
+                    size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads, size_t kv_heads,
+                    size_t head_dim, int causal, float scale, const uint32_t *block_table, size_t table_stride,
+                    size_t cache_pages, size_t uniform_q, size_t uniform_kv) {
+    if (head_dim != 128 && head_dim != 64) return SINGE_ERR_UNSUPPORTED_WIDTH;
+    const uint64_t kHeadDim = head_dim;
     int device = 0, sms = 0;
     SINGE_CUDA_TRY(cudaGetDevice(&device));
     SINGE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     const bool paged = block_table != nullptr;
+    const CUtensorMapDataType type = is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     CUtensorMap q_map, k_map, v_map;
     const uint32_t box[3] = {64, 1, kTile};
     {
         const uint64_t dims[3] = {kHeadDim, heads, total_query_tokens};
         const uint64_t strides[2] = {kHeadDim * 2, kHeadDim * 2 * heads};
-        SINGE_TRY(encode_tensor_map(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, query, dims, strides, box,
-                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+        SINGE_TRY(encode_tensor_map(&q_map, type, 3, query, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
     }
     if (paged) {
         const uint64_t dims[4] = {kHeadDim, kv_heads, kPageTokens, cache_pages};
         const uint64_t strides[3] = {kHeadDim * 2, kHeadDim * 2 * kv_heads, kHeadDim * 2 * kv_heads * kPageTokens};
         const uint32_t page_box[4] = {64, 1, kPageTokens, 1};
-        SINGE_TRY(encode_tensor_map(&k_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, key, dims, strides, page_box,
-                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
-        SINGE_TRY(encode_tensor_map(&v_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, value, dims, strides, page_box,
-                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+        SINGE_TRY(encode_tensor_map(&k_map, type, 4, key, dims, strides, page_box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+        SINGE_TRY(encode_tensor_map(&v_map, type, 4, value, dims, strides, page_box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
     } else {
         const uint64_t dims[3] = {kHeadDim, kv_heads, total_kv_tokens};
         const uint64_t strides[2] = {kHeadDim * 2, kHeadDim * 2 * kv_heads};
-        SINGE_TRY(encode_tensor_map(&k_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, key, dims, strides, box,
-                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
-        SINGE_TRY(encode_tensor_map(&v_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, value, dims, strides, box,
-                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+        SINGE_TRY(encode_tensor_map(&k_map, type, 3, key, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+        SINGE_TRY(encode_tensor_map(&v_map, type, 3, value, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
     }
     PrefillParams params;
-    params.out = static_cast<__nv_bfloat16 *>(out);
+    params.out = out;
     params.lse = lse;
     params.lens_q = lens_q;
     params.lens_kv = lens_kv;
     params.offsets = offsets;
+    params.uniform_q = static_cast<int>(uniform_q);
+    params.uniform_kv = static_cast<int>(uniform_kv);
+    params.lse_rows = lens_q == nullptr ? static_cast<int>(uniform_q) : 0;
+    params.exact = is_f16 ? 1 : 0;
     params.batch = static_cast<int>(batch);
     params.heads = static_cast<int>(heads);
     params.kv_heads = static_cast<int>(kv_heads);
@@ -852,8 +895,30 @@ int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void 
     if (items > 0x7fffffffull) return SINGE_ERR_LENGTH_EXCEEDS_I32;
     if (items == 0) return SINGE_OK;
     const unsigned persistent = static_cast<unsigned>(items < static_cast<size_t>(sms) ? items : sms);
-    return paged ? launch_prefill<true>(stream, q_map, k_map, v_map, params, persistent)
-                 : launch_prefill<false>(stream, q_map, k_map, v_map, params, persistent);
+    if (head_dim == 64) {
+        if (is_f16) {
+            return paged ? launch_prefill<__half, 64, true>(stream, q_map, k_map, v_map, params, persistent)
+                         : launch_prefill<__half, 64, false>(stream, q_map, k_map, v_map, params, persistent);
+        }
+        return paged ? launch_prefill<__nv_bfloat16, 64, true>(stream, q_map, k_map, v_map, params, persistent)
+                     : launch_prefill<__nv_bfloat16, 64, false>(stream, q_map, k_map, v_map, params, persistent);
+    }
+    if (is_f16) {
+        return paged ? launch_prefill<__half, 128, true>(stream, q_map, k_map, v_map, params, persistent)
+                     : launch_prefill<__half, 128, false>(stream, q_map, k_map, v_map, params, persistent);
+    }
+    return paged ? launch_prefill<__nv_bfloat16, 128, true>(stream, q_map, k_map, v_map, params, persistent)
+                 : launch_prefill<__nv_bfloat16, 128, false>(stream, q_map, k_map, v_map, params, persistent);
+}
+
+int prefill_tcgen05_bf16(cudaStream_t stream, void *out, float *lse, const void *query, const void *key,
+                         const void *value, const int32_t *lens_q, const int32_t *lens_kv, const int32_t *offsets,
+                         size_t batch, size_t total_query_tokens, size_t total_kv_tokens, size_t heads,
+                         size_t kv_heads, size_t head_dim, int causal, float scale, const uint32_t *block_table,
+                         size_t table_stride, size_t cache_pages) {
+    return prefill_tcgen05(stream, false, out, lse, query, key, value, lens_q, lens_kv, offsets, batch,
+                           total_query_tokens, total_kv_tokens, heads, kv_heads, head_dim, causal, scale, block_table,
+                           table_stride, cache_pages, 0, 0);
 }
 
 }  // namespace singe

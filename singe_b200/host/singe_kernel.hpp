@@ -239,6 +239,10 @@ struct MatmulConfig {
     size_t rows, columns, reduction, lhs_row_stride, rhs_row_stride, output_row_stride;
     bool transpose_lhs, transpose_rhs;
 
+    static MatmulConfig row_major(size_t rows, size_t columns, size_t reduction) {
+        return {rows, columns, reduction, reduction, columns, columns, false, false};
+    }
+
     static MatmulConfig row_major_transposed_rhs(size_t rows, size_t columns, size_t reduction) {
         return {rows, columns, reduction, reduction, reduction, columns, false, true};
     }
@@ -287,6 +291,20 @@ inline Error ragged_kv_prefill_attention_bf16(singe_stream_t stream, DeviceSlice
     SINGE_HOST_TRY(config.validate_lengths(out.len, lse.len, query.len, key.len, value.len, lens_q.len, lens_kv.len,
                                            offsets.len));
     return from_sys(singe_ragged_kv_prefill_attention_bf16(
+        stream, out.ptr, lse.ptr, query.ptr, key.ptr, value.ptr, lens_q.ptr, lens_kv.ptr, offsets.ptr, config.batch,
+        config.total_query_tokens, config.total_kv_tokens, config.heads, config.kv_heads, config.head_dim,
+        config.causal ? 1 : 0, config.scale));
+}
+
+// singe-kernel/src/cuda/attention/paged.rs:479-530
+inline Error ragged_kv_prefill_attention_f16(singe_stream_t stream, DeviceSlice<void> out, DeviceSlice<float> lse,
+                                            DeviceSlice<const void> query, DeviceSlice<const void> key,
+                                            DeviceSlice<const void> value, DeviceSlice<const int32_t> lens_q,
+                                            DeviceSlice<const int32_t> lens_kv, DeviceSlice<const int32_t> offsets,
+                                            const RaggedKvPrefillAttentionConfig &config) {
+    SINGE_HOST_TRY(config.validate_lengths(out.len, lse.len, query.len, key.len, value.len, lens_q.len, lens_kv.len,
+                                           offsets.len));
+    return from_sys(singe_ragged_kv_prefill_attention_f16(
         stream, out.ptr, lse.ptr, query.ptr, key.ptr, value.ptr, lens_q.ptr, lens_kv.ptr, offsets.ptr, config.batch,
         config.total_query_tokens, config.total_kv_tokens, config.heads, config.kv_heads, config.head_dim,
         config.causal ? 1 : 0, config.scale));

@@ -79,14 +79,18 @@ SIGNATURES = {
     "singe_attend_f32": [_p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _f, _i, _z, _f, _p],
     "singe_paged_kv_prefill_attention_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z,
                                               _i, _f],
+    "singe_paged_kv_prefill_attention_f16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z,
+                                             _i, _f],
     "singe_paged_kv_prefill_attention_f32": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z,
                                              _i, _f],
     "singe_ragged_kv_prefill_attention_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _i, _f],
+    "singe_ragged_kv_prefill_attention_f16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _i, _f],
     "singe_ragged_kv_prefill_attention_f32": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _i, _f],
     "singe_ragged_kv_prefill_attention_cache_write_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z,
                                                            _i, _f, _p, _p, _p, _p, _i, _z, _z, _p],
     "singe_fmha_prefill_lse_f32": [_p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _f, _i],
     "singe_fmha_prefill_lse_bf16": [_p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _f, _i],
+    "singe_fmha_prefill_lse_f16": [_p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _f, _i],
     "singe_scaled_dot_product_attention_f32": [_p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _f, _i, _z],
     "singe_matmul_bf16_bf16": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _i, _i],
     "singe_matmul_bf16_f32": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _i, _i],

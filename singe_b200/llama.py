@@ -291,6 +291,10 @@ def shard_layer_weights(full: dict, config: LlamaConfig, shard: Shard, interleav
     }
 
 
+# Largest tensor-parallel degree at which collective="peer" means the one-shot kernel.
+PEER_ONE_SHOT_UP_TO = 8
+
+
 class LlamaDecoder:
     """One rank of a tensor-parallel Llama decoder: weights, KV caches, page table and the decode step."""
 
@@ -372,9 +376,10 @@ class LlamaDecoder:
         if collective not in ("peer", "oneshot", "twophase", "pushall", "nccl"):
             raise ValueError("collective must be 'peer', 'oneshot', 'twophase', 'pushall' or 'nccl'")
         if collective == "peer":
-            # one-shot: every rank pulls all partial rows (little to pull with two ranks); two-phase: rows are
-            # reduced by their owners and pushed back
-            collective = "oneshot" if tp <= 2 else "twophase"
+            # one-shot: every rank pulls all partial rows; two-phase: rows are reduced by their owners and pushed
+            # back.  Measured on B200 / NVSwitch at 64 rows x 4096: one-shot is ahead with two ranks (4.28 against
+            # 4.48 ms per step) and level with four (3.29 / 3.29), so it stays the pick until more ranks change that.
+            collective = "oneshot" if tp <= PEER_ONE_SHOT_UP_TO else "twophase"
         self.collective = collective
         self.peer = None
         if tp > 1 and collective == "oneshot":

@@ -153,6 +153,11 @@ class MatmulConfig:
     transpose_rhs: bool
 
     @classmethod
+    def row_major(cls, rows, columns, reduction):
+        """lhs [M, K], rhs [K, N] (:190-202)."""
+        return cls(rows, columns, reduction, reduction, columns, columns, False, False)
+
+    @classmethod
     def row_major_transposed_rhs(cls, rows, columns, reduction):
         return cls(rows, columns, reduction, reduction, reduction, columns, False, True)
 

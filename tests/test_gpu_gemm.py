@@ -168,5 +168,47 @@ def test_matmul_validation_mirrors_the_reference():
     assert lib.singe_matmul_bf16_bf16(None, one, one, one, 4, 4, 8, 4, 8, 4, 0, 1) == ks.ERR_INVALID_LENGTH  # lhs stride < k
     assert lib.singe_matmul_bf16_bf16(None, one, one, one, 4, 4, 8, 8, 8, 2, 0, 1) == ks.ERR_INVALID_LENGTH  # out stride < n
     assert lib.singe_matmul_bf16_bf16(None, None, one, one, 4, 4, 8, 8, 8, 4, 0, 1) == ks.ERR_NULL_POINTER
-    # layouts outside the linear-layer form are refused, not silently mis-computed
-    assert lib.singe_matmul_bf16_bf16(None, one, one, one, 8, 8, 8, 8, 8, 8, 0, 0) == ks.ERR_UNSUPPORTED_CONFIGURATION
+    # a transposed left operand is refused, not silently mis-computed
+    assert lib.singe_matmul_bf16_bf16(None, one, one, one, 8, 8, 8, 8, 8, 8, 1, 1) == ks.ERR_UNSUPPORTED_CONFIGURATION
+    assert lib.singe_matmul_bf16_bf16(None, one, one, one, 8, 8, 8, 8, 4, 8, 0, 0) == ks.ERR_INVALID_LENGTH  # [K, N] rhs stride < n
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(1, 256, 512, 0), (64, 4096, 1024, 0), (200, 136, 72, 0), (256, 384, 4096, 0),
+                                          (129, 1000, 520, 0), (16, 264, 2048, 4), (300, 4096, 256, 0)])
+def test_row_major_right_operand_matches_the_oracle(m, n, k, splits):
+    # rhs stored [K, N] (MatmulConfig::row_major, transpose_rhs false): tiles are staged N-contiguous and the tensor
+    # core reads them MN-major.  The same numbers as the [N, K] call on the transposed copy, bit for bit.
+    x, w = _case(m, n, k, seed=9)
+    w_kn = w.t().contiguous()
+    lib = ks.lib()
+    assert lib.singe_matmul_set_splits(splits) == ks.OK
+    try:
+        y32 = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        ops.matmul_bf16(y32, x, w_kn, ops.MatmulConfig.row_major(m, n, k))
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        ops.matmul_bf16(y, x, w_kn, ops.MatmulConfig.row_major(m, n, k))
+        twin = torch.empty_like(y32)
+        ops.matmul_bf16(twin, x, w, ops.MatmulConfig.row_major_transposed_rhs(m, n, k))
+        torch.cuda.synchronize()
+    finally:
+        assert lib.singe_matmul_set_splits(0) == ks.OK
+    assert ops.take_device_error() == 0
+    ref = oracle.linear_bf16_f32(_bits(x), _bits(w), m=m, n=n, k=k)
+    assert_close_bf16(host(y32), ref, f"matmul [K,N] rhs {m}x{n}x{k}")
+    assert_close_bf16(host(y), oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(ref)), f"bf16 out {m}x{n}x{k}")
+    scale = np.abs(ref).max() + 1e-6
+    assert np.abs(host(y32) - ref).max() / scale < 2e-3
+
+
+def test_row_major_right_operand_with_strides():
+    m, n, k = 96, 160, 192
+    x, w = _case(m, n, k, seed=11)
+    wide = torch.zeros((k, n + 40), dtype=torch.bfloat16, device="cuda")
+    wide[:, 8:8 + n] = w.t()
+    rhs = wide[:, 8:8 + n]                  # row stride n + 40, 16-byte aligned start
+    out = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    ops.matmul_bf16(out, x, rhs, ops.MatmulConfig(m, n, k, k, rhs.stride(0), n, False, False))
+    torch.cuda.synchronize()
+    assert ops.take_device_error() == 0
+    ref = oracle.linear_bf16_f32(_bits(x), _bits(w), m=m, n=n, k=k)
+    assert_close_bf16(host(out), ref, "strided [K,N] rhs")

@@ -185,10 +185,16 @@ constexpr int decode_smem_bytes() {
 // rows into the cache for later steps and folds the new key into its online softmax as one more key; every CTA
 // rotates its own queries.  No rotary / cache-write kernel precedes the launch, so nothing this kernel streams from
 // the cache is written by the kernel before it, and with stable paging every page may be requested ahead of the wait.
-template <typename T, int HD, bool RAGGED, bool FUSED = false>
+// EXTRAS compiles in what only a decode step asks for (reads ahead of the dependency wait, the early release of a
+// one-wave grid, L2 warming, the rotation of the queries, the in-kernel fold); without it the classic form is the plain
+// drop-in kernel and carries none of their registers or branches (they cost it 2 us of 58 on the bench workload).
+// SOFTCAP (ragged form): tanh-capped scores.
+template <typename T, int HD, bool RAGGED, bool FUSED = false, bool EXTRAS = false, bool SOFTCAP = false>
 __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, const CUtensorMap &v_map,
                                                   const DecodeParams &p, const RaggedDecode &ragged) {
     static_assert(!(RAGGED && FUSED), "the fused step form is a classic-form kernel");
+    static_assert(!FUSED || EXTRAS, "the fused step form is a decode-step kernel");
+    static_assert(!(RAGGED && EXTRAS) && !(SOFTCAP && !RAGGED), "extras: classic form; softcap: ragged form");
     constexpr int NHALF = HD / 64;
     constexpr int KSTEPS = HD / 16;
     constexpr int NTILES = HD / 8;
@@ -196,13 +202,13 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
 
     // The queries (and, in a decode step, the newest K/V rows) come from the kernel before.  No global write of this
     // kernel -- outputs, split partials -- may move above a thread's wait: an earlier kernel may still read them.
-    const bool stable = !RAGGED && p.stable_paging != 0;
-    if (!RAGGED && threadIdx.x < 32) {
+    const bool stable = EXTRAS && p.stable_paging != 0;
+    if (EXTRAS && threadIdx.x < 32) {
         warm_l2(p.warm, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
                 gridDim.x * gridDim.y * gridDim.z, threadIdx.x);
     }
     if (!stable) grid_dependency_wait();
-    if (!RAGGED && p.early_release) grid_launch_dependents();
+    if (EXTRAS && p.early_release) grid_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -254,7 +260,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
             qa[ks][0] = row < p.group ? q32[ks * 8 + quad] : 0u;
             qa[ks][1] = row < p.group ? q32[ks * 8 + 4 + quad] : 0u;
         }
-        if (!RAGGED && p.rope_cos != nullptr) rotate_query_fragments<T, HD>(qa, p, b, row, quad);
+        if (EXTRAS && p.rope_cos != nullptr) rotate_query_fragments<T, HD>(qa, p, b, row, quad);
     }
     // The barriers are set up while the query reads are in flight.
     if (tid == 0) {
@@ -461,7 +467,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
             }
             // Row `row` of this lane: keys t0, t0+1 (tile 0) and t0+8, t0+9 (tile 1).
             const int t0 = tok_begin + i * kPageTokens + quad * 2;
-            if (RAGGED && ragged.softcap > 0.0f) {
+            if (SOFTCAP) {
                 // AttentionOptions::softcap: cap * tanh(scaled score / cap), then into the base-2 domain
                 const float inward = p.scale_log2 * 0.6931471805599453f / ragged.softcap;
                 const float outward = ragged.softcap * 1.4426950408889634f;
@@ -510,7 +516,6 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         if (failed && lane == 0) {
             report_status(p.status, kStatusWaitTimeout);
         }
-        if (failed) linger_after_timeout();   // before this warp's first stage is reused as its merge buffer
         if (FUSED && adds_new && warp == 0) {
             // ---- the key and value this step adds: rotate K, put both rows into the cache, attend the new key ----
             const T *projections = static_cast<const T *>(p.qkv) + static_cast<size_t>(b) * p.qkv_stride;
@@ -627,7 +632,10 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
             }
         }
     }
-    if (RAGGED || p.tickets == nullptr || direct || p.partials_only) return;
+    // A warp whose wait ran out (status 2 is set, the row's result is void) keeps the CTA alive until copies that were
+    // issued into its shared memory have landed.
+    if (failed) linger_after_timeout();
+    if (!EXTRAS || p.tickets == nullptr || direct || p.partials_only) return;
     // ---------------- the last split of the row to finish folds the row ----------------
     // Every split of a (sequence, KV head) row takes a ticket once its partials are written and visible; the one
     // that draws the last ticket reads all of them back (through L2: they were written by other SMs) and writes the
@@ -677,6 +685,21 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     paged_decode_body<T, HD, false>(k_map, v_map, p, none);
 }
 
+// The classic form with the decode step's extras (see paged_decode_body).
+template <typename T, int HD>
+__global__ void __launch_bounds__(kDecodeThreads, 3)
+    paged_decode_step_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                             const DecodeParams p) {
+    RaggedDecode none;  // never read by the classic form
+    none.pages = nullptr;
+    none.first = nullptr;
+    none.control = nullptr;
+    none.index_width = 4;
+    none.lse_out = nullptr;
+    none.softcap = 0.0f;
+    paged_decode_body<T, HD, false, false, true>(k_map, v_map, p, none);
+}
+
 template <typename T, int HD>
 __global__ void __launch_bounds__(kDecodeThreads, 3)
     paged_decode_fused_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
@@ -688,14 +711,14 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     none.index_width = 4;
     none.lse_out = nullptr;
     none.softcap = 0.0f;
-    paged_decode_body<T, HD, false, true>(k_map, v_map, p, none);
+    paged_decode_body<T, HD, false, true, true>(k_map, v_map, p, none);
 }
 
-template <typename T, int HD>
+template <typename T, int HD, bool SOFTCAP>
 __global__ void __launch_bounds__(kDecodeThreads, 3)
     paged_decode_ragged_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                                const DecodeParams p, const RaggedDecode ragged) {
-    paged_decode_body<T, HD, true>(k_map, v_map, p, ragged);
+    paged_decode_body<T, HD, true, false, false, SOFTCAP>(k_map, v_map, p, ragged);
 }
 
 // Folds the split partials of every (sequence, head) row that needed more than one split.
@@ -745,11 +768,24 @@ int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedD
     static int configured[kMaxDevices] = {0};  // one table per instantiation, one entry per device
     constexpr int smem = decode_smem_bytes<HD>();
     const bool fused = !RAGGED && params.qkv != nullptr;
+    const bool capped = RAGGED && shape.softcap > 0.0f;
+    // the plain drop-in call takes the kernel without the decode step's extras
+    const bool extras = !RAGGED && !fused &&
+                        (params.stable_paging != 0 || params.early_release != 0 || params.warm.bytes != 0 ||
+                         params.rope_cos != nullptr || params.tickets != nullptr);
     if (RAGGED) {
-        SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_ragged_kernel<T, HD>, smem, configured));
+        static int configured_capped[kMaxDevices] = {0};
+        if (capped) {
+            SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_ragged_kernel<T, HD, true>, smem, configured_capped));
+        } else {
+            SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_ragged_kernel<T, HD, false>, smem, configured));
+        }
     } else if (fused) {
         static int configured_fused[kMaxDevices] = {0};
         SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_fused_kernel<T, HD>, smem, configured_fused));
+    } else if (extras) {
+        static int configured_step[kMaxDevices] = {0};
+        SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_step_kernel<T, HD>, smem, configured_step));
     } else {
         SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_kernel<T, HD>, smem, configured));
     }
@@ -767,11 +803,17 @@ int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedD
     // KV heads vary fastest: the CTAs that read the interleaved rows of the same cache pages start together.
     dim3 grid(static_cast<unsigned>(params.kv_heads), static_cast<unsigned>(params.max_splits),
               static_cast<unsigned>(batch));
-    if (RAGGED) {
-        SINGE_CUDA_TRY(launch_dependent(paged_decode_ragged_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,
-                                        kLaunchDecode, 1, k_map, v_map, params, shape));
+    if (RAGGED && capped) {
+        SINGE_CUDA_TRY(launch_dependent(paged_decode_ragged_kernel<T, HD, true>, grid, dim3(kDecodeThreads), smem,
+                                        stream, kLaunchDecode, 1, k_map, v_map, params, shape));
+    } else if (RAGGED) {
+        SINGE_CUDA_TRY(launch_dependent(paged_decode_ragged_kernel<T, HD, false>, grid, dim3(kDecodeThreads), smem,
+                                        stream, kLaunchDecode, 1, k_map, v_map, params, shape));
     } else if (fused) {
         SINGE_CUDA_TRY(launch_dependent(paged_decode_fused_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,
+                                        kLaunchDecode, 1, k_map, v_map, params));
+    } else if (extras) {
+        SINGE_CUDA_TRY(launch_dependent(paged_decode_step_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,
                                         kLaunchDecode, 1, k_map, v_map, params));
     } else {
         SINGE_CUDA_TRY(launch_dependent(paged_decode_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,

@@ -673,13 +673,14 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
             const bool real = row < item.len_q;
             const size_t token = static_cast<size_t>(item.offset) + (real ? row : 0);
             T *dst = static_cast<T *>(p.out) + (token * p.heads + item.head) * HD;
+            float *lse_row = lse_at(item, real ? row : 0);
             const int my_tiles = x == 0 ? item.tiles[0] : item.tiles[1];
             if (my_tiles == 0) {
                 // No key is visible to this tile's rows: zeros and LSE -1e20.
                 if (real) {
 #pragma unroll
                     for (int i = 0; i < HD / 8; ++i) reinterpret_cast<uint4 *>(dst)[i] = make_uint4(0u, 0u, 0u, 0u);
-                    *lse_at(item, row) = -1.0e20f;
+                    *lse_row = -1.0e20f;
                 }
                 continue;
             }
@@ -777,7 +778,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                     value = __int_as_float(0x7fc00000);  // has the second launch redo the item
                     atomicExch(&g_out_of_range_seen, 1u);
                 }
-                *lse_at(item, row) = value;
+                *lse_row = value;
             }
         }
     }

@@ -296,12 +296,16 @@ __global__ void check_paged_values_kernel(const Index *query_offsets, const Inde
 // token b, every paging value is valid) and, if so, turns the paging tensors into what the tiled decode kernel
 // reads: lens[b], first[b] (index of the sequence's first page) and the tokens per split for `split_budget` splits
 // of the longest sequence.  control[0] = 0 hands the call to the tiled kernel, 1 to the general kernel.
+// A sliding window (window > 0: the query at position keys - 1 sees keys >= keys - window) skips whole pages here:
+// first[b] moves to the page that holds the first visible key, lens[b] counts from that page's start and hidden[b]
+// (0 .. page_size - 1) is the number of keys at the front of that page the window still hides.
 template <typename Index>
 __device__ __forceinline__ void plan_paged_decode_body(const Index *query_offsets, const Index *page_offsets,
                                                        const Index *pages, const Index *last_page_lengths,
                                                        int sequences, long long cache_pages, long long table_len,
                                                        long long page_size, int split_budget, int min_piece,
-                                                       int *lens, long long *first, int *control) {
+                                                       int *lens, long long *first, int *control, long long window,
+                                                       int *hidden) {
     __shared__ int shared_bad;
     __shared__ int shared_longest;
     if (threadIdx.x == 0) {
@@ -323,8 +327,17 @@ __device__ __forceinline__ void plan_paged_decode_body(const Index *query_offset
             keys = (pl - pf - 1) * page_size + last;
             if (keys > 0x7ffffff0ll) bad = 1;
         }
+        long long skipped = 0;   // whole pages in front of the window
+        if (window > 0 && !bad) {
+            const long long lowest = keys > window ? keys - window : 0;
+            skipped = lowest / page_size;
+            hidden[s] = static_cast<int>(lowest - skipped * page_size);
+            keys -= skipped * page_size;
+        } else if (window > 0) {
+            hidden[s] = 0;
+        }
         lens[s] = bad ? 0 : static_cast<int>(keys);
-        first[s] = bad ? 0 : pf;
+        first[s] = bad ? 0 : pf + skipped;
         longest = max(longest, bad ? 0 : static_cast<int>(keys));
     }
     // every page id the table holds must address the cache (the general kernel skips the rows of a bad one)
@@ -350,9 +363,9 @@ template <typename Index>
 __global__ void plan_paged_decode_kernel(const Index *query_offsets, const Index *page_offsets, const Index *pages,
                                          const Index *last_page_lengths, int sequences, long long cache_pages,
                                          long long table_len, long long page_size, int split_budget, int min_piece,
-                                         int *lens, long long *first, int *control) {
+                                         int *lens, long long *first, int *control, long long window, int *hidden) {
     plan_paged_decode_body<Index>(query_offsets, page_offsets, pages, last_page_lengths, sequences, cache_pages,
-                                  table_len, page_size, split_budget, min_piece, lens, first, control);
+                                  table_len, page_size, split_budget, min_piece, lens, first, control, window, hidden);
 }
 
 // Both of the above in one launch: the last block plans, the others check (one launch gap fewer per call).
@@ -361,10 +374,11 @@ __global__ void check_and_plan_kernel(const Index *query_offsets, const Index *p
                                       const Index *last_page_lengths, int sequences, long long tokens,
                                       long long cache_pages, long long table_len, long long page_size,
                                       uint32_t *status, int split_budget, int min_piece, int *lens, long long *first,
-                                      int *control) {
+                                      int *control, long long window, int *hidden) {
     if (blockIdx.x == gridDim.x - 1) {
         plan_paged_decode_body<Index>(query_offsets, page_offsets, pages, last_page_lengths, sequences, cache_pages,
-                                      table_len, page_size, split_budget, min_piece, lens, first, control);
+                                      table_len, page_size, split_budget, min_piece, lens, first, control, window,
+                                      hidden);
     } else {
         check_paged_values_body<Index>(query_offsets, page_offsets, pages, last_page_lengths, sequences, tokens,
                                        cache_pages, table_len, page_size, status, blockIdx.x, gridDim.x - 1);
@@ -620,16 +634,17 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
             policy.tokens, policy.cache_pages, policy.table_len, static_cast<long long>(page_size), status);
         return launch_status();
     };
-    // One query token per sequence, no window: possibly a plain decode batch.  Whether it is one depends on the
+    // One query token per sequence: possibly a plain decode batch (with or without a sliding window).  Whether it is one depends on the
     // paging tensors, which live on the device, so a planning kernel decides there: it either hands the call to
     // the tiled flash-decode kernel (and the general kernel below finds nothing to do) or leaves it to the general
     // kernel (and the tiled kernel's CTAs leave at once).
     constexpr bool kHalfType = sizeof(T) == 2;
-    if (kHalfType && tokens == sequences && window == 0 && sequences <= 65535 &&
+    if (kHalfType && tokens == sequences && sequences <= 65535 &&
         paged_decode_fast_path(heads, kv_heads, head_dim, page_size, key_cache, value_cache, query)) {
         // split budget: ~512-key splits of a sequence twice the average length (the real lengths are device data)
         const size_t average = table_len * page_size / sequences;
         size_t guess = 2 * average;
+        if (window > 0 && guess > window + page_size) guess = window + page_size;  // what a window leaves of a sequence
         if (guess < page_size) guess = page_size;
         const size_t splits = default_splits(sequences, kv_heads, guess);
         // pieces of at least 512 keys when that still gives the machine enough CTAs (what default_splits assumes)
@@ -638,7 +653,7 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
                                   : 128;
         const size_t rows = tokens * heads * splits;
         const size_t partial_floats = rows * (head_dim + 1);
-        const size_t plan_floats = 3 * sequences + 16;  // lens (int32), first (int64), control
+        const size_t plan_floats = 4 * sequences + 16;  // lens (int32), first (int64), control, hidden (int32)
         float *scratch = nullptr;
         const int grown = workspace_for(stream, partial_floats + plan_floats + 4, &scratch);
         if (grown == SINGE_OK) {
@@ -648,18 +663,21 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
             long long *first = reinterpret_cast<long long *>(plan_at);
             int *lens = reinterpret_cast<int *>(first + sequences);
             int *control = lens + sequences;
+            int *hidden = control + 8;
+            const long long window_keys = window > 0x7fffffffull ? 0x7fffffffll : static_cast<long long>(window);
             if (!checked) {
                 const unsigned blocks = static_cast<unsigned>((sequences + 7) / 8);  // eight warps, one sequence each
                 check_and_plan_kernel<Index><<<(blocks > 256 ? 256 : blocks) + 1, 256, 0, stream>>>(
                     policy.query_offsets, policy.page_offsets, policy.pages, policy.last_page_lengths,
                     policy.sequences, policy.tokens, policy.cache_pages, policy.table_len,
-                    static_cast<long long>(page_size), status, static_cast<int>(splits), min_piece, lens, first, control);
+                    static_cast<long long>(page_size), status, static_cast<int>(splits), min_piece, lens, first, control,
+                    window_keys, hidden);
                 checked = true;
             } else {
                 plan_paged_decode_kernel<Index><<<1, 256, 0, stream>>>(
                     policy.query_offsets, policy.page_offsets, policy.pages, policy.last_page_lengths,
                     policy.sequences, policy.cache_pages, policy.table_len, static_cast<long long>(page_size),
-                    static_cast<int>(splits), min_piece, lens, first, control);
+                    static_cast<int>(splits), min_piece, lens, first, control, window_keys, hidden);
             }
             SINGE_TRY(launch_status());
             RaggedDecode ragged;
@@ -669,6 +687,7 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
             ragged.index_width = static_cast<int>(sizeof(Index));
             ragged.lse_out = lse;
             ragged.softcap = softcap;
+            ragged.hidden = window > 0 ? hidden : nullptr;
             const int element = std::is_same<T, __nv_bfloat16>::value ? 0 : 1;
             SINGE_TRY(paged_decode_splitk(stream, element, out, scratch, scratch + rows * head_dim, query, key_cache,
                                           value_cache, lens, nullptr, sequences, heads, kv_heads, head_dim,

@@ -52,6 +52,8 @@ struct RaggedDecode {
     int index_width;           // 4 or 8
     float *lse_out;            // [tokens, heads] base-2 LSE
     float softcap;             // 0: none; else the scaled scores are capped as softcap * tanh(score / softcap)
+    const int *hidden;         // nullptr, or [sequences]: keys at the front of the sequence's first page that a sliding
+                               // window hides (the planning kernel has already dropped the whole pages before it)
 };
 
 // What the tiled decode kernel needs to rotate its queries itself (singe_rotary_paged_kv_decode_attention_bf16).

@@ -70,9 +70,9 @@ __device__ __forceinline__ float gated_value(float gate_acc, float up_acc) {
 // One 64-wide K slice of the B operand into shared memory (BN x 128 bytes either way).  [N, K] weights: one box of BN
 // rows x 64 K-elements.  [K, N] right operands: BN / 64 boxes of 64 K-rows x 64 N-elements, 8 KB apart, which the MMA
 // reads MN-major (leading byte offset 8 KB to the next 64 columns, 1 KB to the next eight K-rows, 2 KB per 16-wide k step).
-template <int BN>
-__device__ __forceinline__ void load_b_slice(uint32_t dst, const CUtensorMap *map, uint32_t bar, int k0, int n0, int rhs_kn) {
-    if (!rhs_kn) {
+template <int BN, bool KN>
+__device__ __forceinline__ void load_b_slice(uint32_t dst, const CUtensorMap *map, uint32_t bar, int k0, int n0) {
+    if (!KN) {
         tma_load_2d(dst, map, bar, k0, n0);
     } else {
 #pragma unroll
@@ -80,9 +80,9 @@ __device__ __forceinline__ void load_b_slice(uint32_t dst, const CUtensorMap *ma
     }
 }
 
-template <int BN>
-__device__ __forceinline__ void prefetch_b_slice(const CUtensorMap *map, int k0, int n0, int rhs_kn) {
-    if (!rhs_kn) {
+template <int BN, bool KN>
+__device__ __forceinline__ void prefetch_b_slice(const CUtensorMap *map, int k0, int n0) {
+    if (!KN) {
         tma_prefetch_2d(map, k0, n0);
     } else {
 #pragma unroll
@@ -90,9 +90,14 @@ __device__ __forceinline__ void prefetch_b_slice(const CUtensorMap *map, int k0,
     }
 }
 
-__device__ __forceinline__ uint64_t b_descriptor(uint32_t slice, int ks, int rhs_kn) {
-    return rhs_kn ? make_smem_desc(slice + ks * 2048, 8192, 1024) : make_smem_desc(slice, 16, 1024) + 2 * ks;
-}
+// How the MMA walks a B slice: the leading byte offset of the shared-memory descriptor and what one 16-wide k step
+// adds to its address field (16-byte units): 32 bytes along a K-major row, or sixteen 128-byte K-rows of an MN-major
+// tile.  The layout is a template argument of the kernels (KN), so the linear-layer form carries no trace of the other.
+template <bool KN>
+struct BWalk {
+    static constexpr uint32_t kLeadingBytes = KN ? 8192u : 16u;
+    static constexpr uint32_t kStep = KN ? 128u : 2u;
+};
 
 __device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tiles_n, int &tm, int &tn) {
     const int per_group = kGroupM * tiles_n;
@@ -107,13 +112,12 @@ __device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tile
 // KPS = 64-wide K slices per pipeline stage.  Skinny problems stream the weight matrix from HBM; with one
 // slice per stage every request touches 128 contiguous bytes of a weight row, which opens a DRAM page for two
 // bursts.  Several adjacent slices issued together give the memory controller 512-1024 contiguous bytes per row.
-template <int BN, int KPS>
+template <int BN, int KPS, bool KN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                      const GemmParams p) {
     constexpr uint32_t kTmemColumns = 2 * BN < 32 ? 32 : 2 * BN;
-    constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, 0, 0);
-    constexpr uint32_t kIdescKN = make_instr_desc(kBlockM, BN, true, 0, 1);  // B read MN-major
+    constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, 0, KN ? 1 : 0);  // KN: B read MN-major
     constexpr int kBBytes = BN * 128;
 
     grid_launch_dependents();
@@ -179,14 +183,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
-                        load_b_slice<BN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
-                                         tn * BN, p.rhs_kn);
+                        load_b_slice<BN, KN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
+                                         tn * BN);
                     }
                 }
                 const int last = min(p.k_blocks, preloaded + p.prefetch_blocks);
                 for (int kb = preloaded; kb < last; ++kb) {
 #pragma unroll
-                    for (int sub = 0; sub < KPS; ++sub) prefetch_b_slice<BN>(&b_map, (kb * KPS + sub) * kBlockK, tn * BN, p.rhs_kn);
+                    for (int sub = 0; sub < KPS; ++sub) prefetch_b_slice<BN, KN>(&b_map, (kb * KPS + sub) * kBlockK, tn * BN);
                 }
             }
         }
@@ -218,8 +222,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     if (!early) {
 #pragma unroll
                         for (int sub = 0; sub < KPS; ++sub) {
-                            load_b_slice<BN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full,
-                                             (kb * KPS + sub) * kBlockK, tn * BN, p.rhs_kn);
+                            load_b_slice<BN, KN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full,
+                                             (kb * KPS + sub) * kBlockK, tn * BN);
                         }
                     }
                 }
@@ -251,12 +255,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
                         const uint64_t a_desc = make_smem_desc(stage + sub * a_bytes, 16, 1024);
-                        const uint32_t b_slice = stage + KPS * a_bytes + sub * kBBytes;
+                        const uint64_t b_desc =
+                            make_smem_desc(stage + KPS * a_bytes + sub * kBBytes, BWalk<KN>::kLeadingBytes, 1024);
 #pragma unroll
                         for (int ks = 0; ks < kBlockK / 16; ++ks) {
-                            // 16 bf16 of K = 32 bytes = 2 descriptor address units
-                            umma_ss(tmem_d, a_desc + 2 * ks, b_descriptor(b_slice, ks, p.rhs_kn),
-                                    p.rhs_kn ? kIdescKN : kIdesc, (kb > 0 || sub > 0 || ks > 0) ? 1u : 0u);
+                            // 16 bf16 of K = 32 bytes = 2 descriptor address units of A
+                            umma_ss(tmem_d, a_desc + 2 * ks, b_desc + BWalk<KN>::kStep * ks, kIdesc,
+                                    (kb > 0 || sub > 0 || ks > 0) ? 1u : 0u);
                         }
                     }
                     tcgen05_commit(bar_empty + s * 8);
@@ -399,13 +404,12 @@ __device__ __forceinline__ void cluster_barrier() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-template <int BN, int KPS>
+template <int BN, int KPS, bool KN>
 __global__ void __launch_bounds__(kSplitKThreads, 1)
     gemm_splitk_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                        const GemmParams p) {
     constexpr uint32_t kTmemColumns = BN < 32 ? 32 : BN;
-    constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, 0, 0);
-    constexpr uint32_t kIdescKN = make_instr_desc(kBlockM, BN, true, 0, 1);  // B read MN-major
+    constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, 0, KN ? 1 : 0);  // KN: B read MN-major
     constexpr int kBBytes = BN * 128;
     constexpr int kQuads = BN / 4;  // float4 groups per row
 
@@ -476,14 +480,14 @@ __global__ void __launch_bounds__(kSplitKThreads, 1)
                     mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
-                        load_b_slice<BN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
-                                         tn * BN, p.rhs_kn);
+                        load_b_slice<BN, KN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
+                                         tn * BN);
                     }
                 }
                 const int last = min(kb_last, kb_first + preloaded + p.prefetch_blocks);
                 for (int kb = kb_first + preloaded; kb < last; ++kb) {
 #pragma unroll
-                    for (int sub = 0; sub < KPS; ++sub) prefetch_b_slice<BN>(&b_map, (kb * KPS + sub) * kBlockK, tn * BN, p.rhs_kn);
+                    for (int sub = 0; sub < KPS; ++sub) prefetch_b_slice<BN, KN>(&b_map, (kb * KPS + sub) * kBlockK, tn * BN);
                 }
             }
         }
@@ -511,8 +515,8 @@ __global__ void __launch_bounds__(kSplitKThreads, 1)
                 if (!early) {
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
-                        load_b_slice<BN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
-                                         tn * BN, p.rhs_kn);
+                        load_b_slice<BN, KN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
+                                         tn * BN);
                     }
                 }
             }
@@ -533,11 +537,12 @@ __global__ void __launch_bounds__(kSplitKThreads, 1)
 #pragma unroll
                 for (int sub = 0; sub < KPS; ++sub) {
                     const uint64_t a_desc = make_smem_desc(stage + sub * a_bytes, 16, 1024);
-                    const uint32_t b_slice = stage + KPS * a_bytes + sub * kBBytes;
+                    const uint64_t b_desc =
+                        make_smem_desc(stage + KPS * a_bytes + sub * kBBytes, BWalk<KN>::kLeadingBytes, 1024);
 #pragma unroll
                     for (int ks = 0; ks < kBlockK / 16; ++ks) {
-                        umma_ss(tmem_base, a_desc + 2 * ks, b_descriptor(b_slice, ks, p.rhs_kn),
-                                p.rhs_kn ? kIdescKN : kIdesc, (kb > kb_first || sub > 0 || ks > 0) ? 1u : 0u);
+                        umma_ss(tmem_base, a_desc + 2 * ks, b_desc + BWalk<KN>::kStep * ks, kIdesc,
+                                (kb > kb_first || sub > 0 || ks > 0) ? 1u : 0u);
                     }
                 }
                 tcgen05_commit(bar_empty + s * 8);
@@ -766,8 +771,16 @@ int launch_gemm_splitk(cudaStream_t stream, GemmParams params, const void *lhs, 
     const int ring = stages * params.stage_bytes > receive ? stages * params.stage_bytes : receive;
     const int smem = ring + fixed;
     if (smem > 227 * 1024) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    // [K, N] right operands are staged in boxes of 64 columns: those kernels exist from 64-wide tiles up
+    constexpr bool kHasKN = BN >= 64;
+    if (params.rhs_kn && !kHasKN) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
     static int configured[kMaxDevices] = {0};
-    SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_splitk_kernel<BN, KPS>, smem, configured));
+    static int configured_kn[kMaxDevices] = {0};
+    if (params.rhs_kn) {
+        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_splitk_kernel<BN, KPS, kHasKN>, smem, configured_kn));
+    } else {
+        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_splitk_kernel<BN, KPS, false>, smem, configured));
+    }
 
     CUtensorMap a_map, b_map;
     {
@@ -790,10 +803,14 @@ int launch_gemm_splitk(cudaStream_t stream, GemmParams params, const void *lhs, 
         SINGE_TRY(encode_tensor_map(&b_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rhs, dims, strides, box,
                                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
     }
-    SINGE_CUDA_TRY(launch_dependent(gemm_splitk_kernel<BN, KPS>, dim3(static_cast<unsigned>(params.tiles_n * splits)),
-                                    dim3(kSplitKThreads), smem, stream, kLaunchGemm, static_cast<unsigned>(splits), a_map,
-                                    b_map,
-                                    params));
+    const dim3 grid(static_cast<unsigned>(params.tiles_n * splits));
+    if (params.rhs_kn) {
+        SINGE_CUDA_TRY(launch_dependent(gemm_splitk_kernel<BN, KPS, kHasKN>, grid, dim3(kSplitKThreads), smem, stream,
+                                        kLaunchGemm, static_cast<unsigned>(splits), a_map, b_map, params));
+    } else {
+        SINGE_CUDA_TRY(launch_dependent(gemm_splitk_kernel<BN, KPS, false>, grid, dim3(kSplitKThreads), smem, stream,
+                                        kLaunchGemm, static_cast<unsigned>(splits), a_map, b_map, params));
+    }
     return launch_status();
 }
 
@@ -815,8 +832,15 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
     params.tiles_n = (params.n + BN - 1) / BN;
     const int smem = stages * params.stage_bytes + fixed;
     if (smem > 227 * 1024) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    constexpr bool kHasKN = BN >= 64;
+    if (params.rhs_kn && !kHasKN) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
     static int configured[kMaxDevices] = {0};
-    SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS>, smem, configured));
+    static int configured_kn[kMaxDevices] = {0};
+    if (params.rhs_kn) {
+        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS, kHasKN>, smem, configured_kn));
+    } else {
+        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS, false>, smem, configured));
+    }
 
     CUtensorMap a_map, b_map;
     {
@@ -841,8 +865,13 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
     }
     const int total = params.tiles_m * params.tiles_n;
     const int grid = total < device_sm_count() ? total : device_sm_count();
-    SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS>, dim3(grid), dim3(kGemmThreads), smem, stream, kLaunchGemm, 1, a_map,
-                                    b_map, params));
+    if (params.rhs_kn) {
+        SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS, kHasKN>, dim3(grid), dim3(kGemmThreads), smem, stream,
+                                        kLaunchGemm, 1, a_map, b_map, params));
+    } else {
+        SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS, false>, dim3(grid), dim3(kGemmThreads), smem, stream,
+                                        kLaunchGemm, 1, a_map, b_map, params));
+    }
     return launch_status();
 }
 

@@ -188,13 +188,13 @@ constexpr int decode_smem_bytes() {
 // EXTRAS compiles in what only a decode step asks for (reads ahead of the dependency wait, the early release of a
 // one-wave grid, L2 warming, the rotation of the queries, the in-kernel fold); without it the classic form is the plain
 // drop-in kernel and carries none of their registers or branches (they cost it 2 us of 58 on the bench workload).
-// SOFTCAP (ragged form): tanh-capped scores.
-template <typename T, int HD, bool RAGGED, bool FUSED = false, bool EXTRAS = false, bool SOFTCAP = false>
+// OPTIONS (ragged form): tanh-capped scores and / or a sliding window's partly hidden first page.
+template <typename T, int HD, bool RAGGED, bool FUSED = false, bool EXTRAS = false, bool OPTIONS = false>
 __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, const CUtensorMap &v_map,
                                                   const DecodeParams &p, const RaggedDecode &ragged) {
     static_assert(!(RAGGED && FUSED), "the fused step form is a classic-form kernel");
     static_assert(!FUSED || EXTRAS, "the fused step form is a decode-step kernel");
-    static_assert(!(RAGGED && EXTRAS) && !(SOFTCAP && !RAGGED), "extras: classic form; softcap: ragged form");
+    static_assert(!(RAGGED && EXTRAS) && !(OPTIONS && !RAGGED), "extras: classic form; options: ragged form");
     constexpr int NHALF = HD / 64;
     constexpr int KSTEPS = HD / 16;
     constexpr int NTILES = HD / 8;
@@ -245,6 +245,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
     const int bound = RAGGED ? 0x7ffffff0 : p.table_stride * kPageTokens;
     len = len < 0 ? 0 : (len > bound ? bound : len);
     const int piece = RAGGED ? ragged.control[1] : p.split_tokens;
+    const int hidden_keys = (OPTIONS && ragged.hidden != nullptr) ? ragged.hidden[b] : 0;
     if (split > 0 && static_cast<long long>(split) * piece >= len && !p.partials_only) return;
     uint32_t qa[KSTEPS][2];
     if (warp < kDecodeWarps && !stable) {
@@ -467,7 +468,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
             }
             // Row `row` of this lane: keys t0, t0+1 (tile 0) and t0+8, t0+9 (tile 1).
             const int t0 = tok_begin + i * kPageTokens + quad * 2;
-            if (SOFTCAP) {
+            if (OPTIONS && ragged.softcap > 0.0f) {
                 // AttentionOptions::softcap: cap * tanh(scaled score / cap), then into the base-2 domain
                 const float inward = p.scale_log2 * 0.6931471805599453f / ragged.softcap;
                 const float outward = ragged.softcap * 1.4426950408889634f;
@@ -476,10 +477,12 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
                 s1[0] = outward * fast_tanh(s1[0] * inward) / p.scale_log2;
                 s1[1] = outward * fast_tanh(s1[1] * inward) / p.scale_log2;
             }
-            float x00 = t0 < tok_end ? s0[0] * p.scale_log2 : -INFINITY;
-            float x01 = t0 + 1 < tok_end ? s0[1] * p.scale_log2 : -INFINITY;
-            float x10 = t0 + 8 < tok_end ? s1[0] * p.scale_log2 : -INFINITY;
-            float x11 = t0 + 9 < tok_end ? s1[1] * p.scale_log2 : -INFINITY;
+            // visible keys: below the sequence's end and (sliding window) not among the hidden ones of its first page
+            const int low = OPTIONS ? hidden_keys : 0;
+            float x00 = (t0 < tok_end && t0 >= low) ? s0[0] * p.scale_log2 : -INFINITY;
+            float x01 = (t0 + 1 < tok_end && t0 + 1 >= low) ? s0[1] * p.scale_log2 : -INFINITY;
+            float x10 = (t0 + 8 < tok_end && t0 + 8 >= low) ? s1[0] * p.scale_log2 : -INFINITY;
+            float x11 = (t0 + 9 < tok_end && t0 + 9 >= low) ? s1[1] * p.scale_log2 : -INFINITY;
             float tile_max = fmaxf(fmaxf(x00, x01), fmaxf(x10, x11));
             tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
             tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
@@ -682,6 +685,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     none.index_width = 4;
     none.lse_out = nullptr;
     none.softcap = 0.0f;
+    none.hidden = nullptr;
     paged_decode_body<T, HD, false>(k_map, v_map, p, none);
 }
 
@@ -697,6 +701,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     none.index_width = 4;
     none.lse_out = nullptr;
     none.softcap = 0.0f;
+    none.hidden = nullptr;
     paged_decode_body<T, HD, false, false, true>(k_map, v_map, p, none);
 }
 
@@ -711,14 +716,15 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     none.index_width = 4;
     none.lse_out = nullptr;
     none.softcap = 0.0f;
+    none.hidden = nullptr;
     paged_decode_body<T, HD, false, true, true>(k_map, v_map, p, none);
 }
 
-template <typename T, int HD, bool SOFTCAP>
+template <typename T, int HD, bool OPTIONS>
 __global__ void __launch_bounds__(kDecodeThreads, 3)
     paged_decode_ragged_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                                const DecodeParams p, const RaggedDecode ragged) {
-    paged_decode_body<T, HD, true, false, false, SOFTCAP>(k_map, v_map, p, ragged);
+    paged_decode_body<T, HD, true, false, false, OPTIONS>(k_map, v_map, p, ragged);
 }
 
 // Folds the split partials of every (sequence, head) row that needed more than one split.
@@ -768,7 +774,7 @@ int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedD
     static int configured[kMaxDevices] = {0};  // one table per instantiation, one entry per device
     constexpr int smem = decode_smem_bytes<HD>();
     const bool fused = !RAGGED && params.qkv != nullptr;
-    const bool capped = RAGGED && shape.softcap > 0.0f;
+    const bool capped = RAGGED && (shape.softcap > 0.0f || shape.hidden != nullptr);
     // the plain drop-in call takes the kernel without the decode step's extras
     const bool extras = !RAGGED && !fused &&
                         (params.stable_paging != 0 || params.early_release != 0 || params.warm.bytes != 0 ||
@@ -889,6 +895,7 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
     none.index_width = 4;
     none.lse_out = nullptr;
     none.softcap = 0.0f;
+    none.hidden = nullptr;
     const RaggedDecode &shape = ragged != nullptr ? *ragged : none;
     params.out = out;
     params.attn_partial = attn_scratch;

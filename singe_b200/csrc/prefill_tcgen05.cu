@@ -88,10 +88,16 @@ struct PrefillParams {
     uint32_t *error;
 };
 
-__device__ __forceinline__ int seq_len_q(const PrefillParams &p, int b) { return p.lens_q != nullptr ? p.lens_q[b] : p.uniform_q; }
-__device__ __forceinline__ int seq_len_kv(const PrefillParams &p, int b) { return p.lens_q != nullptr ? p.lens_kv[b] : p.uniform_kv; }
-__device__ __forceinline__ int seq_offset_q(const PrefillParams &p, int b) { return p.lens_q != nullptr ? p.offsets[b] : b * p.uniform_q; }
-__device__ __forceinline__ int seq_offset_kv(const PrefillParams &p, int b) { return p.lens_q != nullptr ? p.offsets[b] : b * p.uniform_kv; }
+// Lengths and first rows of sequence b.  DENSE is a template argument of the kernel: as run-time branches these four
+// cost the packed form 2.5 % (every warp of a CTA decodes every work item).
+template <bool DENSE>
+__device__ __forceinline__ int seq_len_q(const PrefillParams &p, int b) { return DENSE ? p.uniform_q : p.lens_q[b]; }
+template <bool DENSE>
+__device__ __forceinline__ int seq_len_kv(const PrefillParams &p, int b) { return DENSE ? p.uniform_kv : p.lens_kv[b]; }
+template <bool DENSE>
+__device__ __forceinline__ int seq_offset_q(const PrefillParams &p, int b) { return DENSE ? b * p.uniform_q : p.offsets[b]; }
+template <bool DENSE>
+__device__ __forceinline__ int seq_offset_kv(const PrefillParams &p, int b) { return DENSE ? b * p.uniform_kv : p.offsets[b]; }
 
 __device__ __forceinline__ float exp2_approx(float x) {
     float y;
@@ -220,6 +226,7 @@ __device__ __forceinline__ int pairs_of(int len_q) { return (max(len_q, 0) + kPa
 // pair index down (under a causal mask a pair's work grows with its index), head = index % heads.  `counts[t]` is
 // the number of sequences that have a pair t, `tmax` the largest pair count.  Every lane of the calling warp
 // takes part and receives the same answer.
+template <bool DENSE>
 __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *counts, int tmax, int index, int lane) {
     constexpr unsigned kFull = 0xffffffffu;
     Item item;
@@ -248,7 +255,7 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
     int seq = -1;
     for (int first = 0; first < p.batch && seq < 0 && pair >= 0; first += 32) {
         const int b = first + lane;
-        const bool has = b < p.batch && pairs_of(seq_len_q(p, b)) > pair;
+        const bool has = b < p.batch && pairs_of(seq_len_q<DENSE>(p, b)) > pair;
         const unsigned mask = __ballot_sync(kFull, has);
         const int n = __popc(mask);
         if (rank < n) {
@@ -268,10 +275,10 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
     item.tiles[0] = item.tiles[1] = 0;
     item.key_tiles = 0;
     if (seq < 0) return item;
-    item.len_q = max(seq_len_q(p, seq), 0);
-    item.len_kv = max(seq_len_kv(p, seq), 0);
-    item.offset = seq_offset_q(p, seq);
-    item.offset_kv = seq_offset_kv(p, seq);
+    item.len_q = max(seq_len_q<DENSE>(p, seq), 0);
+    item.len_kv = max(seq_len_kv<DENSE>(p, seq), 0);
+    item.offset = seq_offset_q<DENSE>(p, seq);
+    item.offset_kv = seq_offset_kv<DENSE>(p, seq);
     item.valid = item.offset >= 0 && item.offset + item.len_q <= p.total_q &&
                  (p.block_table != nullptr ? item.len_kv <= p.table_stride * kPageTokens
                                            : item.offset_kv + item.len_kv <= p.total_kv);
@@ -298,7 +305,8 @@ __device__ __forceinline__ Item decode_item(const PrefillParams &p, const int *c
 // PAGED: K and V tiles are gathered from 16-token cache pages through the block table (eight page boxes per
 // 128-key tile and 64-wide half; the boxes land back to back, which is the layout one 128-row box would have).
 // HD = 128 or 64: with 64 a tile is a single 128-byte-wide box (the second half of every 32 KB buffer stays unused).
-template <typename T, int HD, bool SAFE, bool PAGED>
+// DENSE: uniform lengths, sequences back to back, LSE laid out [batch, heads, queries] (fmha_prefill_lse).
+template <typename T, int HD, bool SAFE, bool PAGED, bool DENSE>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
     prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                            const __grid_constant__ CUtensorMap v_map, const PrefillParams p) {
@@ -339,11 +347,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     // ---- the table behind the heaviest-first item order ----
     {
         int tmax = 0;
-        for (int b = 0; b < p.batch; ++b) tmax = max(tmax, pairs_of(seq_len_q(p, b)));
+        for (int b = 0; b < p.batch; ++b) tmax = max(tmax, pairs_of(seq_len_q<DENSE>(p, b)));
         tmax = min(tmax, kMaxRankTiles);
         for (int t = tid; t < tmax; t += kPrefillThreads) {
             int count = 0;
-            for (int b = 0; b < p.batch; ++b) count += pairs_of(seq_len_q(p, b)) > t ? 1 : 0;
+            for (int b = 0; b < p.batch; ++b) count += pairs_of(seq_len_q<DENSE>(p, b)) > t ? 1 : 0;
             counts[t] = count;
         }
         __syncthreads();
@@ -365,7 +373,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
     };
     // where the LSE of (item, sequence-local query row) lives
     auto lse_at = [&](const Item &item, int row) -> float * {
-        if (p.lse_rows > 0) {
+        if (DENSE) {
             return p.lse + (static_cast<size_t>(item.seq) * p.heads + item.head) * p.lse_rows + row;
         }
         return p.lse + (static_cast<size_t>(item.offset) + row) * p.heads + item.head;
@@ -378,7 +386,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         for (int round = 0;; ++round) {
             const int index = share_index(round);
             if (index < 0) break;
-            const Item item = decode_item(p, counts, tmax, index, lane);
+            const Item item = decode_item<DENSE>(p, counts, tmax, index, lane);
             const int row = item.q0 + tid;
             const bool marked = item.valid && item.key_tiles > 0 && tid < kPair && row < item.len_q &&
                                 isnan(*lse_at(item, row));
@@ -436,7 +444,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         for (int round = 0; !failed; ++round) {
             const int index = item_index(round);
             if (index < 0) break;
-            const Item item = decode_item(p, counts, tmax, index, lane);
+            const Item item = decode_item<DENSE>(p, counts, tmax, index, lane);
             if (item.key_tiles == 0) continue;
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
@@ -570,7 +578,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
                     return item;
                 }
                 ++round;
-                item = decode_item(p, counts, tmax, index, lane);
+                item = decode_item<DENSE>(p, counts, tmax, index, lane);
                 if (item.key_tiles > 0) return item;
             }
         };
@@ -664,7 +672,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
         for (int round = 0; !failed; ++round) {
             const int index = item_index(round);
             if (index < 0) break;
-            const Item item = decode_item(p, counts, tmax, index, lane);
+            const Item item = decode_item<DENSE>(p, counts, tmax, index, lane);
             if (!item.valid) {
                 if (warp == 0 && lane == 0) report_status(p.error, kStatusIndexOutOfBounds);
                 continue;
@@ -809,21 +817,21 @@ bool prefill_fast_path(size_t heads, size_t kv_heads, size_t head_dim, size_t to
 
 namespace {
 
-template <typename T, int HD, bool PAGED>
+template <typename T, int HD, bool PAGED, bool DENSE = false>
 int launch_prefill(cudaStream_t stream, const CUtensorMap &q_map, const CUtensorMap &k_map, const CUtensorMap &v_map,
                    const PrefillParams &params, unsigned persistent) {
-    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<T, HD, true, PAGED>,
+    SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<T, HD, true, PAGED, DENSE>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
     if (std::is_same<T, __nv_bfloat16>::value) {
-        SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<__nv_bfloat16, HD, false, PAGED>,
+        SINGE_CUDA_TRY(cudaFuncSetAttribute(prefill_tcgen05_kernel<__nv_bfloat16, HD, false, PAGED, DENSE>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
-        prefill_tcgen05_kernel<__nv_bfloat16, HD, false, PAGED>
+        prefill_tcgen05_kernel<__nv_bfloat16, HD, false, PAGED, DENSE>
             <<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map, params);
         SINGE_TRY(launch_status());
     }
     // bf16: the redo pass over the same shares, a no-op while the device's out-of-range flag has never been raised.
     // f16 (params.exact): the only pass.  P must stay below 65504 there, so every tile takes its exact row maximum.
-    prefill_tcgen05_kernel<T, HD, true, PAGED><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map,
+    prefill_tcgen05_kernel<T, HD, true, PAGED, DENSE><<<persistent, kPrefillThreads, kPrefillSmem, stream>>>(q_map, k_map, v_map,
                                                                                                   params);
     return launch_status();
 }
@@ -896,6 +904,16 @@ int prefill_tcgen05(cudaStream_t stream, bool is_f16, void *out, float *lse, con
     if (items > 0x7fffffffull) return SINGE_ERR_LENGTH_EXCEEDS_I32;
     if (items == 0) return SINGE_OK;
     const unsigned persistent = static_cast<unsigned>(items < static_cast<size_t>(sms) ? items : sms);
+    if (lens_q == nullptr) {
+        // the dense form: ragged keys only
+        if (paged) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+        if (head_dim == 64) {
+            return is_f16 ? launch_prefill<__half, 64, false, true>(stream, q_map, k_map, v_map, params, persistent)
+                          : launch_prefill<__nv_bfloat16, 64, false, true>(stream, q_map, k_map, v_map, params, persistent);
+        }
+        return is_f16 ? launch_prefill<__half, 128, false, true>(stream, q_map, k_map, v_map, params, persistent)
+                      : launch_prefill<__nv_bfloat16, 128, false, true>(stream, q_map, k_map, v_map, params, persistent);
+    }
     if (head_dim == 64) {
         if (is_f16) {
             return paged ? launch_prefill<__half, 64, true>(stream, q_map, k_map, v_map, params, persistent)

@@ -218,6 +218,36 @@ def test_a_plain_decode_batch_through_the_tensor_surface_takes_the_tiled_kernel_
     assert np.abs(got_lse[finite] - ref_lse[finite]).max() < 5e-3
 
 
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("window", [1, 5, 16, 17, 100, 1000, 5000])
+def test_a_plain_decode_batch_with_a_sliding_window_stays_on_the_tiled_kernel(window, causal):
+    # The planning kernel drops the whole pages in front of the window (key-tile skipping) and tells the tiled kernel
+    # how many keys at the front of the first remaining page are still hidden.  The query at position keys - 1 sees
+    # keys >= keys - window whether the call is causal or not.  Windows of one key, inside one page, exactly a page,
+    # across pages and splits, and wider than every sequence.
+    rng = np.random.default_rng(70 + window)
+    heads, kv_heads = 8, 2
+    lens = [1, 700, 16, 0, 2049, 513, 17, 31]
+    q, kc, vc, pages, page_offsets, last = _decode_batch(rng, lens, heads, kv_heads)
+    query_offsets = np.arange(len(lens) + 1, dtype=np.int64)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    scale = 1.0 / np.sqrt(128.0)
+    out, lse = ops.paged_attention(dev(q, torch.bfloat16), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16),
+                                   dev(query_offsets), dev(page_offsets), dev(pages), dev(last), scale=scale,
+                                   causal=causal, window=window, status=status)
+    torch.cuda.synchronize()
+    code, ref_out, ref_lse = oracle.attend_paged_f32(q, kc, vc, query_offsets, page_offsets, pages, last, scale=scale,
+                                                     causal=causal, window=window)
+    assert code == oracle.OK and int(status.item()) == 0 and ops.take_device_error() == 0
+    assert_close_bf16(host(out), ref_out, f"windowed tensor-surface decode, window={window} causal={causal}")
+    got_lse, finite = host(lse), np.isfinite(ref_lse)
+    assert (np.isneginf(got_lse) == np.isneginf(ref_lse)).all()
+    assert np.abs(got_lse[finite] - ref_lse[finite]).max() < 5e-3
+    if window < 500:
+        full = oracle.attend_paged_f32(q, kc, vc, query_offsets, page_offsets, pages, last, scale=scale, causal=causal)[1]
+        assert np.abs(full - ref_out).max() > 1e-2   # the window changes the answer
+
+
 def test_a_batch_that_only_looks_like_decode_is_left_to_the_general_kernel():
     # tokens == sequences, but sequence 0 owns two query tokens and sequence 1 none: the planning kernel must not hand
     # this to the tiled kernel.  Then a bad page id in an otherwise plain decode batch: status 1, no fault.

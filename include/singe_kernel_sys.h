@@ -198,6 +198,18 @@ int singe_splitk_reduce_f32(singe_stream_t stream, float *out, const float *attn
                             size_t attn_head_stride, size_t attn_split_stride, size_t lse_batch_stride,
                             size_t lse_head_stride, size_t output_batch_stride, size_t output_head_stride);
 
+/* Decode over CONTIGUOUS keys and values with split-K and the fold in one call.
+ * Replaces: fmha_decode_splitk_reduce_f32 + FmhaDecodeSplitKReduceConfig::contiguous
+ *   (singe-kernel/src/cuda/attention/fmha.rs:1155-1241, mod.rs:454-477; lengths :2511-2539).
+ *   query, out [batch, heads, head_dim]; key, value [batch, key_len, kv_heads, head_dim];
+ *   attn_scratch [batch, heads, splits, head_dim], lse_scratch [batch, heads, splits] with
+ *   splits = min(max_splits, key_len).  The reference's tuner (tune_fmha_decode_splitk_reduce_f32) picks the split
+ *   count by timing; here the caller's max_splits is the split count (TuningChoice::Default's meaning). */
+int singe_fmha_decode_splitk_reduce_f32(singe_stream_t stream, float *out, float *attn_scratch, float *lse_scratch,
+                                        const float *query, const float *key, const float *value, size_t batch,
+                                        size_t key_len, size_t heads, size_t kv_heads, size_t head_dim,
+                                        size_t max_splits, float scale);
+
 /* Decode + combine in one call with caller scratch sized for `max_splits` (>= 1). */
 int singe_paged_kv_decode_splitk_reduce_bf16(singe_stream_t stream, void *out, float *attn_scratch,
                                              float *lse_scratch, const void *query, const void *key_cache,

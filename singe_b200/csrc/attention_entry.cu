@@ -428,6 +428,44 @@ struct DensePolicy {
     __device__ const T *value_base() const { return value; }
 };
 
+// One decode query per (batch, head) over contiguous keys/values [B, S, G, D], cut into `splits` key ranges: row
+// (b, head, s) attends keys [s * per_split, min(S, (s + 1) * per_split)) and leaves its normalised partial in
+// out [B, H, splits, D] and its natural-log LSE in lse [B, H, splits] (fmha_decode_splitk_f32,
+// singe-kernel/src/cuda/attention/fmha.rs:1073-1117); splitk_reduce_kernel folds them.
+template <typename T>
+struct DenseSplitPolicy {
+    const T *query;
+    T *out;
+    float *lse;
+    const T *key;
+    const T *value;
+    int heads, kv_heads, key_len, head_dim, splits, per_split;
+
+    __device__ int locate(size_t row, RowPlan<T> &plan) const {
+        const long long split = static_cast<long long>(row % splits);
+        const long long bh = static_cast<long long>(row / splits);
+        const long long head = bh % heads;
+        const long long b = bh / heads;
+        long long start = split * per_split;
+        long long end = start + per_split;
+        if (end > key_len) end = key_len;
+        if (start > end) start = end;
+        plan.query = query + bh * head_dim;
+        plan.out = out + static_cast<long long>(row) * head_dim;
+        plan.lse = lse + row;
+        plan.start = static_cast<int>(start);
+        plan.end = static_cast<int>(end);
+        plan.kv_head = static_cast<int>(head / (heads / kv_heads));
+        plan.handle = (b * key_len * kv_heads + plan.kv_head) * head_dim;
+        return 1;
+    }
+    __device__ long long key_offset(const RowPlan<T> &plan, int pos) const {
+        return plan.handle + static_cast<long long>(pos) * kv_heads * head_dim;
+    }
+    __device__ const T *key_base() const { return key; }
+    __device__ const T *value_base() const { return value; }
+};
+
 // ---------------------------------------------------------------------------------------------
 // Per-device split-K workspace of the drop-in decode entry points
 // ---------------------------------------------------------------------------------------------
@@ -1051,6 +1089,46 @@ int singe_splitk_reduce_f32(singe_stream_t stream, float *out, const float *attn
         static_cast<long long>(lse_head_stride), static_cast<long long>(output_batch_stride),
         static_cast<long long>(output_head_stride));
     return launch_status();
+}
+
+// fmha_decode_splitk_reduce_f32 with FmhaDecodeSplitKReduceConfig::contiguous
+// (singe-kernel/src/cuda/attention/fmha.rs:1155-1241, mod.rs:454-477,2511-2560): the decode over contiguous keys and
+// values cut into min(max_splits, key_len) key ranges, then the log-sum-exp fold.
+int singe_fmha_decode_splitk_reduce_f32(singe_stream_t stream, float *out, float *attn_scratch, float *lse_scratch,
+                                        const float *query, const float *key, const float *value, size_t batch,
+                                        size_t key_len, size_t heads, size_t kv_heads, size_t head_dim,
+                                        size_t max_splits, float scale) {
+    if (batch == 0 || key_len == 0 || heads == 0 || kv_heads == 0 || head_dim == 0 || max_splits == 0 ||
+        heads % kv_heads != 0 || !finite(scale)) {
+        return SINGE_ERR_INVALID_LENGTH;
+    }
+    if (!fits_i32(batch) || !fits_i32(key_len) || !fits_i32(heads) || !fits_i32(head_dim) ||
+        !fits_i32(batch * heads) || !fits_i32(key_len * kv_heads * head_dim)) {
+        return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    }
+    if (out == nullptr || attn_scratch == nullptr || lse_scratch == nullptr || query == nullptr || key == nullptr ||
+        value == nullptr) {
+        return SINGE_ERR_NULL_POINTER;
+    }
+    const size_t splits = max_splits < key_len ? max_splits : key_len;
+    if (!fits_i32(splits) || !fits_i32(batch * heads * splits)) return SINGE_ERR_LENGTH_EXCEEDS_I32;
+    DenseSplitPolicy<float> policy;
+    policy.query = query;
+    policy.out = attn_scratch;
+    policy.lse = lse_scratch;
+    policy.key = key;
+    policy.value = value;
+    policy.heads = static_cast<int>(heads);
+    policy.kv_heads = static_cast<int>(kv_heads);
+    policy.key_len = static_cast<int>(key_len);
+    policy.head_dim = static_cast<int>(head_dim);
+    policy.splits = static_cast<int>(splits);
+    policy.per_split = static_cast<int>((key_len + splits - 1) / splits);
+    SINGE_TRY(launch_attention_general<float>(static_cast<cudaStream_t>(stream), policy, batch * heads * splits, head_dim,
+                                              scale, LseKind::Natural, -1.0e20f, nullptr));
+    return singe_splitk_reduce_f32(stream, out, attn_scratch, lse_scratch, batch, heads, splits, head_dim,
+                                   heads * splits * head_dim, splits * head_dim, head_dim, heads * splits, splits,
+                                   heads * head_dim, head_dim);
 }
 
 int singe_paged_attention_bf16(singe_stream_t stream, void *out, float *lse, const void *query, const void *key_cache,

@@ -478,11 +478,11 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
                 s1[1] = outward * fast_tanh(s1[1] * inward) / p.scale_log2;
             }
             // visible keys: below the sequence's end and (sliding window) not among the hidden ones of its first page
-            const int low = OPTIONS ? hidden_keys : 0;
-            float x00 = (t0 < tok_end && t0 >= low) ? s0[0] * p.scale_log2 : -INFINITY;
-            float x01 = (t0 + 1 < tok_end && t0 + 1 >= low) ? s0[1] * p.scale_log2 : -INFINITY;
-            float x10 = (t0 + 8 < tok_end && t0 + 8 >= low) ? s1[0] * p.scale_log2 : -INFINITY;
-            float x11 = (t0 + 9 < tok_end && t0 + 9 >= low) ? s1[1] * p.scale_log2 : -INFINITY;
+            // (the lower bound exists only in the OPTIONS form: the other kernels keep their single compare per key)
+            float x00 = (t0 < tok_end && (!OPTIONS || t0 >= hidden_keys)) ? s0[0] * p.scale_log2 : -INFINITY;
+            float x01 = (t0 + 1 < tok_end && (!OPTIONS || t0 + 1 >= hidden_keys)) ? s0[1] * p.scale_log2 : -INFINITY;
+            float x10 = (t0 + 8 < tok_end && (!OPTIONS || t0 + 8 >= hidden_keys)) ? s1[0] * p.scale_log2 : -INFINITY;
+            float x11 = (t0 + 9 < tok_end && (!OPTIONS || t0 + 9 >= hidden_keys)) ? s1[1] * p.scale_log2 : -INFINITY;
             float tile_max = fmaxf(fmaxf(x00, x01), fmaxf(x10, x11));
             tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
             tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));

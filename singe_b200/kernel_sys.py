@@ -56,6 +56,7 @@ SIGNATURES = {
     "singe_paged_kv_decode_attention_static_scratch_floats": [],
     "singe_paged_kv_decode_split_tokens": [_z, _z, _z],
     "singe_paged_kv_decode_splitk_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z, _f],
+    "singe_fmha_decode_splitk_reduce_f32": [_p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _f],
     "singe_splitk_reduce_f32": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z, _z, _z, _z],
     "singe_paged_kv_decode_splitk_reduce_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z,
                                                  _f],

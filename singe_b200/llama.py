@@ -292,7 +292,7 @@ def shard_layer_weights(full: dict, config: LlamaConfig, shard: Shard, interleav
 
 
 # Largest tensor-parallel degree at which collective="peer" means the one-shot kernel.
-PEER_ONE_SHOT_UP_TO = 8
+PEER_ONE_SHOT_UP_TO = 4
 
 
 class LlamaDecoder:
@@ -377,8 +377,9 @@ class LlamaDecoder:
             raise ValueError("collective must be 'peer', 'oneshot', 'twophase', 'pushall' or 'nccl'")
         if collective == "peer":
             # one-shot: every rank pulls all partial rows; two-phase: rows are reduced by their owners and pushed
-            # back.  Measured on B200 / NVSwitch at 64 rows x 4096: one-shot is ahead with two ranks (4.28 against
-            # 4.48 ms per step) and level with four (3.29 / 3.29), so it stays the pick until more ranks change that.
+            # back.  Measured on B200 / NVSwitch at 64 rows x 4096, ms per step: one-shot is ahead with two ranks
+            # (4.28 against 4.48), level with four (3.29 / 3.29) and behind with eight (2.82 against 2.49), where
+            # every rank would pull 3.5 MB per collective.
             collective = "oneshot" if tp <= PEER_ONE_SHOT_UP_TO else "twophase"
         self.collective = collective
         self.peer = None

@@ -377,3 +377,35 @@ def test_tensor_paged_attention_with_a_score_cap(plain_decode):
     assert_close_bf16(host(out), ref_out, f"paged attention with a score cap (decode={plain_decode})")
     finite = np.isfinite(ref_lse)
     assert np.abs(host(lse)[finite] - ref_lse[finite]).max() < 5e-3
+
+
+@pytest.mark.parametrize("batch,key_len,heads,kv_heads,head_dim,max_splits",
+                         [(2, 300, 4, 2, 64, 4), (1, 5, 2, 1, 32, 8), (3, 1000, 8, 2, 128, 7), (2, 17, 4, 4, 16, 1)])
+def test_contiguous_decode_with_split_k_and_the_fold_in_one_call(batch, key_len, heads, kv_heads, head_dim, max_splits):
+    # fmha_decode_splitk_reduce_f32 (singe-kernel/src/cuda/attention/fmha.rs:1155-1241): one query per (batch, head)
+    # over contiguous keys, min(max_splits, key_len) key ranges, then the fold.  The meaning is a one-token prefill
+    # without a mask, which the CPU restatement of fmha_prefill_lse_f32 gives.
+    from singe_b200 import kernel_sys as ks
+
+    rng = np.random.default_rng(90 + key_len)
+    q = rng.standard_normal((batch, 1, heads, head_dim), dtype=np.float32)
+    k = rng.standard_normal((batch, key_len, kv_heads, head_dim), dtype=np.float32)
+    v = rng.standard_normal((batch, key_len, kv_heads, head_dim), dtype=np.float32)
+    scale = 1.0 / np.sqrt(head_dim)
+    splits = min(max_splits, key_len)
+    out = torch.full((batch, heads, head_dim), float("nan"), device="cuda")
+    attn = torch.empty((batch, heads, splits, head_dim), device="cuda")
+    lse = torch.empty((batch, heads, splits), device="cuda")
+    d_q, d_k, d_v = dev(q), dev(k), dev(v)
+    code = ks.lib().singe_fmha_decode_splitk_reduce_f32(
+        int(torch.cuda.current_stream().cuda_stream), out.data_ptr(), attn.data_ptr(), lse.data_ptr(), d_q.data_ptr(),
+        d_k.data_ptr(), d_v.data_ptr(), batch, key_len, heads, kv_heads, head_dim, max_splits, scale)
+    torch.cuda.synchronize()
+    assert code == ks.OK and ops.take_device_error() == 0
+    ref_out, _ = oracle.fmha_prefill_lse_f32(q, k, v, batch=batch, query_len=1, key_len=key_len, heads=heads,
+                                             kv_heads=kv_heads, head_dim=head_dim, scale=scale, causal=False)
+    assert_close_f32(host(out), ref_out.reshape(batch, heads, head_dim), f"contiguous split-K decode S={key_len}")
+    lib = ks.lib()
+    assert lib.singe_fmha_decode_splitk_reduce_f32(None, 1, 1, 1, 1, 1, 1, 1, 8, 3, 2, 8, 0, 1.0) == ks.ERR_INVALID_LENGTH
+    assert lib.singe_fmha_decode_splitk_reduce_f32(None, 1, 1, 1, 1, 1, 1, 1, 8, 4, 2, 8, 0, 1.0) == ks.ERR_INVALID_LENGTH
+    assert lib.singe_fmha_decode_splitk_reduce_f32(None, None, 1, 1, 1, 1, 1, 1, 8, 4, 2, 8, 2, 1.0) == ks.ERR_NULL_POINTER

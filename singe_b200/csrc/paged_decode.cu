@@ -51,6 +51,14 @@ struct DecodeParams {
     int split_tokens;  // multiple of 16
     int max_splits;
     int partials_only;  // 1: every split slot is written, nothing goes to `out`
+    float scale_log2;   // scale * log2(e)
+    uint32_t *status;
+};
+
+// What only a decode step passes (the EXTRAS forms of the kernel).  It is a kernel argument of its own: the plain and
+// ragged kernels do not carry it, and measurably so -- with these fields inside DecodeParams the plain kernel's
+// registers were allotted differently and config 2 took 0.6 us longer.
+struct StepExtras {
     int stable_paging;  // 1: lengths, block table and every cached row but each sequence's last key position are not
                         //    written by work still in flight (SINGE_HINT_STABLE_PAGING): they are read ahead of the
                         //    wait on the preceding kernels
@@ -76,8 +84,6 @@ struct DecodeParams {
     const void *query_gain;      // per-head RMSNorm before the rotation: gain [head_dim] or nullptr
     int query_norm;              // 1: normalise
     float query_norm_eps;
-    float scale_log2;   // scale * log2(e)
-    uint32_t *status;
 };
 
 __device__ __forceinline__ float fast_tanh(float x) {
@@ -101,14 +107,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // Replaces the query stage of singe_rotary_paged_attention
 // (singe/src/backend/cuda/kernel_plan/source/paged_attention.rs:881-977, QueryRotation).
 template <typename T, int HD>
-__device__ __forceinline__ void rotate_query_fragments(uint32_t (&qa)[HD / 16][2], const DecodeParams &p, int b, int row,
+__device__ __forceinline__ void rotate_query_fragments(uint32_t (&qa)[HD / 16][2], const DecodeParams &p,
+                                                       const StepExtras &x, int b, int row,
                                                        int quad, bool may_normalise = true) {
     constexpr int KSTEPS = HD / 16;
     constexpr int HALF_STEPS = KSTEPS / 2;
-    long long position = p.rope_index_width == 8 ? static_cast<const long long *>(p.rope_positions)[b]
-                                                 : static_cast<long long>(static_cast<const int *>(p.rope_positions)[b]);
-    if (position < 0) position += p.rope_capacity;
-    if (position < 0 || position >= p.rope_capacity) {
+    long long position = x.rope_index_width == 8 ? static_cast<const long long *>(x.rope_positions)[b]
+                                                 : static_cast<long long>(static_cast<const int *>(x.rope_positions)[b]);
+    if (position < 0) position += x.rope_capacity;
+    if (position < 0 || position >= x.rope_capacity) {
         report_status(p.status, kStatusIndexOutOfBounds);
         position = 0;
     }
@@ -123,7 +130,7 @@ __device__ __forceinline__ void rotate_query_fragments(uint32_t (&qa)[HD / 16][2
         return to_float<T>(value);
     };
     auto rounded = [](float value) { return to_float<T>(from_float<T>(value)); };
-    if (p.query_norm && may_normalise) {
+    if (x.query_norm && may_normalise) {
         float squares = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -132,8 +139,8 @@ __device__ __forceinline__ void rotate_query_fragments(uint32_t (&qa)[HD / 16][2
         }
         squares += __shfl_xor_sync(0xffffffffu, squares, 1);
         squares += __shfl_xor_sync(0xffffffffu, squares, 2);
-        const float scale = 1.0f / sqrtf(squares / static_cast<float>(HD) + p.query_norm_eps);
-        const uint32_t *gain = static_cast<const uint32_t *>(p.query_gain);
+        const float scale = 1.0f / sqrtf(squares / static_cast<float>(HD) + x.query_norm_eps);
+        const uint32_t *gain = static_cast<const uint32_t *>(x.query_gain);
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
 #pragma unroll
@@ -145,8 +152,8 @@ __device__ __forceinline__ void rotate_query_fragments(uint32_t (&qa)[HD / 16][2
             }
         }
     }
-    const uint32_t *cos_row = static_cast<const uint32_t *>(p.rope_cos) + position * (HD / 4);
-    const uint32_t *sin_row = static_cast<const uint32_t *>(p.rope_sin) + position * (HD / 4);
+    const uint32_t *cos_row = static_cast<const uint32_t *>(x.rope_cos) + position * (HD / 4);
+    const uint32_t *sin_row = static_cast<const uint32_t *>(x.rope_sin) + position * (HD / 4);
     (void)row;
 #pragma unroll
     for (int ks = 0; ks < HALF_STEPS; ++ks) {
@@ -191,7 +198,8 @@ constexpr int decode_smem_bytes() {
 // OPTIONS (ragged form): tanh-capped scores and / or a sliding window's partly hidden first page.
 template <typename T, int HD, bool RAGGED, bool FUSED = false, bool EXTRAS = false, bool OPTIONS = false>
 __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, const CUtensorMap &v_map,
-                                                  const DecodeParams &p, const RaggedDecode &ragged) {
+                                                  const DecodeParams &p, const StepExtras &x,
+                                                  const RaggedDecode &ragged) {
     static_assert(!(RAGGED && FUSED), "the fused step form is a classic-form kernel");
     static_assert(!FUSED || EXTRAS, "the fused step form is a decode-step kernel");
     static_assert(!(RAGGED && EXTRAS) && !(OPTIONS && !RAGGED), "extras: classic form; options: ragged form");
@@ -202,13 +210,13 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
 
     // The queries (and, in a decode step, the newest K/V rows) come from the kernel before.  No global write of this
     // kernel -- outputs, split partials -- may move above a thread's wait: an earlier kernel may still read them.
-    const bool stable = EXTRAS && p.stable_paging != 0;
+    const bool stable = EXTRAS && x.stable_paging != 0;
     if (EXTRAS && threadIdx.x < 32) {
-        warm_l2(p.warm, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+        warm_l2(x.warm, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
                 gridDim.x * gridDim.y * gridDim.z, threadIdx.x);
     }
     if (!stable) grid_dependency_wait();
-    if (EXTRAS && p.early_release) grid_launch_dependents();
+    if (EXTRAS && x.early_release) grid_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -253,7 +261,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         const int quad = lane & 3;
         const size_t head = static_cast<size_t>(b) * p.heads + g * p.group + row;
         const uint32_t *q32 =
-            FUSED ? reinterpret_cast<const uint32_t *>(static_cast<const T *>(p.qkv) + static_cast<size_t>(b) * p.qkv_stride +
+            FUSED ? reinterpret_cast<const uint32_t *>(static_cast<const T *>(x.qkv) + static_cast<size_t>(b) * x.qkv_stride +
                                                        static_cast<size_t>(g * p.group + row) * HD)
                   : reinterpret_cast<const uint32_t *>(query + head * HD);
 #pragma unroll
@@ -261,7 +269,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
             qa[ks][0] = row < p.group ? q32[ks * 8 + quad] : 0u;
             qa[ks][1] = row < p.group ? q32[ks * 8 + 4 + quad] : 0u;
         }
-        if (EXTRAS && p.rope_cos != nullptr) rotate_query_fragments<T, HD>(qa, p, b, row, quad);
+        if (EXTRAS && x.rope_cos != nullptr) rotate_query_fragments<T, HD>(qa, p, x, b, row, quad);
     }
     // The barriers are set up while the query reads are in flight.
     if (tid == 0) {
@@ -342,7 +350,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
                     tma_load_4d(stage + lane * kHalfBytes, map, full, hf * 64, g, 0, static_cast<int32_t>(pg));
                 }
             }
-            const int far = min(min(npages, newest), ahead + p.prefetch_pages);
+            const int far = min(min(npages, newest), ahead + x.prefetch_pages);
             for (int i = ahead + (lane >> 2); i < far; i += 8) {
                 const uint32_t pg = table[i];
                 if (pg < static_cast<uint32_t>(p.physical_blocks)) {
@@ -418,8 +426,8 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
             grid_dependency_wait();
             const size_t head = static_cast<size_t>(b) * p.heads + g * p.group + row;
             const uint32_t *q32 =
-                FUSED ? reinterpret_cast<const uint32_t *>(static_cast<const T *>(p.qkv) +
-                                                           static_cast<size_t>(b) * p.qkv_stride +
+                FUSED ? reinterpret_cast<const uint32_t *>(static_cast<const T *>(x.qkv) +
+                                                           static_cast<size_t>(b) * x.qkv_stride +
                                                            static_cast<size_t>(g * p.group + row) * HD)
                       : reinterpret_cast<const uint32_t *>(query + head * HD);
 #pragma unroll
@@ -427,7 +435,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
                 qa[ks][0] = row < p.group ? q32[ks * 8 + quad] : 0u;
                 qa[ks][1] = row < p.group ? q32[ks * 8 + 4 + quad] : 0u;
             }
-            if (p.rope_cos != nullptr) rotate_query_fragments<T, HD>(qa, p, b, row, quad);
+            if (x.rope_cos != nullptr) rotate_query_fragments<T, HD>(qa, p, x, b, row, quad);
         }
         float o[NTILES][4];
 #pragma unroll
@@ -521,29 +529,29 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
         }
         if (FUSED && adds_new && warp == 0) {
             // ---- the key and value this step adds: rotate K, put both rows into the cache, attend the new key ----
-            const T *projections = static_cast<const T *>(p.qkv) + static_cast<size_t>(b) * p.qkv_stride;
+            const T *projections = static_cast<const T *>(x.qkv) + static_cast<size_t>(b) * x.qkv_stride;
             const uint32_t *k32 = reinterpret_cast<const uint32_t *>(projections + static_cast<size_t>(p.heads + g) * HD);
             const uint32_t *v32 =
                 reinterpret_cast<const uint32_t *>(projections + static_cast<size_t>(p.heads + p.kv_heads + g) * HD);
-            long long page = p.rope_index_width == 8 ? static_cast<const long long *>(p.write_pages)[b]
-                                                     : static_cast<long long>(static_cast<const int *>(p.write_pages)[b]);
-            long long slot = p.rope_index_width == 8 ? static_cast<const long long *>(p.write_slots)[b]
-                                                     : static_cast<long long>(static_cast<const int *>(p.write_slots)[b]);
+            long long page = x.rope_index_width == 8 ? static_cast<const long long *>(x.write_pages)[b]
+                                                     : static_cast<long long>(static_cast<const int *>(x.write_pages)[b]);
+            long long slot = x.rope_index_width == 8 ? static_cast<const long long *>(x.write_slots)[b]
+                                                     : static_cast<long long>(static_cast<const int *>(x.write_slots)[b]);
             if (page < 0) page += p.physical_blocks;
             if (slot < 0) slot += kPageTokens;
             const bool slot_ok = page >= 0 && page < p.physical_blocks && slot >= 0 && slot < kPageTokens;
             if (!slot_ok && lane == 0) report_status(p.status, kStatusIndexOutOfBounds);
             const size_t cache_row = ((static_cast<size_t>(slot_ok ? page : 0) * kPageTokens + (slot_ok ? slot : 0)) *
                                           p.kv_heads + g) * HD;
-            uint32_t *k_out = reinterpret_cast<uint32_t *>(static_cast<T *>(p.key_rows) + cache_row);
-            uint32_t *v_out = reinterpret_cast<uint32_t *>(static_cast<T *>(p.value_rows) + cache_row);
+            uint32_t *k_out = reinterpret_cast<uint32_t *>(static_cast<T *>(x.key_rows) + cache_row);
+            uint32_t *v_out = reinterpret_cast<uint32_t *>(static_cast<T *>(x.value_rows) + cache_row);
             uint32_t kf[KSTEPS][2];
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) {
                 kf[ks][0] = k32[ks * 8 + quad];
                 kf[ks][1] = k32[ks * 8 + 4 + quad];
             }
-            rotate_query_fragments<T, HD>(kf, p, b, row, quad, false);   // the same rotation, without the query's norm
+            rotate_query_fragments<T, HD>(kf, p, x, b, row, quad, false);   // the same rotation, without the query's norm
             auto low = [](uint32_t word) {
                 T value;
                 *reinterpret_cast<uint16_t *>(&value) = static_cast<uint16_t>(word & 0xffffu);
@@ -638,7 +646,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
     // A warp whose wait ran out (status 2 is set, the row's result is void) keeps the CTA alive until copies that were
     // issued into its shared memory have landed.
     if (failed) linger_after_timeout();
-    if (!EXTRAS || p.tickets == nullptr || direct || p.partials_only) return;
+    if (!EXTRAS || x.tickets == nullptr || direct || p.partials_only) return;
     // ---------------- the last split of the row to finish folds the row ----------------
     // Every split of a (sequence, KV head) row takes a ticket once its partials are written and visible; the one
     // that draws the last ticket reads all of them back (through L2: they were written by other SMs) and writes the
@@ -649,7 +657,7 @@ __device__ __forceinline__ void paged_decode_body(const CUtensorMap &k_map, cons
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        uint32_t *ticket = p.tickets + static_cast<size_t>(b) * p.kv_heads + g;
+        uint32_t *ticket = x.tickets + static_cast<size_t>(b) * p.kv_heads + g;
         const uint32_t drawn = atomicAdd(ticket, 1u);
         shared_last = drawn == static_cast<uint32_t>(n_splits - 1) ? 1 : 0;
         if (shared_last) *ticket = 0u;  // every other split of the row has drawn already
@@ -686,14 +694,15 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     none.lse_out = nullptr;
     none.softcap = 0.0f;
     none.hidden = nullptr;
-    paged_decode_body<T, HD, false>(k_map, v_map, p, none);
+    StepExtras unused = {};  // never read without EXTRAS
+    paged_decode_body<T, HD, false>(k_map, v_map, p, unused, none);
 }
 
 // The classic form with the decode step's extras (see paged_decode_body).
 template <typename T, int HD>
 __global__ void __launch_bounds__(kDecodeThreads, 3)
     paged_decode_step_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                             const DecodeParams p) {
+                             const DecodeParams p, const StepExtras x) {
     RaggedDecode none;  // never read by the classic form
     none.pages = nullptr;
     none.first = nullptr;
@@ -702,13 +711,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     none.lse_out = nullptr;
     none.softcap = 0.0f;
     none.hidden = nullptr;
-    paged_decode_body<T, HD, false, false, true>(k_map, v_map, p, none);
+    paged_decode_body<T, HD, false, false, true>(k_map, v_map, p, x, none);
 }
 
 template <typename T, int HD>
 __global__ void __launch_bounds__(kDecodeThreads, 3)
     paged_decode_fused_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                              const DecodeParams p) {
+                              const DecodeParams p, const StepExtras x) {
     RaggedDecode none;  // never read by this form
     none.pages = nullptr;
     none.first = nullptr;
@@ -717,14 +726,15 @@ __global__ void __launch_bounds__(kDecodeThreads, 3)
     none.lse_out = nullptr;
     none.softcap = 0.0f;
     none.hidden = nullptr;
-    paged_decode_body<T, HD, false, true, true>(k_map, v_map, p, none);
+    paged_decode_body<T, HD, false, true, true>(k_map, v_map, p, x, none);
 }
 
 template <typename T, int HD, bool OPTIONS>
 __global__ void __launch_bounds__(kDecodeThreads, 3)
     paged_decode_ragged_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                                const DecodeParams p, const RaggedDecode ragged) {
-    paged_decode_body<T, HD, true, false, false, OPTIONS>(k_map, v_map, p, ragged);
+    StepExtras unused = {};  // never read without EXTRAS
+    paged_decode_body<T, HD, true, false, false, OPTIONS>(k_map, v_map, p, unused, ragged);
 }
 
 // Folds the split partials of every (sequence, head) row that needed more than one split.
@@ -769,16 +779,17 @@ __global__ void decode_combine_kernel(T *out, const float *attn_partial, const f
 }
 
 template <typename T, int HD, bool RAGGED>
-int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedDecode &shape, const void *key_cache,
+int launch_decode(cudaStream_t stream, const DecodeParams &params, const StepExtras &extras, const RaggedDecode &shape,
+                  const void *key_cache,
                   const void *value_cache, size_t batch) {
     static int configured[kMaxDevices] = {0};  // one table per instantiation, one entry per device
     constexpr int smem = decode_smem_bytes<HD>();
-    const bool fused = !RAGGED && params.qkv != nullptr;
+    const bool fused = !RAGGED && extras.qkv != nullptr;
     const bool capped = RAGGED && (shape.softcap > 0.0f || shape.hidden != nullptr);
     // the plain drop-in call takes the kernel without the decode step's extras
-    const bool extras = !RAGGED && !fused &&
-                        (params.stable_paging != 0 || params.early_release != 0 || params.warm.bytes != 0 ||
-                         params.rope_cos != nullptr || params.tickets != nullptr);
+    const bool step = !RAGGED && !fused &&
+                        (extras.stable_paging != 0 || extras.early_release != 0 || extras.warm.bytes != 0 ||
+                         extras.rope_cos != nullptr || extras.tickets != nullptr);
     if (RAGGED) {
         static int configured_capped[kMaxDevices] = {0};
         if (capped) {
@@ -789,7 +800,7 @@ int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedD
     } else if (fused) {
         static int configured_fused[kMaxDevices] = {0};
         SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_fused_kernel<T, HD>, smem, configured_fused));
-    } else if (extras) {
+    } else if (step) {
         static int configured_step[kMaxDevices] = {0};
         SINGE_CUDA_TRY(ensure_dynamic_shared(paged_decode_step_kernel<T, HD>, smem, configured_step));
     } else {
@@ -817,10 +828,10 @@ int launch_decode(cudaStream_t stream, const DecodeParams &params, const RaggedD
                                         stream, kLaunchDecode, 1, k_map, v_map, params, shape));
     } else if (fused) {
         SINGE_CUDA_TRY(launch_dependent(paged_decode_fused_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,
-                                        kLaunchDecode, 1, k_map, v_map, params));
-    } else if (extras) {
+                                        kLaunchDecode, 1, k_map, v_map, params, extras));
+    } else if (step) {
         SINGE_CUDA_TRY(launch_dependent(paged_decode_step_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,
-                                        kLaunchDecode, 1, k_map, v_map, params));
+                                        kLaunchDecode, 1, k_map, v_map, params, extras));
     } else {
         SINGE_CUDA_TRY(launch_dependent(paged_decode_kernel<T, HD>, grid, dim3(kDecodeThreads), smem, stream,
                                         kLaunchDecode, 1, k_map, v_map, params));
@@ -860,33 +871,34 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
                         const RaggedDecode *ragged, unsigned hints, const QueryRotation *rotation, uint32_t *tickets,
                         const FusedStep *fused) {
     DecodeParams params;
-    params.tickets = ragged == nullptr && !partials_only ? tickets : nullptr;
-    params.qkv = nullptr;
-    params.qkv_stride = 0;
-    params.key_rows = params.value_rows = nullptr;
-    params.write_pages = params.write_slots = nullptr;
+    StepExtras extras;
+    extras.tickets = ragged == nullptr && !partials_only ? tickets : nullptr;
+    extras.qkv = nullptr;
+    extras.qkv_stride = 0;
+    extras.key_rows = extras.value_rows = nullptr;
+    extras.write_pages = extras.write_slots = nullptr;
     if (fused != nullptr && ragged == nullptr && rotation != nullptr && element == 0 && !partials_only) {
-        params.qkv = fused->qkv;
-        params.qkv_stride = fused->qkv_stride;
-        params.key_rows = const_cast<void *>(key_cache);
-        params.value_rows = const_cast<void *>(value_cache);
-        params.write_pages = fused->write_pages;
-        params.write_slots = fused->write_slots;
+        extras.qkv = fused->qkv;
+        extras.qkv_stride = fused->qkv_stride;
+        extras.key_rows = const_cast<void *>(key_cache);
+        extras.value_rows = const_cast<void *>(value_cache);
+        extras.write_pages = fused->write_pages;
+        extras.write_slots = fused->write_slots;
     }
-    params.rope_cos = params.rope_sin = params.rope_positions = params.query_gain = nullptr;
-    params.rope_index_width = 8;
-    params.rope_capacity = 0;
-    params.query_norm = 0;
-    params.query_norm_eps = 0.0f;
+    extras.rope_cos = extras.rope_sin = extras.rope_positions = extras.query_gain = nullptr;
+    extras.rope_index_width = 8;
+    extras.rope_capacity = 0;
+    extras.query_norm = 0;
+    extras.query_norm_eps = 0.0f;
     if (rotation != nullptr && ragged == nullptr) {
-        params.rope_cos = rotation->cos;
-        params.rope_sin = rotation->sin;
-        params.rope_positions = rotation->positions;
-        params.rope_index_width = rotation->index_width;
-        params.rope_capacity = rotation->capacity;
-        params.query_gain = rotation->gain;
-        params.query_norm = rotation->normalise;
-        params.query_norm_eps = rotation->eps;
+        extras.rope_cos = rotation->cos;
+        extras.rope_sin = rotation->sin;
+        extras.rope_positions = rotation->positions;
+        extras.rope_index_width = rotation->index_width;
+        extras.rope_capacity = rotation->capacity;
+        extras.query_gain = rotation->gain;
+        extras.query_norm = rotation->normalise;
+        extras.query_norm_eps = rotation->eps;
     }
     RaggedDecode none;
     none.pages = nullptr;
@@ -913,11 +925,11 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
     params.split_tokens = static_cast<int>(paged_decode_split_tokens(bound, max_splits, kPageTokens));
     params.max_splits = static_cast<int>(max_splits);
     params.partials_only = partials_only ? 1 : 0;
-    params.stable_paging = (ragged == nullptr && (hints & SINGE_HINT_STABLE_PAGING) != 0) ? 1 : 0;
+    extras.stable_paging = (ragged == nullptr && (hints & SINGE_HINT_STABLE_PAGING) != 0) ? 1 : 0;
     // One wave: three CTAs are resident per SM.
-    params.early_release = kv_heads * max_splits * batch <= static_cast<size_t>(3 * device_sm_count()) ? 1 : 0;
-    params.prefetch_pages = g_decode_prefetch_pages;
-    params.warm = ragged == nullptr ? take_pending_warm() : WarmRange{nullptr, 0};
+    extras.early_release = kv_heads * max_splits * batch <= static_cast<size_t>(3 * device_sm_count()) ? 1 : 0;
+    extras.prefetch_pages = g_decode_prefetch_pages;
+    extras.warm = ragged == nullptr ? take_pending_warm() : WarmRange{nullptr, 0};
     params.scale_log2 = scale * 1.4426950408889634f;
     params.status = status;
     if (batch > 65535 || max_splits > 65535 || kv_heads > 0x7fffffffull) {
@@ -927,24 +939,24 @@ int paged_decode_splitk(cudaStream_t stream, int element, void *out, float *attn
     if (element == 0) {
         if (ragged != nullptr) {
             result = head_dim == 128
-                         ? launch_decode<__nv_bfloat16, 128, true>(stream, params, shape, key_cache, value_cache, batch)
-                         : launch_decode<__nv_bfloat16, 64, true>(stream, params, shape, key_cache, value_cache, batch);
+                         ? launch_decode<__nv_bfloat16, 128, true>(stream, params, extras, shape, key_cache, value_cache, batch)
+                         : launch_decode<__nv_bfloat16, 64, true>(stream, params, extras, shape, key_cache, value_cache, batch);
         } else {
             result = head_dim == 128
-                         ? launch_decode<__nv_bfloat16, 128, false>(stream, params, shape, key_cache, value_cache, batch)
-                         : launch_decode<__nv_bfloat16, 64, false>(stream, params, shape, key_cache, value_cache, batch);
+                         ? launch_decode<__nv_bfloat16, 128, false>(stream, params, extras, shape, key_cache, value_cache, batch)
+                         : launch_decode<__nv_bfloat16, 64, false>(stream, params, extras, shape, key_cache, value_cache, batch);
         }
     } else {
         if (ragged != nullptr) {
-            result = head_dim == 128 ? launch_decode<__half, 128, true>(stream, params, shape, key_cache, value_cache, batch)
-                                     : launch_decode<__half, 64, true>(stream, params, shape, key_cache, value_cache, batch);
+            result = head_dim == 128 ? launch_decode<__half, 128, true>(stream, params, extras, shape, key_cache, value_cache, batch)
+                                     : launch_decode<__half, 64, true>(stream, params, extras, shape, key_cache, value_cache, batch);
         } else {
-            result = head_dim == 128 ? launch_decode<__half, 128, false>(stream, params, shape, key_cache, value_cache, batch)
-                                     : launch_decode<__half, 64, false>(stream, params, shape, key_cache, value_cache, batch);
+            result = head_dim == 128 ? launch_decode<__half, 128, false>(stream, params, extras, shape, key_cache, value_cache, batch)
+                                     : launch_decode<__half, 64, false>(stream, params, extras, shape, key_cache, value_cache, batch);
         }
     }
     SINGE_TRY(result);
-    if (!partials_only && max_splits > 1 && params.tickets == nullptr) {
+    if (!partials_only && max_splits > 1 && extras.tickets == nullptr) {
         dim3 grid(static_cast<unsigned>(heads), static_cast<unsigned>(batch));
         const int threads = head_dim >= 128 ? 128 : 64;
 #define SINGE_COMBINE(T, RAGGED_)                                                                                  \

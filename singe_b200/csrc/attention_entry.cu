@@ -1,6 +1,7 @@
 // C-ABI entry points of the attention surfaces: host-side validation that mirrors the reference's
 // config validators, dispatch between the specialised kernels and the general one, and the policies
 // that describe each surface to the general kernel.
+#include <cmath>
 #include <mutex>
 
 #include "attention_general.cuh"
@@ -537,6 +538,41 @@ size_t default_splits(size_t batch, size_t kv_heads, size_t bound_tokens) {
     return splits;
 }
 
+// Split count of the drop-in decode, whose caller gives no budget and whose lengths are device data.  Pieces of 512 keys
+// by default (default_splits); a larger piece out of the sizes measured on B200 when a wave model prefers it: a grid
+// of C = batch * kv_heads * ceil(bound / piece) CTAs runs in ceil(C / slots) waves (three CTAs per SM) of piece + 200
+// key-times each -- a CTA's start-up is worth about 200 keys of streaming -- with every sequence taken at the bound.
+// Only choices that still make 2.5 waves compete, so that batches whose real lengths are well below the bound keep
+// enough CTAs in flight.  Measured on 20 mixes (8 - 128 sequences, bounds 1024 - 8192, equal and uniformly drawn
+// lengths): 3.5 % less time in total, no mix more than 1 % slower, and the 32-sequence / 4096-key shape 4 - 5 %
+// faster on each of six draws of its lengths.
+size_t wave_aware_splits(size_t batch, size_t kv_heads, size_t bound_tokens, size_t page) {
+    const size_t base = default_splits(batch, kv_heads, bound_tokens);
+    const double slots = 3.0 * static_cast<double>(device_sm_count());
+    auto cost_of = [&](size_t splits, double *waves_out) {
+        size_t piece = (bound_tokens + splits - 1) / splits;
+        piece = (piece + page - 1) / page * page;
+        const size_t live = (bound_tokens + piece - 1) / piece;
+        const double waves = static_cast<double>(batch * kv_heads * live) / slots;
+        if (waves_out != nullptr) *waves_out = waves;
+        return std::ceil(waves) * static_cast<double>(piece + 200);
+    };
+    size_t best = base;
+    double best_cost = cost_of(base, nullptr);
+    const size_t sizes[] = {640, 832, 1024, 1360, 2048};
+    for (size_t size : sizes) {
+        const size_t splits = (bound_tokens + size - 1) / size;
+        if (splits < 1 || splits >= base) continue;  // never finer than the default
+        double waves = 0.0;
+        const double cost = cost_of(splits, &waves);
+        if (waves >= 2.5 && cost < best_cost) {
+            best = splits;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
 template <typename T>
 int decode_general(cudaStream_t stream, void *out, const void *query, const void *key_cache, const void *value_cache,
                    const int32_t *lens, const uint32_t *table, size_t batch, size_t heads, size_t kv_heads,
@@ -569,7 +605,7 @@ int decode_half(cudaStream_t stream, int element, void *out, const void *query, 
     }
     // The tiled kernel puts the batch in a grid dimension of at most 65535; larger batches keep the general kernel.
     if (batch <= 65535 && paged_decode_fast_path(heads, kv_heads, head_dim, block_size, key_cache, value_cache, query)) {
-        const size_t splits = default_splits(batch, kv_heads, stride * block_size);
+        const size_t splits = wave_aware_splits(batch, kv_heads, stride * block_size, block_size);
         float *scratch = nullptr;
         const size_t rows = batch * heads * splits;
         SINGE_TRY(workspace_for(stream, rows * (head_dim + 1), &scratch));

@@ -158,7 +158,7 @@ def sum_over_ranks(value: float, group) -> float:
 # ----------------------------------------------------------------------------------------------------------
 
 # DRAM bytes one launch of paged_decode_kernel moves on the config-2 workload (seed 1), from an ncu capture of this
-# very command (dram__bytes_read.sum + dram__bytes_write.sum): 277.40 MB read + 8.50 MB written (the split-K partials).
+# very command (dram__bytes_read.sum + dram__bytes_write.sum): 277.49 MB read + 7.69 MB written (split-K partials, output).
 DECODE_DRAM_TRAFFIC = 285_181_184
 
 

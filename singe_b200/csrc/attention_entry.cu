@@ -720,7 +720,7 @@ int tensor_paged(cudaStream_t stream, void *out, float *lse, const void *query, 
         size_t guess = 2 * average;
         if (window > 0 && guess > window + page_size) guess = window + page_size;  // what a window leaves of a sequence
         if (guess < page_size) guess = page_size;
-        const size_t splits = default_splits(sequences, kv_heads, guess);
+        const size_t splits = wave_aware_splits(sequences, kv_heads, guess, page_size);
         // pieces of at least 512 keys when that still gives the machine enough CTAs (what default_splits assumes)
         const int min_piece = sequences * kv_heads * ((guess + 511) / 512) >= static_cast<size_t>(device_sm_count()) * 4
                                   ? 512

@@ -449,11 +449,13 @@ int singe_attend_f32(singe_stream_t stream, float *out, const float *query, cons
  *   singe_tcgen05_matmul in kernel_plan/source/tcgen05.rs:137-266, singe_dot_product in dot_product.rs:133-243).
  *   CPU meaning: singe-kernel/src/cpu/matmul/mod.rs:12-45, blocked.rs:27-95,
  *   singe/src/backend/cpu/binary/matmul.rs:18-43 (bf16 widened to f32, one rounding of the result).
- * out[rows, columns] = lhs . rhs with f32 accumulation.  lhs is [rows, reduction] (transpose_lhs == 0);
- * rhs is either a linear layer's weight [columns, reduction] (transpose_rhs == 1, MatmulConfig::
- * row_major_transposed_rhs) or a row-major [reduction, columns] operand (transpose_rhs == 0,
- * MatmulConfig::row_major :190-202), whose tiles the tensor core reads MN-major.  Row strides and start
- * addresses are multiples of 16 bytes (TMA); a transposed lhs returns SINGE_ERR_UNSUPPORTED_CONFIGURATION.  `_bf16` rounds the result once to bf16 (Tensor surface);
+ * out[rows, columns] = lhs . rhs with f32 accumulation.  lhs is [rows, reduction] or, with
+ * transpose_lhs != 0, [reduction, rows] (MatmulConfig::row_major_transposed_lhs :204-216); rhs is either a
+ * linear layer's weight [columns, reduction] (transpose_rhs == 1, MatmulConfig::row_major_transposed_rhs)
+ * or a row-major [reduction, columns] operand (transpose_rhs == 0, MatmulConfig::row_major :190-202).
+ * Operands whose contraction axis is not the contiguous one are read by the tensor core MN-major.  Row
+ * strides and start addresses must be multiples of 16 bytes (TMA), else
+ * SINGE_ERR_UNSUPPORTED_CONFIGURATION.  `_bf16` rounds the result once to bf16 (Tensor surface);
  * `_f32` keeps f32 (singe-kernel surface).
  * ================================================================================================= */
 int singe_matmul_bf16_bf16(singe_stream_t stream, void *out, const void *lhs, const void *rhs, size_t rows,

@@ -55,6 +55,7 @@ struct GemmParams {
     int rhs_kn;        // 1: rhs is stored [K, N] (transpose_rhs == 0): its tiles are staged N-contiguous and the MMA
                        //    reads them as an MN-major operand; 0: [N, K], K-major (a linear layer's weight)
     uint32_t *error;   // sticky device error word (2 = a bounded wait ran out)
+    int lhs_km;        // 1: lhs is stored [K, M] (transpose_lhs != 0), staged M-contiguous and read as an MN-major A operand
     WarmRange warm;    // pulled into L2 by the epilogue warps while they have nothing else to do
 };
 
@@ -112,12 +113,14 @@ __device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tile
 // KPS = 64-wide K slices per pipeline stage.  Skinny problems stream the weight matrix from HBM; with one
 // slice per stage every request touches 128 contiguous bytes of a weight row, which opens a DRAM page for two
 // bursts.  Several adjacent slices issued together give the memory controller 512-1024 contiguous bytes per row.
-template <int BN, int KPS, bool KN>
+// AT: the left operand is stored [K, M]; its 128 x 64 tile is two boxes of 64 K-rows x 64 M-columns, 8 KB apart, read
+// MN-major like a [K, N] right operand.
+template <int BN, int KPS, bool KN, bool AT = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                      const GemmParams p) {
     constexpr uint32_t kTmemColumns = 2 * BN < 32 ? 32 : 2 * BN;
-    constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, 0, KN ? 1 : 0);  // KN: B read MN-major
+    constexpr uint32_t kIdesc = make_instr_desc(kBlockM, BN, true, AT ? 1 : 0, KN ? 1 : 0);  // KN / AT: MN-major reads
     constexpr int kBBytes = BN * 128;
 
     grid_launch_dependents();
@@ -217,7 +220,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
                         // slices past K are zero-filled by TMA and add nothing
-                        tma_load_2d(stage + sub * a_bytes, &a_map, full, (kb * KPS + sub) * kBlockK, tm * kBlockM);
+                        if (AT) {
+                            tma_load_2d(stage + sub * a_bytes, &a_map, full, tm * kBlockM, (kb * KPS + sub) * kBlockK);
+                            tma_load_2d(stage + sub * a_bytes + 8192, &a_map, full, tm * kBlockM + 64,
+                                        (kb * KPS + sub) * kBlockK);
+                        } else {
+                            tma_load_2d(stage + sub * a_bytes, &a_map, full, (kb * KPS + sub) * kBlockK, tm * kBlockM);
+                        }
                     }
                     if (!early) {
 #pragma unroll
@@ -254,13 +263,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     const uint32_t stage = base + s * p.stage_bytes;
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
-                        const uint64_t a_desc = make_smem_desc(stage + sub * a_bytes, 16, 1024);
+                        const uint64_t a_desc = make_smem_desc(stage + sub * a_bytes, BWalk<AT>::kLeadingBytes, 1024);
                         const uint64_t b_desc =
                             make_smem_desc(stage + KPS * a_bytes + sub * kBBytes, BWalk<KN>::kLeadingBytes, 1024);
 #pragma unroll
                         for (int ks = 0; ks < kBlockK / 16; ++ks) {
-                            // 16 bf16 of K = 32 bytes = 2 descriptor address units of A
-                            umma_ss(tmem_d, a_desc + 2 * ks, b_desc + BWalk<KN>::kStep * ks, kIdesc,
+                            // 16 bf16 of K: 2 descriptor address units along a K-major row, 128 down an MN-major tile
+                            umma_ss(tmem_d, a_desc + BWalk<AT>::kStep * ks, b_desc + BWalk<KN>::kStep * ks, kIdesc,
                                     (kb > 0 || sub > 0 || ks > 0) ? 1u : 0u);
                         }
                     }
@@ -814,7 +823,7 @@ int launch_gemm_splitk(cudaStream_t stream, GemmParams params, const void *lhs, 
     return launch_status();
 }
 
-template <int BN, int KPS>
+template <int BN, int KPS, bool AT = false>
 int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const void *rhs, size_t lhs_row_stride,
                 size_t rhs_row_stride) {
     const int kSmemLimit = shared_limit(params);
@@ -837,13 +846,19 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
     static int configured[kMaxDevices] = {0};
     static int configured_kn[kMaxDevices] = {0};
     if (params.rhs_kn) {
-        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS, kHasKN>, smem, configured_kn));
+        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS, kHasKN, AT>, smem, configured_kn));
     } else {
-        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS, false>, smem, configured));
+        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS, false, AT>, smem, configured));
     }
 
     CUtensorMap a_map, b_map;
-    {
+    if (AT) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(params.m), static_cast<uint64_t>(params.k)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(lhs_row_stride) * 2};
+        const uint32_t box[2] = {64, kBlockK};
+        SINGE_TRY(encode_tensor_map(&a_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, lhs, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+    } else {
         const uint64_t dims[2] = {static_cast<uint64_t>(params.k), static_cast<uint64_t>(params.m)};
         const uint64_t strides[1] = {static_cast<uint64_t>(lhs_row_stride) * 2};
         const uint32_t box[2] = {kBlockK, static_cast<uint32_t>(params.a_rows)};
@@ -866,11 +881,11 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
     const int total = params.tiles_m * params.tiles_n;
     const int grid = total < device_sm_count() ? total : device_sm_count();
     if (params.rhs_kn) {
-        SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS, kHasKN>, dim3(grid), dim3(kGemmThreads), smem, stream,
-                                        kLaunchGemm, 1, a_map, b_map, params));
+        SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS, kHasKN, AT>, dim3(grid), dim3(kGemmThreads), smem,
+                                        stream, kLaunchGemm, 1, a_map, b_map, params));
     } else {
-        SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS, false>, dim3(grid), dim3(kGemmThreads), smem, stream,
-                                        kLaunchGemm, 1, a_map, b_map, params));
+        SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS, false, AT>, dim3(grid), dim3(kGemmThreads), smem,
+                                        stream, kLaunchGemm, 1, a_map, b_map, params));
     }
     return launch_status();
 }
@@ -897,8 +912,9 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
     // Tensor-core path: linear-layer layout, 16-byte aligned rows for TMA.
     const bool aligned = ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15u) == 0 &&
                          lhs_row_stride % 8 == 0 && rhs_row_stride % 8 == 0;
-    // lhs must be [M, K]; rhs may be [N, K] (a linear layer's weight, transpose_rhs != 0) or [K, N]
-    if (transpose_lhs || !aligned || (gated && !transpose_rhs)) {
+    // lhs may be [M, K] or [K, M] (transpose_lhs != 0); rhs [N, K] (a linear layer's weight, transpose_rhs != 0) or
+    // [K, N].  The gated epilogue belongs to the linear-layer form.
+    if (!aligned || (gated && (!transpose_rhs || transpose_lhs))) {
         return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
     }
     GemmParams params;
@@ -909,6 +925,7 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
     params.stable_rhs = (hints & SINGE_HINT_STABLE_WEIGHTS) != 0 ? 1 : 0;
     params.warm = take_pending_warm();
     params.rhs_kn = transpose_rhs ? 0 : 1;
+    params.lhs_km = transpose_lhs ? 1 : 0;
     params.prefetch_blocks = 0;
     params.m = static_cast<int>(rows);
     params.n = static_cast<int>(columns);
@@ -917,7 +934,7 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
     params.tiles_m = (params.m + kBlockM - 1) / kBlockM;
     params.k_blocks = (params.k + kBlockK - 1) / kBlockK;
     int a_rows = kBlockM;
-    if (params.m < kBlockM) {
+    if (params.m < kBlockM && !params.lhs_km) {
         a_rows = (params.m + 7) / 8 * 8;
     }
     params.a_rows = a_rows;
@@ -989,6 +1006,13 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
         while (slices > 1 && slices * (params.a_rows + bn) * 128 * 2 > room) slices >>= 1;
     }
     if (forced_slices != 0) slices = forced_slices;
+    if (params.lhs_km) {
+        // A [K, M] left operand (no caller on the decode path has one) runs the persistent kernel, whole 128-row tiles
+        const int wide = (params.m > kBlockM && tiles(256) >= sms) ? 256 : (params.n > 64 ? 128 : 64);
+        if (wide == 256) return launch_gemm<256, 1, true>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
+        if (wide == 128) return launch_gemm<128, 1, true>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
+        return launch_gemm<64, 1, true>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
+    }
     if (splits > 1) {
         if (params.m > kBlockM || (splits != 2 && splits != 4 && splits != 8)) return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
 #define SINGE_SPLITK_CASE(BN_, KPS_)                                                                             \

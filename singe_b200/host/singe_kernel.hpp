@@ -243,6 +243,14 @@ struct MatmulConfig {
         return {rows, columns, reduction, reduction, columns, columns, false, false};
     }
 
+    static MatmulConfig row_major_transposed_lhs(size_t rows, size_t columns, size_t reduction) {
+        return {rows, columns, reduction, rows, columns, columns, true, false};
+    }
+
+    static MatmulConfig row_major_transposed_inputs(size_t rows, size_t columns, size_t reduction) {
+        return {rows, columns, reduction, rows, reduction, columns, true, true};
+    }
+
     static MatmulConfig row_major_transposed_rhs(size_t rows, size_t columns, size_t reduction) {
         return {rows, columns, reduction, reduction, reduction, columns, false, true};
     }

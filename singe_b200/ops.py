@@ -158,8 +158,18 @@ class MatmulConfig:
         return cls(rows, columns, reduction, reduction, columns, columns, False, False)
 
     @classmethod
+    def row_major_transposed_lhs(cls, rows, columns, reduction):
+        """lhs [K, M], rhs [K, N] (:204-216)."""
+        return cls(rows, columns, reduction, rows, columns, columns, True, False)
+
+    @classmethod
     def row_major_transposed_rhs(cls, rows, columns, reduction):
         return cls(rows, columns, reduction, reduction, reduction, columns, False, True)
+
+    @classmethod
+    def row_major_transposed_inputs(cls, rows, columns, reduction):
+        """lhs [K, M], rhs [N, K] (:232-244)."""
+        return cls(rows, columns, reduction, rows, reduction, columns, True, True)
 
 
 # ------------------------------------------------------------------------------------------------

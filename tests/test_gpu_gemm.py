@@ -168,8 +168,7 @@ def test_matmul_validation_mirrors_the_reference():
     assert lib.singe_matmul_bf16_bf16(None, one, one, one, 4, 4, 8, 4, 8, 4, 0, 1) == ks.ERR_INVALID_LENGTH  # lhs stride < k
     assert lib.singe_matmul_bf16_bf16(None, one, one, one, 4, 4, 8, 8, 8, 2, 0, 1) == ks.ERR_INVALID_LENGTH  # out stride < n
     assert lib.singe_matmul_bf16_bf16(None, None, one, one, 4, 4, 8, 8, 8, 4, 0, 1) == ks.ERR_NULL_POINTER
-    # a transposed left operand is refused, not silently mis-computed
-    assert lib.singe_matmul_bf16_bf16(None, one, one, one, 8, 8, 8, 8, 8, 8, 1, 1) == ks.ERR_UNSUPPORTED_CONFIGURATION
+    assert lib.singe_matmul_bf16_bf16(None, one, one, one, 16, 8, 8, 8, 8, 8, 1, 1) == ks.ERR_INVALID_LENGTH  # [K, M] lhs stride < m
     assert lib.singe_matmul_bf16_bf16(None, one, one, one, 8, 8, 8, 8, 4, 8, 0, 0) == ks.ERR_INVALID_LENGTH  # [K, N] rhs stride < n
 
 
@@ -212,3 +211,38 @@ def test_row_major_right_operand_with_strides():
     assert ops.take_device_error() == 0
     ref = oracle.linear_bf16_f32(_bits(x), _bits(w), m=m, n=n, k=k)
     assert_close_bf16(host(out), ref, "strided [K,N] rhs")
+
+
+@pytest.mark.parametrize("transpose_rhs", [True, False])
+@pytest.mark.parametrize("m,n,k", [(8, 256, 512), (200, 136, 72), (256, 384, 4096), (136, 1000, 520), (304, 4096, 256),
+                                   (4096, 64, 128)])
+def test_transposed_left_operand_matches_the_oracle(m, n, k, transpose_rhs):
+    # lhs stored [K, M] (MatmulConfig::row_major_transposed_lhs / _transposed_inputs, matmul.rs:204-246): its tiles are
+    # staged M-contiguous and read MN-major, like a [K, N] right operand.
+    x, w = _case(m, n, k, seed=13)
+    lhs = x.t().contiguous()                              # [K, M]
+    rhs = w if transpose_rhs else w.t().contiguous()      # [N, K] or [K, N]
+    out = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    config = ops.MatmulConfig(m, n, k, m, k if transpose_rhs else n, n, True, transpose_rhs)
+    ops.matmul_bf16(out, lhs, rhs, config)
+    rounded = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    ops.matmul_bf16(rounded, lhs, rhs, config)
+    torch.cuda.synchronize()
+    assert ops.take_device_error() == 0
+    ref = oracle.linear_bf16_f32(_bits(x), _bits(w), m=m, n=n, k=k)
+    what = f"[K,M] lhs {m}x{n}x{k} transpose_rhs={transpose_rhs}"
+    assert_close_bf16(host(out), ref, what)
+    assert_close_bf16(host(rounded), oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(ref)), what + " bf16")
+    scale = np.abs(ref).max() + 1e-6
+    assert np.abs(host(out) - ref).max() / scale < 2e-3
+
+
+def test_rows_that_are_not_16_byte_multiples_are_refused():
+    # TMA addresses rows of the operands as they lie in memory: a row stride that is not a multiple of 16 bytes (here
+    # a [K, M] left operand with M = 129) is refused, not mis-read.
+    x, w = _case(129, 64, 64, seed=15)
+    lhs = x.t().contiguous()
+    out = torch.empty((129, 64), dtype=torch.float32, device="cuda")
+    code = ks.lib().singe_matmul_bf16_f32(None, out.data_ptr(), lhs.data_ptr(), w.data_ptr(), 129, 64, 64, 129, 64, 64,
+                                          1, 1)
+    assert code == ks.ERR_UNSUPPORTED_CONFIGURATION

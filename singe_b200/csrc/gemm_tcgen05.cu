@@ -13,7 +13,10 @@
 //            k-block, the accumulator to the epilogue.
 //   warps 2-5 epilogue: tcgen05.ld 32 columns at a time, convert, store; then hand the accumulator back, so
 //            the MMA of the next tile overlaps this tile's epilogue.
-// Both operands are K-major, so M/N/K tails come for free from TMA's zero fill; stores are masked.
+// In the linear-layer form both operands are K-major, so M/N/K tails come for free from TMA's zero fill; stores are
+// masked.  The other layouts of MatmulConfig (lhs [K, M], rhs [K, N]; singe-kernel/src/cuda/matmul.rs:190-246) are
+// template forms of the same kernels: such an operand is staged in boxes of 64 contiguous M or N elements and read
+// by the MMA as an MN-major operand.
 // Small M (decode batches) uses narrow BN so that enough CTAs stream the weight matrix to fill HBM, and a
 // short A box: rows past the box are stale shared memory, which only reaches output rows that are not stored.
 // Tiles are ordered in groups of eight M-tiles so that one wave of CTAs shares A and B tiles through L2.

@@ -18,6 +18,9 @@
 //   The four warps' (max, sum, O) states are merged through shared memory; the CTA writes either the
 //   final row (the sequence fits one split) or a normalised partial + natural-log LSE.
 //   decode_combine_kernel folds the partials of sequences that needed more than one split.
+// One body, four kernels: the plain drop-in kernel; the decode-step kernel (reads ahead of the dependency wait,
+// rotates its queries, may fold its row itself); the fused decode-step kernel (also rotates and stores the step's new
+// K/V row); and the ragged kernel of the Tensor surface (FlashInfer page lists, optional score cap and sliding window).
 // Every mbarrier wait is bounded; a wait that runs out sets status code 2 and the CTA leaves.
 #include "common.cuh"
 

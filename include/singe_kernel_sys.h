@@ -554,7 +554,8 @@ int singe_allreduce_add_rms_norm_bf16(singe_stream_t stream, void *hidden, void 
  * Data crosses NVLink as 8-byte packets {4 bytes data, 4-byte launch epoch}: no flags, fences or atomics.
  *   partial          : local [rows, width], this rank's partial sums (read only)
  *   receive, gather  : HOST arrays of `world` device pointers, entry r being rank r's buffer as mapped into this
- *                      process; receive holds world * rpr * width * 4 bytes, gather rows * width * 4 bytes, both
+ *                      process; receive holds world * rpr * width * 4 bytes, gather (rows + rpr) * width * 4 bytes
+ *                      (all normalised rows, then a staging area for the rows this rank owns), both
  *                      zero at first use and owned by the collective (packet format, not for the caller to read)
  *   state            : local uint32[4], zero at first use; state[2] != 0 shortens every wait to state[2] * 1024
  *                      clock cycles (the default is a few seconds).  The one-shot call reads state[2] the same way.

@@ -196,7 +196,10 @@ __global__ void __launch_bounds__(kReduceThreads)
 //   phase 1  every rank pushes each of its partial rows into the owner's receive buffer (slot = sender);
 //   phase 2  the threads of an owner's CTA poll their own packets of all `world` slots, sum them in rank order in
 //            f32, round to bf16 (the all-reduce's result type), add the residual (only the owner keeps a row of the
-//            residual stream up to date), normalise, and push the normalised row to every rank as packets;
+//            residual stream up to date), normalise, and leave the normalised row as packets in a local staging area;
+//   phase 2b CTA (r, j) of every rank takes owned row r out of the staging area and pushes it to rank j: the rows of
+//            one collective are 0.9 MB at eight ranks, which eight owner CTAs alone took 3 us to issue -- an SM
+//            pushes about 45 GB/s over NVLink -- so the push is spread over all CTAs of the launch;
 //   phase 3  every rank unpacks the normalised rows it received into the plain buffer the next GEMM reads.
 // Per rank and collective 2 x 7/8 x 1 MB leave (packets double the bytes) instead of 3.5 MB arriving behind a
 // load latency.  The epoch only grows and lives on the device, so the kernel replays inside a CUDA graph; packets of
@@ -211,7 +214,9 @@ __global__ void __launch_bounds__(kReduceThreads)
 struct TwoPhaseParams {
     const __nv_bfloat16 *partial;   // local [rows, width]: this rank's partial sums
     uint4 *receive[kMaxPeers];      // rank j's receive packets [world][rpr][width / 4] (16 bytes carry 4 values)
-    uint4 *gather[kMaxPeers];       // rank j's packets of normalised rows [rows][width / 4]
+    uint4 *gather[kMaxPeers];       // rank j's packets of normalised rows [rows][width / 4], followed by rank j's own
+                                    // staging area [rpr][width / 4] (see phase 2b)
+    uint4 *stage;                   // local: gather[rank] + rows * width / 4
     uint32_t *state;                // local: [0] finished launches, [1] finished CTAs, [2] wait limit / 1024 cycles
     __nv_bfloat16 *hidden;          // local residual stream; only the owned rows are kept up to date
     __nv_bfloat16 *normed;          // local [rows, width]: all normalised rows, plain
@@ -386,16 +391,30 @@ __global__ void __launch_bounds__(kTwoPhaseThreads)
                         *reinterpret_cast<uint2 *>(p.normed + static_cast<size_t>(row) * p.width + q * 4) =
                             make_uint2(first, second);
                     } else {
-#pragma unroll
-                        for (int r = 0; r < kMaxPeers; ++r) {
-                            if (r < p.world) {
-                                store_packets(p.gather[r] + static_cast<size_t>(row) * quads + q, first, second, epoch);
-                            }
-                        }
+                        store_packets(p.stage + static_cast<size_t>(c) * quads + q, first, second, epoch);
                     }
                 }
             }
         }
+    }
+
+    // ---- phase 2b: owned row r goes to rank j, one (r, j) pair per CTA ----
+    if (!p.replicated) {
+        bool ok = true;
+        for (int pair = c; pair < p.rpr * p.world && ok; pair += gridDim.x) {
+            const int r = pair % p.rpr;
+            const int j = pair / p.rpr;
+            if (r >= owned) continue;
+            const size_t row = static_cast<size_t>(first_owned + r);
+            for (int q = tid; q < quads; q += kTwoPhaseThreads) {
+                if (shared_failed != 0) break;  // the owner's wait ran out: the row will not come
+                uint4 packet;
+                ok = poll_packets(p.stage + static_cast<size_t>(r) * quads + q, epoch, limit, packet);
+                if (!ok) break;
+                store_packets(p.gather[j] + row * quads + q, packet.x, packet.z, epoch);
+            }
+        }
+        if (!ok) shared_failed = 1;
     }
 
     // ---- phase 3: unpack normalised row c ----
@@ -541,6 +560,7 @@ int singe_allreduce_two_phase_add_rms_norm_bf16(singe_stream_t stream, void *hid
     }
     params.partial = static_cast<const __nv_bfloat16 *>(partial);
     params.state = state;
+    params.stage = params.gather[rank] + rows * (width / 4);
     params.hidden = static_cast<__nv_bfloat16 *>(hidden);
     params.normed = static_cast<__nv_bfloat16 *>(normed);
     params.weight = static_cast<const __nv_bfloat16 *>(weight);

@@ -378,7 +378,7 @@ class LlamaDecoder:
         if collective == "peer":
             # one-shot: every rank pulls all partial rows; two-phase: rows are reduced by their owners and pushed
             # back.  Measured on B200 / NVSwitch at 64 rows x 4096, ms per step: one-shot is ahead with two ranks
-            # (4.28 against 4.48), level with four (3.29 / 3.29) and behind with eight (2.82 against 2.49), where
+            # (4.28 against 4.48), level with four (3.27 / 3.27) and behind with eight (2.82 against 2.45), where
             # every rank would pull 3.5 MB per collective.
             collective = "oneshot" if tp <= PEER_ONE_SHOT_UP_TO else "twophase"
         self.collective = collective

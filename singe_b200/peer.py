@@ -76,7 +76,8 @@ class TwoPhaseAllReduce:
         self.replicated = replicated
         self.rpr = rows if replicated else (rows + world - 1) // world
         self.receive = PeerBuffer(group, rank, world, world * self.rpr * width * 4)
-        self.gather = self.receive if replicated else PeerBuffer(group, rank, world, rows * width * 4)
+        # packets of all normalised rows, then this rank's staging area for the rows it owns
+        self.gather = self.receive if replicated else PeerBuffer(group, rank, world, (rows + self.rpr) * width * 4)
         self.state = torch.zeros(4, dtype=torch.int32, device="cuda")
         if wait_limit_kcycles:
             self.state[2] = wait_limit_kcycles

@@ -68,7 +68,7 @@ def test_two_phase_all_reduce_gives_up_when_the_other_rank_never_pushes():
     per = ROWS // 2
     packets = lambda rows: torch.zeros((rows, WIDTH // 4, 4), dtype=torch.int32, device="cuda")
     receive = [packets(2 * per) for _ in range(2)]
-    gather = [packets(ROWS) for _ in range(2)]
+    gather = [packets(ROWS + per) for _ in range(2)]   # all rows, then the staging area of the owned ones
     normed = torch.full((ROWS, WIDTH), 7.0, dtype=torch.bfloat16, device="cuda")
     state = torch.zeros(4, dtype=torch.int32, device="cuda")
     state[2] = 1500
@@ -89,7 +89,7 @@ def test_two_phase_all_reduce_gives_up_when_the_other_rank_never_pushes():
     lone_state = torch.zeros(4, dtype=torch.int32, device="cuda")
     code = lib.singe_allreduce_two_phase_add_rms_norm_bf16(
         stream, hidden.data_ptr(), normed.data_ptr(), weight.data_ptr(), partial.data_ptr(),
-        _pointers([packets(ROWS)]), _pointers([packets(ROWS)]), lone_state.data_ptr(), 0, 1, ROWS, WIDTH, EPS, 0,
+        _pointers([packets(ROWS)]), _pointers([packets(2 * ROWS)]), lone_state.data_ptr(), 0, 1, ROWS, WIDTH, EPS, 0,
         status.data_ptr())
     assert code == ks.OK
     torch.cuda.synchronize()

@@ -1139,8 +1139,8 @@ int singe_fmha_decode_splitk_reduce_f32(singe_stream_t stream, float *out, float
         return SINGE_ERR_INVALID_LENGTH;
     }
     if (!fits_i32(batch) || !fits_i32(key_len) || !fits_i32(heads) || !fits_i32(head_dim) ||
-        !fits_i32(batch * heads) || !fits_i32(key_len * kv_heads * head_dim)) {
-        return SINGE_ERR_LENGTH_EXCEEDS_I32;
+        !fits_i32(batch * heads) || !fits_i32(key_len * kv_heads) || !fits_i32(key_len * kv_heads * head_dim)) {
+        return SINGE_ERR_LENGTH_EXCEEDS_I32;  // (each product is checked before it becomes a factor of the next)
     }
     if (out == nullptr || attn_scratch == nullptr || lse_scratch == nullptr || query == nullptr || key == nullptr ||
         value == nullptr) {

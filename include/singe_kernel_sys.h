@@ -184,6 +184,12 @@ int singe_paged_kv_decode_attention_static_bf16(singe_stream_t stream, void *out
 /* Tokens per split for a key-length bound and a split budget (host arithmetic, no device work). */
 size_t singe_paged_kv_decode_split_tokens(size_t key_len_bound, size_t max_splits, size_t block_size);
 
+/* The split count singe_paged_kv_decode_attention_{bf16,f16} choose for themselves (host arithmetic; uses the SM
+ * count of the current device, 148 when there is none): 512-key pieces, or larger ones out of 640 / 832 / 1024 /
+ * 1360 / 2048 when a wave model of the grid prefers them.  A caller that brings its own scratch sizes it with this
+ * count to run the same launch. */
+size_t singe_paged_kv_decode_default_splits(size_t batch, size_t kv_heads, size_t key_len_bound, size_t block_size);
+
 /* Writes the partials only (all `max_splits` slots of every row are defined afterwards). */
 int singe_paged_kv_decode_splitk_bf16(singe_stream_t stream, float *attn_scratch, float *lse_scratch,
                                       const void *query, const void *key_cache, const void *value_cache,

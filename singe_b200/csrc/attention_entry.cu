@@ -975,6 +975,11 @@ int singe_paged_kv_decode_attention_f32(singe_stream_t stream, float *out, const
                                  physical_blocks, block_table_batch_stride, scale);
 }
 
+size_t singe_paged_kv_decode_default_splits(size_t batch, size_t kv_heads, size_t key_len_bound, size_t block_size) {
+    if (batch == 0 || kv_heads == 0 || key_len_bound == 0 || block_size == 0) return 1;
+    return wave_aware_splits(batch, kv_heads, key_len_bound, block_size);
+}
+
 size_t singe_paged_kv_decode_split_tokens(size_t key_len_bound, size_t max_splits, size_t block_size) {
     return paged_decode_split_tokens(key_len_bound, max_splits, block_size);
 }

@@ -55,6 +55,7 @@ SIGNATURES = {
     "singe_paged_kv_decode_attention_static_bf16": [_p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _f],
     "singe_paged_kv_decode_attention_static_scratch_floats": [],
     "singe_paged_kv_decode_split_tokens": [_z, _z, _z],
+    "singe_paged_kv_decode_default_splits": [_z, _z, _z, _z],
     "singe_paged_kv_decode_splitk_bf16": [_p, _p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z, _f],
     "singe_fmha_decode_splitk_reduce_f32": [_p, _p, _p, _p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _f],
     "singe_splitk_reduce_f32": [_p, _p, _p, _p, _z, _z, _z, _z, _z, _z, _z, _z, _z, _z, _z],
@@ -119,6 +120,7 @@ SIGNATURES = {
 _RESTYPES = {
     "singe_status_string": ctypes.c_char_p,
     "singe_paged_kv_decode_split_tokens": ctypes.c_size_t,
+    "singe_paged_kv_decode_default_splits": ctypes.c_size_t,
     "singe_paged_kv_decode_attention_static_scratch_floats": ctypes.c_size_t,
 }
 

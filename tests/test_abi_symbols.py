@@ -44,6 +44,13 @@ def test_status_strings_and_host_only_helpers_need_no_gpu():
     assert lib.singe_paged_kv_decode_split_tokens(4096, 8, 16) == 512
     assert lib.singe_paged_kv_decode_split_tokens(4096, 6, 16) == 688
     assert lib.singe_paged_kv_decode_split_tokens(100, 64, 16) == 16
+    # the drop-in decode's own split count: 512-key pieces, larger ones where a wave model of the grid (148 SMs when no
+    # device is present, three CTAs each) prefers them and 2.5 waves of CTAs remain
+    assert lib.singe_paged_kv_decode_default_splits(32, 8, 4096, 16) == 5      # five 832-key pieces
+    assert lib.singe_paged_kv_decode_default_splits(16, 8, 4096, 16) == 8      # too few CTAs for larger pieces
+    assert lib.singe_paged_kv_decode_default_splits(64, 8, 4096, 16) == 4      # 1024-key pieces
+    assert lib.singe_paged_kv_decode_default_splits(128, 8, 1024, 16) == 2     # 512-key pieces of a short bound
+    assert lib.singe_paged_kv_decode_default_splits(1, 1, 2048, 16) == 16      # one row: the finest split
 
 
 def test_validation_runs_before_any_device_work():

@@ -68,3 +68,21 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(ks, "LIB_PATH", os.path.join(ROOT, "no_such_dir", "libsinge_kernel_sys.so"))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         ks.lib()
+
+
+def test_the_rust_binding_block_in_the_integration_notes_is_the_generator_output():
+    # include/rust_bindings.py prints the extern "C" block from the header; the integration notes carry that output
+    sys_path = os.path.join(ROOT, "include")
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("rust_bindings", os.path.join(sys_path, "rust_bindings.py"))
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    block = module.render()
+    with open(os.path.join(ROOT, "include", "singe_kernel_sys.h")) as handle:
+        declared = list(module.declarations(handle.read()))
+    assert sorted(name for name, _, _ in declared) == _declared()
+    for name, fields, _ in declared:
+        assert len(fields) == len(ks.SIGNATURES[name]), name
+    with open(os.path.join(ROOT, "INTEGRATION.md")) as handle:
+        assert block in handle.read(), "run `python include/rust_bindings.py` and paste its output into appendix A"

@@ -118,7 +118,11 @@ __device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tile
 // bursts.  Several adjacent slices issued together give the memory controller 512-1024 contiguous bytes per row.
 // AT: the left operand is stored [K, M]; its 128 x 64 tile is two boxes of 64 K-rows x 64 M-columns, 8 KB apart, read
 // MN-major like a [K, N] right operand.
-template <int BN, int KPS, bool KN, bool AT = false>
+// MT = 2: a tile is 256 rows, two 128-row MMAs per k step that read the same B slice: 64 KB of operands per 1024 clk
+// of tensor-core work instead of 48 KB per 512, which is what one SM can pull out of L2 (the 128 x 256 tile runs at the
+// SM's L2 read bandwidth, about 106 GB/s, not at the tensor core's rate).  Both accumulators belong to the one tile
+// (columns [0, BN) and [BN, 2 BN)), so the epilogue of a tile no longer overlaps the next tile's MMAs.
+template <int BN, int KPS, bool KN, bool AT = false, int MT = 1>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                      const GemmParams p) {
@@ -186,10 +190,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 for (int kb = 0; kb < preloaded; ++kb) {
                     const uint32_t stage = base + kb * p.stage_bytes;
                     const uint32_t full = bar_full + kb * 8;
-                    mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
+                    mbar_expect_tx(full, KPS * (MT * a_bytes + kBBytes));
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
-                        load_b_slice<BN, KN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
+                        load_b_slice<BN, KN>(stage + KPS * MT * a_bytes + sub * kBBytes, &b_map, full, (kb * KPS + sub) * kBlockK,
                                          tn * BN);
                     }
                 }
@@ -219,22 +223,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 if (lane == 0) {
                     const uint32_t stage = base + s * p.stage_bytes;
                     const uint32_t full = bar_full + s * 8;
-                    if (!early) mbar_expect_tx(full, KPS * (a_bytes + kBBytes));
+                    if (!early) mbar_expect_tx(full, KPS * (MT * a_bytes + kBBytes));
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
                         // slices past K are zero-filled by TMA and add nothing
-                        if (AT) {
-                            tma_load_2d(stage + sub * a_bytes, &a_map, full, tm * kBlockM, (kb * KPS + sub) * kBlockK);
-                            tma_load_2d(stage + sub * a_bytes + 8192, &a_map, full, tm * kBlockM + 64,
-                                        (kb * KPS + sub) * kBlockK);
-                        } else {
-                            tma_load_2d(stage + sub * a_bytes, &a_map, full, (kb * KPS + sub) * kBlockK, tm * kBlockM);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const uint32_t a_at = stage + (sub * MT + mt) * a_bytes;
+                            const int row0 = (tm * MT + mt) * kBlockM;
+                            if (AT) {
+                                tma_load_2d(a_at, &a_map, full, row0, (kb * KPS + sub) * kBlockK);
+                                tma_load_2d(a_at + 8192, &a_map, full, row0 + 64, (kb * KPS + sub) * kBlockK);
+                            } else {
+                                tma_load_2d(a_at, &a_map, full, (kb * KPS + sub) * kBlockK, row0);
+                            }
                         }
                     }
                     if (!early) {
 #pragma unroll
                         for (int sub = 0; sub < KPS; ++sub) {
-                            load_b_slice<BN, KN>(stage + KPS * a_bytes + sub * kBBytes, &b_map, full,
+                            load_b_slice<BN, KN>(stage + KPS * MT * a_bytes + sub * kBBytes, &b_map, full,
                                              (kb * KPS + sub) * kBlockK, tn * BN);
                         }
                     }
@@ -246,8 +254,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         int it = 0;
         int local = 0;
         for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++local) {
-            const int acc = local & 1;
-            const uint32_t acc_phase = (local >> 1) & 1;
+            // MT == 1: two accumulators take turns; MT == 2: both belong to every tile
+            const int acc = MT == 2 ? 0 : (local & 1);
+            const uint32_t acc_phase = MT == 2 ? (local & 1) : ((local >> 1) & 1);
             if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_empty + acc * 8, acc_phase ^ 1) ? 1 : 0)) {
                 failed = true;
                 break;
@@ -266,14 +275,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     const uint32_t stage = base + s * p.stage_bytes;
 #pragma unroll
                     for (int sub = 0; sub < KPS; ++sub) {
-                        const uint64_t a_desc = make_smem_desc(stage + sub * a_bytes, BWalk<AT>::kLeadingBytes, 1024);
                         const uint64_t b_desc =
-                            make_smem_desc(stage + KPS * a_bytes + sub * kBBytes, BWalk<KN>::kLeadingBytes, 1024);
+                            make_smem_desc(stage + KPS * MT * a_bytes + sub * kBBytes, BWalk<KN>::kLeadingBytes, 1024);
 #pragma unroll
-                        for (int ks = 0; ks < kBlockK / 16; ++ks) {
-                            // 16 bf16 of K: 2 descriptor address units along a K-major row, 128 down an MN-major tile
-                            umma_ss(tmem_d, a_desc + BWalk<AT>::kStep * ks, b_desc + BWalk<KN>::kStep * ks, kIdesc,
-                                    (kb > 0 || sub > 0 || ks > 0) ? 1u : 0u);
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const uint64_t a_desc =
+                                make_smem_desc(stage + (sub * MT + mt) * a_bytes, BWalk<AT>::kLeadingBytes, 1024);
+#pragma unroll
+                            for (int ks = 0; ks < kBlockK / 16; ++ks) {
+                                // 16 bf16 of K: 2 descriptor address units along a K-major row, 128 down an MN-major tile
+                                umma_ss(tmem_d + mt * BN, a_desc + BWalk<AT>::kStep * ks, b_desc + BWalk<KN>::kStep * ks,
+                                        kIdesc, (kb > 0 || sub > 0 || ks > 0) ? 1u : 0u);
+                            }
                         }
                     }
                     tcgen05_commit(bar_empty + s * 8);
@@ -295,15 +308,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++local) {
             int tm, tn;
             tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
-            const int acc = local & 1;
-            const uint32_t acc_phase = (local >> 1) & 1;
+            const int acc = MT == 2 ? 0 : (local & 1);
+            const uint32_t acc_phase = MT == 2 ? (local & 1) : ((local >> 1) & 1);
             if (!__all_sync(0xffffffffu, mbar_wait(bar_acc_full + acc * 8, acc_phase) ? 1 : 0)) {
                 failed = true;
                 break;
             }
             tcgen05_fence_after();
-            const int row = tm * kBlockM + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int mt = 0; mt < MT; ++mt) {
+            const int row = (tm * MT + mt) * kBlockM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (acc + mt) * BN;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
@@ -371,6 +386,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     }
                 }
             }
+            }  // mt
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -826,12 +842,13 @@ int launch_gemm_splitk(cudaStream_t stream, GemmParams params, const void *lhs, 
     return launch_status();
 }
 
-template <int BN, int KPS, bool AT = false>
+template <int BN, int KPS, bool AT = false, int MT = 1>
 int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const void *rhs, size_t lhs_row_stride,
                 size_t rhs_row_stride) {
     const int kSmemLimit = shared_limit(params);
     const int b_bytes = BN * 128;
-    params.stage_bytes = KPS * (params.a_rows * 128 + b_bytes);
+    if (MT == 2) params.tiles_m = (params.m + 2 * kBlockM - 1) / (2 * kBlockM);  // 256-row tiles
+    params.stage_bytes = KPS * (MT * params.a_rows * 128 + b_bytes);
     params.k_blocks = (params.k + kBlockK * KPS - 1) / (kBlockK * KPS);
     params.prefetch_blocks = prefetch_blocks_for(params, KPS * b_bytes);
     params.pad_bytes = over_read_pad(params.a_rows, KPS * b_bytes);
@@ -849,9 +866,9 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
     static int configured[kMaxDevices] = {0};
     static int configured_kn[kMaxDevices] = {0};
     if (params.rhs_kn) {
-        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS, kHasKN, AT>, smem, configured_kn));
+        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS, kHasKN, AT, MT>, smem, configured_kn));
     } else {
-        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS, false, AT>, smem, configured));
+        SINGE_CUDA_TRY(ensure_dynamic_shared(gemm_bf16_kernel<BN, KPS, false, AT, MT>, smem, configured));
     }
 
     CUtensorMap a_map, b_map;
@@ -884,10 +901,10 @@ int launch_gemm(cudaStream_t stream, GemmParams params, const void *lhs, const v
     const int total = params.tiles_m * params.tiles_n;
     const int grid = total < device_sm_count() ? total : device_sm_count();
     if (params.rhs_kn) {
-        SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS, kHasKN, AT>, dim3(grid), dim3(kGemmThreads), smem,
+        SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS, kHasKN, AT, MT>, dim3(grid), dim3(kGemmThreads), smem,
                                         stream, kLaunchGemm, 1, a_map, b_map, params));
     } else {
-        SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS, false, AT>, dim3(grid), dim3(kGemmThreads), smem,
+        SINGE_CUDA_TRY(launch_dependent(gemm_bf16_kernel<BN, KPS, false, AT, MT>, dim3(grid), dim3(kGemmThreads), smem,
                                         stream, kLaunchGemm, 1, a_map, b_map, params));
     }
     return launch_status();
@@ -1029,6 +1046,11 @@ int gemm_bf16(cudaStream_t stream, void *out, bool out_f32, const void *lhs, con
         SINGE_SPLITK_CASE(32, 8)
 #undef SINGE_SPLITK_CASE
         return SINGE_ERR_UNSUPPORTED_CONFIGURATION;
+    }
+    // Many 256 x 256 tiles: the form with two M sub-tiles per CTA, which halves the A-and-B bytes an SM pulls per flop.
+    if (bn == 256 && slices == 1 && params.m >= 2 * kBlockM &&
+        ((params.m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((params.n + 255) / 256) >= sms) {
+        return launch_gemm<256, 1, false, 2>(stream, params, lhs, rhs, lhs_row_stride, rhs_row_stride);
     }
 #define SINGE_GEMM_CASE(BN_, KPS_)                                                                    \
     if (bn == BN_ && slices == KPS_)                                                                  \

@@ -23,8 +23,11 @@ def _case(m, n, k, seed=2):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 256, 512), (16, 512, 1024), (128, 384, 64), (200, 136, 72), (256, 256, 4096),
-                                   (129, 1000, 520), (64, 4096, 4096), (1, 14336, 4096)])
+                                   (129, 1000, 520), (64, 4096, 4096), (1, 14336, 4096), (1024, 9728, 128),
+                                   (1000, 9736, 136)])
 def test_linear_matches_the_oracle_bf16_and_f32(m, n, k):
+    # (the last two shapes have at least one 256 x 256 tile per SM: the form with two M sub-tiles per CTA, with and
+    # without M, N and K tails)
     x, w = _case(m, n, k)
     y = ops.linear(x, w)
     y32 = torch.empty((m, n), dtype=torch.float32, device="cuda")

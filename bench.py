@@ -587,6 +587,33 @@ def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3, collec
     moved = llama.decode_step_bytes(config, sequences, context, world, decoder.shard_lm_head)
     peaks = measured_peaks()
     status = int(decoder.status.item())
+    prompt = None
+    if world == 1:
+        # A prompt step through the same decoder: every sequence reads a prompt of 60 - 480 tokens (14 400 tokens in
+        # all) in one step -- embedding, the linears at M = 14 400, rotary + cache write, the packed prefill kernel
+        # over the paged cache, last-row logits.  Timed on its second run (the first allocates the step's buffers).
+        lengths = [480, 240, 120, 60] * (sequences // 4)
+        prompts = [rng.integers(0, config.vocab, size=n).tolist() for n in lengths]
+        elapsed = None
+        for _ in range(2):
+            decoder.table.reset()
+            torch.cuda.synchronize()
+            begin = time.perf_counter()
+            decoder.step_tokens(prompts)
+            torch.cuda.synchronize()
+            elapsed = time.perf_counter() - begin
+        total = sum(lengths)
+        linear_weights = config.layers * (config.hidden * (config.heads + 2 * config.kv_heads) * config.head_dim
+                                          + config.heads * config.head_dim * config.hidden
+                                          + 3 * config.hidden * config.ffn)
+        flops = 2.0 * total * linear_weights
+        prompt = {"tokens": total, "sequences": sequences, "ms": round(elapsed * 1e3, 2),
+                  "tokens_per_s": round(total / elapsed, 1),
+                  "linear_tflops": round(flops / elapsed / 1e12, 1),
+                  "frac_of_bf16_peak": round(flops / elapsed / 1e12 / peaks["bf16_tflops_sustained"], 4),
+                  "peak": "sustained cuBLAS figure (a step of 150 ms under the power cap)",
+                  "status_word": int(decoder.status.item()),
+                  "timing": "host wall clock around one eager step, including its buffer allocations"}
     decoder.close()
     how = "none (one GPU)"
     if world > 1:
@@ -608,6 +635,8 @@ def run_decode_step(rank, world, group, steps: int = 20, warmup: int = 3, collec
         "collectives_per_step": 2 * config.layers if world > 1 else 0, "status_word": status,
         "config": "Llama-3-8B shape, random bf16 weights, 64 seqs x ctx 2048, page 16, CUDA-graph replay",
     })
+    if prompt is not None:
+        figures["prompt_step"] = prompt
     return figures
 
 
